@@ -1,0 +1,328 @@
+#!/usr/bin/env python
+"""Headline benchmark: batch-1 greedy decode of random-init Qwen2.5-7B W4A16 at an 8K-token KV context.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--model 7b] [--quant int4] [--ctx 8192]
+
+One "step" is one decode token (one pass of the hot path).  Rank 0 prints ONE JSON line:
+  value   tokens/s with the token fed back on the device (cuqwen_decode_n: K graph replays between two CUDA events)
+  e2e     tokens/s through cuqwen_step, the call a host makes per token: host token in (H2D), sampled token out (D2H)
+  roofline    the dominant kernel (gate/up W4A16 GEMV + SwiGLU) timed alone over all layers' weights, algorithmic
+              bytes / CUDA-event time against the measured HBM copy bandwidth; `step` gives the same for the whole step
+  cpu_baseline  the scalar CPU oracle of the same step on the host cores (N=1, rank 0, bounded sample)
+--impl reference times the reference's own CUDA build (oracle/_ref, its qwen_forward loop) on the same file and context.
+Under torchrun (N>1) the model is tensor-parallel over the N GPUs (strong scaling: the work per token is fixed).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "B=1 decode tok/s (7B W4A16, 1/2/4/8 B200); GEMV HBM GB/s vs peak"
+SEED = 42
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel from an ncu capture (see profiles/);
+# None until a capture exists for the shape.
+NCU_TRAFFIC_BYTES = {("7b", "int4"): None}
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+def model_path(model: str, quant: str) -> Path:
+    base = Path("/dev/shm") if os.access("/dev/shm", os.W_OK) else Path("/tmp")
+    return base / f"cuqwen_bench_{model.replace('.', '_')}_{quant}_seed{SEED}.bin"
+
+
+def ensure_model_file(model: str, quant: str) -> Path:
+    from cuqwen_b200 import binfmt, build
+    p = model_path(model, quant)
+    want = binfmt.file_nbytes(binfmt.MODELS[model], binfmt.QUANT_ID[quant])
+    if not p.exists() or p.stat().st_size != want:
+        build.build_gen()
+        tmp = p.with_suffix(f".tmp{os.getpid()}")
+        subprocess.run([str(build.GEN_BIN), "--out", str(tmp), "--model", model, "--quant", quant, "--seed", str(SEED)], check=True)
+        os.replace(tmp, p)
+    return p
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device: int):
+        self.device, self.proc = device, None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.device)],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *a):
+        self.result = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill(); out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        for line in out.splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if sm:
+            self.result = {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def dist_setup(n: int):
+    """Returns (rank, world, local_rank, torch.distributed or None)."""
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", str(rank)))
+    if world == 1:
+        return 0, 1, 0, None
+    import torch
+    import torch.distributed as dist
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    return rank, world, local, dist
+
+
+def max_over_ranks(dist, local: int, v: float) -> float:
+    if dist is None:
+        return v
+    import torch
+    t = torch.tensor([v], dtype=torch.float64, device=f"cuda:{local}")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def barrier(dist, local: int):
+    if dist is not None:
+        import torch
+        dist.barrier()
+        torch.cuda.synchronize(local)
+
+
+def dominant_kernel_roofline(eng, E, K, model_cfg, quant_id: int, iters: int = 20):
+    """gate/up GEMV + SwiGLU alone, cycling over every layer's weights (inputs far larger than L2)."""
+    dim, inter_l = model_cfg["dim"], eng.ptr("GATE")[1] // 2
+    L = model_cfg["layers"]
+    x = E.DevBuf.from_numpy(np.random.default_rng(0).standard_normal(dim).astype(np.float16), eng.device)
+    out = E.DevBuf(inter_l * 2, eng.device)
+    ptrs = [(eng.ptr("WGATE", l)[0], eng.ptr("WUP", l)[0], eng.ptr("SGATE", l)[0] or None, eng.ptr("SUP", l)[0] or None) for l in range(L)]
+    wbytes = eng.ptr("WGATE", 0)[1] + eng.ptr("SGATE", 0)[1]
+
+    def sweep():
+        for wg, wu, sg, su in ptrs:
+            K.fused_mlp_stage1(quant_id, x, wg, wu, sg, su, out, dim, inter_l, device=eng.device)
+
+    for _ in range(3):
+        sweep()
+    E.sync(eng.device)
+    K.bench_begin(eng.device)
+    for _ in range(iters):
+        sweep()
+    ms = K.bench_end(eng.device)
+    per_launch_s = ms / 1e3 / (iters * L)
+    alg = 2 * wbytes + dim * 2 + inter_l * 2
+    return alg, per_launch_s
+
+
+def run_ours(a):
+    rank, world, local, dist = dist_setup(a.gpus)
+    from cuqwen_b200 import binfmt
+    from cuqwen_b200 import engine as E
+    from cuqwen_b200 import kernels as K
+    qid = E.QUANT_ID[a.quant]
+    cfg = binfmt.MODELS[a.model]
+    if rank == 0:
+        path = ensure_model_file(a.model, a.quant)
+    barrier(dist, local)
+    path = model_path(a.model, a.quant)
+    prm = E.model_params(a.model, a.quant)
+    prm.device, prm.tp_rank, prm.tp_size = local, rank, world
+    eng = E.Engine(prm)
+    eng.load(str(path))
+    if world > 1:
+        import torch
+        idt = torch.zeros(128, dtype=torch.uint8, device=f"cuda:{local}")
+        if rank == 0:
+            idt = torch.tensor(list(E.nccl_unique_id()), dtype=torch.uint8, device=f"cuda:{local}")
+        dist.broadcast(idt, 0)
+        eng.tp_init(bytes(idt.cpu().tolist()))
+    ctx, Kst, W = a.ctx, a.steps, max(a.warmup, 3)
+    eng.kv_fill_normal(ctx, SEED)
+    first = 1234 % cfg["vocab"]
+
+    # ---- value: device-resident token feedback, K graph replays between two events ----
+    eng.decode_n(first, ctx, W)
+    barrier(dist, local)
+    with ClockSampler(local) as cs:
+        eng.decode_n(first, ctx, Kst)
+        ms = eng.last_decode_ms
+    barrier(dist, local)
+    ms = max_over_ranks(dist, local, ms)
+    value = Kst / (ms / 1e3)
+
+    # ---- e2e: one cuqwen_step per token, host token in, sampled token out ----
+    tok = first
+    for i in range(W):
+        tok = eng.step(tok, ctx + i)
+    barrier(dist, local)
+    t0 = time.perf_counter()
+    tok = first
+    for i in range(Kst):
+        tok = eng.step(tok, ctx + i)
+    e2e_s = time.perf_counter() - t0
+    barrier(dist, local)
+    e2e_s = max_over_ranks(dist, local, e2e_s)
+    e2e = Kst / e2e_s
+
+    peak, peak_src = peaks()
+    mean_ctx = ctx + Kst / 2
+    step_bytes_total = binfmt.step_bytes(cfg, qid, int(mean_ctx))
+    out = {
+        "metric": METRIC, "value": round(value, 2), "unit": "tok/s", "n_gpus": world, "steps": Kst, "warmup": W,
+        "ms_per_step": round(ms / Kst, 5), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "int4 weights x fp16 activations, fp32 accumulate", "data": "synthetic",
+        "config": {"workload": f"Qwen2.5-{a.model.upper()} {a.quant} random-init (N(0,0.02) weights, seed {SEED}), B=1 greedy decode, "
+                               f"KV context {ctx} prefilled with N(0,1) fp16, {Kst} steps",
+                   "parallelism": f"tp{world}", "l2": f"inputs exceed L2: {step_bytes_total / 1e9:.2f} GB streamed per step vs 126 MB",
+                   "attn_splits": eng.params.attn_splits},
+        "e2e": {"value": round(e2e, 2), "unit": "tok/s", "h2d_bytes_per_step": 32, "d2h_bytes_per_step": 4},
+        "gpu_launches": Kst * eng.step_launches,
+        "clocks": cs.result,
+    }
+    step_gbs = step_bytes_total / (ms / 1e3 / Kst) / 1e9
+    out["step"] = {"algorithmic_bytes": step_bytes_total, "achieved_gbs_all_gpus": round(step_gbs, 1), "frac_of_n_x_peak": round(step_gbs / (peak * world), 4),
+                   "launches_per_step": eng.step_launches}
+    if rank == 0:
+        alg, sec = dominant_kernel_roofline(eng, E, K, cfg, qid)
+        ach = alg / sec / 1e9
+        out["roofline"] = {"bound": "hbm", "kernel": "gemv_kernel<int4, SWIGLU> (gate/up GEMV + SwiGLU)", "achieved": round(ach, 1), "peak": peak,
+                           "unit": "GB/s", "frac": round(ach / peak, 4), "peak_source": peak_src, "bytes_per_launch": alg,
+                           "us_per_launch": round(sec * 1e6, 3), "traffic": NCU_TRAFFIC_BYTES.get((a.model, a.quant))}
+    eng.close()
+    if rank == 0 and world == 1 and not a.no_cpu_baseline:
+        out["cpu_baseline"] = cpu_baseline(path, cfg, ctx)
+    if rank == 0:
+        print(json.dumps(out), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def cpu_baseline(path: Path, cfg: dict, ctx: int, steps: int = 2):
+    """Scalar CPU oracle of the same step on the host cores: a bounded sample (1 untimed + `steps` timed tokens)."""
+    from oracle import oracle_py as O
+    m = O.OracleModel(str(path), ctx + steps + 2)
+    Kc, Vc = m.kv_views()
+    rng = np.random.default_rng(SEED)
+    blk = rng.standard_normal((cfg["kv"], 512, cfg["hd"])).astype(np.float16)
+    for l in range(cfg["layers"]):
+        for s in range(0, ctx, 512):
+            n = min(512, ctx - s)
+            Kc[l, :, s:s + n] = blk[:, :n]; Vc[l, :, s:s + n] = blk[:, :n]
+    tok = m.step(1234 % cfg["vocab"], ctx)
+    t0 = time.perf_counter()
+    for i in range(steps):
+        tok = m.step(tok, ctx + 1 + i)
+    dt = time.perf_counter() - t0
+    cores = O.lib().orc_threads()
+    m.close()
+    return {"value": round(steps / dt, 4), "unit": "tok/s", "cores": cores, "kind": "port",
+            "sample": f"{steps} decode steps (after 1 untimed) of the same model file at KV context {ctx}, scalar C oracle, OpenMP over output rows"}
+
+
+def run_reference(a):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import oracle_py as O
+    from cuqwen_b200 import binfmt
+    from cuqwen_b200 import engine as E
+    ref = O.ref_lib(a.model, a.quant)
+    if ref is None:
+        print(json.dumps({"impl": "reference", "unavailable": f"oracle/_ref/{O.ref_lib_path(a.model, a.quant).name} was not built (needs the CuQwen sources at build time)"}), flush=True)
+        return
+    cfg = binfmt.MODELS[a.model]
+    path = ensure_model_file(a.model, a.quant)
+    ctx, Kst, W = a.ctx, a.steps, max(a.warmup, 3)
+    m = ref.ref_model_load(str(path).encode())
+    ref.ref_kv_fill_normal(m, ctx, SEED)
+    first = 1234 % cfg["vocab"]
+    import ctypes as C
+    toks = (C.c_int * max(Kst, W))()
+    ref.ref_decode_n(m, first, ctx, W, toks)           # first call also captures the reference's CUDA graph
+    with ClockSampler(0) as cs:
+        t0 = time.perf_counter()
+        ms = ref.ref_decode_n(m, first, ctx, Kst, toks)
+        wall = time.perf_counter() - t0
+    ref.ref_model_free(m)
+    value, e2e = Kst / (ms / 1e3), Kst / wall
+    qid = E.QUANT_ID[a.quant]
+    nl = 1 + 10 * cfg["layers"] + 5
+    out = {
+        "impl": "reference", "metric": METRIC, "value": round(value, 2), "unit": "tok/s", "n_gpus": 1, "steps": Kst, "warmup": W,
+        "ms_per_step": round(ms / Kst, 5), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "int4 weights x fp16 activations, fp32 accumulate", "data": "synthetic",
+        "config": {"workload": f"Qwen2.5-{a.model.upper()} {a.quant} random-init (N(0,0.02) weights, seed {SEED}), B=1 greedy decode, "
+                               f"KV context {ctx} prefilled with N(0,1) fp16, {Kst} steps",
+                   "parallelism": "tp1 (the reference is single-GPU)", "l2": "inputs exceed L2",
+                   "build": "CuQwen src/kernels.cu + model.cu + load_weights.cpp, nvcc -O3 --use_fast_math sm_100a, stock tuning constants"},
+        "e2e": {"value": round(e2e, 2), "unit": "tok/s", "h2d_bytes_per_step": 12, "d2h_bytes_per_step": 4},
+        "gpu_launches": Kst * nl, "clocks": cs.result,
+        "cpu_baseline": {"value": round(value, 2), "unit": "tok/s", "cores": 0, "kind": "reference",
+                         "sample": "the reference has no CPU implementation of this path; this arm is its own CUDA build run on the GPU "
+                                   f"({Kst} qwen_forward calls)"},
+        "step": {"algorithmic_bytes": binfmt.step_bytes(cfg, qid, int(ctx + Kst / 2))},
+    }
+    print(json.dumps(out), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=16)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="7b")
+    ap.add_argument("--quant", default="int4")
+    ap.add_argument("--ctx", type=int, default=8192)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    a = ap.parse_args()
+    if a.impl == "reference":
+        run_reference(a)
+    else:
+        run_ours(a)
+
+
+if __name__ == "__main__":
+    main()

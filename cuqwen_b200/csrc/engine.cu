@@ -1,0 +1,721 @@
+// Host side of the decode engine: model table, weight loader, state, the
+// per-step launch sequence and its CUDA graph, tensor-parallel plumbing, and
+// the extern "C" boundary declared in include/cuqwen_b200.h.
+#include <dlfcn.h>
+#include <fcntl.h>
+#include <nccl.h>
+#include <sys/mman.h>
+#include <sys/stat.h>
+#include <unistd.h>
+
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../include/cuqwen_b200.h"
+#include "attn.cuh"
+#include "gemv.cuh"
+#include "launch.h"
+#include "tp_plan.h"
+
+using namespace cq;
+
+// ---------------------------------------------------------------------------
+// errors
+// ---------------------------------------------------------------------------
+static thread_local char g_err[512] = "";
+static int fail(int code, const char* fmt, ...) {
+    va_list ap; va_start(ap, fmt); vsnprintf(g_err, sizeof g_err, fmt, ap); va_end(ap);
+    return code;
+}
+#define CK(call) do { cudaError_t e_ = (cudaError_t)(call); if (e_ != cudaSuccess) return fail(CUQWEN_ERR_CUDA, "%s: %s (%s:%d)", #call, cudaGetErrorString(e_), __FILE__, __LINE__); } while (0)
+
+extern "C" const char* cuqwen_last_error(void) { return g_err; }
+extern "C" const char* cuqwen_strerror(int code) {
+    switch (code) {
+        case CUQWEN_OK: return "ok";
+        case CUQWEN_ERR_ARG: return "bad argument or unsupported shape";
+        case CUQWEN_ERR_IO: return "weight file cannot be read";
+        case CUQWEN_ERR_MAGIC: return "weight file magic mismatch";
+        case CUQWEN_ERR_DIMS: return "weight file dimensions do not match the engine";
+        case CUQWEN_ERR_QUANT: return "weight file quantisation does not match the engine";
+        case CUQWEN_ERR_CUDA: return "CUDA error";
+        case CUQWEN_ERR_NCCL: return "NCCL error";
+        case CUQWEN_ERR_STATE: return "call made in the wrong state";
+        case CUQWEN_ERR_TIMEOUT: return "device-side wait timed out";
+    }
+    return "unknown error";
+}
+
+// ---------------------------------------------------------------------------
+// model table (reference include/config.h:55-113)
+// ---------------------------------------------------------------------------
+struct ModelRow { int vocab, dim, inter, layers, heads, kv, hd; };
+static const ModelRow kModels[5] = {
+    {151936, 896, 4864, 24, 14, 2, 64},     // 0.5B
+    {151936, 1536, 8960, 28, 12, 2, 128},   // 1.5B
+    {151936, 2048, 11008, 36, 16, 2, 128},  // 3B
+    {152064, 3584, 18944, 28, 28, 4, 128},  // 7B
+    {152064, 5120, 13824, 48, 40, 8, 128},  // 14B
+};
+
+extern "C" int cuqwen_model_params(int model_id, int quant, cuqwen_params* p) {
+    if (!p || model_id < 0 || model_id > 4 || quant < 0 || quant > 2) return fail(CUQWEN_ERR_ARG, "model_id %d / quant %d out of range", model_id, quant);
+    memset(p, 0, sizeof *p);
+    const ModelRow& m = kModels[model_id];
+    p->model_id = model_id; p->vocab_size = m.vocab; p->dim = m.dim; p->intermediate_size = m.inter; p->n_layers = m.layers;
+    p->n_heads = m.heads; p->n_kv_heads = m.kv; p->head_dim = m.hd; p->max_seq_len = 32768; p->quant = quant;
+    p->tp_size = 1; p->norm_eps = 1e-6f; p->rope_theta = 1000000.0f; p->repetition_penalty = 1.1f;
+    return CUQWEN_OK;
+}
+
+// ---------------------------------------------------------------------------
+// per-device context for the stand-alone kernel entry points
+// ---------------------------------------------------------------------------
+struct DevCtx { bool init = false; cudaStream_t stream = nullptr; int sms = 0; cudaEvent_t ev0 = nullptr, ev1 = nullptr; };
+static DevCtx g_dev[64];
+static std::mutex g_dev_mu;
+static int dev_ctx(int device, DevCtx** out) {
+    if (device < 0 || device >= 64) return fail(CUQWEN_ERR_ARG, "device %d out of range", device);
+    std::lock_guard<std::mutex> lk(g_dev_mu);
+    CK(cudaSetDevice(device));
+    DevCtx& d = g_dev[device];
+    if (!d.init) {
+        CK(cudaStreamCreateWithFlags(&d.stream, cudaStreamNonBlocking));
+        CK(cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, device));
+        CK(cudaEventCreate(&d.ev0)); CK(cudaEventCreate(&d.ev1));
+        d.init = true;
+    }
+    *out = &d;
+    return CUQWEN_OK;
+}
+#define DEV(device) DevCtx* dc; { int r_ = dev_ctx(device, &dc); if (r_) return r_; } LaunchCfg cfg{dc->stream, dc->sms, false}
+
+// ---------------------------------------------------------------------------
+// NCCL through dlopen (no link-time dependency; single-GPU use never loads it)
+// ---------------------------------------------------------------------------
+struct Nccl {
+    void* lib = nullptr;
+    decltype(&ncclGetUniqueId) GetUniqueId = nullptr;
+    decltype(&ncclCommInitRank) CommInitRank = nullptr;
+    decltype(&ncclAllReduce) AllReduce = nullptr;
+    decltype(&ncclAllGather) AllGather = nullptr;
+    decltype(&ncclCommDestroy) CommDestroy = nullptr;
+    decltype(&ncclGetErrorString) GetErrorString = nullptr;
+};
+static Nccl g_nccl;
+static int nccl_load() {
+    static std::mutex mu; std::lock_guard<std::mutex> lk(mu);
+    if (g_nccl.lib) return CUQWEN_OK;
+    void* h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+    if (!h) return fail(CUQWEN_ERR_NCCL, "dlopen libnccl.so.2: %s", dlerror());
+#define SYM(n) g_nccl.n = (decltype(g_nccl.n))dlsym(h, "nccl" #n); if (!g_nccl.n) return fail(CUQWEN_ERR_NCCL, "nccl" #n " missing")
+    SYM(GetUniqueId); SYM(CommInitRank); SYM(AllReduce); SYM(AllGather); SYM(CommDestroy); SYM(GetErrorString);
+#undef SYM
+    g_nccl.lib = h;
+    return CUQWEN_OK;
+}
+#define NK(call) do { ncclResult_t r_ = (call); if (r_ != ncclSuccess) return fail(CUQWEN_ERR_NCCL, "%s: %s", #call, g_nccl.GetErrorString(r_)); } while (0)
+
+// ---------------------------------------------------------------------------
+// engine
+// ---------------------------------------------------------------------------
+struct Mat { uint8_t* w = nullptr; __half* s = nullptr; int rows = 0, cols = 0; };
+struct Layer {
+    __half *in_norm = nullptr, *post_norm = nullptr, *bq = nullptr, *bk = nullptr, *bv = nullptr;
+    Mat q, k, v, o, gate, up, down;
+};
+
+struct cuqwen_engine {
+    cuqwen_params p{};
+    int sms = 0;
+    cudaStream_t stream = nullptr;
+    TpPlan plan{};
+    int tp = 1, rank = 0;
+    // local sizes
+    int n_heads_l = 0, n_kv_l = 0, q_dim_l = 0, kv_dim_l = 0, inter_l = 0, vocab_l = 0, nsplit = 0;
+    // weights
+    uint8_t* warena = nullptr; size_t warena_bytes = 0;
+    std::vector<Layer> layers;
+    __half *embed = nullptr, *norm = nullptr;
+    Mat lm; int lm_quant = 0; int lm_kind = 0;   // kind: 0 fp16 separate, 1 int8, 2 tied
+    bool loaded = false;
+    uint64_t weight_bytes = 0;                   // algorithmic bytes of all tensors a step reads (this rank)
+    // state
+    __half *x = nullptr, *xn = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *att = nullptr, *gate = nullptr, *logits = nullptr;
+    __half *kc = nullptr, *vc = nullptr;
+    float *part_o = nullptr, *part_ml = nullptr; unsigned* counters = nullptr;
+    StepCtl* ctl = nullptr; StepCtl* h_ctl = nullptr;
+    int* d_hist = nullptr; unsigned* bitmap = nullptr; unsigned long long* best = nullptr; unsigned* ticket = nullptr;
+    int* out_ring = nullptr; int ring_cap = 65536; int* h_out = nullptr;
+    float* tp_partial = nullptr; unsigned long long* tp_keys = nullptr;
+    // graph
+    cudaGraph_t graph = nullptr; cudaGraphExec_t gexec = nullptr; bool graph_ready = false;
+    int launches = 0;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr; float last_ms = 0.f;
+    // nccl
+    ncclComm_t comm = nullptr;
+};
+
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+static size_t elem_bytes2(int quant, size_t rows, size_t cols) { return quant == 2 ? rows * cols / 2 : quant == 1 ? rows * cols : rows * cols * 2; }
+
+extern "C" int cuqwen_create(const cuqwen_params* pin, cuqwen_engine** out) {
+    if (!pin || !out) return fail(CUQWEN_ERR_ARG, "null argument");
+    cuqwen_params p = *pin;
+    if (p.model_id >= 0) {
+        if (p.model_id > 4) return fail(CUQWEN_ERR_ARG, "model_id %d out of range", p.model_id);
+        const ModelRow& m = kModels[p.model_id];
+        p.vocab_size = m.vocab; p.dim = m.dim; p.intermediate_size = m.inter; p.n_layers = m.layers; p.n_heads = m.heads; p.n_kv_heads = m.kv; p.head_dim = m.hd;
+    }
+    if (p.max_seq_len <= 0) p.max_seq_len = 32768;
+    if (p.tp_size <= 0) p.tp_size = 1;
+    if (p.norm_eps == 0.f) p.norm_eps = 1e-6f;
+    if (p.rope_theta == 0.f) p.rope_theta = 1000000.0f;
+    if (p.repetition_penalty == 0.f) p.repetition_penalty = 1.1f;
+    if (p.quant < 0 || p.quant > 2) return fail(CUQWEN_ERR_ARG, "quant %d out of range", p.quant);
+    if (p.dim <= 0 || p.dim % 128 || p.intermediate_size <= 0 || p.intermediate_size % 128 || p.vocab_size <= 0 || p.vocab_size % 16 ||
+        p.n_layers <= 0 || p.n_heads <= 0 || p.n_kv_heads <= 0 || p.n_heads % p.n_kv_heads || (p.head_dim != 64 && p.head_dim != 128) ||
+        (p.n_heads * p.head_dim) % 128 || p.n_heads / p.n_kv_heads > kMaxGroup)
+        return fail(CUQWEN_ERR_ARG, "unsupported dims: dim %d inter %d vocab %d layers %d heads %d/%d hd %d", p.dim, p.intermediate_size, p.vocab_size,
+                    p.n_layers, p.n_heads, p.n_kv_heads, p.head_dim);
+    TpPlan plan;
+    if (int r = tp_plan(p.n_heads, p.n_kv_heads, p.head_dim, p.intermediate_size, p.vocab_size, p.tp_rank, p.tp_size, &plan))
+        return fail(CUQWEN_ERR_ARG, "model cannot be split over tp_size %d (rule %d)", p.tp_size, r);
+
+    CK(cudaSetDevice(p.device));
+    cuqwen_engine* e = new cuqwen_engine();
+    e->p = p; e->plan = plan; e->tp = p.tp_size; e->rank = p.tp_rank;
+    e->n_heads_l = plan.qh1 - plan.qh0; e->n_kv_l = plan.kvh1 - plan.kvh0;
+    e->q_dim_l = e->n_heads_l * p.head_dim; e->kv_dim_l = e->n_kv_l * p.head_dim;
+    e->inter_l = plan.i1 - plan.i0; e->vocab_l = plan.v1 - plan.v0;
+    CK(cudaDeviceGetAttribute(&e->sms, cudaDevAttrMultiProcessorCount, p.device));
+    e->nsplit = p.attn_splits > 0 ? p.attn_splits : (e->sms + e->n_kv_l - 1) / e->n_kv_l;
+    if (e->nsplit > kMaxSplit) e->nsplit = kMaxSplit;
+    CK(cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking));
+    CK(cudaEventCreate(&e->ev0)); CK(cudaEventCreate(&e->ev1));
+
+    auto dalloc = [&](void** ptr, size_t bytes) -> cudaError_t { cudaError_t r = cudaMalloc(ptr, bytes); if (r == cudaSuccess) r = cudaMemset(*ptr, 0, bytes); return r; };
+    const size_t kvn = (size_t)p.n_layers * e->n_kv_l * p.max_seq_len * p.head_dim;
+    CK(dalloc((void**)&e->x, p.dim * 2)); CK(dalloc((void**)&e->xn, p.dim * 2));
+    CK(dalloc((void**)&e->q, e->q_dim_l * 2)); CK(dalloc((void**)&e->k, e->kv_dim_l * 2)); CK(dalloc((void**)&e->v, e->kv_dim_l * 2));
+    CK(dalloc((void**)&e->att, e->q_dim_l * 2)); CK(dalloc((void**)&e->gate, e->inter_l * 2)); CK(dalloc((void**)&e->logits, e->vocab_l * 2));
+    CK(dalloc((void**)&e->kc, kvn * 2)); CK(dalloc((void**)&e->vc, kvn * 2));     // zeroed like src/model.cu:37-38
+    CK(dalloc((void**)&e->part_o, attn_scratch_floats_o(e->n_kv_l, e->nsplit, p.head_dim) * 4));
+    CK(dalloc((void**)&e->part_ml, attn_scratch_floats_ml(e->n_kv_l, e->nsplit) * 4));
+    CK(dalloc((void**)&e->counters, e->n_kv_l * 4));
+    CK(dalloc((void**)&e->ctl, sizeof(StepCtl))); CK(cudaMallocHost((void**)&e->h_ctl, sizeof(StepCtl)));
+    CK(dalloc((void**)&e->d_hist, (size_t)p.max_seq_len * 4));
+    CK(dalloc((void**)&e->bitmap, ((size_t)e->vocab_l + 31) / 32 * 4));
+    CK(dalloc((void**)&e->best, 8)); CK(dalloc((void**)&e->ticket, 4));
+    CK(dalloc((void**)&e->out_ring, (size_t)e->ring_cap * 4)); CK(cudaMallocHost((void**)&e->h_out, (size_t)e->ring_cap * 4));
+    if (e->tp > 1) { CK(dalloc((void**)&e->tp_partial, (size_t)p.dim * 4)); CK(dalloc((void**)&e->tp_keys, (size_t)(e->tp + 1) * 8)); }
+    *out = e;
+    return CUQWEN_OK;
+}
+
+extern "C" void cuqwen_destroy(cuqwen_engine* e) {
+    if (!e) return;
+    cudaSetDevice(e->p.device);
+    cudaStreamSynchronize(e->stream);
+    if (e->gexec) cudaGraphExecDestroy(e->gexec);
+    if (e->graph) cudaGraphDestroy(e->graph);
+    if (e->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(e->comm);
+    void* bufs[] = {e->x, e->xn, e->q, e->k, e->v, e->att, e->gate, e->logits, e->kc, e->vc, e->part_o, e->part_ml, e->counters, e->ctl, e->d_hist,
+                    e->bitmap, e->best, e->ticket, e->out_ring, e->tp_partial, e->tp_keys, e->warena};
+    for (void* b : bufs) if (b) cudaFree(b);
+    if (e->h_ctl) cudaFreeHost(e->h_ctl);
+    if (e->h_out) cudaFreeHost(e->h_out);
+    cudaEventDestroy(e->ev0); cudaEventDestroy(e->ev1);
+    cudaStreamDestroy(e->stream);
+    delete e;
+}
+
+// ---------------------------------------------------------------------------
+// loader (file layout: export_weights.py:267-323; validation: src/load_weights.cpp:46-84)
+// ---------------------------------------------------------------------------
+namespace {
+struct Slice { size_t r0, r1, c0, c1; };   // rows [r0,r1), cols [c0,c1) of a [rows, cols] matrix
+struct Cursor {
+    const uint8_t* base; size_t size, off;
+    bool take(size_t n, const uint8_t** ptr) { if (off + n > size) return false; *ptr = base + off; off += n; return true; }
+};
+struct Arena {
+    uint8_t* base = nullptr; size_t used = 0; bool dry = true;
+    void* get(size_t bytes) { size_t o = used; used = align_up(used + bytes, 256); return dry ? (void*)(uintptr_t)(o + 256) : base + o; }
+};
+}  // namespace
+
+// Copies the slice of a projection (weights + scales) from the file image into the arena.
+static int load_proj(Cursor& cur, Arena& ar, int quant, size_t rows, size_t cols, const Slice& sl, Mat* m, uint64_t* bytes) {
+    const uint8_t* wsrc; const uint8_t* ssrc = nullptr;
+    if (!cur.take(elem_bytes2(quant, rows, cols), &wsrc)) return CUQWEN_ERR_IO;
+    if (quant && !cur.take(rows * (cols / kGroup) * 2, &ssrc)) return CUQWEN_ERR_IO;
+    const size_t nr = sl.r1 - sl.r0, nc = sl.c1 - sl.c0;
+    const size_t src_pitch = elem_bytes2(quant, 1, cols), dst_pitch = elem_bytes2(quant, 1, nc), c0b = elem_bytes2(quant, 1, sl.c0);
+    m->rows = (int)nr; m->cols = (int)nc;
+    m->w = (uint8_t*)ar.get(nr * dst_pitch);
+    m->s = quant ? (__half*)ar.get(nr * (nc / kGroup) * 2) : nullptr;
+    *bytes += nr * dst_pitch + (quant ? nr * (nc / kGroup) * 2 : 0);
+    if (ar.dry) return CUQWEN_OK;
+    if (cudaMemcpy2D(m->w, dst_pitch, wsrc + sl.r0 * src_pitch + c0b, src_pitch, dst_pitch, nr, cudaMemcpyHostToDevice) != cudaSuccess) return CUQWEN_ERR_CUDA;
+    if (quant) {
+        const size_t sp = (cols / kGroup) * 2, dp = (nc / kGroup) * 2;
+        if (cudaMemcpy2D(m->s, dp, ssrc + sl.r0 * sp + (sl.c0 / kGroup) * 2, sp, dp, nr, cudaMemcpyHostToDevice) != cudaSuccess) return CUQWEN_ERR_CUDA;
+    }
+    return CUQWEN_OK;
+}
+static int load_vec(Cursor& cur, Arena& ar, size_t n, size_t e0, size_t e1, __half** dst, uint64_t* bytes) {
+    const uint8_t* src;
+    if (!cur.take(n * 2, &src)) return CUQWEN_ERR_IO;
+    *dst = (__half*)ar.get((e1 - e0) * 2);
+    *bytes += (e1 - e0) * 2;
+    if (ar.dry) return CUQWEN_OK;
+    return cudaMemcpy(*dst, src + e0 * 2, (e1 - e0) * 2, cudaMemcpyHostToDevice) == cudaSuccess ? CUQWEN_OK : CUQWEN_ERR_CUDA;
+}
+
+// One walk over the file; dry = size the arena only.
+static int walk_file(cuqwen_engine* e, Cursor cur, Arena& ar, int lm_fmt) {
+    const cuqwen_params& p = e->p; const TpPlan& pl = e->plan;
+    const size_t d = p.dim, hd = p.head_dim, qd = (size_t)p.n_heads * hd, kd = (size_t)p.n_kv_heads * hd, I = p.intermediate_size, V = p.vocab_size;
+    const int Q = p.quant;
+    uint64_t wb = 0, dummy = 0;
+    int r;
+#define TRY(x) do { r = (x); if (r) return r; } while (0)
+    TRY(load_vec(cur, ar, V * d, 0, V * d, &e->embed, &dummy));
+    e->layers.resize(p.n_layers);
+    for (int l = 0; l < p.n_layers; ++l) {
+        Layer& L = e->layers[l];
+        TRY(load_vec(cur, ar, d, 0, d, &L.in_norm, &wb));
+        TRY(load_proj(cur, ar, Q, qd, d, Slice{pl.qh0 * hd, pl.qh1 * hd, 0, d}, &L.q, &wb));
+        TRY(load_vec(cur, ar, qd, pl.qh0 * hd, pl.qh1 * hd, &L.bq, &wb));
+        TRY(load_proj(cur, ar, Q, kd, d, Slice{pl.kvh0 * hd, pl.kvh1 * hd, 0, d}, &L.k, &wb));
+        TRY(load_vec(cur, ar, kd, pl.kvh0 * hd, pl.kvh1 * hd, &L.bk, &wb));
+        TRY(load_proj(cur, ar, Q, kd, d, Slice{pl.kvh0 * hd, pl.kvh1 * hd, 0, d}, &L.v, &wb));
+        TRY(load_vec(cur, ar, kd, pl.kvh0 * hd, pl.kvh1 * hd, &L.bv, &wb));
+        TRY(load_proj(cur, ar, Q, d, qd, Slice{0, d, pl.qh0 * hd, pl.qh1 * hd}, &L.o, &wb));
+        TRY(load_vec(cur, ar, d, 0, d, &L.post_norm, &wb));
+        TRY(load_proj(cur, ar, Q, I, d, Slice{(size_t)pl.i0, (size_t)pl.i1, 0, d}, &L.gate, &wb));
+        TRY(load_proj(cur, ar, Q, I, d, Slice{(size_t)pl.i0, (size_t)pl.i1, 0, d}, &L.up, &wb));
+        TRY(load_proj(cur, ar, Q, d, I, Slice{0, d, (size_t)pl.i0, (size_t)pl.i1}, &L.down, &wb));
+    }
+    TRY(load_vec(cur, ar, d, 0, d, &e->norm, &wb));
+    if (lm_fmt == 1) {
+        TRY(load_proj(cur, ar, 1, V, d, Slice{(size_t)pl.v0, (size_t)pl.v1, 0, d}, &e->lm, &wb));
+        e->lm_quant = 1; e->lm_kind = 1;
+    } else if (cur.size - cur.off >= V * d * 2) {      // untied fp16 head detected by remaining length (src/load_weights.cpp:148-156)
+        TRY(load_proj(cur, ar, 0, V, d, Slice{(size_t)pl.v0, (size_t)pl.v1, 0, d}, &e->lm, &wb));
+        e->lm_quant = 0; e->lm_kind = 0;
+    } else {                                           // tied: alias the embedding rows (src/load_weights.cpp:157-160)
+        e->lm.w = (uint8_t*)(e->embed + (size_t)pl.v0 * d); e->lm.s = nullptr; e->lm.rows = pl.v1 - pl.v0; e->lm.cols = (int)d;
+        e->lm_quant = 0; e->lm_kind = 2;
+        wb += (uint64_t)(pl.v1 - pl.v0) * d * 2;
+    }
+#undef TRY
+    e->weight_bytes = wb + d * 2;    // + one embedding row
+    return CUQWEN_OK;
+}
+
+extern "C" int cuqwen_load(cuqwen_engine* e, const char* path) {
+    if (!e || !path) return fail(CUQWEN_ERR_ARG, "null argument");
+    if (e->loaded) return fail(CUQWEN_ERR_STATE, "weights already loaded");
+    CK(cudaSetDevice(e->p.device));
+    int fd = open(path, O_RDONLY);
+    if (fd < 0) return fail(CUQWEN_ERR_IO, "cannot open binary file at: %s", path);
+    struct stat st; fstat(fd, &st);
+    const size_t size = (size_t)st.st_size;
+    if (size < 11 * 4) { close(fd); return fail(CUQWEN_ERR_IO, "failed to read binary weight header"); }
+    void* map = mmap(nullptr, size, PROT_READ, MAP_PRIVATE, fd, 0);
+    close(fd);
+    if (map == MAP_FAILED) return fail(CUQWEN_ERR_IO, "mmap failed for %s", path);
+    struct Unmap { void* p; size_t n; ~Unmap() { munmap(p, n); } } unmap{map, size};
+    int32_t h[11]; memcpy(h, map, sizeof h);
+    const cuqwen_params& p = e->p;
+    if (h[0] != 0x5157454E) return fail(CUQWEN_ERR_MAGIC, "magic number mismatch: expected 0x5157454e, found 0x%x", h[0]);
+    if (h[1] != p.vocab_size || h[2] != p.dim || h[3] != p.intermediate_size || h[4] != p.n_layers || h[5] != p.n_heads || h[6] != p.n_kv_heads || h[7] != p.head_dim)
+        return fail(CUQWEN_ERR_DIMS, "binary header dimensions do not match the engine configuration");
+    if (h[9] != p.quant) return fail(CUQWEN_ERR_QUANT, "quantization mismatch: engine is %d, file is %d", p.quant, h[9]);
+    if (size < 256) return fail(CUQWEN_ERR_IO, "unexpected end of file while reading tensor data");
+    Cursor cur{(const uint8_t*)map, size, 256};
+    Arena dry;
+    int r = walk_file(e, cur, dry, h[10]);
+    if (r) return fail(r, r == CUQWEN_ERR_IO ? "unexpected end of file while reading tensor data" : "load failed");
+    e->warena_bytes = dry.used + 256;
+    CK(cudaMalloc((void**)&e->warena, e->warena_bytes));
+    Arena real; real.base = e->warena; real.dry = false;
+    r = walk_file(e, cur, real, h[10]);
+    if (r) { cudaFree(e->warena); e->warena = nullptr; return fail(r, "copying weights to the device failed: %s", cudaGetErrorString(cudaGetLastError())); }
+    CK(cudaDeviceSynchronize());
+    e->loaded = true;
+    return CUQWEN_OK;
+}
+
+// ---------------------------------------------------------------------------
+// one decode step as a sequence of launches (order: reference src/model.cu:76-181)
+// ---------------------------------------------------------------------------
+static GemvArgs gv(const __half* x, int K) { GemvArgs a; memset(&a, 0, sizeof a); a.x = x; a.K = K; return a; }
+
+static int tp_allreduce(cuqwen_engine* e, float* buf, int n, cudaStream_t s) {
+    NK(g_nccl.AllReduce(buf, buf, n, ncclFloat32, ncclSum, e->comm, s));
+    return CUQWEN_OK;
+}
+
+static int record_step(cuqwen_engine* e, cudaStream_t s, bool pdl) {
+    const cuqwen_params& p = e->p;
+    LaunchCfg cfg{s, e->sms, pdl};
+    LaunchCfg cfg_plain{s, e->sms, false};
+    int n = 0;
+    const size_t kv_layer = (size_t)e->n_kv_l * p.max_seq_len * p.head_dim;
+    const float eps = __half2float(__float2half(p.norm_eps));   // the reference narrows eps to fp16 (src/model.cu:96)
+    const float pen = __half2float(__float2half(p.repetition_penalty));
+#define LK(call) do { int r_ = (call); if (r_) return fail(CUQWEN_ERR_CUDA, "%s: %s", #call, cudaGetErrorString((cudaError_t)r_)); ++n; } while (0)
+    LK(launch_embed(e->embed, &e->ctl->token, e->x, p.dim, cfg_plain));
+    for (int l = 0; l < p.n_layers; ++l) {
+        const Layer& L = e->layers[l];
+        {   // RMSNorm + QKV + bias + RoPE + KV store
+            GemvArgs a = gv(e->x, p.dim);
+            a.norm_w = L.in_norm; a.eps = eps;
+            a.w[0] = L.q.w; a.w[1] = L.k.w; a.w[2] = L.v.w; a.s[0] = L.q.s; a.s[1] = L.k.s; a.s[2] = L.v.s;
+            a.bias[0] = L.bq; a.bias[1] = L.bk; a.bias[2] = L.bv;
+            a.q_out = e->q; a.k_out = e->k; a.v_out = e->v;
+            a.kcache = e->kc + l * kv_layer; a.vcache = e->vc + l * kv_layer;
+            a.d_pos = &e->ctl->pos; a.n_heads = e->n_heads_l; a.n_kv = e->n_kv_l; a.hd = p.head_dim; a.max_seq = p.max_seq_len;
+            a.theta = p.rope_theta; a.rope_fast = (p.flags & CUQWEN_FLAG_ACCURATE_ROPE) ? 0 : 1;
+            LK(launch_gemv(p.quant, EPI_QKV, a, cfg));
+        }
+        {   // split-KV attention + combine
+            AttnArgs a{};
+            a.q = e->q; a.kc = e->kc + l * kv_layer; a.vc = e->vc + l * kv_layer; a.out = e->att; a.d_pos = &e->ctl->pos;
+            a.n_kv = e->n_kv_l; a.grp = e->plan.grp; a.max_seq = p.max_seq_len; a.nsplit = e->nsplit;
+            a.scale_log2 = (1.0f / sqrtf((float)p.head_dim)) * 1.4426950408889634f;
+            a.part_o = e->part_o; a.part_ml = e->part_ml; a.counters = e->counters;
+            LK(launch_attn(p.head_dim, a, cfg));
+        }
+        {   // o_proj + residual
+            GemvArgs a = gv(e->att, e->q_dim_l);
+            a.w[0] = L.o.w; a.s[0] = L.o.s; a.rows = p.dim;
+            if (e->tp == 1) { a.out_h = e->x; LK(launch_gemv(p.quant, EPI_RESID, a, cfg)); }
+            else {
+                a.out_f = e->tp_partial; LK(launch_gemv(p.quant, EPI_F32, a, cfg));
+                if (int r = tp_allreduce(e, e->tp_partial, p.dim, s)) return r; ++n;
+                LK(launch_resid_sum(e->x, e->tp_partial, 1, 0, p.dim, cfg_plain));
+            }
+        }
+        {   // RMSNorm + gate/up + SwiGLU
+            GemvArgs a = gv(e->x, p.dim);
+            a.norm_w = L.post_norm; a.eps = eps;
+            a.w[0] = L.gate.w; a.w[1] = L.up.w; a.s[0] = L.gate.s; a.s[1] = L.up.s; a.rows = e->inter_l; a.out_h = e->gate;
+            LK(launch_gemv(p.quant, EPI_SWIGLU, a, e->tp == 1 ? cfg : cfg));
+        }
+        {   // down + residual
+            GemvArgs a = gv(e->gate, e->inter_l);
+            a.w[0] = L.down.w; a.s[0] = L.down.s; a.rows = p.dim;
+            if (e->tp == 1) { a.out_h = e->x; LK(launch_gemv(p.quant, EPI_RESID, a, cfg)); }
+            else {
+                a.out_f = e->tp_partial; LK(launch_gemv(p.quant, EPI_F32, a, cfg));
+                if (int r = tp_allreduce(e, e->tp_partial, p.dim, s)) return r; ++n;
+                LK(launch_resid_sum(e->x, e->tp_partial, 1, 0, p.dim, cfg_plain));
+            }
+        }
+    }
+    {   // final RMSNorm + lm_head
+        GemvArgs a = gv(e->x, p.dim);
+        a.norm_w = e->norm; a.eps = eps; a.w[0] = e->lm.w; a.s[0] = e->lm.s; a.rows = e->vocab_l; a.out_h = e->logits;
+        LK(launch_gemv(e->lm_quant, EPI_F16, a, cfg));
+    }
+    LK(launch_penalty(e->logits, e->d_hist, &e->ctl->hist_len, e->vocab_l, e->plan.v0, pen, e->bitmap, cfg));
+    if (e->tp == 1) {
+        LK(launch_argmax(e->logits, e->vocab_l, 0, e->ctl, e->out_ring, e->ring_cap, e->d_hist, e->bitmap, e->best, e->ticket, nullptr, nullptr, cfg));
+    } else {
+        LK(launch_argmax(e->logits, e->vocab_l, e->plan.v0, e->ctl, e->out_ring, e->ring_cap, e->d_hist, e->bitmap, e->best, e->ticket, e->tp_keys + e->tp, nullptr, cfg));
+        NK(g_nccl.AllGather(e->tp_keys + e->tp, e->tp_keys, 1, ncclUint64, e->comm, s)); ++n;
+        LK(launch_merge_keys(e->tp_keys, e->tp, e->ctl, e->out_ring, e->ring_cap, cfg_plain));
+    }
+#undef LK
+    e->launches = n;
+    return CUQWEN_OK;
+}
+
+static int ensure_graph(cuqwen_engine* e) {
+    if (e->graph_ready || (e->p.flags & CUQWEN_FLAG_NO_GRAPH)) return CUQWEN_OK;
+    const bool pdl = !(e->p.flags & CUQWEN_FLAG_NO_PDL);
+    CK(cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeThreadLocal));
+    int r = record_step(e, e->stream, pdl);
+    cudaGraph_t g = nullptr;
+    cudaError_t ce = cudaStreamEndCapture(e->stream, &g);
+    if (r) { if (g) cudaGraphDestroy(g); return r; }
+    CK(ce);
+    e->graph = g;
+    CK(cudaGraphInstantiate(&e->gexec, e->graph, 0));
+    e->graph_ready = true;
+    return CUQWEN_OK;
+}
+
+static int run_step(cuqwen_engine* e) {
+    if (e->p.flags & CUQWEN_FLAG_NO_GRAPH) return record_step(e, e->stream, !(e->p.flags & CUQWEN_FLAG_NO_PDL));
+    CK(cudaGraphLaunch(e->gexec, e->stream));
+    return CUQWEN_OK;
+}
+
+extern "C" int cuqwen_step(cuqwen_engine* e, int token, int pos, const int* history, int history_len, int* out_token) {
+    if (!e) return fail(CUQWEN_ERR_ARG, "null engine");
+    if (!e->loaded) return fail(CUQWEN_ERR_STATE, "cuqwen_step before cuqwen_load");
+    if (e->tp > 1 && !e->comm) return fail(CUQWEN_ERR_STATE, "cuqwen_step before cuqwen_tp_init");
+    if (token < 0 || token >= e->p.vocab_size || pos < 0 || pos >= e->p.max_seq_len || history_len < 0 || history_len > e->p.max_seq_len)
+        return fail(CUQWEN_ERR_ARG, "token %d / pos %d / history_len %d out of range", token, pos, history_len);
+    CK(cudaSetDevice(e->p.device));
+    if (int r = ensure_graph(e)) return r;
+    StepCtl c{}; c.token = token; c.pos = pos; c.hist_len = (history && history_len > 0) ? history_len : 0;
+    *e->h_ctl = c;
+    CK(cudaMemcpyAsync(e->ctl, e->h_ctl, sizeof(StepCtl), cudaMemcpyHostToDevice, e->stream));
+    if (c.hist_len) CK(cudaMemcpyAsync(e->d_hist, history, (size_t)c.hist_len * 4, cudaMemcpyHostToDevice, e->stream));
+    if (int r = run_step(e)) return r;
+    CK(cudaMemcpyAsync(e->h_out, &e->ctl->sampled, 4, cudaMemcpyDeviceToHost, e->stream));
+    CK(cudaStreamSynchronize(e->stream));
+    if (out_token) *out_token = e->h_out[0];
+    return CUQWEN_OK;
+}
+
+extern "C" int cuqwen_decode_n(cuqwen_engine* e, int first_token, int start_pos, int n, int* out_tokens) {
+    if (!e) return fail(CUQWEN_ERR_ARG, "null engine");
+    if (!e->loaded) return fail(CUQWEN_ERR_STATE, "cuqwen_decode_n before cuqwen_load");
+    if (e->tp > 1 && !e->comm) return fail(CUQWEN_ERR_STATE, "cuqwen_decode_n before cuqwen_tp_init");
+    if (n < 1 || n > e->ring_cap || first_token < 0 || first_token >= e->p.vocab_size || start_pos < 0 || start_pos + n > e->p.max_seq_len)
+        return fail(CUQWEN_ERR_ARG, "decode_n arguments out of range");
+    CK(cudaSetDevice(e->p.device));
+    if (int r = ensure_graph(e)) return r;
+    StepCtl c{}; c.token = first_token; c.pos = start_pos; c.auto_advance = 1;
+    *e->h_ctl = c;
+    CK(cudaMemcpyAsync(e->ctl, e->h_ctl, sizeof(StepCtl), cudaMemcpyHostToDevice, e->stream));
+    CK(cudaEventRecord(e->ev0, e->stream));
+    for (int i = 0; i < n; ++i) if (int r = run_step(e)) return r;
+    CK(cudaEventRecord(e->ev1, e->stream));
+    CK(cudaMemcpyAsync(e->h_out, e->out_ring, (size_t)n * 4, cudaMemcpyDeviceToHost, e->stream));
+    CK(cudaStreamSynchronize(e->stream));
+    CK(cudaEventElapsedTime(&e->last_ms, e->ev0, e->ev1));
+    if (out_tokens) memcpy(out_tokens, e->h_out, (size_t)n * 4);
+    return CUQWEN_OK;
+}
+
+extern "C" float cuqwen_last_decode_ms(const cuqwen_engine* e) { return e ? e->last_ms : 0.f; }
+
+extern "C" int cuqwen_kv_fill_normal(cuqwen_engine* e, int ctx_len, uint64_t seed) {
+    if (!e || ctx_len < 0 || ctx_len > e->p.max_seq_len) return fail(CUQWEN_ERR_ARG, "ctx_len out of range");
+    CK(cudaSetDevice(e->p.device));
+    const cuqwen_params& p = e->p;
+    LaunchCfg cfg{e->stream, e->sms, false};
+    const size_t head_stride = (size_t)p.max_seq_len * p.head_dim;
+    for (int l = 0; l < p.n_layers; ++l)
+        for (int h = 0; h < e->n_kv_l; ++h) {
+            const size_t local = ((size_t)l * e->n_kv_l + h) * head_stride;
+            const uint64_t global = ((uint64_t)l * p.n_kv_heads + (e->plan.kvh0 + h)) * head_stride;
+            CK(launch_fill_normal(e->kc + local, (size_t)ctx_len * p.head_dim, seed * 2 + 0, global, cfg));
+            CK(launch_fill_normal(e->vc + local, (size_t)ctx_len * p.head_dim, seed * 2 + 1, global, cfg));
+        }
+    CK(cudaStreamSynchronize(e->stream));
+    return CUQWEN_OK;
+}
+
+extern "C" int cuqwen_nccl_unique_id(void* out, size_t cap) {
+    if (!out || cap < sizeof(ncclUniqueId)) return fail(CUQWEN_ERR_ARG, "buffer too small for an ncclUniqueId (%zu bytes)", sizeof(ncclUniqueId));
+    if (int r = nccl_load()) return r;
+    ncclUniqueId id; NK(g_nccl.GetUniqueId(&id));
+    memcpy(out, &id, sizeof id);
+    return CUQWEN_OK;
+}
+
+extern "C" int cuqwen_tp_init(cuqwen_engine* e, const void* id_bytes, size_t n) {
+    if (!e || !id_bytes || n < sizeof(ncclUniqueId)) return fail(CUQWEN_ERR_ARG, "bad ncclUniqueId");
+    if (e->tp <= 1) return CUQWEN_OK;
+    if (int r = nccl_load()) return r;
+    CK(cudaSetDevice(e->p.device));
+    ncclUniqueId id; memcpy(&id, id_bytes, sizeof id);
+    NK(g_nccl.CommInitRank(&e->comm, e->tp, id, e->rank));
+    return CUQWEN_OK;
+}
+
+extern "C" int cuqwen_tp_plan(int n_heads, int n_kv, int hd, int inter, int vocab, int rank, int size, int* out9) {
+    if (!out9) return fail(CUQWEN_ERR_ARG, "null argument");
+    TpPlan p;
+    if (int r = tp_plan(n_heads, n_kv, hd, inter, vocab, rank, size, &p)) return fail(CUQWEN_ERR_ARG, "model cannot be split over tp_size %d (rule %d)", size, r);
+    int v[9] = {p.qh0, p.qh1, p.kvh0, p.kvh1, p.grp, p.i0, p.i1, p.v0, p.v1};
+    memcpy(out9, v, sizeof v);
+    return CUQWEN_OK;
+}
+
+extern "C" int cuqwen_lm_head_kind(const cuqwen_engine* e) { return e ? e->lm_kind : -1; }
+extern "C" int cuqwen_get_params(const cuqwen_engine* e, cuqwen_params* out) { if (!e || !out) return fail(CUQWEN_ERR_ARG, "null argument"); *out = e->p; out->attn_splits = e->nsplit; return CUQWEN_OK; }
+extern "C" int cuqwen_step_launches(const cuqwen_engine* e) { return e ? e->launches : 0; }
+extern "C" uint64_t cuqwen_step_bytes(const cuqwen_engine* e, int ctx) {
+    if (!e) return 0;
+    return e->weight_bytes + (uint64_t)2 * e->p.n_layers * e->n_kv_l * e->p.head_dim * 2 * (uint64_t)ctx;
+}
+
+extern "C" int cuqwen_get_ptr(cuqwen_engine* e, int which, int layer, void** ptr, size_t* bytes) {
+    if (!e || !ptr) return fail(CUQWEN_ERR_ARG, "null argument");
+    const cuqwen_params& p = e->p;
+    void* r = nullptr; size_t b = 0;
+    auto matb = [&](const Mat& m, int quant) { return elem_bytes2(quant, m.rows, m.cols); };
+    auto scb = [&](const Mat& m) { return (size_t)m.rows * (m.cols / kGroup) * 2; };
+    if (which >= CUQWEN_PTR_IN_NORM) {
+        if (!e->loaded || layer < 0 || layer >= p.n_layers) return fail(CUQWEN_ERR_ARG, "layer %d out of range or weights not loaded", layer);
+        const Layer& L = e->layers[layer];
+        switch (which) {
+            case CUQWEN_PTR_IN_NORM: r = L.in_norm; b = p.dim * 2; break;
+            case CUQWEN_PTR_WQ: r = L.q.w; b = matb(L.q, p.quant); break;
+            case CUQWEN_PTR_SQ: r = L.q.s; b = scb(L.q); break;
+            case CUQWEN_PTR_BQ: r = L.bq; b = e->q_dim_l * 2; break;
+            case CUQWEN_PTR_WK: r = L.k.w; b = matb(L.k, p.quant); break;
+            case CUQWEN_PTR_SK: r = L.k.s; b = scb(L.k); break;
+            case CUQWEN_PTR_BK: r = L.bk; b = e->kv_dim_l * 2; break;
+            case CUQWEN_PTR_WV: r = L.v.w; b = matb(L.v, p.quant); break;
+            case CUQWEN_PTR_SV: r = L.v.s; b = scb(L.v); break;
+            case CUQWEN_PTR_BV: r = L.bv; b = e->kv_dim_l * 2; break;
+            case CUQWEN_PTR_WO: r = L.o.w; b = matb(L.o, p.quant); break;
+            case CUQWEN_PTR_SO: r = L.o.s; b = scb(L.o); break;
+            case CUQWEN_PTR_POST_NORM: r = L.post_norm; b = p.dim * 2; break;
+            case CUQWEN_PTR_WGATE: r = L.gate.w; b = matb(L.gate, p.quant); break;
+            case CUQWEN_PTR_SGATE: r = L.gate.s; b = scb(L.gate); break;
+            case CUQWEN_PTR_WUP: r = L.up.w; b = matb(L.up, p.quant); break;
+            case CUQWEN_PTR_SUP: r = L.up.s; b = scb(L.up); break;
+            case CUQWEN_PTR_WDOWN: r = L.down.w; b = matb(L.down, p.quant); break;
+            case CUQWEN_PTR_SDOWN: r = L.down.s; b = scb(L.down); break;
+            default: return fail(CUQWEN_ERR_ARG, "unknown pointer id %d", which);
+        }
+    } else if (which >= CUQWEN_PTR_EMBED) {
+        if (!e->loaded) return fail(CUQWEN_ERR_STATE, "weights not loaded");
+        switch (which) {
+            case CUQWEN_PTR_EMBED: r = e->embed; b = (size_t)p.vocab_size * p.dim * 2; break;
+            case CUQWEN_PTR_NORM: r = e->norm; b = p.dim * 2; break;
+            case CUQWEN_PTR_LM_HEAD: r = e->lm.w; b = matb(e->lm, e->lm_quant); break;
+            case CUQWEN_PTR_LM_HEAD_SCALE: r = e->lm.s; b = e->lm.s ? scb(e->lm) : 0; break;
+            default: return fail(CUQWEN_ERR_ARG, "unknown pointer id %d", which);
+        }
+    } else {
+        const size_t kvb = (size_t)p.n_layers * e->n_kv_l * p.max_seq_len * p.head_dim * 2;
+        switch (which) {
+            case CUQWEN_PTR_X: r = e->x; b = p.dim * 2; break;
+            case CUQWEN_PTR_XN: r = e->xn; b = p.dim * 2; break;
+            case CUQWEN_PTR_Q: r = e->q; b = e->q_dim_l * 2; break;
+            case CUQWEN_PTR_K: r = e->k; b = e->kv_dim_l * 2; break;
+            case CUQWEN_PTR_V: r = e->v; b = e->kv_dim_l * 2; break;
+            case CUQWEN_PTR_ATT: r = e->att; b = e->q_dim_l * 2; break;
+            case CUQWEN_PTR_GATE: r = e->gate; b = e->inter_l * 2; break;
+            case CUQWEN_PTR_LOGITS: r = e->logits; b = e->vocab_l * 2; break;
+            case CUQWEN_PTR_KEY_CACHE: r = e->kc; b = kvb; break;
+            case CUQWEN_PTR_VALUE_CACHE: r = e->vc; b = kvb; break;
+            case CUQWEN_PTR_HISTORY: r = e->d_hist; b = (size_t)p.max_seq_len * 4; break;
+            default: return fail(CUQWEN_ERR_ARG, "unknown pointer id %d", which);
+        }
+    }
+    *ptr = r; if (bytes) *bytes = b;
+    return CUQWEN_OK;
+}
+
+// ---------------------------------------------------------------------------
+// raw device helpers
+// ---------------------------------------------------------------------------
+extern "C" int cuqwen_dev_alloc(int device, size_t bytes, void** p) { DEV(device); (void)cfg; CK(cudaMalloc(p, bytes ? bytes : 1)); return CUQWEN_OK; }
+extern "C" int cuqwen_dev_free(int device, void* p) { DEV(device); (void)cfg; CK(cudaStreamSynchronize(dc->stream)); CK(cudaFree(p)); return CUQWEN_OK; }
+extern "C" int cuqwen_dev_upload(int device, void* d, const void* h, size_t n) { DEV(device); (void)cfg; CK(cudaMemcpyAsync(d, h, n, cudaMemcpyHostToDevice, dc->stream)); CK(cudaStreamSynchronize(dc->stream)); return CUQWEN_OK; }
+extern "C" int cuqwen_dev_download(int device, void* h, const void* d, size_t n) { DEV(device); (void)cfg; CK(cudaMemcpyAsync(h, d, n, cudaMemcpyDeviceToHost, dc->stream)); CK(cudaStreamSynchronize(dc->stream)); return CUQWEN_OK; }
+extern "C" int cuqwen_dev_memset(int device, void* p, int v, size_t n) { DEV(device); (void)cfg; CK(cudaMemsetAsync(p, v, n, dc->stream)); return CUQWEN_OK; }
+extern "C" int cuqwen_dev_sync(int device) { DEV(device); (void)cfg; CK(cudaStreamSynchronize(dc->stream)); CK(cudaGetLastError()); return CUQWEN_OK; }
+extern "C" int cuqwen_bench_begin(int device) { DEV(device); (void)cfg; CK(cudaEventRecord(dc->ev0, dc->stream)); return CUQWEN_OK; }
+extern "C" int cuqwen_bench_end(int device, float* ms) { DEV(device); (void)cfg; CK(cudaEventRecord(dc->ev1, dc->stream)); CK(cudaEventSynchronize(dc->ev1)); CK(cudaEventElapsedTime(ms, dc->ev0, dc->ev1)); return CUQWEN_OK; }
+
+// ---------------------------------------------------------------------------
+// per-kernel entry points
+// ---------------------------------------------------------------------------
+#define KK(call) do { int r_ = (call); if (r_) return fail(r_ == (int)cudaErrorInvalidValue ? CUQWEN_ERR_ARG : CUQWEN_ERR_CUDA, "%s: %s", #call, cudaGetErrorString((cudaError_t)r_)); } while (0)
+static bool bad_q(int q) { return q < 0 || q > 2; }
+
+extern "C" int cuqwen_k_embedding(int device, const void* table, const int* d_token, void* out, int dim) {
+    DEV(device); if (dim <= 0 || dim % 8) return fail(CUQWEN_ERR_ARG, "dim must be a positive multiple of 8");
+    KK(launch_embed((const __half*)table, d_token, (__half*)out, dim, cfg)); return CUQWEN_OK;
+}
+extern "C" int cuqwen_k_rmsnorm(int device, const void* x, const void* w, void* out, int dim, float eps) {
+    DEV(device); if (dim <= 0) return fail(CUQWEN_ERR_ARG, "dim must be positive");
+    KK(launch_rmsnorm((const __half*)x, (const __half*)w, (__half*)out, dim, eps, cfg)); return CUQWEN_OK;
+}
+extern "C" int cuqwen_k_qkv(int device, int quant, const void* x, const void* norm_w, float eps, const void* wq, const void* wk, const void* wv,
+                            const void* sq, const void* sk, const void* sv, const void* bq, const void* bk, const void* bv, void* q_out, void* k_out,
+                            void* v_out, void* kcache, void* vcache, int dim, int n_heads, int n_kv, int hd, int max_seq, const int* d_pos, float theta, int fast) {
+    DEV(device);
+    if (bad_q(quant) || dim <= 0 || dim % kGroup || (hd != 64 && hd != 128) || n_heads < 1 || n_kv < 1) return fail(CUQWEN_ERR_ARG, "unsupported qkv shape");
+    GemvArgs a = gv((const __half*)x, dim);
+    a.norm_w = (const __half*)norm_w; a.eps = eps;
+    a.w[0] = (const uint8_t*)wq; a.w[1] = (const uint8_t*)wk; a.w[2] = (const uint8_t*)wv;
+    a.s[0] = (const __half*)sq; a.s[1] = (const __half*)sk; a.s[2] = (const __half*)sv;
+    a.bias[0] = (const __half*)bq; a.bias[1] = (const __half*)bk; a.bias[2] = (const __half*)bv;
+    a.q_out = (__half*)q_out; a.k_out = (__half*)k_out; a.v_out = (__half*)v_out; a.kcache = (__half*)kcache; a.vcache = (__half*)vcache;
+    a.d_pos = d_pos; a.n_heads = n_heads; a.n_kv = n_kv; a.hd = hd; a.max_seq = max_seq; a.theta = theta; a.rope_fast = fast;
+    KK(launch_gemv(quant, EPI_QKV, a, cfg)); return CUQWEN_OK;
+}
+extern "C" int cuqwen_k_rope(int device, void* q, void* k, int n_heads, int n_kv, int hd, const int* d_pos, float theta, int fast) {
+    DEV(device); KK(launch_rope((__half*)q, (__half*)k, n_heads, n_kv, hd, d_pos, theta, fast, cfg)); return CUQWEN_OK;
+}
+extern "C" int cuqwen_k_kv_store(int device, const void* k, const void* v, void* kc, void* vc, const int* d_pos, int n_kv, int max_seq, int hd) {
+    DEV(device); KK(launch_kv_store((const __half*)k, (const __half*)v, (__half*)kc, (__half*)vc, d_pos, n_kv, max_seq, hd, cfg)); return CUQWEN_OK;
+}
+extern "C" int cuqwen_attn_scratch_bytes(int n_kv, int hd, int nsplit, size_t* bo, size_t* bml, size_t* bc) {
+    if (n_kv < 1 || nsplit < 1 || nsplit > kMaxSplit || (hd != 64 && hd != 128)) return fail(CUQWEN_ERR_ARG, "unsupported attention shape");
+    if (bo) *bo = attn_scratch_floats_o(n_kv, nsplit, hd) * 4;
+    if (bml) *bml = attn_scratch_floats_ml(n_kv, nsplit) * 4;
+    if (bc) *bc = (size_t)n_kv * 4;
+    return CUQWEN_OK;
+}
+extern "C" int cuqwen_k_attention(int device, const void* q, const void* kc, const void* vc, void* out, const int* d_pos, int n_heads, int n_kv, int hd,
+                                  int max_seq, int nsplit, void* so, void* sml, void* counters) {
+    DEV(device);
+    if (n_kv < 1 || n_heads % n_kv || n_heads / n_kv > kMaxGroup || (hd != 64 && hd != 128) || nsplit < 1 || nsplit > kMaxSplit)
+        return fail(CUQWEN_ERR_ARG, "unsupported attention shape (heads %d/%d, head_dim %d, splits %d)", n_heads, n_kv, hd, nsplit);
+    AttnArgs a{};
+    a.q = (const __half*)q; a.kc = (const __half*)kc; a.vc = (const __half*)vc; a.out = (__half*)out; a.d_pos = d_pos;
+    a.n_kv = n_kv; a.grp = n_heads / n_kv; a.max_seq = max_seq; a.nsplit = nsplit;
+    a.scale_log2 = (1.0f / sqrtf((float)hd)) * 1.4426950408889634f;
+    a.part_o = (float*)so; a.part_ml = (float*)sml; a.counters = (unsigned*)counters;
+    KK(launch_attn(hd, a, cfg)); return CUQWEN_OK;
+}
+extern "C" int cuqwen_k_gemv_add(int device, int quant, const void* w, const void* s, const void* in, void* x, int rows, int cols) {
+    DEV(device); if (bad_q(quant)) return fail(CUQWEN_ERR_ARG, "quant out of range");
+    GemvArgs a = gv((const __half*)in, cols); a.w[0] = (const uint8_t*)w; a.s[0] = (const __half*)s; a.rows = rows; a.out_h = (__half*)x;
+    KK(launch_gemv(quant, EPI_RESID, a, cfg)); return CUQWEN_OK;
+}
+extern "C" int cuqwen_k_gemv(int device, int quant, const void* w, const void* s, const void* x, const void* norm_w, float eps, void* y, int rows, int cols) {
+    DEV(device); if (bad_q(quant)) return fail(CUQWEN_ERR_ARG, "quant out of range");
+    GemvArgs a = gv((const __half*)x, cols); a.norm_w = (const __half*)norm_w; a.eps = eps; a.w[0] = (const uint8_t*)w; a.s[0] = (const __half*)s; a.rows = rows; a.out_h = (__half*)y;
+    KK(launch_gemv(quant, EPI_F16, a, cfg)); return CUQWEN_OK;
+}
+extern "C" int cuqwen_k_gemv_f32(int device, int quant, const void* w, const void* s, const void* x, float* y, int rows, int cols) {
+    DEV(device); if (bad_q(quant)) return fail(CUQWEN_ERR_ARG, "quant out of range");
+    GemvArgs a = gv((const __half*)x, cols); a.w[0] = (const uint8_t*)w; a.s[0] = (const __half*)s; a.rows = rows; a.out_f = y;
+    KK(launch_gemv(quant, EPI_F32, a, cfg)); return CUQWEN_OK;
+}
+extern "C" int cuqwen_k_mlp1(int device, int quant, const void* x, const void* norm_w, float eps, const void* wg, const void* wu, const void* sg,
+                             const void* su, void* out, int dim, int inter) {
+    DEV(device); if (bad_q(quant)) return fail(CUQWEN_ERR_ARG, "quant out of range");
+    GemvArgs a = gv((const __half*)x, dim); a.norm_w = (const __half*)norm_w; a.eps = eps;
+    a.w[0] = (const uint8_t*)wg; a.w[1] = (const uint8_t*)wu; a.s[0] = (const __half*)sg; a.s[1] = (const __half*)su; a.rows = inter; a.out_h = (__half*)out;
+    KK(launch_gemv(quant, EPI_SWIGLU, a, cfg)); return CUQWEN_OK;
+}
+extern "C" int cuqwen_k_penalty(int device, void* logits, const int* hist, const int* d_len, int vocab, float pen, void* bitmap) {
+    DEV(device);
+    KK(launch_penalty((__half*)logits, hist, d_len, vocab, 0, pen, (unsigned*)bitmap, cfg));
+    KK(launch_clear_bitmap(hist, d_len, vocab, 0, (unsigned*)bitmap, cfg));
+    return CUQWEN_OK;
+}
+extern "C" int cuqwen_k_argmax(int device, const void* logits, int* d_out, int vocab, void* scratch16) {
+    DEV(device);
+    unsigned long long* best = (unsigned long long*)scratch16;
+    KK(launch_argmax((const __half*)logits, vocab, 0, nullptr, nullptr, 0, nullptr, nullptr, best, (unsigned*)(best + 1), nullptr, d_out, cfg));
+    return CUQWEN_OK;
+}
+extern "C" int cuqwen_k_dequant(int device, int quant, const void* w, const void* s, void* out, long rows, long cols) {
+    DEV(device); if (quant != 1 && quant != 2) return fail(CUQWEN_ERR_ARG, "dequant needs quant 1 or 2");
+    KK(launch_dequant(quant, w, (const __half*)s, (__half*)out, rows, cols, cfg)); return CUQWEN_OK;
+}

@@ -1,0 +1,29 @@
+// Instantiations of the GEMV kernel family for one weight format.
+#include "gemv.cuh"
+#include "launch.h"
+
+namespace cq {
+
+template <int EPI>
+static int go(const GemvArgs& a, dim3 grid, dim3 block, size_t smem, const LaunchCfg& cfg) {
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = grid; lc.blockDim = block; lc.dynamicSmemBytes = smem; lc.stream = cfg.stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs = at; lc.numAttrs = cfg.pdl ? 1 : 0;
+    return (int)cudaLaunchKernelEx(&lc, gemv_kernel<Q_I8, EPI>, a);
+}
+
+int launch_gemv_i8(int epi, const GemvArgs& a, dim3 grid, dim3 block, size_t smem, const LaunchCfg& cfg) {
+    switch (epi) {
+        case EPI_F16: return go<EPI_F16>(a, grid, block, smem, cfg);
+        case EPI_F32: return go<EPI_F32>(a, grid, block, smem, cfg);
+        case EPI_RESID: return go<EPI_RESID>(a, grid, block, smem, cfg);
+        case EPI_SWIGLU: return go<EPI_SWIGLU>(a, grid, block, smem, cfg);
+        case EPI_QKV: return go<EPI_QKV>(a, grid, block, smem, cfg);
+    }
+    return (int)cudaErrorInvalidValue;
+}
+
+}  // namespace cq

@@ -1,0 +1,266 @@
+// Small kernels of the decode step (embedding row, stand-alone RMSNorm / RoPE /
+// KV store, repetition penalty, greedy sampler, tensor-parallel helpers) and
+// the launch wrappers for the attention kernel.
+#include "attn.cuh"
+#include "gemv.cuh"
+#include "launch.h"
+#include "rng.cuh"
+
+namespace cq {
+
+template <typename... KArgs, typename... Args>
+static int launch_k(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, const LaunchCfg& cfg, Args... args) {
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = grid; lc.blockDim = block; lc.dynamicSmemBytes = smem; lc.stream = cfg.stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs = at; lc.numAttrs = cfg.pdl ? 1 : 0;
+    return (int)cudaLaunchKernelEx(&lc, kern, KArgs(args)...);
+}
+
+// ---- embedding row copy (reference src/kernels.cu:85-96) -------------------
+__global__ void embed_kernel(const __half* __restrict__ table, const int* __restrict__ d_token, __half* __restrict__ out, int dim) {
+    pdl_wait(); pdl_launch_dependents();
+    const uint4* src = reinterpret_cast<const uint4*>(table + (size_t)(*d_token) * dim);
+    uint4* dst = reinterpret_cast<uint4*>(out);
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < dim / 8; i += gridDim.x * blockDim.x) dst[i] = src[i];
+}
+int launch_embed(const __half* table, const int* d_token, __half* out, int dim, const LaunchCfg& cfg) {
+    return launch_k(embed_kernel, dim3((dim / 8 + 255) / 256), dim3(256), 0, cfg, table, d_token, out, dim);
+}
+
+// ---- stand-alone RMSNorm (reference src/kernels.cu:689-751) ----------------
+__global__ void rmsnorm_kernel(const __half* __restrict__ x, const __half* __restrict__ w, __half* __restrict__ out, int dim, float eps) {
+    __shared__ float red[40];
+    pdl_wait(); pdl_launch_dependents();
+    const float inv = block_inv_rms(x, dim, eps, red);
+    for (int i = threadIdx.x; i < dim; i += blockDim.x)
+        out[i] = __float2half(__half2float(x[i]) * inv * __half2float(w[i]));
+}
+int launch_rmsnorm(const __half* x, const __half* w, __half* out, int dim, float eps, const LaunchCfg& cfg) {
+    return launch_k(rmsnorm_kernel, dim3(1), dim3(256), 0, cfg, x, w, out, dim, eps);
+}
+
+// ---- stand-alone RoPE (reference src/kernels.cu:370-398) -------------------
+__global__ void rope_kernel(__half* q, __half* k, int n_heads, int n_kv, int hd, const int* d_pos, float theta, int fast) {
+    pdl_wait(); pdl_launch_dependents();
+    const int half_hd = hd / 2, tid = blockIdx.x * blockDim.x + threadIdx.x;
+    if (tid >= (n_heads + n_kv) * half_hd) return;
+    const bool is_q = tid < n_heads * half_hd;
+    const int lt = is_q ? tid : tid - n_heads * half_hd;
+    const int head = lt / half_hd, i = lt % half_hd;
+    float c, s;
+    rope_cs(i, hd, *d_pos, theta, fast, &c, &s);
+    __half* buf = is_q ? q : k;
+    const int b = head * hd + i;
+    const float v0 = __half2float(buf[b]), v1 = __half2float(buf[b + half_hd]);
+    buf[b] = __float2half(v0 * c - v1 * s);
+    buf[b + half_hd] = __float2half(v1 * c + v0 * s);
+}
+int launch_rope(__half* q, __half* k, int n_heads, int n_kv, int hd, const int* d_pos, float theta, int fast, const LaunchCfg& cfg) {
+    int n = (n_heads + n_kv) * (hd / 2);
+    return launch_k(rope_kernel, dim3((n + 255) / 256), dim3(256), 0, cfg, q, k, n_heads, n_kv, hd, d_pos, theta, fast);
+}
+
+// ---- stand-alone KV store (reference src/kernels.cu:326-347) ---------------
+__global__ void kv_store_kernel(const __half* __restrict__ k, const __half* __restrict__ v, __half* __restrict__ kc, __half* __restrict__ vc,
+                                const int* __restrict__ d_pos, int n_kv, int max_seq, int hd) {
+    pdl_wait(); pdl_launch_dependents();
+    const int tid = blockIdx.x * blockDim.x + threadIdx.x;
+    if (tid >= n_kv * hd) return;
+    const int h = tid / hd, d = tid % hd;
+    const size_t dst = ((size_t)h * max_seq + *d_pos) * hd + d;
+    kc[dst] = k[tid]; vc[dst] = v[tid];
+}
+int launch_kv_store(const __half* k, const __half* v, __half* kc, __half* vc, const int* d_pos, int n_kv, int max_seq, int hd, const LaunchCfg& cfg) {
+    return launch_k(kv_store_kernel, dim3((n_kv * hd + 255) / 256), dim3(256), 0, cfg, k, v, kc, vc, d_pos, n_kv, max_seq, hd);
+}
+
+// ---- repetition penalty (reference src/kernels.cu:873-891) -----------------
+// The reference visits the first min(hist_len, 4096) history entries and rescales once per
+// occurrence, racing on duplicates.  Here the first thread to set the id's bit in `bitmap`
+// applies the penalty, so every distinct id is penalised exactly once.
+__global__ void penalty_kernel(__half* logits, const int* __restrict__ hist, const int* __restrict__ d_hist_len,
+                               int vocab, int vocab_base, float pen, unsigned* bitmap) {
+    pdl_wait(); pdl_launch_dependents();
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= *d_hist_len) return;
+    const int id = hist[idx] - vocab_base;
+    if (id < 0 || id >= vocab) return;
+    const unsigned bit = 1u << (id & 31);
+    if (atomicOr(bitmap + (id >> 5), bit) & bit) return;
+    const float l = __half2float(logits[id]);
+    logits[id] = __float2half(l < 0.f ? l * pen : l / pen);
+}
+__global__ void clear_bitmap_kernel(const int* __restrict__ hist, const int* __restrict__ d_hist_len, int vocab, int vocab_base, unsigned* bitmap) {
+    pdl_wait(); pdl_launch_dependents();
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= *d_hist_len) return;
+    const int id = hist[idx] - vocab_base;
+    if (id >= 0 && id < vocab) bitmap[id >> 5] = 0u;
+}
+int launch_penalty(__half* logits, const int* hist, const int* d_hist_len, int vocab, int vocab_base, float penalty, unsigned* bitmap, const LaunchCfg& cfg) {
+    return launch_k(penalty_kernel, dim3(16), dim3(256), 0, cfg, logits, hist, d_hist_len, vocab, vocab_base, penalty, bitmap);
+}
+int launch_clear_bitmap(const int* hist, const int* d_hist_len, int vocab, int vocab_base, unsigned* bitmap, const LaunchCfg& cfg) {
+    return launch_k(clear_bitmap_kernel, dim3(16), dim3(256), 0, cfg, hist, d_hist_len, vocab, vocab_base, bitmap);
+}
+
+// ---- greedy sampler (reference src/kernels.cu:907-950) ---------------------
+__device__ __forceinline__ unsigned long long argmax_pack(float v, int idx) {
+    unsigned fu = __float_as_uint(v);
+    unsigned key = (fu & 0x80000000u) ? ~fu : (fu | 0x80000000u);
+    return ((unsigned long long)key << 32) | (unsigned)(~idx);
+}
+__device__ __forceinline__ void finish_step(StepCtl* ctl, int token, int* out_ring, int ring_cap) {
+    ctl->sampled = token;
+    if (ctl->auto_advance) {
+        ctl->token = token;
+        ctl->pos += 1;
+        const int o = ctl->out_idx;
+        if (out_ring && o < ring_cap) out_ring[o] = token;
+        ctl->out_idx = o + 1;
+    }
+}
+__global__ void argmax_kernel(const __half* __restrict__ logits, int vocab, int vocab_base, StepCtl* ctl, int* out_ring, int ring_cap,
+                              const int* __restrict__ hist, unsigned* bitmap, unsigned long long* best, unsigned* ticket,
+                              unsigned long long* key_out, int* token_out) {
+    __shared__ unsigned long long sbest[8];
+    pdl_wait(); pdl_launch_dependents();
+    // undo the penalty pass's marks (idempotent stores of zero)
+    if (hist && bitmap) {
+        const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+        if (idx < min(ctl->hist_len, 4096)) {
+            const int id = hist[idx] - vocab_base;
+            if (id >= 0 && id < vocab) bitmap[id >> 5] = 0u;
+        }
+    }
+    unsigned long long b = 0ull;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < vocab; i += gridDim.x * blockDim.x) {
+        unsigned long long p = argmax_pack(__half2float(logits[i]), i + vocab_base);
+        b = p > b ? p : b;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) { unsigned long long y = __shfl_xor_sync(0xffffffffu, b, o); b = y > b ? y : b; }
+    if ((threadIdx.x & 31) == 0) sbest[threadIdx.x >> 5] = b;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < (int)(blockDim.x >> 5); ++w) b = sbest[w] > b ? sbest[w] : b;
+        atomicMax(best, b);
+        __threadfence();
+        if (atomicAdd(ticket, 1u) == gridDim.x - 1) {
+            __threadfence();
+            const unsigned long long fin = atomicExch(best, 0ull);
+            *ticket = 0u;
+            const int token = (int)(~((unsigned)(fin & 0xffffffffu)));
+            if (key_out) *key_out = fin;
+            else if (ctl) finish_step(ctl, token, out_ring, ring_cap);
+            if (token_out) *token_out = token;
+        }
+    }
+}
+int launch_argmax(const __half* logits, int vocab, int vocab_base, StepCtl* ctl, int* out_ring, int ring_cap, const int* hist, unsigned* bitmap,
+                  unsigned long long* best, unsigned* ticket, unsigned long long* key_out, int* token_out, const LaunchCfg& cfg) {
+    int blocks = cfg.sm_count > 16 ? cfg.sm_count : 16;   // >= 16 blocks x 256 threads cover the 4096 history slots
+    return launch_k(argmax_kernel, dim3(blocks), dim3(256), 0, cfg, logits, vocab, vocab_base, ctl, out_ring, ring_cap, hist, bitmap, best, ticket, key_out, token_out);
+}
+__global__ void merge_keys_kernel(const unsigned long long* __restrict__ keys, int n, StepCtl* ctl, int* out_ring, int ring_cap) {
+    pdl_wait(); pdl_launch_dependents();
+    if (threadIdx.x != 0) return;
+    unsigned long long b = 0ull;
+    for (int i = 0; i < n; ++i) b = keys[i] > b ? keys[i] : b;
+    finish_step(ctl, (int)(~((unsigned)(b & 0xffffffffu))), out_ring, ring_cap);
+}
+int launch_merge_keys(const unsigned long long* keys, int n, StepCtl* ctl, int* out_ring, int ring_cap, const LaunchCfg& cfg) {
+    return launch_k(merge_keys_kernel, dim3(1), dim3(32), 0, cfg, keys, n, ctl, out_ring, ring_cap);
+}
+
+// ---- tensor-parallel residual: x = half(float(x) + sum_r partial_r) --------
+__global__ void resid_sum_kernel(__half* x, const float* __restrict__ partial, int n_parts, size_t stride, int dim) {
+    pdl_wait(); pdl_launch_dependents();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= dim) return;
+    float s = 0.f;
+    for (int r = 0; r < n_parts; ++r) s += partial[(size_t)r * stride + i];
+    x[i] = __float2half(__half2float(x[i]) + s);
+}
+int launch_resid_sum(__half* x, const float* partial, int n_parts, size_t part_stride, int dim, const LaunchCfg& cfg) {
+    return launch_k(resid_sum_kernel, dim3((dim + 255) / 256), dim3(256), 0, cfg, x, partial, n_parts, part_stride, dim);
+}
+
+// ---- dequantised fp16 weights: half(float(q) * float(scale)) ---------------
+__global__ void dequant_kernel(int quant, const uint8_t* __restrict__ w, const __half* __restrict__ s, __half* __restrict__ out, long rows, long cols) {
+    const long n = rows * cols, ng = cols / kGroup;
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+        const long r = i / cols, c = i % cols;
+        int q;
+        if (quant == Q_I4) {
+            const unsigned b = w[r * (cols / 2) + c / 2];
+            const unsigned nib = (c & 1) ? (b >> 4) : (b & 0xF);
+            q = (int)(nib ^ 8u) - 8;
+        } else {
+            q = (int)reinterpret_cast<const int8_t*>(w)[i];
+        }
+        out[i] = __float2half((float)q * __half2float(s[r * ng + c / kGroup]));
+    }
+}
+int launch_dequant(int quant, const void* w, const __half* s, __half* out, long rows, long cols, const LaunchCfg& cfg) {
+    long n = rows * cols;
+    int blocks = (int)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096);
+    return launch_k(dequant_kernel, dim3(blocks), dim3(256), 0, cfg, quant, (const uint8_t*)w, s, out, rows, cols);
+}
+
+int launch_fill_normal(__half* dst, size_t n, uint64_t seed, uint64_t base, const LaunchCfg& cfg) {
+    int blocks = (int)((n + 255) / 256 < 8192 ? (n + 255) / 256 : 8192);
+    if (blocks < 1) blocks = 1;
+    return launch_k(fill_normal_kernel, dim3(blocks), dim3(256), 0, cfg, dst, n, seed, base);
+}
+
+// ---- attention -------------------------------------------------------------
+size_t attn_scratch_floats_o(int n_kv, int nsplit, int head_dim) { return (size_t)n_kv * nsplit * kMaxGroup * head_dim; }
+size_t attn_scratch_floats_ml(int n_kv, int nsplit) { return (size_t)n_kv * nsplit * kMaxGroup * 2; }
+
+int launch_attn(int head_dim, const AttnArgs& a, const LaunchCfg& cfg) {
+    if (a.grp < 1 || a.grp > kMaxGroup || a.nsplit < 1 || a.nsplit > kMaxSplit) return (int)cudaErrorInvalidValue;
+    dim3 grid(a.n_kv, a.nsplit), block(kAttnWarps * 32);
+    if (head_dim == 128) return launch_k(attn_decode_kernel<128>, grid, block, 0, cfg, a);
+    if (head_dim == 64) return launch_k(attn_decode_kernel<64>, grid, block, 0, cfg, a);
+    return (int)cudaErrorInvalidValue;
+}
+
+// ---- GEMV dispatch ---------------------------------------------------------
+int launch_gemv_i4(int epi, const GemvArgs& a, dim3 grid, dim3 block, size_t smem, const LaunchCfg& cfg);
+int launch_gemv_i8(int epi, const GemvArgs& a, dim3 grid, dim3 block, size_t smem, const LaunchCfg& cfg);
+int launch_gemv_f16(int epi, const GemvArgs& a, dim3 grid, dim3 block, size_t smem, const LaunchCfg& cfg);
+
+int launch_gemv(int quant, int epi, GemvArgs& a, const LaunchCfg& cfg) {
+    if (a.K <= 0 || a.K % kGroup != 0 || a.K > 22528) return (int)cudaErrorInvalidValue;
+    if (epi == EPI_QKV) {
+        if (a.hd % 32 != 0) return (int)cudaErrorInvalidValue;
+        a.nsets = (a.n_heads + 2 * a.n_kv) * (a.hd / 32);
+    } else {
+        if (a.rows <= 0) return (int)cudaErrorInvalidValue;
+        a.nsets = (a.rows + 15) / 16;
+    }
+    const int ngrp = a.K / kGroup;
+    dim3 grid, block;
+    if (a.nsets >= 8 * cfg.sm_count) {
+        a.ksplit = 0;
+        int g = (a.nsets + 7) / 8;
+        grid = dim3(g < 2 * cfg.sm_count ? g : 2 * cfg.sm_count);
+        block = dim3(256);
+    } else {
+        a.ksplit = 1;
+        grid = dim3(a.nsets);
+        int nw = ngrp < 8 ? ngrp : 8;
+        block = dim3(32 * nw);
+    }
+    const size_t smem = gemv_smem_bytes(a.K);
+    if (quant == Q_I4) return launch_gemv_i4(epi, a, grid, block, smem, cfg);
+    if (quant == Q_I8) return launch_gemv_i8(epi, a, grid, block, smem, cfg);
+    if (quant == Q_F16) return launch_gemv_f16(epi, a, grid, block, smem, cfg);
+    return (int)cudaErrorInvalidValue;
+}
+
+}  // namespace cq

@@ -1,0 +1,171 @@
+/*
+ * C ABI of libcuqwen_b200.so: a B200 (sm_100a) batch-1 decode engine for the
+ * Qwen2.5 family that is a drop-in for CuQwen's weight file format, model
+ * table and host API.  Plain pointers and sizes only; every function returns a
+ * status code (0 = ok) instead of exiting the process, and a message for the
+ * last failure of the calling thread is available from cuqwen_last_error().
+ *
+ * Each entry point names the CuQwen interface it stands in for
+ * (file:line within that project).  Device pointers are marked "dev".
+ */
+#ifndef CUQWEN_B200_H
+#define CUQWEN_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct cuqwen_engine cuqwen_engine;
+
+enum {
+    CUQWEN_OK = 0,
+    CUQWEN_ERR_ARG = 1,       /* bad argument / unsupported shape */
+    CUQWEN_ERR_IO = 2,        /* file cannot be opened / short read / truncated tensor data */
+    CUQWEN_ERR_MAGIC = 3,     /* header magic is not 0x5157454E */
+    CUQWEN_ERR_DIMS = 4,      /* header dims differ from the engine's configuration */
+    CUQWEN_ERR_QUANT = 5,     /* header quantisation differs from the engine's configuration */
+    CUQWEN_ERR_CUDA = 6,
+    CUQWEN_ERR_NCCL = 7,
+    CUQWEN_ERR_STATE = 8,     /* call made in the wrong order (e.g. step before load) */
+    CUQWEN_ERR_TIMEOUT = 9    /* a bounded device-side wait expired */
+};
+
+enum { CUQWEN_FP16 = 0, CUQWEN_INT8 = 1, CUQWEN_INT4 = 2 };          /* include/config.h:18-32 QUANT_TYPE_ID */
+
+/* Rows of the model table, include/config.h:55-113. */
+enum { CUQWEN_MODEL_0_5B = 0, CUQWEN_MODEL_1_5B = 1, CUQWEN_MODEL_3B = 2, CUQWEN_MODEL_7B = 3, CUQWEN_MODEL_14B = 4, CUQWEN_MODEL_CUSTOM = -1 };
+
+enum {
+    CUQWEN_FLAG_ACCURATE_ROPE = 1,  /* accurate pow/sin/cos instead of the fast-math forms the reference build uses */
+    CUQWEN_FLAG_NO_PDL = 2,         /* plain stream order between kernels (no programmatic dependent launch) */
+    CUQWEN_FLAG_NO_GRAPH = 4        /* launch the step kernel by kernel instead of replaying a CUDA graph */
+};
+
+/* Mirrors QwenConfig (include/config.h:52-127) as run-time data. */
+typedef struct cuqwen_params {
+    int32_t model_id;        /* CUQWEN_MODEL_*; CUSTOM uses the explicit dims below */
+    int32_t vocab_size, dim, intermediate_size, n_layers, n_heads, n_kv_heads, head_dim;
+    int32_t max_seq_len;     /* KV rows per head; 0 = 32768 (include/config.h:65) */
+    int32_t quant;           /* CUQWEN_FP16 / INT8 / INT4 */
+    int32_t device;          /* CUDA device ordinal */
+    int32_t tp_rank, tp_size;/* tensor-parallel position; tp_size 0 or 1 = single GPU */
+    int32_t attn_splits;     /* split-KV CTAs per KV head; 0 = choose from the SM count */
+    uint32_t flags;
+    float norm_eps, rope_theta, repetition_penalty;   /* 0 = 1e-6, 1e6, 1.1 (include/config.h:124-126) */
+} cuqwen_params;
+
+/* Fill `p` from the model table.  Replaces the -Dmodel/-Dquant compile-time selection (CMakeLists.txt:18-82). */
+int cuqwen_model_params(int model_id, int quant, cuqwen_params* p);
+
+/* malloc_qwen_state (src/model.cu:5-44): activations, KV cache, scratch, stream. */
+int cuqwen_create(const cuqwen_params* p, cuqwen_engine** out);
+/* free_qwen_state + free_weights (src/model.cu:46-74, src/load_weights.cpp:167-200). */
+void cuqwen_destroy(cuqwen_engine* e);
+
+/* load_weights (src/load_weights.cpp:36-165): same file format, same validation; returns a code instead of exit(). */
+int cuqwen_load(cuqwen_engine* e, const char* bin_path);
+
+/* qwen_forward (src/model.cu:183-223): one decode step; host token in, host token out, synchronous. */
+int cuqwen_step(cuqwen_engine* e, int token, int pos, const int* history, int history_len, int* out_token);
+
+/* n greedy steps with the sampled token fed back on the device (no counterpart in the reference, which pays
+ * a host round trip per token, src/main.cu:95-112).  out_tokens receives n ids.  history_len = 0 semantics. */
+int cuqwen_decode_n(cuqwen_engine* e, int first_token, int start_pos, int n, int* out_tokens);
+/* Milliseconds the device spent in the last cuqwen_decode_n (CUDA events around the n graph launches). */
+float cuqwen_last_decode_ms(const cuqwen_engine* e);
+
+/* Benchmark / test hook: fill K and V of every layer for positions [0, ctx_len) with N(0,1) fp16 values that
+ * depend only on (seed, layer, global kv head, position, d).  Stands in for the prefill the reference benchmark
+ * skips (benchmark/cuqwen_benchmark.cu:57-62). */
+int cuqwen_kv_fill_normal(cuqwen_engine* e, int ctx_len, uint64_t seed);
+
+/* Tensor-parallel set-up.  nccl_unique_id: the 128 bytes of an ncclUniqueId created by rank 0 and broadcast by
+ * the host program.  Must be called on every rank after cuqwen_create. */
+int cuqwen_tp_init(cuqwen_engine* e, const void* nccl_unique_id, size_t id_bytes);
+int cuqwen_nccl_unique_id(void* out, size_t cap);
+/* The partition cuqwen_create applies for (tp_rank, tp_size): out9 = {q_head0, q_head1, kv_head0, kv_head1,
+ * q_heads_per_kv_head, inter0, inter1, vocab0, vocab1} (half-open global ranges).  Pure host arithmetic. */
+int cuqwen_tp_plan(int n_heads, int n_kv_heads, int head_dim, int intermediate_size, int vocab_size, int rank, int size, int* out9);
+
+/* Device pointers of engine-owned buffers, for harnesses that poke state directly the way the reference's do
+ * (QwenState / QwenWeights fields, include/model.cuh:9-46, include/load_weights.h:17-54). */
+enum {
+    CUQWEN_PTR_X = 0, CUQWEN_PTR_XN, CUQWEN_PTR_Q, CUQWEN_PTR_K, CUQWEN_PTR_V, CUQWEN_PTR_ATT, CUQWEN_PTR_GATE,
+    CUQWEN_PTR_LOGITS, CUQWEN_PTR_KEY_CACHE, CUQWEN_PTR_VALUE_CACHE, CUQWEN_PTR_HISTORY,
+    CUQWEN_PTR_EMBED = 32, CUQWEN_PTR_NORM, CUQWEN_PTR_LM_HEAD, CUQWEN_PTR_LM_HEAD_SCALE,
+    CUQWEN_PTR_IN_NORM = 64, CUQWEN_PTR_WQ, CUQWEN_PTR_SQ, CUQWEN_PTR_BQ, CUQWEN_PTR_WK, CUQWEN_PTR_SK, CUQWEN_PTR_BK,
+    CUQWEN_PTR_WV, CUQWEN_PTR_SV, CUQWEN_PTR_BV, CUQWEN_PTR_WO, CUQWEN_PTR_SO, CUQWEN_PTR_POST_NORM,
+    CUQWEN_PTR_WGATE, CUQWEN_PTR_SGATE, CUQWEN_PTR_WUP, CUQWEN_PTR_SUP, CUQWEN_PTR_WDOWN, CUQWEN_PTR_SDOWN
+};
+int cuqwen_get_ptr(cuqwen_engine* e, int which, int layer, void** dev_ptr, size_t* bytes);
+/* 1 when the loaded file carries an INT8 lm_head (QwenWeights::lm_head_quantized), 0 fp16, 2 fp16 tied to the embedding. */
+int cuqwen_lm_head_kind(const cuqwen_engine* e);
+int cuqwen_get_params(const cuqwen_engine* e, cuqwen_params* out);
+/* Algorithmic bytes one decode step reads at context length ctx on this rank: all weights, scales, biases,
+ * norms, one embedding row, and K+V rows [0, ctx) of every layer. */
+uint64_t cuqwen_step_bytes(const cuqwen_engine* e, int ctx);
+/* Kernel launches in one decode step. */
+int cuqwen_step_launches(const cuqwen_engine* e);
+
+/* ---- raw device memory helpers (so a host language needs no CUDA binding of its own) ---- */
+int cuqwen_dev_alloc(int device, size_t bytes, void** dev_ptr);
+int cuqwen_dev_free(int device, void* dev_ptr);
+int cuqwen_dev_upload(int device, void* dev_dst, const void* host_src, size_t bytes);
+int cuqwen_dev_download(int device, void* host_dst, const void* dev_src, size_t bytes);
+int cuqwen_dev_memset(int device, void* dev_ptr, int value, size_t bytes);
+int cuqwen_dev_sync(int device);
+/* CUDA events on the library's per-device stream, to time a sequence of cuqwen_k_* calls from a host language. */
+int cuqwen_bench_begin(int device);
+int cuqwen_bench_end(int device, float* ms);
+
+/* ---- per-kernel entry points: the launch_* functions of include/kernels.cuh:19-160 with run-time dims.
+ * All pointers are device pointers; work is queued on the device's default stream of this library
+ * (cuqwen_dev_sync waits for it). ---- */
+
+/* launch_embedding_lookup (kernels.cuh:19) */
+int cuqwen_k_embedding(int device, const void* embed_table, const int* d_token, void* out, int dim);
+/* launch_rmsnorm (kernels.cuh:132-139); eps as the fp16-rounded value the reference passes. */
+int cuqwen_k_rmsnorm(int device, const void* x, const void* weight, void* out, int dim, float eps);
+/* launch_fused_attn_block (kernels.cuh:62-87): q/k/v = W.x + b, then RoPE on q and k.  norm_weight non-null
+ * fuses the RMSNorm of x; kcache/vcache non-null also stores k, v at row *d_pos (launch_kv_cache_store, :38-48). */
+int cuqwen_k_qkv(int device, int quant, const void* x, const void* norm_weight, float eps,
+                 const void* wq, const void* wk, const void* wv, const void* sq, const void* sk, const void* sv,
+                 const void* bq, const void* bk, const void* bv, void* q_out, void* k_out, void* v_out,
+                 void* kcache, void* vcache, int dim, int n_heads, int n_kv_heads, int head_dim, int max_seq_len,
+                 const int* d_pos, float rope_theta, int rope_fast);
+/* apply_rope_kernel alone (src/kernels.cu:370-398) */
+int cuqwen_k_rope(int device, void* q, void* k, int n_heads, int n_kv_heads, int head_dim, const int* d_pos, float rope_theta, int rope_fast);
+/* launch_kv_cache_store (kernels.cuh:38-48) */
+int cuqwen_k_kv_store(int device, const void* k, const void* v, void* kcache, void* vcache, const int* d_pos, int n_kv_heads, int max_seq_len, int head_dim);
+/* launch_gqa_attention_decode (kernels.cuh:21-36).  scratch_o / scratch_ml / counters sized by
+ * cuqwen_attn_scratch_bytes; counters must be zero on first use. */
+int cuqwen_k_attention(int device, const void* q, const void* kcache, const void* vcache, void* out, const int* d_pos,
+                       int n_heads, int n_kv_heads, int head_dim, int max_seq_len, int n_splits,
+                       void* scratch_o, void* scratch_ml, void* counters);
+int cuqwen_attn_scratch_bytes(int n_kv_heads, int head_dim, int n_splits, size_t* bytes_o, size_t* bytes_ml, size_t* bytes_counters);
+/* launch_gemv_add_fp16 / launch_fused_mlp_stage2 (kernels.cuh:120-128, :108-116): x_inout += W . input */
+int cuqwen_k_gemv_add(int device, int quant, const void* w, const void* scale, const void* input, void* x_inout, int rows, int cols);
+/* Plain GEMV y = W . x (fp16 out), optional fused RMSNorm of x.  launch_compute_logits(_int8) (kernels.cuh:141-158). */
+int cuqwen_k_gemv(int device, int quant, const void* w, const void* scale, const void* x, const void* norm_weight, float eps, void* y, int rows, int cols);
+/* Same with fp32 output (row-parallel partial sums under tensor parallelism). */
+int cuqwen_k_gemv_f32(int device, int quant, const void* w, const void* scale, const void* x, float* y, int rows, int cols);
+/* launch_fused_mlp_stage1 (kernels.cuh:90-102): h = silu(Wg.x) * (Wu.x), optional fused RMSNorm of x. */
+int cuqwen_k_mlp1(int device, int quant, const void* x, const void* norm_weight, float eps, const void* wg, const void* wu,
+                  const void* sg, const void* su, void* out, int dim, int inter);
+/* launch_apply_repetition_penalty (kernels.cuh:50-57); bitmap: ceil(vocab/32) zeroed u32, left zeroed. */
+int cuqwen_k_penalty(int device, void* logits, const int* d_history, const int* d_history_len, int vocab, float penalty, void* bitmap);
+/* launch_argmax (kernels.cuh:59-60); scratch: 16 zeroed bytes, left zeroed. */
+int cuqwen_k_argmax(int device, const void* logits, int* d_token_out, int vocab, void* scratch16);
+/* Dequantised fp16 weights half(float(q) * float(scale)) (the value dot8 multiplies by, src/kernels.cu:27-42). */
+int cuqwen_k_dequant(int device, int quant, const void* w, const void* scale, void* out_fp16, long rows, long cols);
+
+const char* cuqwen_strerror(int code);
+const char* cuqwen_last_error(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,322 @@
+"""GPU parity of every kernel entry point, called through the C ABI, against the CPU oracle on the same seeded
+inputs and - where oracle/_ref was built - against the reference's own CUDA kernels.
+
+Tolerance for fp16 outputs: 2e-3 relative or 1e-2 absolute; integer / bit-pattern results must be identical."""
+import numpy as np
+import pytest
+
+from cuqwen_b200 import kernels as K
+from oracle import oracle_py as O
+from tests.gpu_util import ATOL, EPS_H, QNAME, RTOL, DevBuf, Pool, close, dev, dint, quant_mats, report, sync
+
+pytestmark = pytest.mark.gpu
+
+
+def d2h(buf, dtype=np.float16, count=None):
+    sync()
+    return buf.numpy(dtype, count)
+
+
+def maybe(b):
+    return dev(b) if b is not None else None
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("quant", [1, 2])
+def test_dequantised_values_bit_exact(built, quant):
+    rng = np.random.default_rng(quant)
+    rows, cols = 96, 896
+    w, s = quant_mats(rng, rows, cols, quant)
+    out = DevBuf(rows * cols * 2)
+    K.dequant(quant, dev(w), dev(s), out, rows, cols)
+    got = d2h(out).reshape(rows, cols)
+    want = O.dequant(quant, w, s, rows, cols)
+    assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
+
+
+def run_gemv(quant, w, s, x, rows, cols, norm_w=None):
+    y = DevBuf(rows * 2)
+    K.gemv(quant, dev(w), maybe(s), dev(x), y, rows, cols, norm_weight=maybe(norm_w), eps=EPS_H if norm_w is not None else 0.0)
+    return d2h(y)
+
+
+def test_config1_w4a16_gemv_4864x896(built):
+    """BASELINE config 1: int4 uniform in [-8,7], scales U(0.002,0.02), x ~ N(0,1), fp32 accumulate, fp16 out."""
+    rng = np.random.default_rng(1234)
+    rows, cols = 4864, 896
+    w, s = quant_mats(rng, rows, cols, 2)
+    x = rng.standard_normal(cols).astype(np.float16)
+    got = run_gemv(2, w, s, x, rows, cols)
+    want = O.gemv_f32(2, w, s, x, rows, cols).astype(np.float16)
+    assert close(got, want), report(got, want)
+    assert (got.view(np.uint16) == want.view(np.uint16)).mean() > 0.97      # same sums up to fp32 reordering
+    ref = O.ref_lib("0.5b", "int4")
+    if ref is not None:
+        acc, P = DevBuf(rows * 2), Pool()
+        ref.ref_gemv_add(P.p(w), P.p(s), P.p(x), acc.ptr, rows, cols)
+        assert ref.ref_sync() == 0
+        r = acc.numpy(np.float16)
+        assert close(got, r), report(got, r)
+
+
+@pytest.mark.parametrize("quant", [0, 1, 2])
+@pytest.mark.parametrize("rows,cols", [(4864, 896), (896, 4864), (3584, 18944), (50, 256), (19000, 256), (16, 128), (1, 128)])
+def test_gemv_shapes_and_strategies(built, quant, rows, cols):
+    """Tall (warp per tile), wide (K split across a CTA), ragged and minimal shapes."""
+    rng = np.random.default_rng(rows + cols + quant)
+    w, s = quant_mats(rng, rows, cols, quant)
+    x = rng.standard_normal(cols).astype(np.float16)
+    got = run_gemv(quant, w, s, x, rows, cols)
+    want = O.gemv_f32(quant, w, s, x, rows, cols).astype(np.float16)
+    assert close(got, want), report(got, want)
+
+
+def test_gemv_rejects_bad_shapes(built):
+    from cuqwen_b200 import CuQwenError
+    b = DevBuf(4096)
+    for rows, cols in ((16, 100), (0, 128), (16, 0)):
+        with pytest.raises(CuQwenError) as e:
+            K.gemv(2, b, b, b, b, rows, cols)
+        assert e.value.code == 1
+    with pytest.raises(CuQwenError):
+        K.gemv(5, b, b, b, b, 16, 128)
+
+
+@pytest.mark.parametrize("quant", [0, 1, 2])
+def test_gemv_with_fused_rmsnorm(built, quant):
+    rng = np.random.default_rng(40 + quant)
+    rows, cols = 640, 896
+    w, s = quant_mats(rng, rows, cols, quant, full_range=False)
+    x = (3 * rng.standard_normal(cols)).astype(np.float16)
+    nw = (1 + 0.02 * rng.standard_normal(cols)).astype(np.float16)
+    got = run_gemv(quant, w, s, x, rows, cols, norm_w=nw)
+    xn = O.rmsnorm(x, nw)
+    want = O.gemv_f32(quant, w, s, xn, rows, cols).astype(np.float16)
+    assert close(got, want), report(got, want)
+    # stand-alone norm agrees with the fused one
+    out = DevBuf(cols * 2)
+    K.rmsnorm(dev(x), dev(nw), out, cols, EPS_H)
+    g = d2h(out)
+    assert close(g, xn, atol=1e-3), report(g, xn)
+
+
+@pytest.mark.parametrize("quant", [0, 1, 2])
+@pytest.mark.parametrize("rows,cols", [(896, 896), (3584, 3584), (896, 4864)])
+def test_gemv_add_residual(built, quant, rows, cols):
+    rng = np.random.default_rng(7 * quant + rows)
+    w, s = quant_mats(rng, rows, cols, quant, full_range=False)
+    inp = rng.standard_normal(cols).astype(np.float16)
+    x0 = rng.standard_normal(rows).astype(np.float16)
+    xb = dev(x0)
+    K.gemv_add(quant, dev(w), maybe(s), dev(inp), xb, rows, cols)
+    got = d2h(xb)
+    want = O.gemv_add(quant, w, s, inp, x0, rows, cols)
+    assert close(got, want), report(got, want)
+    ref = O.ref_lib("0.5b" if cols in (896, 4864) and rows == 896 else "7b", QNAME[quant])
+    if ref is not None:
+        xr, P = dev(x0), Pool()
+        ref.ref_gemv_add(P.p(w), P.p(s), P.p(inp), xr.ptr, rows, cols)
+        assert ref.ref_sync() == 0
+        r = xr.numpy(np.float16)
+        assert close(got, r), report(got, r)
+
+
+@pytest.mark.parametrize("quant", [0, 1, 2])
+@pytest.mark.parametrize("dim,inter", [(896, 4864), (3584, 18944), (256, 48)])
+def test_gate_up_swiglu(built, quant, dim, inter):
+    rng = np.random.default_rng(dim + inter + quant)
+    wg, sg = quant_mats(rng, inter, dim, quant, full_range=False)
+    wu, su = quant_mats(rng, inter, dim, quant, full_range=False)
+    x = rng.standard_normal(dim).astype(np.float16)
+    out = DevBuf(inter * 2)
+    K.fused_mlp_stage1(quant, dev(x), dev(wg), dev(wu), maybe(sg), maybe(su), out, dim, inter)
+    got = d2h(out)
+    want = O.mlp1(quant, x, wg, wu, sg, su, dim, inter)
+    assert close(got, want), report(got, want)
+    ref = O.ref_lib("7b" if dim == 3584 else "0.5b", QNAME[quant])
+    if ref is not None:
+        o2, P = DevBuf(inter * 2), Pool()
+        ref.ref_mlp1(P.p(x), P.p(wg), P.p(wu), P.p(sg), P.p(su), o2.ptr, dim, inter)
+        assert ref.ref_sync() == 0
+        r = o2.numpy(np.float16)
+        assert close(got, r), report(got, r)
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+def qkv_inputs(rng, quant, dim, nh, nkv, hd):
+    ws = [quant_mats(rng, r, dim, quant, full_range=False) for r in (nh * hd, nkv * hd, nkv * hd)]
+    bs = [(0.02 * rng.standard_normal(r)).astype(np.float16) for r in (nh * hd, nkv * hd, nkv * hd)]
+    x = rng.standard_normal(dim).astype(np.float16)
+    nw = (1 + 0.02 * rng.standard_normal(dim)).astype(np.float16)
+    return ws, bs, x, nw
+
+
+@pytest.mark.parametrize("quant", [0, 1, 2])
+@pytest.mark.parametrize("dim,nh,nkv,hd", [(896, 14, 2, 64), (3584, 28, 4, 128), (256, 3, 1, 128)])
+def test_fused_norm_qkv_rope_kvstore_vs_oracle(built, quant, dim, nh, nkv, hd):
+    rng = np.random.default_rng(dim + quant)
+    (wq, sq), (wk, sk), (wv, sv) = (ws := qkv_inputs(rng, quant, dim, nh, nkv, hd))[0]
+    bq, bk, bv = ws[1]
+    x, nw = ws[2], ws[3]
+    pos, max_seq = 37, 64
+    q, k, v = DevBuf(nh * hd * 2), DevBuf(nkv * hd * 2), DevBuf(nkv * hd * 2)
+    kc, vc = DevBuf(nkv * max_seq * hd * 2), DevBuf(nkv * max_seq * hd * 2)
+    K.fused_attn_block(quant, dev(x), dev(wq), dev(wk), dev(wv), maybe(sq), maybe(sk), maybe(sv), dev(bq), dev(bk), dev(bv), q, k, v,
+                       dim, nh, nkv, hd, dint(pos), rope_fast=0, norm_weight=dev(nw), eps=EPS_H, kcache=kc, vcache=vc, max_seq_len=max_seq)
+    xn = O.rmsnorm(x, nw)
+    oq, ok, ov = O.qkv(quant, xn, wq, wk, wv, sq, sk, sv, bq, bk, bv, dim, nh * hd, nkv * hd)
+    oq, ok = O.rope(oq, ok, nh, nkv, hd, pos)
+    gq, gk, gv = d2h(q), d2h(k), d2h(v)
+    for got, want in ((gq, oq), (gk, ok), (gv, ov)):
+        assert close(got, want), report(got, want)
+    gkc, gvc = d2h(kc).reshape(nkv, max_seq, hd), d2h(vc).reshape(nkv, max_seq, hd)
+    assert np.array_equal(gkc[:, pos], gk.reshape(nkv, hd)) and np.array_equal(gvc[:, pos], gv.reshape(nkv, hd))
+    gkc[:, pos] = 0; gvc[:, pos] = 0
+    assert not gkc.any() and not gvc.any()                                 # only row `pos` was written
+    # stand-alone rope and kv-store agree with the fused path
+    q2, k2 = dev(O.qkv(quant, xn, wq, wk, wv, sq, sk, sv, bq, bk, bv, dim, nh * hd, nkv * hd)[0]), dev(O.qkv(quant, xn, wq, wk, wv, sq, sk, sv, bq, bk, bv, dim, nh * hd, nkv * hd)[1])
+    K.rope(q2, k2, nh, nkv, hd, dint(pos), rope_fast=0)
+    assert close(d2h(q2), oq) and close(d2h(k2), ok)
+    kc2, vc2 = DevBuf(nkv * max_seq * hd * 2), DevBuf(nkv * max_seq * hd * 2)
+    K.kv_cache_store(k2, dev(ov), kc2, vc2, dint(5), nkv, max_seq, hd)
+    assert np.array_equal(d2h(kc2).reshape(nkv, max_seq, hd)[:, 5], d2h(k2).reshape(nkv, hd))
+
+
+@pytest.mark.parametrize("quant", [0, 1, 2])
+@pytest.mark.parametrize("model,dim,nh,nkv,hd", [("0.5b", 896, 14, 2, 64), ("7b", 3584, 28, 4, 128)])
+@pytest.mark.parametrize("pos", [3, 31000])
+def test_qkv_rope_vs_reference_kernels(built, quant, model, dim, nh, nkv, hd, pos):
+    """Same inputs through the reference's launch_fused_attn_block (fast-math RoPE) and this library's fused kernel in
+    its reference-compatible RoPE mode, including a long position where fast-math angles drift from libm's."""
+    ref = O.ref_lib(model, QNAME[quant])
+    if ref is None:
+        pytest.skip("oracle/_ref not built")
+    rng = np.random.default_rng(pos + quant)
+    (wq, sq), (wk, sk), (wv, sv) = (ws := qkv_inputs(rng, quant, dim, nh, nkv, hd))[0]
+    bq, bk, bv = ws[1]
+    x = ws[2]
+    dp = dint(pos)
+    bufs = [dev(a) if a is not None else None for a in (wq, wk, wv, sq, sk, sv, bq, bk, bv)]
+    ptr = lambda b: b.ptr if b is not None else None
+    q, k, v = DevBuf(nh * hd * 2), DevBuf(nkv * hd * 2), DevBuf(nkv * hd * 2)
+    dx = dev(x)
+    K.fused_attn_block(quant, dx, *bufs, q, k, v, dim, nh, nkv, hd, dp, rope_fast=1)
+    rq, rk, rv = DevBuf(nh * hd * 2), DevBuf(nkv * hd * 2), DevBuf(nkv * hd * 2)
+    ref.ref_qkv(dx.ptr, *[ptr(b) for b in bufs], rq.ptr, rk.ptr, rv.ptr, dim, nh, nkv, hd, dp.ptr, 1e6)
+    assert ref.ref_sync() == 0
+    for got, want in ((d2h(q), rq.numpy(np.float16)), (d2h(k), rk.numpy(np.float16)), (d2h(v), rv.numpy(np.float16))):
+        assert close(got, want), report(got, want)
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+def run_attention(q, Kc, Vc, nh, nkv, hd, max_seq, length, nsplit, twice=False):
+    bo, bml, bc = K.attn_scratch_bytes(nkv, hd, nsplit)
+    so, sml, cnt = DevBuf(bo, zero=False), DevBuf(bml, zero=False), DevBuf(bc)
+    so.upload(np.full(bo // 4, np.nan, np.float32)); sml.upload(np.full(bml // 4, np.nan, np.float32))   # stale scratch must not leak
+    out = DevBuf(nh * hd * 2)
+    dq, dk, dv, dp = dev(q), dev(Kc), dev(Vc), dint(length - 1)
+    for _ in range(2 if twice else 1):
+        K.gqa_attention_decode(dq, dk, dv, out, dp, nh, nkv, hd, max_seq, nsplit, so, sml, cnt)
+    got = d2h(out)
+    assert not cnt.numpy(np.uint32).any()                                  # the kernel leaves its tickets at zero
+    return got
+
+
+@pytest.mark.parametrize("nh,nkv,hd", [(28, 4, 128), (40, 8, 128), (14, 2, 64), (12, 2, 128), (16, 2, 128)])
+@pytest.mark.parametrize("length", [1, 15, 16, 17, 100, 512, 2048])
+def test_attention_vs_exact_oracle(built, nh, nkv, hd, length):
+    rng = np.random.default_rng(length * nh)
+    max_seq = length + 33
+    q = rng.standard_normal((nh, hd)).astype(np.float16)
+    Kc = rng.standard_normal((nkv, max_seq, hd)).astype(np.float16)
+    Vc = rng.standard_normal((nkv, max_seq, hd)).astype(np.float16)
+    Kc[:, length:] = np.float16(np.nan); Vc[:, length:] = np.float16(np.nan)     # poison: rows past the context are never read
+    want = O.attention(q, Kc, Vc, nh, nkv, hd, max_seq, length)
+    for nsplit in (1, 37, 128):
+        got = run_attention(q, Kc, Vc, nh, nkv, hd, max_seq, length, nsplit, twice=(nsplit == 37))
+        assert np.isfinite(got.astype(np.float32)).all()
+        assert close(got, want), f"nsplit {nsplit}: " + report(got, want)
+
+
+@pytest.mark.parametrize("nh,nkv", [(28, 4), (40, 8)])
+@pytest.mark.parametrize("length", [8192, 32768])
+def test_attention_long_context_and_reference_kernel(built, nh, nkv, length):
+    hd, max_seq = 128, 32768
+    rng = np.random.default_rng(length + nh)
+    q = rng.standard_normal((nh, hd)).astype(np.float16)
+    Kc = np.zeros((nkv, max_seq, hd), np.float16); Vc = np.zeros((nkv, max_seq, hd), np.float16)
+    Kc[:, :length] = rng.standard_normal((nkv, length, hd)).astype(np.float16)
+    Vc[:, :length] = rng.standard_normal((nkv, length, hd)).astype(np.float16)
+    want = O.attention(q, Kc, Vc, nh, nkv, hd, max_seq, length)
+    got = run_attention(q, Kc, Vc, nh, nkv, hd, max_seq, length, 148 // nkv)
+    assert close(got, want), report(got, want)
+    ref = O.ref_lib("7b" if nh == 28 else "14b", "fp16")
+    if ref is not None:
+        n = nkv * 16 * 64
+        po, pm, ps, out, P = DevBuf(n * hd * 4), DevBuf(n * 4), DevBuf(n * 4), DevBuf(nh * hd * 2), Pool()
+        ref.ref_attention(P.p(q), P.p(Kc), P.p(Vc), out.ptr, P.p(dint(length - 1)), nh, nkv, hd, max_seq, po.ptr, pm.ptr, ps.ptr)
+        assert ref.ref_sync() == 0
+        r = out.numpy(np.float16)
+        assert close(got, r), report(got, r)
+
+
+def test_attention_rejects_unsupported_shapes(built):
+    from cuqwen_b200 import CuQwenError
+    b = DevBuf(1 << 16)
+    for nh, nkv, hd, ns in ((18, 2, 128, 8), (14, 2, 96, 8), (14, 2, 64, 0), (14, 2, 64, 129), (15, 2, 64, 8)):
+        with pytest.raises(CuQwenError):
+            K.gqa_attention_decode(b, b, b, b, b, nh, nkv, hd, 64, ns, b, b, b)
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("model,quant,vocab,dim", [("0.5b", 0, 151936, 896), ("7b", 1, 152064, 3584)])
+def test_lm_head_logits_with_final_norm(built, model, quant, vocab, dim):
+    rng = np.random.default_rng(vocab + quant)
+    w, s = quant_mats(rng, vocab, dim, quant, full_range=False)
+    x = rng.standard_normal(dim).astype(np.float16)
+    nw = (1 + 0.02 * rng.standard_normal(dim)).astype(np.float16)
+    got = run_gemv(quant, w, s, x, vocab, dim, norm_w=nw)
+    xn = O.rmsnorm(x, nw)
+    want = O.logits(quant, w, s, xn, vocab, dim)
+    assert close(got, want), report(got, want)
+    assert O.argmax(got) == O.argmax(want) or abs(float(want[O.argmax(got)]) - float(want[O.argmax(want)])) < 1e-2
+    ref = O.ref_lib(model, "int4" if quant else "fp16")
+    if ref is not None:
+        lg, P = DevBuf(vocab * 2), Pool()
+        if quant:
+            ref.ref_logits_int8(P.p(xn), P.p(w), P.p(s), lg.ptr, vocab, dim)
+        else:
+            ref.ref_logits(P.p(xn), P.p(w), lg.ptr, vocab, dim)
+        assert ref.ref_sync() == 0
+        r = lg.numpy(np.float16)
+        assert close(r, want), report(r, want)
+
+
+def test_penalty_and_argmax(built):
+    rng = np.random.default_rng(3)
+    vocab = 151936
+    lg = rng.standard_normal(vocab).astype(np.float16)
+    hist = np.concatenate([rng.choice(vocab, 3000, replace=False), [5, 5, 5, vocab + 7, -1]]).astype(np.int32)
+    hist = np.concatenate([hist, rng.choice(vocab, 3000, replace=False).astype(np.int32)])   # > 4096 entries: the tail is ignored
+    dl, bitmap = dev(lg), DevBuf((vocab + 31) // 32 * 4)
+    K.apply_repetition_penalty(dl, dev(hist), dint(len(hist)), vocab, float(np.float16(1.1)), bitmap)
+    got = d2h(dl)
+    want = O.penalty(lg, hist, vocab)
+    assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
+    assert not bitmap.numpy(np.uint32).any()
+    tok, scratch = DevBuf(4), DevBuf(16)
+    for arr in (got, np.where(np.arange(vocab) % 1000 == 7, np.float16(9.0), got).astype(np.float16)):   # second case: many ties
+        K.argmax(dev(arr), tok, vocab, scratch)
+        assert d2h(tok, np.int32)[0] == O.argmax(arr)
+        assert not scratch.numpy(np.uint32).any()
+    nanv = got.copy(); nanv[1234] = np.float16(np.nan)
+    K.argmax(dev(nanv), tok, vocab, scratch)
+    assert d2h(tok, np.int32)[0] == O.argmax(nanv)
+
+
+def test_embedding_lookup(built):
+    rng = np.random.default_rng(8)
+    table = rng.standard_normal((1000, 896)).astype(np.float16)
+    out = DevBuf(896 * 2)
+    K.embedding_lookup(dev(table), dint(777), out, 896)
+    assert np.array_equal(d2h(out), table[777])

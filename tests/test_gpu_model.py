@@ -1,0 +1,179 @@
+"""Whole decode step through the C ABI (cuqwen_create / cuqwen_load / cuqwen_step / cuqwen_decode_n) against the
+scalar oracle on small models, and against the reference's own CUDA build on Qwen2.5-0.5B-shaped random weights
+(BASELINE config 2: fp16 / int8 / int4, 128 seeded prompt tokens then greedy steps, teacher-forced top-1)."""
+import subprocess
+
+import numpy as np
+import pytest
+
+from cuqwen_b200 import CuQwenError, binfmt, build
+from cuqwen_b200 import engine as E
+from oracle import oracle_py as O
+from tests.gpu_util import QNAME, close, report
+
+pytestmark = pytest.mark.gpu
+
+SMALL = {
+    "hd64": dict(vocab=1024, dim=256, inter=512, layers=3, heads=4, kv=2, hd=64, tied=True),
+    "hd128": dict(vocab=2048, dim=384, inter=768, layers=2, heads=6, kv=2, hd=128, tied=False),
+}
+
+
+def write_small(tmp_path, name, quant, seed=1):
+    cfg = SMALL[name]
+    p = tmp_path / f"{name}_{quant}.bin"
+    binfmt.write_model(p, cfg, quant, binfmt.random_tensors(cfg, seed))
+    return cfg, p
+
+
+def make_engine(cfg, quant, path, flags=0, max_seq=128, splits=0):
+    prm = E.custom_params(cfg["vocab"], cfg["dim"], cfg["inter"], cfg["layers"], cfg["heads"], cfg["kv"], cfg["hd"], quant, max_seq_len=max_seq)
+    prm.flags = flags
+    prm.attn_splits = splits
+    e = E.Engine(prm)
+    e.load(str(path))
+    return e
+
+
+@pytest.mark.parametrize("name", ["hd64", "hd128"])
+@pytest.mark.parametrize("quant", [0, 1, 2])
+def test_small_model_step_vs_oracle(built, tmp_path, name, quant):
+    cfg, path = write_small(tmp_path, name, quant)
+    eng = make_engine(cfg, quant, path, flags=E.FLAG_ACCURATE_ROPE)
+    assert eng.lm_head_kind == (2 if cfg["tied"] else (1 if quant else 0))
+    assert eng.step_bytes(0) == binfmt.step_bytes(cfg, quant, 0) and eng.step_bytes(10) == binfmt.step_bytes(cfg, quant, 10)
+    orc = O.OracleModel(str(path), 128)
+    rng = np.random.default_rng(5)
+    toks = rng.integers(0, cfg["vocab"], 40)
+    agree = 0
+    for pos, t in enumerate(toks):                     # teacher-forced: both sides see the same token stream
+        a = eng.step(int(t), pos)
+        b = orc.step(int(t), pos)
+        lg, lo = eng.read("LOGITS"), orc.logits
+        assert close(lg, lo), f"pos {pos}: " + report(lg, lo)
+        agree += a == b or abs(float(lo[a]) - float(lo[b])) <= 2e-3 * abs(float(lo[b])) + 1e-3
+    assert agree == len(toks)
+    # KV rows written by the engine equal the oracle's within tolerance, untouched rows stay zero
+    Kc = eng.read("KEY_CACHE").reshape(cfg["layers"], cfg["kv"], 128, cfg["hd"])
+    Ko, _ = orc.kv_views()
+    assert close(Kc[:, :, :40], Ko[:, :, :40]) and not Kc[:, :, 40:].any()
+    assert eng.step_launches == 1 + 5 * cfg["layers"] + 3
+    eng.close(); orc.close()
+
+
+def test_graph_pdl_and_eager_paths_are_bit_identical(built, tmp_path):
+    cfg, path = write_small(tmp_path, "hd128", 2)
+    outs = []
+    for flags in (0, E.FLAG_NO_PDL, E.FLAG_NO_GRAPH | E.FLAG_NO_PDL, E.FLAG_NO_GRAPH):
+        eng = make_engine(cfg, 2, path, flags=flags)
+        toks = [eng.step(7 + i, i) for i in range(12)]
+        outs.append((toks, eng.read("LOGITS").view(np.uint16).copy()))
+        eng.close()
+    for t, lg in outs[1:]:
+        assert t == outs[0][0] and np.array_equal(lg, outs[0][1])
+
+
+def test_decode_n_equals_step_loop_and_history_penalty(built, tmp_path):
+    cfg, path = write_small(tmp_path, "hd64", 1)
+    a, b = make_engine(cfg, 1, path), make_engine(cfg, 1, path)
+    for pos in range(5):
+        a.step(3 + pos, pos); b.step(3 + pos, pos)
+    loop, tok = [], 9
+    for i in range(20):
+        tok = a.step(tok, 5 + i)
+        loop.append(tok)
+    got = b.decode_n(9, 5, 20)
+    assert got.tolist() == loop and b.last_decode_ms > 0
+    # penalty: distinct ids are rescaled exactly once, on top of the un-penalised logits
+    base = a.step(11, 25)
+    plain = a.read("LOGITS").copy()
+    hist = np.array([base, 1, 2, 3, base], dtype=np.int32)
+    a.step(11, 25, history=hist)
+    assert np.array_equal(a.read("LOGITS").view(np.uint16), O.penalty(plain, hist, cfg["vocab"]).view(np.uint16))
+    a.close(); b.close()
+
+
+def test_attention_split_count_does_not_change_tokens(built, tmp_path):
+    cfg, path = write_small(tmp_path, "hd128", 0)
+    ref = None
+    for splits in (1, 5, 64):
+        eng = make_engine(cfg, 0, path, splits=splits)
+        eng.kv_fill_normal(100, seed=3)
+        toks = eng.decode_n(4, 100, 8).tolist()
+        lg = eng.read("LOGITS").astype(np.float32)
+        if ref is None:
+            ref = (toks, lg)
+        assert close(lg, ref[1], atol=2e-3), report(lg, ref[1])
+        eng.close()
+
+
+def test_loader_error_codes(built, tmp_path):
+    cfg, path = write_small(tmp_path, "hd64", 2)
+    raw = path.read_bytes()
+    prm = lambda q=2, dim=None: E.custom_params(cfg["vocab"], dim or cfg["dim"], cfg["inter"], cfg["layers"], cfg["heads"], cfg["kv"], cfg["hd"], q, max_seq_len=64)
+
+    def code(p, file):
+        e = E.Engine(p)
+        try:
+            e.load(str(file))
+            return 0
+        except CuQwenError as err:
+            return err.code
+        finally:
+            e.close()
+
+    assert code(prm(), tmp_path / "missing.bin") == 2                    # io
+    bad = tmp_path / "bad.bin"
+    bad.write_bytes(b"\x00" * 4 + raw[4:]); assert code(prm(), bad) == 3   # magic
+    assert code(prm(dim=384), path) == 4                                  # dims
+    assert code(prm(q=1), path) == 5                                      # quant
+    bad.write_bytes(raw[:len(raw) // 2]); assert code(prm(), bad) == 2     # truncated tensor data
+    bad.write_bytes(raw[:20]); assert code(prm(), bad) == 2               # short header
+    e = E.Engine(prm())
+    with pytest.raises(CuQwenError) as err:
+        e.step(1, 0)
+    assert err.value.code == 8                                            # step before load
+    e.load(str(path))
+    with pytest.raises(CuQwenError):
+        e.step(cfg["vocab"], 0)
+    with pytest.raises(CuQwenError):
+        e.step(0, 64)
+    e.close()
+    with pytest.raises(CuQwenError):
+        E.Engine(E.custom_params(1000, 250, 512, 1, 4, 2, 64, 0))         # dim not a multiple of 128
+
+
+@pytest.mark.parametrize("quant", [0, 1, 2])
+def test_qwen25_0_5b_vs_reference_build(built, tmpdir_big, quant):
+    """BASELINE config 2 at full model size: random-init 0.5B, 128 seeded prompt tokens, then greedy steps; the
+    reference's qwen_forward supplies the token stream, this engine is teacher-forced with it."""
+    ref = O.ref_lib("0.5b", QNAME[quant])
+    if ref is None:
+        pytest.skip("oracle/_ref not built")
+    path = tmpdir_big / f"m05_{QNAME[quant]}.bin"
+    subprocess.run([str(build.GEN_BIN), "--out", str(path), "--model", "0.5b", "--quant", QNAME[quant], "--seed", "42"], check=True)
+    eng = E.Engine(E.model_params("0.5b", quant))
+    eng.load(str(path))
+    rm = ref.ref_model_load(str(path).encode())
+    rng = np.random.default_rng(42)
+    prompt = rng.integers(0, 151936, 128)
+    n_prompt, n_gen = 128, 256
+    agree, total, worst = 0, 0, 0.0
+    tok_r = 0
+    for pos in range(n_prompt + n_gen):
+        t = int(prompt[pos]) if pos < n_prompt else tok_r
+        tok_r = ref.ref_forward(rm, t, pos, None, 0)
+        tok_e = eng.step(t, pos)
+        if pos >= n_prompt - 1:
+            total += 1
+            agree += tok_r == tok_e
+        if pos in (0, n_prompt - 1, n_prompt + n_gen - 1):
+            lr = E.download(0, ref.ref_state_ptr(rm, 0), np.float16, 151936)
+            le = eng.read("LOGITS")
+            assert close(le, lr), f"pos {pos}: " + report(le, lr)
+            worst = max(worst, float(np.abs(le.astype(np.float32) - lr.astype(np.float32)).max()))
+    ref.ref_model_free(rm)
+    eng.close()
+    path.unlink()
+    print(f"0.5B {QNAME[quant]}: top-1 agreement {agree}/{total}, worst logit diff {worst:.3e}")
+    assert agree / total >= 0.99
