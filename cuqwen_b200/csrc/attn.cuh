@@ -54,8 +54,8 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_kernel(const Attn
     __shared__ float sm_w[kMaxGroup][kMaxSplit];
     __shared__ int sm_last;
 
-    pdl_wait();
     pdl_launch_dependents();
+    pdl_wait();
 
     const int len = *a.d_pos + 1;
     int chunk = (len + a.nsplit - 1) / a.nsplit;
@@ -91,9 +91,14 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_kernel(const Attn
             uint4 kA[NCH], kB[NCH];
             const bool vA = kb + g < t1, vB = kb + 8 + g < t1;
 #pragma unroll
-            for (int i = 0; i < NCH; ++i) {
-                kA[i] = vA ? ldg_stream(kbase + (size_t)(kb + g) * HD + (i * 4 + t) * 8) : make_uint4(0, 0, 0, 0);
-                kB[i] = vB ? ldg_stream(kbase + (size_t)(kb + 8 + g) * HD + (i * 4 + t) * 8) : make_uint4(0, 0, 0, 0);
+            for (int i = 0; i < NCH; ++i) { kA[i] = make_uint4(0, 0, 0, 0); kB[i] = make_uint4(0, 0, 0, 0); }
+            if (vA) {
+#pragma unroll
+                for (int i = 0; i < NCH; ++i) kA[i] = ldg_stream(kbase + (size_t)(kb + g) * HD + (i * 4 + t) * 8);
+            }
+            if (vB) {
+#pragma unroll
+                for (int i = 0; i < NCH; ++i) kB[i] = ldg_stream(kbase + (size_t)(kb + 8 + g) * HD + (i * 4 + t) * 8);
             }
             // V: lane reads keys kb+2t, +2t+1, +2t+8, +2t+9, d chunk (c*8+g)
             uint4 vv[4][NC];
@@ -101,8 +106,11 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_kernel(const Attn
             for (int r = 0; r < 4; ++r) {
                 const int key = kb + 2 * t + (r & 1) + (r >> 1) * 8;
 #pragma unroll
-                for (int c = 0; c < NC; ++c)
-                    vv[r][c] = key < t1 ? ldg_stream(vbase + (size_t)key * HD + (c * 8 + g) * 8) : make_uint4(0, 0, 0, 0);
+                for (int c = 0; c < NC; ++c) vv[r][c] = make_uint4(0, 0, 0, 0);
+                if (key < t1) {
+#pragma unroll
+                    for (int c = 0; c < NC; ++c) vv[r][c] = ldg_stream(vbase + (size_t)key * HD + (c * 8 + g) * 8);
+                }
             }
 
             float sA[4] = {0.f, 0.f, 0.f, 0.f}, sB[4] = {0.f, 0.f, 0.f, 0.f};

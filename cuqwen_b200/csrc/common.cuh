@@ -18,9 +18,11 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {
                  : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
     return v;
 }
-__device__ __forceinline__ uint16_t ldg_u16(const void* p) {
-    uint16_t v;
-    asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(v) : "l"(p));
+// 16-bit read into a full 32-bit register (zero-extended): the value can sit in flight without the
+// compiler packing it next to a neighbour, which would put a dependent instruction right behind the load.
+__device__ __forceinline__ uint32_t ldg_u16(const void* p) {
+    uint32_t v;
+    asm volatile("ld.global.nc.u16 %0, [%1];" : "=r"(v) : "l"(p));
     return v;
 }
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {

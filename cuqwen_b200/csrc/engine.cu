@@ -76,7 +76,9 @@ extern "C" int cuqwen_model_params(int model_id, int quant, cuqwen_params* p) {
 // ---------------------------------------------------------------------------
 // per-device context for the stand-alone kernel entry points
 // ---------------------------------------------------------------------------
-struct DevCtx { bool init = false; cudaStream_t stream = nullptr; int sms = 0; cudaEvent_t ev0 = nullptr, ev1 = nullptr; };
+struct DevCtx { bool init = false; cudaStream_t stream = nullptr; int sms = 0; cudaEvent_t ev0 = nullptr, ev1 = nullptr; unsigned* err = nullptr; unsigned* h_err = nullptr; };
+// device word that kernels launched by the calling thread report an expired bounded wait to
+static thread_local unsigned* t_err = nullptr;
 static DevCtx g_dev[64];
 static std::mutex g_dev_mu;
 static int dev_ctx(int device, DevCtx** out) {
@@ -88,12 +90,13 @@ static int dev_ctx(int device, DevCtx** out) {
         CK(cudaStreamCreateWithFlags(&d.stream, cudaStreamNonBlocking));
         CK(cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, device));
         CK(cudaEventCreate(&d.ev0)); CK(cudaEventCreate(&d.ev1));
+        CK(cudaMalloc((void**)&d.err, 4)); CK(cudaMemset(d.err, 0, 4)); CK(cudaMallocHost((void**)&d.h_err, 4));
         d.init = true;
     }
     *out = &d;
     return CUQWEN_OK;
 }
-#define DEV(device) DevCtx* dc; { int r_ = dev_ctx(device, &dc); if (r_) return r_; } LaunchCfg cfg{dc->stream, dc->sms, false}
+#define DEV(device) DevCtx* dc; { int r_ = dev_ctx(device, &dc); if (r_) return r_; } t_err = dc->err; LaunchCfg cfg{dc->stream, dc->sms, false}
 
 // ---------------------------------------------------------------------------
 // NCCL through dlopen (no link-time dependency; single-GPU use never loads it)
@@ -151,7 +154,7 @@ struct cuqwen_engine {
     float *part_o = nullptr, *part_ml = nullptr; unsigned* counters = nullptr;
     StepCtl* ctl = nullptr; StepCtl* h_ctl = nullptr;
     int* d_hist = nullptr; unsigned* bitmap = nullptr; unsigned long long* best = nullptr; unsigned* ticket = nullptr;
-    int* out_ring = nullptr; int ring_cap = 65536; int* h_out = nullptr;
+    int* out_ring = nullptr; int ring_cap = 65536; int* h_out = nullptr;   // h_out holds ring_cap + 1 ints
     float* tp_partial = nullptr; unsigned long long* tp_keys = nullptr;
     // graph
     cudaGraph_t graph = nullptr; cudaGraphExec_t gexec = nullptr; bool graph_ready = false;
@@ -212,7 +215,7 @@ extern "C" int cuqwen_create(const cuqwen_params* pin, cuqwen_engine** out) {
     CK(dalloc((void**)&e->d_hist, (size_t)p.max_seq_len * 4));
     CK(dalloc((void**)&e->bitmap, ((size_t)e->vocab_l + 31) / 32 * 4));
     CK(dalloc((void**)&e->best, 8)); CK(dalloc((void**)&e->ticket, 4));
-    CK(dalloc((void**)&e->out_ring, (size_t)e->ring_cap * 4)); CK(cudaMallocHost((void**)&e->h_out, (size_t)e->ring_cap * 4));
+    CK(dalloc((void**)&e->out_ring, (size_t)e->ring_cap * 4)); CK(cudaMallocHost((void**)&e->h_out, ((size_t)e->ring_cap + 1) * 4));
     if (e->tp > 1) { CK(dalloc((void**)&e->tp_partial, (size_t)p.dim * 4)); CK(dalloc((void**)&e->tp_keys, (size_t)(e->tp + 1) * 8)); }
     *out = e;
     return CUQWEN_OK;
@@ -357,7 +360,7 @@ extern "C" int cuqwen_load(cuqwen_engine* e, const char* path) {
 // ---------------------------------------------------------------------------
 // one decode step as a sequence of launches (order: reference src/model.cu:76-181)
 // ---------------------------------------------------------------------------
-static GemvArgs gv(const __half* x, int K) { GemvArgs a; memset(&a, 0, sizeof a); a.x = x; a.K = K; return a; }
+static GemvArgs gv(const __half* x, int K) { GemvArgs a; memset(&a, 0, sizeof a); a.x = x; a.K = K; a.err = t_err; return a; }
 
 static int tp_allreduce(cuqwen_engine* e, float* buf, int n, cudaStream_t s) {
     NK(g_nccl.AllReduce(buf, buf, n, ncclFloat32, ncclSum, e->comm, s));
@@ -368,6 +371,7 @@ static int record_step(cuqwen_engine* e, cudaStream_t s, bool pdl) {
     const cuqwen_params& p = e->p;
     LaunchCfg cfg{s, e->sms, pdl};
     LaunchCfg cfg_plain{s, e->sms, false};
+    t_err = reinterpret_cast<unsigned*>(&e->ctl->pad[0]);
     int n = 0;
     const size_t kv_layer = (size_t)e->n_kv_l * p.max_seq_len * p.head_dim;
     const float eps = __half2float(__float2half(p.norm_eps));   // the reference narrows eps to fp16 (src/model.cu:96)
@@ -474,8 +478,9 @@ extern "C" int cuqwen_step(cuqwen_engine* e, int token, int pos, const int* hist
     CK(cudaMemcpyAsync(e->ctl, e->h_ctl, sizeof(StepCtl), cudaMemcpyHostToDevice, e->stream));
     if (c.hist_len) CK(cudaMemcpyAsync(e->d_hist, history, (size_t)c.hist_len * 4, cudaMemcpyHostToDevice, e->stream));
     if (int r = run_step(e)) return r;
-    CK(cudaMemcpyAsync(e->h_out, &e->ctl->sampled, 4, cudaMemcpyDeviceToHost, e->stream));
+    CK(cudaMemcpyAsync(e->h_out, &e->ctl->sampled, 8, cudaMemcpyDeviceToHost, e->stream));   // sampled token + wait-expired word
     CK(cudaStreamSynchronize(e->stream));
+    if (e->h_out[1]) return fail(CUQWEN_ERR_TIMEOUT, "a bounded device-side wait expired (code %d)", e->h_out[1]);
     if (out_token) *out_token = e->h_out[0];
     return CUQWEN_OK;
 }
@@ -495,7 +500,9 @@ extern "C" int cuqwen_decode_n(cuqwen_engine* e, int first_token, int start_pos,
     for (int i = 0; i < n; ++i) if (int r = run_step(e)) return r;
     CK(cudaEventRecord(e->ev1, e->stream));
     CK(cudaMemcpyAsync(e->h_out, e->out_ring, (size_t)n * 4, cudaMemcpyDeviceToHost, e->stream));
+    CK(cudaMemcpyAsync(e->h_out + n, &e->ctl->pad[0], 4, cudaMemcpyDeviceToHost, e->stream));
     CK(cudaStreamSynchronize(e->stream));
+    if (e->h_out[n]) return fail(CUQWEN_ERR_TIMEOUT, "a bounded device-side wait expired (code %d)", e->h_out[n]);
     CK(cudaEventElapsedTime(&e->last_ms, e->ev0, e->ev1));
     if (out_tokens) memcpy(out_tokens, e->h_out, (size_t)n * 4);
     return CUQWEN_OK;
@@ -624,7 +631,13 @@ extern "C" int cuqwen_dev_free(int device, void* p) { DEV(device); (void)cfg; CK
 extern "C" int cuqwen_dev_upload(int device, void* d, const void* h, size_t n) { DEV(device); (void)cfg; CK(cudaMemcpyAsync(d, h, n, cudaMemcpyHostToDevice, dc->stream)); CK(cudaStreamSynchronize(dc->stream)); return CUQWEN_OK; }
 extern "C" int cuqwen_dev_download(int device, void* h, const void* d, size_t n) { DEV(device); (void)cfg; CK(cudaMemcpyAsync(h, d, n, cudaMemcpyDeviceToHost, dc->stream)); CK(cudaStreamSynchronize(dc->stream)); return CUQWEN_OK; }
 extern "C" int cuqwen_dev_memset(int device, void* p, int v, size_t n) { DEV(device); (void)cfg; CK(cudaMemsetAsync(p, v, n, dc->stream)); return CUQWEN_OK; }
-extern "C" int cuqwen_dev_sync(int device) { DEV(device); (void)cfg; CK(cudaStreamSynchronize(dc->stream)); CK(cudaGetLastError()); return CUQWEN_OK; }
+extern "C" int cuqwen_dev_sync(int device) {
+    DEV(device); (void)cfg;
+    CK(cudaMemcpyAsync(dc->h_err, dc->err, 4, cudaMemcpyDeviceToHost, dc->stream));
+    CK(cudaStreamSynchronize(dc->stream)); CK(cudaGetLastError());
+    if (*dc->h_err) { unsigned c = *dc->h_err; CK(cudaMemset(dc->err, 0, 4)); return fail(CUQWEN_ERR_TIMEOUT, "a bounded device-side wait expired (code %u)", c); }
+    return CUQWEN_OK;
+}
 extern "C" int cuqwen_bench_begin(int device) { DEV(device); (void)cfg; CK(cudaEventRecord(dc->ev0, dc->stream)); return CUQWEN_OK; }
 extern "C" int cuqwen_bench_end(int device, float* ms) { DEV(device); (void)cfg; CK(cudaEventRecord(dc->ev1, dc->stream)); CK(cudaEventSynchronize(dc->ev1)); CK(cudaEventElapsedTime(ms, dc->ev0, dc->ev1)); return CUQWEN_OK; }
 

@@ -12,6 +12,10 @@ static int go(const GemvArgs& a, dim3 grid, dim3 block, size_t smem, const Launc
     at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     at[0].val.programmaticStreamSerializationAllowed = 1;
     lc.attrs = at; lc.numAttrs = cfg.pdl ? 1 : 0;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(gemv_kernel<Q_F16, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (e != cudaSuccess) return (int)e;
+    }
     return (int)cudaLaunchKernelEx(&lc, gemv_kernel<Q_F16, EPI>, a);
 }
 

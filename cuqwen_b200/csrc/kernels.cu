@@ -6,6 +6,8 @@
 #include "launch.h"
 #include "rng.cuh"
 
+#include <cstdlib>
+
 namespace cq {
 
 template <typename... KArgs, typename... Args>
@@ -21,7 +23,7 @@ static int launch_k(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, 
 
 // ---- embedding row copy (reference src/kernels.cu:85-96) -------------------
 __global__ void embed_kernel(const __half* __restrict__ table, const int* __restrict__ d_token, __half* __restrict__ out, int dim) {
-    pdl_wait(); pdl_launch_dependents();
+    pdl_launch_dependents(); pdl_wait();
     const uint4* src = reinterpret_cast<const uint4*>(table + (size_t)(*d_token) * dim);
     uint4* dst = reinterpret_cast<uint4*>(out);
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < dim / 8; i += gridDim.x * blockDim.x) dst[i] = src[i];
@@ -33,7 +35,7 @@ int launch_embed(const __half* table, const int* d_token, __half* out, int dim, 
 // ---- stand-alone RMSNorm (reference src/kernels.cu:689-751) ----------------
 __global__ void rmsnorm_kernel(const __half* __restrict__ x, const __half* __restrict__ w, __half* __restrict__ out, int dim, float eps) {
     __shared__ float red[40];
-    pdl_wait(); pdl_launch_dependents();
+    pdl_launch_dependents(); pdl_wait();
     const float inv = block_inv_rms(x, dim, eps, red);
     for (int i = threadIdx.x; i < dim; i += blockDim.x)
         out[i] = __float2half(__half2float(x[i]) * inv * __half2float(w[i]));
@@ -44,7 +46,7 @@ int launch_rmsnorm(const __half* x, const __half* w, __half* out, int dim, float
 
 // ---- stand-alone RoPE (reference src/kernels.cu:370-398) -------------------
 __global__ void rope_kernel(__half* q, __half* k, int n_heads, int n_kv, int hd, const int* d_pos, float theta, int fast) {
-    pdl_wait(); pdl_launch_dependents();
+    pdl_launch_dependents(); pdl_wait();
     const int half_hd = hd / 2, tid = blockIdx.x * blockDim.x + threadIdx.x;
     if (tid >= (n_heads + n_kv) * half_hd) return;
     const bool is_q = tid < n_heads * half_hd;
@@ -66,7 +68,7 @@ int launch_rope(__half* q, __half* k, int n_heads, int n_kv, int hd, const int* 
 // ---- stand-alone KV store (reference src/kernels.cu:326-347) ---------------
 __global__ void kv_store_kernel(const __half* __restrict__ k, const __half* __restrict__ v, __half* __restrict__ kc, __half* __restrict__ vc,
                                 const int* __restrict__ d_pos, int n_kv, int max_seq, int hd) {
-    pdl_wait(); pdl_launch_dependents();
+    pdl_launch_dependents(); pdl_wait();
     const int tid = blockIdx.x * blockDim.x + threadIdx.x;
     if (tid >= n_kv * hd) return;
     const int h = tid / hd, d = tid % hd;
@@ -83,7 +85,7 @@ int launch_kv_store(const __half* k, const __half* v, __half* kc, __half* vc, co
 // applies the penalty, so every distinct id is penalised exactly once.
 __global__ void penalty_kernel(__half* logits, const int* __restrict__ hist, const int* __restrict__ d_hist_len,
                                int vocab, int vocab_base, float pen, unsigned* bitmap) {
-    pdl_wait(); pdl_launch_dependents();
+    pdl_launch_dependents(); pdl_wait();
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= *d_hist_len) return;
     const int id = hist[idx] - vocab_base;
@@ -94,7 +96,7 @@ __global__ void penalty_kernel(__half* logits, const int* __restrict__ hist, con
     logits[id] = __float2half(l < 0.f ? l * pen : l / pen);
 }
 __global__ void clear_bitmap_kernel(const int* __restrict__ hist, const int* __restrict__ d_hist_len, int vocab, int vocab_base, unsigned* bitmap) {
-    pdl_wait(); pdl_launch_dependents();
+    pdl_launch_dependents(); pdl_wait();
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= *d_hist_len) return;
     const int id = hist[idx] - vocab_base;
@@ -127,7 +129,7 @@ __global__ void argmax_kernel(const __half* __restrict__ logits, int vocab, int 
                               const int* __restrict__ hist, unsigned* bitmap, unsigned long long* best, unsigned* ticket,
                               unsigned long long* key_out, int* token_out) {
     __shared__ unsigned long long sbest[8];
-    pdl_wait(); pdl_launch_dependents();
+    pdl_launch_dependents(); pdl_wait();
     // undo the penalty pass's marks (idempotent stores of zero)
     if (hist && bitmap) {
         const int idx = blockIdx.x * blockDim.x + threadIdx.x;
@@ -166,7 +168,7 @@ int launch_argmax(const __half* logits, int vocab, int vocab_base, StepCtl* ctl,
     return launch_k(argmax_kernel, dim3(blocks), dim3(256), 0, cfg, logits, vocab, vocab_base, ctl, out_ring, ring_cap, hist, bitmap, best, ticket, key_out, token_out);
 }
 __global__ void merge_keys_kernel(const unsigned long long* __restrict__ keys, int n, StepCtl* ctl, int* out_ring, int ring_cap) {
-    pdl_wait(); pdl_launch_dependents();
+    pdl_launch_dependents(); pdl_wait();
     if (threadIdx.x != 0) return;
     unsigned long long b = 0ull;
     for (int i = 0; i < n; ++i) b = keys[i] > b ? keys[i] : b;
@@ -178,7 +180,7 @@ int launch_merge_keys(const unsigned long long* keys, int n, StepCtl* ctl, int* 
 
 // ---- tensor-parallel residual: x = half(float(x) + sum_r partial_r) --------
 __global__ void resid_sum_kernel(__half* x, const float* __restrict__ partial, int n_parts, size_t stride, int dim) {
-    pdl_wait(); pdl_launch_dependents();
+    pdl_launch_dependents(); pdl_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= dim) return;
     float s = 0.f;
@@ -234,8 +236,41 @@ int launch_gemv_i4(int epi, const GemvArgs& a, dim3 grid, dim3 block, size_t sme
 int launch_gemv_i8(int epi, const GemvArgs& a, dim3 grid, dim3 block, size_t smem, const LaunchCfg& cfg);
 int launch_gemv_f16(int epi, const GemvArgs& a, dim3 grid, dim3 block, size_t smem, const LaunchCfg& cfg);
 
+// cuTensorMapEncodeTiled through the runtime's driver-entry-point lookup (no link against libcuda).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) p = nullptr;
+        return (EncodeTiledFn)p;
+    }();
+    return fn;
+}
+// Byte-typed 2-D map of a row-major matrix: dims {row_bytes, rows}, box {piece_bytes, 16}, zero fill out of bounds.
+static int make_weight_map(CUtensorMap* m, const void* w, size_t row_bytes, size_t rows, int piece_bytes) {
+    EncodeTiledFn fn = encode_tiled();
+    if (!fn) return (int)cudaErrorNotSupported;
+    const cuuint64_t dims[2] = {row_bytes, rows}, strides[1] = {row_bytes};
+    const cuuint32_t box[2] = {(cuuint32_t)piece_bytes, 16}, estr[2] = {1, 1};
+    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(w), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
+static int env_int(const char* name, int dflt) {
+    const char* v = getenv(name);
+    return v && *v ? atoi(v) : dflt;
+}
+
+// Picks the work split, the staged piece size and the ring depth for one GEMV launch.
+//   tall matrices (>= 8 tile sets per SM): one CTA per SM, each warp walks its own tile sets over the whole K;
+//   wide ones: one CTA per tile set, K split over the warps, partial sums merged in shared memory.
+// Tuning overrides (development aid): CUQWEN_GEMV_PG, CUQWEN_GEMV_NST.
 int launch_gemv(int quant, int epi, GemvArgs& a, const LaunchCfg& cfg) {
-    if (a.K <= 0 || a.K % kGroup != 0 || a.K > 22528) return (int)cudaErrorInvalidValue;
+    if (a.K <= 0 || a.K % kGroup != 0 || a.K > 24576) return (int)cudaErrorInvalidValue;
+    if (quant < 0 || quant > 2) return (int)cudaErrorInvalidValue;
     if (epi == EPI_QKV) {
         if (a.hd % 32 != 0) return (int)cudaErrorInvalidValue;
         a.nsets = (a.n_heads + 2 * a.n_kv) * (a.hd / 32);
@@ -243,24 +278,66 @@ int launch_gemv(int quant, int epi, GemvArgs& a, const LaunchCfg& cfg) {
         if (a.rows <= 0) return (int)cudaErrorInvalidValue;
         a.nsets = (a.rows + 15) / 16;
     }
+    const int MT = (epi == EPI_SWIGLU || epi == EPI_QKV) ? 2 : 1;
     const int ngrp = a.K / kGroup;
-    dim3 grid, block;
+    const int gb = quant == Q_I4 ? 64 : quant == Q_I8 ? 128 : 256;
+    const int pg_max = 256 / gb;                     // row pieces of at most 256 bytes
+    const int kMaxSmem = 225 * 1024;
+    const int kShare = env_int("CUQWEN_GEMV_CAP_KB", 110) * 1024;    // per-CTA budget that lets two CTAs (e.g. of consecutive kernels) share an SM
+    int nw, pg, nst, cap;
+    dim3 grid;
     if (a.nsets >= 8 * cfg.sm_count) {
-        a.ksplit = 0;
-        int g = (a.nsets + 7) / 8;
-        grid = dim3(g < 2 * cfg.sm_count ? g : 2 * cfg.sm_count);
-        block = dim3(256);
+        a.ksplit = 0; nw = 8;
+        int g = (a.nsets + nw - 1) / nw;
+        grid = dim3(g < cfg.sm_count ? g : cfg.sm_count);
+        pg = ngrp < pg_max ? ngrp : pg_max;
+        nst = 8; cap = kShare;
     } else {
         a.ksplit = 1;
         grid = dim3(a.nsets);
-        int nw = ngrp < 8 ? ngrp : 8;
-        block = dim3(32 * nw);
+        pg = pg_max;
+        while (pg > 1 && (ngrp + pg - 1) / pg < 8) --pg;      // enough pieces to occupy eight warps
+        const int pt = (ngrp + pg - 1) / pg;
+        nw = pt < 8 ? pt : 8;
+        nst = (pt + nw - 1) / nw;                     // everything this warp will ever read can be in flight
+        if (nst > 8) nst = 8;
+        cap = kShare;
     }
-    const size_t smem = gemv_smem_bytes(a.K);
+    const int env_pg = env_int("CUQWEN_GEMV_PG", 0), env_nst = env_int("CUQWEN_GEMV_NST", 0);
+    auto need = [&](int pg_, int nst_) { return gemv_smem_bytes(a.K, quant, MT, nw, pg_, nst_, a.ksplit); };
+    // deepest ring (<= want) that fits `cap_`, 0 if not even one stage fits
+    auto fit = [&](int pg_, int want, int cap_) { int n = want; while (n > 1 && need(pg_, n) > (size_t)cap_) --n; return need(pg_, n) <= (size_t)cap_ ? n : 0; };
+    if (env_pg > 0) pg = env_pg > pg_max ? pg_max : env_pg;
+    for (int pass = 0; pass < 2; ++pass) {
+        int best_pg = 0, best_n = 0;
+        for (int q = pg; q >= 1; --q) {
+            const int pt = (ngrp + q - 1) / q;
+            int want = a.ksplit ? (pt + nw - 1) / nw : 8;
+            if (want > 8) want = 8;
+            if (env_nst > 0) want = env_nst;
+            const int n = fit(q, want, cap);
+            if (n > best_n) { best_n = n; best_pg = q; }
+            if (n >= (want < 2 ? want : 2) || env_pg > 0) break;      // at least two stages (or all the warp needs)
+        }
+        if (best_n > 0) { pg = best_pg; nst = best_n; break; }
+        if (cap == kMaxSmem) return (int)cudaErrorInvalidValue;
+        cap = kMaxSmem;                                              // give up the second CTA per SM
+    }
+    const size_t smem = need(pg, nst);
+    if (smem > (size_t)kMaxSmem) return (int)cudaErrorInvalidValue;
+    a.pg = pg; a.nst = nst;
+    {
+        const size_t rbytes = quant == Q_I4 ? a.K / 2 : quant == Q_I8 ? a.K : (size_t)a.K * 2;
+        const int nmat = epi == EPI_QKV ? 3 : epi == EPI_SWIGLU ? 2 : 1;
+        for (int m = 0; m < nmat; ++m) {
+            const size_t rows_m = epi == EPI_QKV ? (size_t)(m == 0 ? a.n_heads : a.n_kv) * a.hd : (size_t)a.rows;
+            if (int r = make_weight_map(&a.tmap[m], a.w[m], rbytes, rows_m, pg * gb)) return r;
+        }
+    }
+    const dim3 block(32 * nw);
     if (quant == Q_I4) return launch_gemv_i4(epi, a, grid, block, smem, cfg);
     if (quant == Q_I8) return launch_gemv_i8(epi, a, grid, block, smem, cfg);
-    if (quant == Q_F16) return launch_gemv_f16(epi, a, grid, block, smem, cfg);
-    return (int)cudaErrorInvalidValue;
+    return launch_gemv_f16(epi, a, grid, block, smem, cfg);
 }
 
 }  // namespace cq

@@ -37,7 +37,7 @@ class Copies:
     def __init__(self, rng, rows, cols, quant, min_total_bytes, device):
         w, s = _weights(rng, rows, cols, quant)
         self.bytes = w.nbytes + (s.nbytes if s is not None else 0)
-        n = max(2, -(-min_total_bytes // self.bytes))
+        n = max(2, -(-min_total_bytes // self.bytes)) if min_total_bytes > 0 else 1      # 0: a single copy (L2-warm timing)
         self.w = [E.DevBuf.from_numpy(w, device) for _ in range(n)]
         self.s = [E.DevBuf.from_numpy(s, device) if s is not None else None for _ in range(n)]
         self.i = 0
