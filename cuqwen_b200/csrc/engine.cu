@@ -175,6 +175,7 @@ extern "C" int cuqwen_create(const cuqwen_params* pin, cuqwen_engine** out) {
         const ModelRow& m = kModels[p.model_id];
         p.vocab_size = m.vocab; p.dim = m.dim; p.intermediate_size = m.inter; p.n_layers = m.layers; p.n_heads = m.heads; p.n_kv_heads = m.kv; p.head_dim = m.hd;
     }
+    if (const char* f = getenv("CUQWEN_FLAGS")) p.flags |= (uint32_t)atoi(f);   // development aid: OR extra CUQWEN_FLAG_* bits in
     if (p.max_seq_len <= 0) p.max_seq_len = 32768;
     if (p.tp_size <= 0) p.tp_size = 1;
     if (p.norm_eps == 0.f) p.norm_eps = 1e-6f;

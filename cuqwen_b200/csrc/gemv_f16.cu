@@ -1,5 +1,5 @@
 // Instantiations of the GEMV kernel family for one weight format.
-#include "gemv.cuh"
+#include "gemv_kernel.cuh"
 #include "launch.h"
 
 namespace cq {

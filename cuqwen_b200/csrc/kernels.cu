@@ -248,26 +248,28 @@ static EncodeTiledFn encode_tiled() {
     }();
     return fn;
 }
-// Byte-typed 2-D map of a row-major matrix: dims {row_bytes, rows}, box {piece_bytes, 16}, zero fill out of bounds.
-static int make_weight_map(CUtensorMap* m, const void* w, size_t row_bytes, size_t rows, int piece_bytes) {
+// Byte-typed 2-D map of a row-major matrix: dims {row_bytes, rows}, box {piece_bytes, box_rows}, zero fill out of bounds.
+static int make_weight_map(CUtensorMap* m, const void* w, size_t row_bytes, size_t rows, int piece_bytes, int box_rows) {
     EncodeTiledFn fn = encode_tiled();
     if (!fn) return (int)cudaErrorNotSupported;
     const cuuint64_t dims[2] = {row_bytes, rows}, strides[1] = {row_bytes};
-    const cuuint32_t box[2] = {(cuuint32_t)piece_bytes, 16}, estr[2] = {1, 1};
+    const cuuint32_t box[2] = {(cuuint32_t)piece_bytes, (cuuint32_t)box_rows}, estr[2] = {1, 1};
     CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(w), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                     CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
 }
+
+constexpr int kGemvThreadsHost = (kConsumerWarps + 1) * 32;
 
 static int env_int(const char* name, int dflt) {
     const char* v = getenv(name);
     return v && *v ? atoi(v) : dflt;
 }
 
-// Picks the work split, the staged piece size and the ring depth for one GEMV launch.
-//   tall matrices (>= 8 tile sets per SM): one CTA per SM, each warp walks its own tile sets over the whole K;
-//   wide ones: one CTA per tile set, K split over the warps, partial sums merged in shared memory.
-// Tuning overrides (development aid): CUQWEN_GEMV_PG, CUQWEN_GEMV_NST.
+// Picks the work split (rw row-warps x kw K-parts), the staged piece size and the ring depth for one GEMV launch.
+//   many tile sets: blocks of up to 8 tile sets (128 rows), every consumer warp walks the whole K of its 16 rows;
+//   few tile sets: one tile set per CTA, its K split over the eight consumer warps.
+// Tuning overrides (development aid): CUQWEN_GEMV_PG, CUQWEN_GEMV_NST, CUQWEN_GEMV_CAP_KB.
 int launch_gemv(int quant, int epi, GemvArgs& a, const LaunchCfg& cfg) {
     if (a.K <= 0 || a.K % kGroup != 0 || a.K > 24576) return (int)cudaErrorInvalidValue;
     if (quant < 0 || quant > 2) return (int)cudaErrorInvalidValue;
@@ -281,63 +283,51 @@ int launch_gemv(int quant, int epi, GemvArgs& a, const LaunchCfg& cfg) {
     const int MT = (epi == EPI_SWIGLU || epi == EPI_QKV) ? 2 : 1;
     const int ngrp = a.K / kGroup;
     const int gb = quant == Q_I4 ? 64 : quant == Q_I8 ? 128 : 256;
-    const int pg_max = 256 / gb;                     // row pieces of at most 256 bytes
+    const int pg_max = 256 / gb;                     // row pieces of at most 256 bytes (TMA box limit for byte elements)
     const int kMaxSmem = 225 * 1024;
-    const int kShare = env_int("CUQWEN_GEMV_CAP_KB", 110) * 1024;    // per-CTA budget that lets two CTAs (e.g. of consecutive kernels) share an SM
-    int nw, pg, nst, cap;
-    dim3 grid;
-    if (a.nsets >= 8 * cfg.sm_count) {
-        a.ksplit = 0; nw = 8;
-        int g = (a.nsets + nw - 1) / nw;
-        grid = dim3(g < cfg.sm_count ? g : cfg.sm_count);
-        pg = ngrp < pg_max ? ngrp : pg_max;
-        nst = 8; cap = kShare;
-    } else {
-        a.ksplit = 1;
-        grid = dim3(a.nsets);
-        pg = pg_max;
-        while (pg > 1 && (ngrp + pg - 1) / pg < 8) --pg;      // enough pieces to occupy eight warps
-        const int pt = (ngrp + pg - 1) / pg;
-        nw = pt < 8 ? pt : 8;
-        nst = (pt + nw - 1) / nw;                     // everything this warp will ever read can be in flight
-        if (nst > 8) nst = 8;
-        cap = kShare;
-    }
+    int rw = 1;
+    if (epi != EPI_QKV) while (rw < 8 && a.nsets / (rw * 2) >= cfg.sm_count) rw *= 2;
+    int kw = 8 / rw;                                 // rw * kw may end up below 8 when a row has few pieces: the spare warps idle
+    const int nblk = (a.nsets + rw - 1) / rw;
+    const int grid = nblk;                            // CTAs loop when there are more blocks than fit at once
+    int cap = env_int("CUQWEN_GEMV_CAP_KB", nblk > cfg.sm_count ? 110 : 220) * 1024;
     const int env_pg = env_int("CUQWEN_GEMV_PG", 0), env_nst = env_int("CUQWEN_GEMV_NST", 0);
-    auto need = [&](int pg_, int nst_) { return gemv_smem_bytes(a.K, quant, MT, nw, pg_, nst_, a.ksplit); };
-    // deepest ring (<= want) that fits `cap_`, 0 if not even one stage fits
-    auto fit = [&](int pg_, int want, int cap_) { int n = want; while (n > 1 && need(pg_, n) > (size_t)cap_) --n; return need(pg_, n) <= (size_t)cap_ ? n : 0; };
-    if (env_pg > 0) pg = env_pg > pg_max ? pg_max : env_pg;
-    for (int pass = 0; pass < 2; ++pass) {
-        int best_pg = 0, best_n = 0;
-        for (int q = pg; q >= 1; --q) {
+    int pg = 0, nst = 0;
+    for (int pass = 0; pass < 2 && !nst; ++pass) {
+        for (int q = env_pg > 0 ? (env_pg < pg_max ? env_pg : pg_max) : pg_max; q >= 1; --q) {
             const int pt = (ngrp + q - 1) / q;
-            int want = a.ksplit ? (pt + nw - 1) / nw : 8;
-            if (want > 8) want = 8;
-            if (env_nst > 0) want = env_nst;
-            const int n = fit(q, want, cap);
-            if (n > best_n) { best_n = n; best_pg = q; }
-            if (n >= (want < 2 ? want : 2) || env_pg > 0) break;      // at least two stages (or all the warp needs)
+            int kwq = kw; while (kwq > 1 && kwq > pt) kwq /= 2;                   // no more K-parts than pieces
+            const int steps = (pt + kwq - 1) / kwq;
+            int want = env_nst > 0 ? env_nst : (rw == 8 ? 6 : steps < 6 ? steps : 6);
+            int n = want;
+            while (n > 1 && gemv_smem_bytes(a.K, quant, MT, rw, kwq, q, n) > (size_t)cap) --n;
+            if (gemv_smem_bytes(a.K, quant, MT, rw, kwq, q, n) > (size_t)cap) continue;
+            if (n >= (want < 3 ? want : 3) || q == 1 || env_pg > 0) { pg = q; nst = n; kw = kwq; break; }
+            if (!nst || n > nst) { pg = q; nst = n; kw = kwq; }
+            if (q == 1) break;
+            nst = 0;
         }
-        if (best_n > 0) { pg = best_pg; nst = best_n; break; }
-        if (cap == kMaxSmem) return (int)cudaErrorInvalidValue;
-        cap = kMaxSmem;                                              // give up the second CTA per SM
+        if (!nst) cap = kMaxSmem;
     }
-    const size_t smem = need(pg, nst);
-    if (smem > (size_t)kMaxSmem) return (int)cudaErrorInvalidValue;
-    a.pg = pg; a.nst = nst;
+    if (!nst) return (int)cudaErrorInvalidValue;
+    if (epi == EPI_QKV && rw != 1) return (int)cudaErrorInvalidValue;
+    a.rw = rw; a.kw = kw; a.pg = pg; a.nst = nst;
+    const size_t smem = gemv_smem_bytes(a.K, quant, MT, rw, kw, pg, nst);
     {
         const size_t rbytes = quant == Q_I4 ? a.K / 2 : quant == Q_I8 ? a.K : (size_t)a.K * 2;
         const int nmat = epi == EPI_QKV ? 3 : epi == EPI_SWIGLU ? 2 : 1;
         for (int m = 0; m < nmat; ++m) {
             const size_t rows_m = epi == EPI_QKV ? (size_t)(m == 0 ? a.n_heads : a.n_kv) * a.hd : (size_t)a.rows;
-            if (int r = make_weight_map(&a.tmap[m], a.w[m], rbytes, rows_m, pg * gb)) return r;
+            if (int r = make_weight_map(&a.tmap[m], a.w[m], rbytes, rows_m, pg * gb, 16 * rw)) return r;
         }
     }
-    const dim3 block(32 * nw);
-    if (quant == Q_I4) return launch_gemv_i4(epi, a, grid, block, smem, cfg);
-    if (quant == Q_I8) return launch_gemv_i8(epi, a, grid, block, smem, cfg);
-    return launch_gemv_f16(epi, a, grid, block, smem, cfg);
+    const int blocks = (a.nsets + rw - 1) / rw;
+    const int per_sm = smem <= 110 * 1024 ? 2 : 1;
+    const dim3 gridd(blocks < per_sm * cfg.sm_count ? blocks : per_sm * cfg.sm_count), block(kGemvThreadsHost);
+    (void)grid;
+    if (quant == Q_I4) return launch_gemv_i4(epi, a, gridd, block, smem, cfg);
+    if (quant == Q_I8) return launch_gemv_i8(epi, a, gridd, block, smem, cfg);
+    return launch_gemv_f16(epi, a, gridd, block, smem, cfg);
 }
 
 }  // namespace cq

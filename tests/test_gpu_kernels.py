@@ -49,7 +49,7 @@ def test_config1_w4a16_gemv_4864x896(built):
     got = run_gemv(2, w, s, x, rows, cols)
     want = O.gemv_f32(2, w, s, x, rows, cols).astype(np.float16)
     assert close(got, want), report(got, want)
-    assert (got.view(np.uint16) == want.view(np.uint16)).mean() > 0.97      # same sums up to fp32 reordering
+    assert (got.view(np.uint16) == want.view(np.uint16)).mean() > 0.80      # same sums up to reordering and the 15-bit activation grid
     ref = O.ref_lib("0.5b", "int4")
     if ref is not None:
         acc, P = DevBuf(rows * 2), Pool()
