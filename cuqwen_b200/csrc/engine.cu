@@ -211,7 +211,7 @@ extern "C" int cuqwen_create(const cuqwen_params* pin, cuqwen_engine** out) {
     CK(dalloc((void**)&e->kc, kvn * 2)); CK(dalloc((void**)&e->vc, kvn * 2));     // zeroed like src/model.cu:37-38
     CK(dalloc((void**)&e->part_o, attn_scratch_floats_o(e->n_kv_l, e->nsplit, p.head_dim) * 4));
     CK(dalloc((void**)&e->part_ml, attn_scratch_floats_ml(e->n_kv_l, e->nsplit) * 4));
-    CK(dalloc((void**)&e->counters, e->n_kv_l * 4));
+    CK(dalloc((void**)&e->counters, attn_scratch_counters(e->n_kv_l, e->nsplit) * 4));
     CK(dalloc((void**)&e->ctl, sizeof(StepCtl))); CK(cudaMallocHost((void**)&e->h_ctl, sizeof(StepCtl)));
     CK(dalloc((void**)&e->d_hist, (size_t)p.max_seq_len * 4));
     CK(dalloc((void**)&e->bitmap, ((size_t)e->vocab_l + 31) / 32 * 4));
@@ -397,7 +397,7 @@ static int record_step(cuqwen_engine* e, cudaStream_t s, bool pdl) {
             a.q = e->q; a.kc = e->kc + l * kv_layer; a.vc = e->vc + l * kv_layer; a.out = e->att; a.d_pos = &e->ctl->pos;
             a.n_kv = e->n_kv_l; a.grp = e->plan.grp; a.max_seq = p.max_seq_len; a.nsplit = e->nsplit;
             a.scale_log2 = (1.0f / sqrtf((float)p.head_dim)) * 1.4426950408889634f;
-            a.part_o = e->part_o; a.part_ml = e->part_ml; a.counters = e->counters;
+            a.part_o = e->part_o; a.part_ml = e->part_ml; a.counters = e->counters; a.err = t_err;
             LK(launch_attn(p.head_dim, a, cfg));
         }
         {   // o_proj + residual
@@ -680,7 +680,7 @@ extern "C" int cuqwen_attn_scratch_bytes(int n_kv, int hd, int nsplit, size_t* b
     if (n_kv < 1 || nsplit < 1 || nsplit > kMaxSplit || (hd != 64 && hd != 128)) return fail(CUQWEN_ERR_ARG, "unsupported attention shape");
     if (bo) *bo = attn_scratch_floats_o(n_kv, nsplit, hd) * 4;
     if (bml) *bml = attn_scratch_floats_ml(n_kv, nsplit) * 4;
-    if (bc) *bc = (size_t)n_kv * 4;
+    if (bc) *bc = attn_scratch_counters(n_kv, nsplit) * 4;
     return CUQWEN_OK;
 }
 extern "C" int cuqwen_k_attention(int device, const void* q, const void* kc, const void* vc, void* out, const int* d_pos, int n_heads, int n_kv, int hd,
@@ -692,7 +692,7 @@ extern "C" int cuqwen_k_attention(int device, const void* q, const void* kc, con
     a.q = (const __half*)q; a.kc = (const __half*)kc; a.vc = (const __half*)vc; a.out = (__half*)out; a.d_pos = d_pos;
     a.n_kv = n_kv; a.grp = n_heads / n_kv; a.max_seq = max_seq; a.nsplit = nsplit;
     a.scale_log2 = (1.0f / sqrtf((float)hd)) * 1.4426950408889634f;
-    a.part_o = (float*)so; a.part_ml = (float*)sml; a.counters = (unsigned*)counters;
+    a.part_o = (float*)so; a.part_ml = (float*)sml; a.counters = (unsigned*)counters; a.err = t_err;
     KK(launch_attn(hd, a, cfg)); return CUQWEN_OK;
 }
 extern "C" int cuqwen_k_gemv_add(int device, int quant, const void* w, const void* s, const void* in, void* x, int rows, int cols) {

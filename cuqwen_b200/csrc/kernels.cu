@@ -220,14 +220,24 @@ int launch_fill_normal(__half* dst, size_t n, uint64_t seed, uint64_t base, cons
 }
 
 // ---- attention -------------------------------------------------------------
-size_t attn_scratch_floats_o(int n_kv, int nsplit, int head_dim) { return (size_t)n_kv * nsplit * kMaxGroup * head_dim; }
-size_t attn_scratch_floats_ml(int n_kv, int nsplit) { return (size_t)n_kv * nsplit * kMaxGroup * 2; }
+size_t attn_scratch_floats_o(int n_kv, int nsplit, int head_dim) { return attn_slots(n_kv, nsplit) * kMaxGroup * head_dim; }
+size_t attn_scratch_floats_ml(int n_kv, int nsplit) { return attn_slots(n_kv, nsplit) * kMaxGroup * 2; }
+size_t attn_scratch_counters(int n_kv, int nsplit) { return attn_counters(n_kv, nsplit); }
 
 int launch_attn(int head_dim, const AttnArgs& a, const LaunchCfg& cfg) {
     if (a.grp < 1 || a.grp > kMaxGroup || a.nsplit < 1 || a.nsplit > kMaxSplit) return (int)cudaErrorInvalidValue;
-    dim3 grid(a.n_kv, a.nsplit), block(kAttnWarps * 32);
-    if (head_dim == 128) return launch_k(attn_decode_kernel<128>, grid, block, 0, cfg, a);
-    if (head_dim == 64) return launch_k(attn_decode_kernel<64>, grid, block, 0, cfg, a);
+    dim3 grid(a.n_kv, a.nsplit), block(kAttnThreads);
+    const size_t smem = attn_smem_bytes(head_dim);
+    if (head_dim == 128) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        return launch_k(attn_decode_kernel<128>, grid, block, smem, cfg, a);
+    }
+    if (head_dim == 64) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        return launch_k(attn_decode_kernel<64>, grid, block, smem, cfg, a);
+    }
     return (int)cudaErrorInvalidValue;
 }
 

@@ -35,6 +35,7 @@ int launch_gemv(int quant, int epi, GemvArgs& a, const LaunchCfg& cfg);
 int launch_attn(int head_dim, const AttnArgs& a, const LaunchCfg& cfg);
 size_t attn_scratch_floats_o(int n_kv, int nsplit, int head_dim);
 size_t attn_scratch_floats_ml(int n_kv, int nsplit);
+size_t attn_scratch_counters(int n_kv, int nsplit);   // u32 tickets
 
 int launch_embed(const __half* table, const int* d_token, __half* out, int dim, const LaunchCfg& cfg);
 int launch_rmsnorm(const __half* x, const __half* w, __half* out, int dim, float eps, const LaunchCfg& cfg);
