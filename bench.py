@@ -233,7 +233,7 @@ def run_ours(a):
     if rank == 0 and world == 1 and not a.no_cpu_baseline:
         out["cpu_baseline"] = cpu_baseline(path, cfg, ctx)
     if rank == 0:
-        print(json.dumps(out), flush=True)
+        emit(out)
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
@@ -261,6 +261,15 @@ def cpu_baseline(path: Path, cfg: dict, ctx: int, steps: int = 2):
             "sample": f"{steps} decode steps (after 1 untimed) of the same model file at KV context {ctx}, scalar C oracle, OpenMP over output rows"}
 
 
+_JSON_OUT = None
+
+
+def emit(obj):
+    out = _JSON_OUT or sys.stdout
+    out.write(json.dumps(obj) + "\n")
+    out.flush()
+
+
 def run_reference(a):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -270,7 +279,7 @@ def run_reference(a):
     from cuqwen_b200 import engine as E
     ref = O.ref_lib(a.model, a.quant)
     if ref is None:
-        print(json.dumps({"impl": "reference", "unavailable": f"oracle/_ref/{O.ref_lib_path(a.model, a.quant).name} was not built (needs the CuQwen sources at build time)"}), flush=True)
+        emit({"impl": "reference", "unavailable": f"oracle/_ref/{O.ref_lib_path(a.model, a.quant).name} was not built (needs the CuQwen sources at build time)"})
         return
     cfg = binfmt.MODELS[a.model]
     path = ensure_model_file(a.model, a.quant)
@@ -304,7 +313,7 @@ def run_reference(a):
                                    f"({Kst} qwen_forward calls)"},
         "step": {"algorithmic_bytes": binfmt.step_bytes(cfg, qid, int(ctx + Kst / 2))},
     }
-    print(json.dumps(out), flush=True)
+    emit(out)
 
 
 def main():
@@ -318,6 +327,12 @@ def main():
     ap.add_argument("--ctx", type=int, default=8192)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     a = ap.parse_args()
+    # Libraries (NCCL's version banner, for one) write to file descriptor 1.  Keep the real stdout aside for the one
+    # JSON line and send everything else to stderr.
+    global _JSON_OUT
+    sys.stdout.flush()
+    _JSON_OUT = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
     if a.impl == "reference":
         run_reference(a)
     else:
