@@ -53,6 +53,7 @@ SIGNATURES = {
     "cuqwen_k_rope": (_i, [_i, _vp, _vp, _i, _i, _i, _vp, _f, _i]),
     "cuqwen_k_kv_store": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i]),
     "cuqwen_k_attention": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp]),
+    "cuqwen_k_attention_static": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i]),
     "cuqwen_attn_scratch_bytes": (_i, [_i, _i, _i, C.POINTER(_sz), C.POINTER(_sz), C.POINTER(_sz)]),
     "cuqwen_k_gemv_add": (_i, [_i, _i, _vp, _vp, _vp, _vp, _i, _i]),
     "cuqwen_k_gemv": (_i, [_i, _i, _vp, _vp, _vp, _vp, _f, _vp, _i, _i]),

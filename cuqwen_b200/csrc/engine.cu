@@ -18,6 +18,7 @@
 
 #include "../../include/cuqwen_b200.h"
 #include "attn.cuh"
+#include "errors.h"
 #include "gemv.cuh"
 #include "launch.h"
 #include "tp_plan.h"
@@ -29,6 +30,10 @@ using namespace cq;
 // ---------------------------------------------------------------------------
 static thread_local char g_err[512] = "";
 static int fail(int code, const char* fmt, ...) {
+    va_list ap; va_start(ap, fmt); vsnprintf(g_err, sizeof g_err, fmt, ap); va_end(ap);
+    return code;
+}
+int cq::report_error(int code, const char* fmt, ...) {
     va_list ap; va_start(ap, fmt); vsnprintf(g_err, sizeof g_err, fmt, ap); va_end(ap);
     return code;
 }

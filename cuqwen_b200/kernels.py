@@ -53,6 +53,14 @@ def gqa_attention_decode(q, kcache, vcache, out, d_pos, n_heads, n_kv_heads, hea
                                         max_seq_len, n_splits, _p(scratch_o), _p(scratch_ml), _p(counters)))
 
 
+def gqa_attention_decode_static(q, kcache, vcache, out, d_pos, n_heads, n_kv_heads, head_dim, max_seq_len, n_splits,
+                                stream=None, device=0):
+    """cuqwen_k_attention_static: same result as gqa_attention_decode, scratch inside the library (no allocation).
+    Queued on `stream` (a cudaStream_t value; None = the CUDA default stream); the caller synchronises."""
+    check(_abi.lib().cuqwen_k_attention_static(device, stream, _p(q), _p(kcache), _p(vcache), _p(out), _p(d_pos), n_heads, n_kv_heads,
+                                               head_dim, max_seq_len, n_splits))
+
+
 def gemv_add(quant, w, scale, inp, x_inout, rows, cols, device=0):
     check(_abi.lib().cuqwen_k_gemv_add(device, quant, _p(w), _p(scale), _p(inp), _p(x_inout), rows, cols))
 

@@ -129,8 +129,8 @@ int cuqwen_bench_end(int device, float* ms);
 int cuqwen_k_embedding(int device, const void* embed_table, const int* d_token, void* out, int dim);
 /* launch_rmsnorm (kernels.cuh:132-139); eps as the fp16-rounded value the reference passes. */
 int cuqwen_k_rmsnorm(int device, const void* x, const void* weight, void* out, int dim, float eps);
-/* launch_fused_attn_block (kernels.cuh:62-87): q/k/v = W.x + b, then RoPE on q and k.  norm_weight non-null
- * fuses the RMSNorm of x; kcache/vcache non-null also stores k, v at row *d_pos (launch_kv_cache_store, :38-48). */
+/* launch_fused_attn_block (kernels.cuh:69-94): q/k/v = W.x + b, then RoPE on q and k.  norm_weight non-null
+ * fuses the RMSNorm of x; kcache/vcache non-null also stores k, v at row *d_pos (launch_kv_cache_store, :37-47). */
 int cuqwen_k_qkv(int device, int quant, const void* x, const void* norm_weight, float eps,
                  const void* wq, const void* wk, const void* wv, const void* sq, const void* sk, const void* sv,
                  const void* bq, const void* bk, const void* bv, void* q_out, void* k_out, void* v_out,
@@ -138,7 +138,7 @@ int cuqwen_k_qkv(int device, int quant, const void* x, const void* norm_weight, 
                  const int* d_pos, float rope_theta, int rope_fast);
 /* apply_rope_kernel alone (src/kernels.cu:370-398) */
 int cuqwen_k_rope(int device, void* q, void* k, int n_heads, int n_kv_heads, int head_dim, const int* d_pos, float rope_theta, int rope_fast);
-/* launch_kv_cache_store (kernels.cuh:38-48) */
+/* launch_kv_cache_store (kernels.cuh:37-47) */
 int cuqwen_k_kv_store(int device, const void* k, const void* v, void* kcache, void* vcache, const int* d_pos, int n_kv_heads, int max_seq_len, int head_dim);
 /* launch_gqa_attention_decode (kernels.cuh:21-36).  scratch_o / scratch_ml / counters sized by
  * cuqwen_attn_scratch_bytes; counters must be zero on first use. */
@@ -146,18 +146,27 @@ int cuqwen_k_attention(int device, const void* q, const void* kcache, const void
                        int n_heads, int n_kv_heads, int head_dim, int max_seq_len, int n_splits,
                        void* scratch_o, void* scratch_ml, void* counters);
 int cuqwen_attn_scratch_bytes(int n_kv_heads, int head_dim, int n_splits, size_t* bytes_o, size_t* bytes_ml, size_t* bytes_counters);
-/* launch_gemv_add_fp16 / launch_fused_mlp_stage2 (kernels.cuh:120-128, :108-116): x_inout += W . input */
+/* No counterpart in the reference.  Same computation as cuqwen_k_attention for hosts that may not allocate device
+ * memory any more (fixed memory budget, or code that must not stall the device's other streams on cudaMalloc):
+ * the scratch is a fixed 1.6 MB array inside this library, one per device, so the call allocates nothing.
+ * Limit: n_kv_heads * (n_splits + ceil(n_splits / 8)) <= 384 and n_kv_heads * (ceil(n_splits / 8) + 1) <= 256, else
+ * CUQWEN_ERR_ARG.  `stream` is a cudaStream_t (NULL = the CUDA default stream); the caller synchronises it.  The
+ * first call per device does one-time set-up (address look-up of the array) and should come before any stream
+ * capture.  Calls that can overlap on one device (different unordered streams) race on the single scratch block. */
+int cuqwen_k_attention_static(int device, void* stream, const void* q, const void* kcache, const void* vcache, void* out,
+                              const int* d_pos, int n_heads, int n_kv_heads, int head_dim, int max_seq_len, int n_splits);
+/* launch_gemv_add_fp16 / launch_fused_mlp_stage2 (kernels.cuh:122-130, :110-120): x_inout += W . input */
 int cuqwen_k_gemv_add(int device, int quant, const void* w, const void* scale, const void* input, void* x_inout, int rows, int cols);
-/* Plain GEMV y = W . x (fp16 out), optional fused RMSNorm of x.  launch_compute_logits(_int8) (kernels.cuh:141-158). */
+/* Plain GEMV y = W . x (fp16 out), optional fused RMSNorm of x.  launch_compute_logits(_int8) (kernels.cuh:141-160). */
 int cuqwen_k_gemv(int device, int quant, const void* w, const void* scale, const void* x, const void* norm_weight, float eps, void* y, int rows, int cols);
 /* Same with fp32 output (row-parallel partial sums under tensor parallelism). */
 int cuqwen_k_gemv_f32(int device, int quant, const void* w, const void* scale, const void* x, float* y, int rows, int cols);
-/* launch_fused_mlp_stage1 (kernels.cuh:90-102): h = silu(Wg.x) * (Wu.x), optional fused RMSNorm of x. */
+/* launch_fused_mlp_stage1 (kernels.cuh:96-108): h = silu(Wg.x) * (Wu.x), optional fused RMSNorm of x. */
 int cuqwen_k_mlp1(int device, int quant, const void* x, const void* norm_weight, float eps, const void* wg, const void* wu,
                   const void* sg, const void* su, void* out, int dim, int inter);
-/* launch_apply_repetition_penalty (kernels.cuh:50-57); bitmap: ceil(vocab/32) zeroed u32, left zeroed. */
+/* launch_apply_repetition_penalty (kernels.cuh:49-56); bitmap: ceil(vocab/32) zeroed u32, left zeroed. */
 int cuqwen_k_penalty(int device, void* logits, const int* d_history, const int* d_history_len, int vocab, float penalty, void* bitmap);
-/* launch_argmax (kernels.cuh:59-60); scratch: 16 zeroed bytes, left zeroed. */
+/* launch_argmax (kernels.cuh:58-67); scratch: 16 zeroed bytes, left zeroed. */
 int cuqwen_k_argmax(int device, const void* logits, int* d_token_out, int vocab, void* scratch16);
 /* Dequantised fp16 weights half(float(q) * float(scale)) (the value dot8 multiplies by, src/kernels.cu:27-42). */
 int cuqwen_k_dequant(int device, int quant, const void* w, const void* scale, void* out_fp16, long rows, long cols);
