@@ -16,7 +16,7 @@
 // Scratch (sizes from attn_slots / attn_counters): part_o [slots][8][hd] fp32, part_ml [slots][8][2] fp32, counters
 // u32 (zero before the first launch; the kernel leaves them zero).
 #pragma once
-#include "attn_combine.cuh"
+#include "attn_tile.cuh"
 #include "tma.cuh"
 
 namespace cq {
@@ -45,14 +45,12 @@ inline size_t attn_smem_bytes(int hd) { return (size_t)kAttnStages * 2 * kAttnSt
 template <int HD>
 __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArgs a) {
     constexpr int NCH = HD / 32;   // 16-byte chunks of a K row per lane (4 lanes cover 64 B)
-    constexpr int NC = HD / 64;    // 16-byte chunks of a V row per lane (8 lanes cover 128 B)
-    constexpr int NMT = HD / 16;   // output m-tiles (16 d values each)
     constexpr int ROWB = HD * 2;   // bytes of one key row
     constexpr int HALF = kAttnStageKeys * ROWB;   // bytes of the K (or V) half of a stage
     constexpr int NCT = kAttnWarps * 32;
     extern __shared__ __align__(128) unsigned char dyn[];
     __shared__ float sm_o[kAttnWarps][kMaxGroup][HD];
-    __shared__ float sm_m[kAttnWarps][kMaxGroup], sm_l[kAttnWarps][kMaxGroup];
+    __shared__ float sm_ml[kAttnWarps][kMaxGroup][2];
     __shared__ __align__(8) unsigned long long sm_bar[2 * kAttnStages];
     __shared__ int sm_last;
 
@@ -95,112 +93,28 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
     // ---------------------------------------------- consumers --------------------------------------------------------
     auto csync = [] { asm volatile("bar.sync 1, %0;" ::"r"(NCT) : "memory"); };
     if (nstage > 0) {
-        // A operand of Q.K^T: q of head g (zero rows for g >= grp)
         uint32_t qa[NCH][4];
-        {
-            const __half* qrow = a.q + (size_t)(kvh * a.grp + g) * HD;
-#pragma unroll
-            for (int i = 0; i < NCH; ++i) {
-                uint4 v = make_uint4(0, 0, 0, 0);
-                if (g < a.grp) v = __ldcg(reinterpret_cast<const uint4*>(qrow + (i * 4 + t) * 8));
-                qa[i][0] = v.x; qa[i][1] = v.y; qa[i][2] = v.z; qa[i][3] = v.w;
-            }
-        }
-        float o[NMT][4];
-#pragma unroll
-        for (int m = 0; m < NMT; ++m) o[m][0] = o[m][1] = o[m][2] = o[m][3] = 0.f;
-        float m_run = -INFINITY, l_run = 0.f;
+        attn_load_q<HD>(qa, a.q + (size_t)kvh * a.grp * HD, a.grp, g, t);
+        AttnState<HD> st;
+        st.reset();
         bool failed = false;
-        for (int st = 0; st < nstage; ++st) {
-            const int s = st % kAttnStages;
-            if (!failed && !mbar_wait(bar_full + s * 8, (st / kAttnStages) & 1)) { failed = true; if (a.err) atomicExch(a.err, 6u); }
-            const int kb = t0 + st * kAttnStageKeys + 16 * warp;       // first key of this warp's tile
+        for (int sn = 0; sn < nstage; ++sn) {
+            const int s = sn % kAttnStages;
+            if (!failed && !mbar_wait(bar_full + s * 8, (sn / kAttnStages) & 1)) { failed = true; if (a.err) atomicExch(a.err, 6u); }
+            const int kb = t0 + sn * kAttnStageKeys + 16 * warp;       // first key of this warp's tile
             if (kb < t1) {
                 const unsigned char* sK = dyn + s * 2 * HALF + 16 * warp * ROWB;
-                const unsigned char* sV = sK + HALF;
-                uint4 kA[NCH], kB[NCH], vv[4][NC];
-                const bool vA = kb + g < t1, vB = kb + 8 + g < t1;
-#pragma unroll
-                for (int i = 0; i < NCH; ++i) {
-                    kA[i] = vA ? *reinterpret_cast<const uint4*>(sK + g * ROWB + (i * 4 + t) * 16) : make_uint4(0, 0, 0, 0);
-                    kB[i] = vB ? *reinterpret_cast<const uint4*>(sK + (g + 8) * ROWB + (i * 4 + t) * 16) : make_uint4(0, 0, 0, 0);
-                }
-#pragma unroll
-                for (int r = 0; r < 4; ++r) {
-                    const int kr = 2 * t + (r & 1) + (r >> 1) * 8;
-#pragma unroll
-                    for (int c = 0; c < NC; ++c)
-                        vv[r][c] = kb + kr < t1 ? *reinterpret_cast<const uint4*>(sV + kr * ROWB + (c * 8 + g) * 16) : make_uint4(0, 0, 0, 0);
-                }
-                float sA[4] = {0.f, 0.f, 0.f, 0.f}, sB[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-                for (int i = 0; i < NCH; ++i) {
-                    mma16816(sA, qa[i][0], 0u, qa[i][1], 0u, kA[i].x, kA[i].y);
-                    mma16816(sA, qa[i][2], 0u, qa[i][3], 0u, kA[i].z, kA[i].w);
-                    mma16816(sB, qa[i][0], 0u, qa[i][1], 0u, kB[i].x, kB[i].y);
-                    mma16816(sB, qa[i][2], 0u, qa[i][3], 0u, kB[i].z, kB[i].w);
-                }
-                // lane holds head g, keys kb+2t, kb+2t+1 (sA) and kb+8+2t, kb+9+2t (sB)
-                const float s0 = kb + 2 * t < t1 ? sA[0] * a.scale_log2 : -INFINITY;
-                const float s1 = kb + 2 * t + 1 < t1 ? sA[1] * a.scale_log2 : -INFINITY;
-                const float s2 = kb + 8 + 2 * t < t1 ? sB[0] * a.scale_log2 : -INFINITY;
-                const float s3 = kb + 9 + 2 * t < t1 ? sB[1] * a.scale_log2 : -INFINITY;
-                float mx = fmaxf(fmaxf(s0, s1), fmaxf(s2, s3));
-                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-                const float m_new = fmaxf(m_run, mx);       // finite: key kb is always valid
-                const float alpha = ex2(m_run - m_new);
-                const float p0 = ex2(s0 - m_new), p1 = ex2(s1 - m_new), p2 = ex2(s2 - m_new), p3 = ex2(s3 - m_new);
-                l_run = l_run * alpha + ((p0 + p1) + (p2 + p3));
-                m_run = m_new;
-                const uint32_t pb0 = pack_h2(p0, p1), pb1 = pack_h2(p2, p3);
-                // O columns of this lane are heads 2t and 2t+1
-                const float al = __shfl_sync(0xffffffffu, alpha, (2 * t) * 4), ah = __shfl_sync(0xffffffffu, alpha, (2 * t + 1) * 4);
-                if (__any_sync(0xffffffffu, alpha != 1.0f)) {
-#pragma unroll
-                    for (int m = 0; m < NMT; ++m) { o[m][0] *= al; o[m][1] *= ah; o[m][2] *= al; o[m][3] *= ah; }
-                }
-#pragma unroll
-                for (int c = 0; c < NC; ++c)
-#pragma unroll
-                    for (int ep = 0; ep < 4; ++ep) {
-                        const uint32_t wA = u4c(vv[0][c], ep), wB = u4c(vv[1][c], ep), wC = u4c(vv[2][c], ep), wD = u4c(vv[3][c], ep);
-                        mma16816(o[c * 4 + ep], prmt(wA, wB, 0x5410), prmt(wA, wB, 0x7632), prmt(wC, wD, 0x5410), prmt(wC, wD, 0x7632), pb0, pb1);
-                    }
+                attn_tile<HD, false>(st, qa, sK, sK + HALF, t1 - kb, a.scale_log2, g, t);
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_empty + s * 8);
         }
-        l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
-        l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
-        if (t == 0) { sm_m[warp][g] = m_run; sm_l[warp][g] = l_run; }
-#pragma unroll
-        for (int c = 0; c < NC; ++c)
-#pragma unroll
-            for (int ep = 0; ep < 4; ++ep) {
-                const int d = (c * 8 + g) * 8 + 2 * ep, m = c * 4 + ep;
-                sm_o[warp][2 * t][d] = o[m][0]; sm_o[warp][2 * t + 1][d] = o[m][1];
-                sm_o[warp][2 * t][d + 1] = o[m][2]; sm_o[warp][2 * t + 1][d + 1] = o[m][3];
-            }
+        attn_state_to_smem<HD>(st, &sm_o[warp][0][0], &sm_ml[warp][0][0], g, t);
         csync();
         // merge the warps of this CTA and publish the partial
         float* po = a.part_o + ((size_t)(kvh * a.nsplit + split) * kMaxGroup) * HD;
         float* pml = a.part_ml + ((size_t)(kvh * a.nsplit + split) * kMaxGroup) * 2;
-        for (int idx = threadIdx.x; idx < a.grp * HD; idx += NCT) {
-            const int h = idx / HD, d = idx % HD;
-            float M = sm_m[0][h];
-#pragma unroll
-            for (int w = 1; w < kAttnWarps; ++w) M = fmaxf(M, sm_m[w][h]);
-            float acc = 0.f, L = 0.f;
-#pragma unroll
-            for (int w = 0; w < kAttnWarps; ++w) {
-                const float f = ex2(sm_m[w][h] - M);
-                acc += sm_o[w][h][d] * f;
-                L += sm_l[w][h] * f;
-            }
-            po[h * HD + d] = acc;
-            if (d == 0) { pml[h * 2] = M; pml[h * 2 + 1] = L; }
-        }
+        attn_merge_warps<HD>(&sm_o[0][0][0], &sm_ml[0][0][0], kAttnWarps, a.grp, po, pml, threadIdx.x, NCT);
     }
     // two-level ticket tree (attn_combine.cuh): nobody waits, the last arrival of each node does that node's fold
     const int G = attn_groups(a.nsplit), gidx = split / kAttnFanIn;

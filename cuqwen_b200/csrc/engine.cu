@@ -21,6 +21,7 @@
 #include "errors.h"
 #include "gemv.cuh"
 #include "launch.h"
+#include "step_kernel.cuh"
 #include "tp_plan.h"
 
 using namespace cq;
@@ -161,6 +162,9 @@ struct cuqwen_engine {
     int* d_hist = nullptr; unsigned* bitmap = nullptr; unsigned long long* best = nullptr; unsigned* ticket = nullptr;
     int* out_ring = nullptr; int ring_cap = 65536; int* h_out = nullptr;   // h_out holds ring_cap + 1 ints
     float* tp_partial = nullptr; unsigned long long* tp_keys = nullptr;
+    // persistent step kernel (single GPU): phase table on the device, its shared-memory map, the grid barrier word
+    StepPhase* d_phases = nullptr; StepArgs step_args{}; unsigned* step_bar = nullptr; bool fused = false; int fused_grid = 0;
+    unsigned long long* step_trace = nullptr; size_t step_trace_bytes = 0;
     // graph
     cudaGraph_t graph = nullptr; cudaGraphExec_t gexec = nullptr; bool graph_ready = false;
     int launches = 0;
@@ -235,7 +239,7 @@ extern "C" void cuqwen_destroy(cuqwen_engine* e) {
     if (e->graph) cudaGraphDestroy(e->graph);
     if (e->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(e->comm);
     void* bufs[] = {e->x, e->xn, e->q, e->k, e->v, e->att, e->gate, e->logits, e->kc, e->vc, e->part_o, e->part_ml, e->counters, e->ctl, e->d_hist,
-                    e->bitmap, e->best, e->ticket, e->out_ring, e->tp_partial, e->tp_keys, e->warena};
+                    e->bitmap, e->best, e->ticket, e->out_ring, e->tp_partial, e->tp_keys, e->warena, e->d_phases, e->step_bar, e->step_trace};
     for (void* b : bufs) if (b) cudaFree(b);
     if (e->h_ctl) cudaFreeHost(e->h_ctl);
     if (e->h_out) cudaFreeHost(e->h_out);
@@ -329,6 +333,8 @@ static int walk_file(cuqwen_engine* e, Cursor cur, Arena& ar, int lm_fmt) {
     return CUQWEN_OK;
 }
 
+static int build_fused_step(cuqwen_engine* e);
+
 extern "C" int cuqwen_load(cuqwen_engine* e, const char* path) {
     if (!e || !path) return fail(CUQWEN_ERR_ARG, "null argument");
     if (e->loaded) return fail(CUQWEN_ERR_STATE, "weights already loaded");
@@ -359,6 +365,7 @@ extern "C" int cuqwen_load(cuqwen_engine* e, const char* path) {
     r = walk_file(e, cur, real, h[10]);
     if (r) { cudaFree(e->warena); e->warena = nullptr; return fail(r, "copying weights to the device failed: %s", cudaGetErrorString(cudaGetLastError())); }
     CK(cudaDeviceSynchronize());
+    if (int fr = build_fused_step(e)) return fr;
     e->loaded = true;
     return CUQWEN_OK;
 }
@@ -373,17 +380,19 @@ static int tp_allreduce(cuqwen_engine* e, float* buf, int n, cudaStream_t s) {
     return CUQWEN_OK;
 }
 
-static int record_step(cuqwen_engine* e, cudaStream_t s, bool pdl) {
+// The matrix and attention work of one step, in order.  `reduce`: a row-parallel matrix whose fp32 partial must be
+// summed over the tensor-parallel ranks and added to the residual stream afterwards.
+struct HostPhase { StepPhase ph; bool reduce; };
+
+static void describe_step(cuqwen_engine* e, std::vector<HostPhase>& out, int nsplit, bool with_fold) {
     const cuqwen_params& p = e->p;
-    LaunchCfg cfg{s, e->sms, pdl};
-    LaunchCfg cfg_plain{s, e->sms, false};
-    t_err = reinterpret_cast<unsigned*>(&e->ctl->pad[0]);
-    int n = 0;
     const size_t kv_layer = (size_t)e->n_kv_l * p.max_seq_len * p.head_dim;
     const float eps = __half2float(__float2half(p.norm_eps));   // the reference narrows eps to fp16 (src/model.cu:96)
-    const float pen = __half2float(__float2half(p.repetition_penalty));
-#define LK(call) do { int r_ = (call); if (r_) return fail(CUQWEN_ERR_CUDA, "%s: %s", #call, cudaGetErrorString((cudaError_t)r_)); ++n; } while (0)
-    LK(launch_embed(e->embed, &e->ctl->token, e->x, p.dim, cfg_plain));
+    auto gemv_phase = [&](int quant, int epi, const GemvArgs& a, bool reduce) {
+        HostPhase h; memset(&h, 0, sizeof h);
+        h.ph.kind = PH_GEMV; h.ph.quant = quant; h.ph.epi = epi; h.ph.g = a; h.reduce = reduce;
+        out.push_back(h);
+    };
     for (int l = 0; l < p.n_layers; ++l) {
         const Layer& L = e->layers[l];
         {   // RMSNorm + QKV + bias + RoPE + KV store
@@ -395,47 +404,105 @@ static int record_step(cuqwen_engine* e, cudaStream_t s, bool pdl) {
             a.kcache = e->kc + l * kv_layer; a.vcache = e->vc + l * kv_layer;
             a.d_pos = &e->ctl->pos; a.n_heads = e->n_heads_l; a.n_kv = e->n_kv_l; a.hd = p.head_dim; a.max_seq = p.max_seq_len;
             a.theta = p.rope_theta; a.rope_fast = (p.flags & CUQWEN_FLAG_ACCURATE_ROPE) ? 0 : 1;
-            LK(launch_gemv(p.quant, EPI_QKV, a, cfg));
+            gemv_phase(p.quant, EPI_QKV, a, false);
         }
         {   // split-KV attention + combine
-            AttnArgs a{};
+            HostPhase h; memset(&h, 0, sizeof h);
+            AttnArgs& a = h.ph.at;
             a.q = e->q; a.kc = e->kc + l * kv_layer; a.vc = e->vc + l * kv_layer; a.out = e->att; a.d_pos = &e->ctl->pos;
-            a.n_kv = e->n_kv_l; a.grp = e->plan.grp; a.max_seq = p.max_seq_len; a.nsplit = e->nsplit;
+            a.n_kv = e->n_kv_l; a.grp = e->plan.grp; a.max_seq = p.max_seq_len; a.nsplit = nsplit;
             a.scale_log2 = (1.0f / sqrtf((float)p.head_dim)) * 1.4426950408889634f;
             a.part_o = e->part_o; a.part_ml = e->part_ml; a.counters = e->counters; a.err = t_err;
-            LK(launch_attn(p.head_dim, a, cfg));
+            h.ph.kind = PH_ATTN; h.ph.k_cur = e->k; h.ph.v_cur = e->v;
+            out.push_back(h);
+            if (with_fold) { h.ph.kind = PH_FOLD; out.push_back(h); }      // the step kernel merges the splits in a phase of its own
         }
         {   // o_proj + residual
             GemvArgs a = gv(e->att, e->q_dim_l);
             a.w[0] = L.o.w; a.s[0] = L.o.s; a.rows = p.dim;
-            if (e->tp == 1) { a.out_h = e->x; LK(launch_gemv(p.quant, EPI_RESID, a, cfg)); }
-            else {
-                a.out_f = e->tp_partial; LK(launch_gemv(p.quant, EPI_F32, a, cfg));
-                if (int r = tp_allreduce(e, e->tp_partial, p.dim, s)) return r; ++n;
-                LK(launch_resid_sum(e->x, e->tp_partial, 1, 0, p.dim, cfg_plain));
-            }
+            if (e->tp == 1) { a.out_h = e->x; gemv_phase(p.quant, EPI_RESID, a, false); }
+            else { a.out_f = e->tp_partial; gemv_phase(p.quant, EPI_F32, a, true); }
         }
         {   // RMSNorm + gate/up + SwiGLU
             GemvArgs a = gv(e->x, p.dim);
             a.norm_w = L.post_norm; a.eps = eps;
             a.w[0] = L.gate.w; a.w[1] = L.up.w; a.s[0] = L.gate.s; a.s[1] = L.up.s; a.rows = e->inter_l; a.out_h = e->gate;
-            LK(launch_gemv(p.quant, EPI_SWIGLU, a, e->tp == 1 ? cfg : cfg));
+            gemv_phase(p.quant, EPI_SWIGLU, a, false);
         }
         {   // down + residual
             GemvArgs a = gv(e->gate, e->inter_l);
             a.w[0] = L.down.w; a.s[0] = L.down.s; a.rows = p.dim;
-            if (e->tp == 1) { a.out_h = e->x; LK(launch_gemv(p.quant, EPI_RESID, a, cfg)); }
-            else {
-                a.out_f = e->tp_partial; LK(launch_gemv(p.quant, EPI_F32, a, cfg));
-                if (int r = tp_allreduce(e, e->tp_partial, p.dim, s)) return r; ++n;
-                LK(launch_resid_sum(e->x, e->tp_partial, 1, 0, p.dim, cfg_plain));
-            }
+            if (e->tp == 1) { a.out_h = e->x; gemv_phase(p.quant, EPI_RESID, a, false); }
+            else { a.out_f = e->tp_partial; gemv_phase(p.quant, EPI_F32, a, true); }
         }
     }
     {   // final RMSNorm + lm_head
         GemvArgs a = gv(e->x, p.dim);
         a.norm_w = e->norm; a.eps = eps; a.w[0] = e->lm.w; a.s[0] = e->lm.s; a.rows = e->vocab_l; a.out_h = e->logits;
-        LK(launch_gemv(e->lm_quant, EPI_F16, a, cfg));
+        gemv_phase(e->lm_quant, EPI_F16, a, false);
+    }
+}
+
+// Plans the persistent step kernel for this engine (single GPU only) and uploads its phase table.  Leaves
+// e->fused false when the shapes do not fit the kernel's shared-memory budget; the step then runs as separate launches.
+static int build_fused_step(cuqwen_engine* e) {
+    e->fused = false;
+    if (e->tp != 1 || !(e->p.flags & CUQWEN_FLAG_FUSED_STEP)) return CUQWEN_OK;
+    const int grid = e->sms;
+    if (e->n_kv_l > grid || e->plan.grp > kMaxGroup) return CUQWEN_OK;
+    int nsplit = grid / e->n_kv_l;
+    if (nsplit > e->nsplit) nsplit = e->nsplit;
+    t_err = reinterpret_cast<unsigned*>(&e->ctl->pad[0]);
+    std::vector<HostPhase> hp;
+    describe_step(e, hp, nsplit, true);
+    const int slot_bytes = 32 * 1024;
+    std::vector<StepPhase> ph(hp.size());
+    for (size_t i = 0; i < hp.size(); ++i) {
+        ph[i] = hp[i].ph;
+        if (ph[i].kind == PH_GEMV && plan_step_gemv(ph[i].quant, ph[i].epi, ph[i].g, grid, slot_bytes)) return CUQWEN_OK;
+    }
+    int max_smem = 0;
+    CK(cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, e->p.device));
+    StepArgs sa{};
+    if (plan_step_smem(sa, ph.data(), (int)ph.size(), e->p.head_dim, slot_bytes, max_smem)) return CUQWEN_OK;
+    CK(cudaMalloc((void**)&e->d_phases, ph.size() * sizeof(StepPhase)));
+    CK(cudaMemcpy(e->d_phases, ph.data(), ph.size() * sizeof(StepPhase), cudaMemcpyHostToDevice));
+    CK(cudaMalloc((void**)&e->step_bar, 256));
+    CK(cudaMemset(e->step_bar, 0, 256));
+    if (e->p.flags & CUQWEN_FLAG_STEP_TRACE) {
+        e->step_trace_bytes = ph.size() * (size_t)grid * 4 * sizeof(unsigned long long);
+        CK(cudaMalloc((void**)&e->step_trace, e->step_trace_bytes));
+        CK(cudaMemset(e->step_trace, 0, e->step_trace_bytes));
+    }
+    sa.phases = e->d_phases; sa.nphases = (int)ph.size(); sa.bar = e->step_bar; sa.err = t_err; sa.trace = e->step_trace;
+    if (const char* d = getenv("CUQWEN_STEP_DEBUG")) sa.debug = atoi(d);
+    e->step_args = sa; e->fused_grid = grid; e->fused = true;
+    return CUQWEN_OK;
+}
+
+static int record_step(cuqwen_engine* e, cudaStream_t s, bool pdl) {
+    const cuqwen_params& p = e->p;
+    LaunchCfg cfg{s, e->sms, pdl};
+    LaunchCfg cfg_plain{s, e->sms, false};
+    t_err = reinterpret_cast<unsigned*>(&e->ctl->pad[0]);
+    int n = 0;
+    const float pen = __half2float(__float2half(p.repetition_penalty));
+#define LK(call) do { int r_ = (call); if (r_) return fail(CUQWEN_ERR_CUDA, "%s: %s", #call, cudaGetErrorString((cudaError_t)r_)); ++n; } while (0)
+    LK(launch_embed(e->embed, &e->ctl->token, e->x, p.dim, cfg_plain));
+    if (e->fused) {
+        CK(cudaMemsetAsync(e->step_bar, 0, 4, s));
+        LK(launch_decode_step(p.quant, e->step_args, e->fused_grid, cfg_plain));
+    } else {
+        std::vector<HostPhase> hp;
+        describe_step(e, hp, e->nsplit, false);
+        for (HostPhase& h : hp) {
+            if (h.ph.kind == PH_ATTN) { LK(launch_attn(p.head_dim, h.ph.at, cfg)); continue; }
+            LK(launch_gemv(h.ph.quant, h.ph.epi, h.ph.g, cfg));
+            if (h.reduce) {
+                if (int r = tp_allreduce(e, e->tp_partial, p.dim, s)) return r; ++n;
+                LK(launch_resid_sum(e->x, e->tp_partial, 1, 0, p.dim, cfg_plain));
+            }
+        }
     }
     LK(launch_penalty(e->logits, e->d_hist, &e->ctl->hist_len, e->vocab_l, e->plan.v0, pen, e->bitmap, cfg));
     if (e->tp == 1) {
@@ -622,6 +689,7 @@ extern "C" int cuqwen_get_ptr(cuqwen_engine* e, int which, int layer, void** ptr
             case CUQWEN_PTR_KEY_CACHE: r = e->kc; b = kvb; break;
             case CUQWEN_PTR_VALUE_CACHE: r = e->vc; b = kvb; break;
             case CUQWEN_PTR_HISTORY: r = e->d_hist; b = (size_t)p.max_seq_len * 4; break;
+            case CUQWEN_PTR_STEP_TRACE: r = e->step_trace; b = e->step_trace_bytes; break;
             default: return fail(CUQWEN_ERR_ARG, "unknown pointer id %d", which);
         }
     }

@@ -32,7 +32,8 @@ struct alignas(64) GemvArgs {
     int K;                    // input columns, multiple of 128
     int rows;                 // output rows of one matrix (QKV: unused)
     int nsets;                // number of 16-row tile sets
-    int rw, kw;               // the 8 consumer warps form rw row-warps x kw K-parts: a CTA block is rw tile sets, each split kw ways along K
+    int rw, kw;               // the consumer warps form rw row-warps x kw K-parts x gw group-parts: a CTA block is rw tile sets, each split kw ways along K
+    int gw;                   // warps that share one (row-warp, K-part) cell: they take the 128-column groups of a staged piece in turn
     int pg;                   // 128-column groups per staged row piece
     int nst;                  // stages in the CTA's ring
     unsigned* err;            // device word that receives a non-zero code when a bounded wait expires (may be null)
@@ -67,7 +68,7 @@ __host__ __device__ inline GemvLayout gemv_layout(int K, int group_bytes, int MT
     L.box_bytes = L.box_rows * L.piece_bytes;
     L.stage_bytes = kw * MT * L.box_bytes;
     L.scale_block_bytes = quantised ? MT * L.box_rows * ng * 2 : 0;
-    int o = K * 2;
+    int o = K <= 8192 ? K * 4 : K * 2;       // x (fp16 or digits), and room for the RMSNorm weight beside it while x is staged
     L.off_corr = o; o += (ng * 4 + 15) / 16 * 16;
     L.off_xscale = o; o += (ng * 4 + 15) / 16 * 16;
     L.off_red = o; o += kConsumerWarps * 32 * 4 + 16;
@@ -122,9 +123,25 @@ __device__ __forceinline__ TileMap<EPI> map_tileset(const GemvArgs& a, int ts) {
     return m;
 }
 
-// Finish one output row (pair).  r = row slot 0..15 inside the tile set.
+// Operands of the epilogue that come from global memory (the residual value, the biases).  Fetched at the start of a
+// block so that their latency hides behind the block's arithmetic.  The residual is read through L2: inside a
+// multi-matrix kernel another SM wrote it and L1 may hold an older copy.
 template <int EPI>
-__device__ __forceinline__ void epilogue(const GemvArgs& a, int row0, int mat, int r, float v0, float v1) {
+__device__ __forceinline__ void epilogue_fetch(const GemvArgs& a, int row0, int mat, int r, float (&pre)[2]) {
+    pre[0] = pre[1] = 0.f;
+    if (EPI == EPI_RESID) {
+        const int row = row0 + r;
+        if (row < a.rows) pre[0] = __half2float(__ldcg(a.out_h + row));
+    } else if (EPI == EPI_QKV) {
+        const int ra = row0 + r;
+        pre[0] = __half2float(a.bias[mat][ra]);
+        pre[1] = __half2float(a.bias[mat][ra + a.hd / 2]);
+    }
+}
+
+// Finish one output row (pair).  r = row slot 0..15 inside the tile set; pre = what epilogue_fetch returned for it.
+template <int EPI>
+__device__ __forceinline__ void epilogue(const GemvArgs& a, int row0, int mat, int r, float v0, float v1, const float (&pre)[2]) {
     if (EPI == EPI_F16) {
         const int row = row0 + r;
         if (row < a.rows) a.out_h[row] = __float2half(v0);
@@ -134,7 +151,7 @@ __device__ __forceinline__ void epilogue(const GemvArgs& a, int row0, int mat, i
     } else if (EPI == EPI_RESID) {
         // reference src/kernels.cu:670-671 and :620-621
         const int row = row0 + r;
-        if (row < a.rows) a.out_h[row] = __float2half(__half2float(a.out_h[row]) + v0);
+        if (row < a.rows) a.out_h[row] = __float2half(pre[0] + v0);
     } else if (EPI == EPI_SWIGLU) {
         // reference src/kernels.cu:565-567 (fast-math exp and divide, as that build uses)
         const int row = row0 + r;
@@ -147,9 +164,8 @@ __device__ __forceinline__ void epilogue(const GemvArgs& a, int row0, int mat, i
         // values (src/kernels.cu:370-398); k and v also go to the cache row `pos` (src/kernels.cu:326-347).
         const int half_hd = a.hd / 2;
         const int ra = row0 + r, rb2 = ra + half_hd;
-        const __half* bias = a.bias[mat];
-        const float f0 = __half2float(__float2half(v0 + __half2float(bias[ra])));
-        const float f1 = __half2float(__float2half(v1 + __half2float(bias[rb2])));
+        const float f0 = __half2float(__float2half(v0 + pre[0]));
+        const float f1 = __half2float(__float2half(v1 + pre[1]));
         __half o0, o1;
         const int pos = *a.d_pos;
         if (mat < 2) {

@@ -1,10 +1,14 @@
-// The GEMV kernel: one producer warp keeps a CTA-wide ring of TMA stages full, eight consumer warps run the
-// tensor-core inner product on it.  See gemv.cuh for the data path and gemv_math.cuh for the arithmetic.
+// The GEMV data path: one producer warp keeps a CTA-wide ring of TMA stages full, eight consumer warps run the
+// tensor-core inner product on it.  See gemv.cuh for the argument block and gemv_math.cuh for the arithmetic.
 //
-// Work split.  The consumer warps form rw row-warps x kw K-parts (rw * kw = 8).  A CTA "block" is rw consecutive
+// Work split.  The consumer warps form rw row-warps x kw K-parts x gw group-parts (rw * kw * gw <= 16).  A CTA "block" is rw consecutive
 // 16-row tile sets; every ring step brings, for each K-part and tile, one box of (16*rw rows) x piece_bytes.  K-part kp
 // handles row pieces kp, kp+kw, ...; partial sums of the K-parts are merged in shared memory.  Blocks go to CTAs
 // round-robin.
+//
+// gemv_produce / gemv_consume are the two halves; they keep their place in the ring in a RingCtx, so that a caller
+// can run several matrices back to back through one ring (the producer then runs ahead into the next matrix while
+// the consumers finish the current one).  gemv_kernel is the one-matrix-per-launch wrapper.
 #pragma once
 #include "gemv.cuh"
 #include "gemv_stage.cuh"
@@ -12,167 +16,243 @@
 namespace cq {
 
 constexpr int kGemvThreads = (kConsumerWarps + 1) * 32;
+constexpr int kConsumerThreads = kConsumerWarps * 32;
+
+// Shared-memory map of a CTA plus this thread's position in the ring.  Layout: [x area at offset 0][corr][xscale]
+// [red][two scale blocks][nslots ring slots][mbarriers: full[nslots], empty[nslots], scale full[2], scale empty[2]].
+struct RingCtx {
+    uint32_t sm0;                 // shared-window address of offset 0
+    unsigned char* base;          // generic pointer to offset 0
+    int off_corr, off_xscale, off_red, off_scales, scale_block_bytes, off_stages, slot_bytes, nslots;
+    uint32_t bar_full, bar_empty, bar_sfull, bar_sempty;
+    int slot;                     // next ring slot
+    uint32_t par;                 // its parity: number of completed laps, mod 2
+    uint32_t sj;                  // scale blocks used so far
+    unsigned* err;                // device word that receives a code when a bounded wait expires (may be null)
+    bool failed;                  // a wait of this thread expired: stop waiting, finish with meaningless numbers
+    bool skip_math;               // development aid: consume the ring without doing the arithmetic
+    unsigned long long* stamp;    // development aid: where this CTA's consumers put the time x staging ended (may be null)
+
+    __device__ __forceinline__ void advance() { if (++slot == nslots) { slot = 0; par ^= 1u; } }
+    __device__ __forceinline__ void wait(uint32_t bar, uint32_t parity, unsigned code) {
+        if (!failed && !mbar_wait(bar, parity)) { failed = true; if (err) atomicExch(err, code); }
+    }
+};
+
+__device__ __forceinline__ void ring_init_barriers(const RingCtx& R) {
+    for (int s = 0; s < R.nslots; ++s) { mbar_init(R.bar_full + s * 8, 1); mbar_init(R.bar_empty + s * 8, kConsumerWarps); }
+    for (int b = 0; b < 2; ++b) { mbar_init(R.bar_sfull + b * 8, 1); mbar_init(R.bar_sempty + b * 8, kConsumerWarps); }
+    mbar_fence_init();
+}
 
 template <int Q, int EPI>
-__global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const __grid_constant__ GemvArgs a) {
+struct GemvGeom {
+    static constexpr int MT = EpiMT<EPI>::MT;
+    static constexpr int GB = QT<Q>::GB;
+    int piece_bytes, box_rows, box_bytes, stage_bytes, ngrp, PT, S, nblk;
+    __device__ __forceinline__ GemvGeom(const GemvArgs& a) {
+        piece_bytes = a.pg * GB; box_rows = 16 * a.rw; box_bytes = box_rows * piece_bytes; stage_bytes = a.kw * MT * box_bytes;
+        ngrp = a.K / kGroup;
+        const int rb = Q == Q_I4 ? a.K / 2 : Q == Q_I8 ? a.K : a.K * 2;     // bytes of one weight row
+        PT = (rb + piece_bytes - 1) / piece_bytes;                          // pieces in a full row
+        S = (PT + a.kw - 1) / a.kw;                                         // ring steps per block
+        nblk = (a.nsets + a.rw - 1) / a.rw;
+    }
+};
+
+// Producer warp (all 32 lanes call): streams the weights and scales of CTA `cta`'s blocks.  Reads nothing that the
+// step itself writes.
+template <int Q, int EPI>
+__device__ __forceinline__ void gemv_produce(const GemvArgs& a, RingCtx& R, int cta, int ncta) {
+    constexpr int MT = EpiMT<EPI>::MT;
+    constexpr bool kInt = Q != Q_F16;
+    const GemvGeom<Q, EPI> G(a);
+    const int lane = threadIdx.x & 31, kw = a.kw;
+    const int n_b = cta < G.nblk ? (G.nblk - cta + ncta - 1) / ncta : 0;
+    for (int j = 0; j < n_b; ++j) {
+        const int blk = cta + j * ncta;
+        const TileMap<EPI> tm = map_tileset<EPI>(a, blk * a.rw);
+        if (kInt) {
+            const int sb = R.sj & 1;
+            R.wait(R.bar_sempty + sb * 8, ((R.sj >> 1) & 1) ^ 1, 3u);
+            const int rows_here = min(G.box_rows, (EPI == EPI_QKV ? 16 : a.rows - tm.row0));
+            const int bytes_m = rows_here * G.ngrp * 2;
+            const uint32_t dst = R.sm0 + R.off_scales + sb * R.scale_block_bytes;
+            if ((bytes_m & 15) == 0) {
+                if (lane == 0) {
+                    mbar_expect_tx(R.bar_sfull + sb * 8, (uint32_t)(bytes_m * MT));
+#pragma unroll
+                    for (int m = 0; m < MT; ++m) bulk_g2s(dst + m * G.box_rows * G.ngrp * 2, tm.sbase[m], bytes_m, R.bar_sfull + sb * 8);
+                }
+            } else {
+                // ragged last block: its scale rows are not a whole number of 16-byte units; copy with plain loads
+                __half* sbp = reinterpret_cast<__half*>(R.base + R.off_scales + sb * R.scale_block_bytes);
+                for (int m = 0; m < MT; ++m)
+                    for (int idx = lane; idx < rows_here * G.ngrp; idx += 32) sbp[m * G.box_rows * G.ngrp + idx] = tm.sbase[m][idx];
+                __syncwarp();
+                if (lane == 0) mbar_arrive(R.bar_sfull + sb * 8);
+            }
+            __syncwarp();
+            ++R.sj;
+        }
+        for (int p = 0; p < G.S; ++p) {
+            const int s = R.slot;
+            R.wait(R.bar_empty + s * 8, R.par ^ 1u, 4u);
+            int nparts = G.PT - p * kw; if (nparts > kw) nparts = kw;        // K-parts that still have a piece at this step
+            if (lane == 0) mbar_expect_tx(R.bar_full + s * 8, (uint32_t)(nparts * MT * G.box_bytes));   // boxes deliver their full size
+            __syncwarp();
+            if (lane < nparts * MT) {
+                const int kp = lane / MT, m = lane - kp * MT;
+                tma_load_3d(R.sm0 + R.off_stages + s * R.slot_bytes + (kp * MT + m) * G.box_bytes, &a.tmap[tm.mmat[m]],
+                            0, tm.mrow[m], (kp + p * kw) * (G.piece_bytes / kChunkBytes), R.bar_full + s * 8);
+            }
+            R.advance();
+        }
+    }
+}
+
+// Consumer warps (the first kConsumerThreads threads call): stage x, run the blocks of CTA `cta`, write the outputs.
+template <int Q, int EPI>
+__device__ __forceinline__ void gemv_consume(const GemvArgs& a, RingCtx& R, int cta, int ncta) {
     constexpr int MT = EpiMT<EPI>::MT;
     constexpr int GB = QT<Q>::GB;
     constexpr bool kInt = Q != Q_F16;
-    constexpr int NC = kConsumerWarps * 32;
-    extern __shared__ __align__(128) unsigned char smem_raw[];
-    pdl_launch_dependents();    // the next kernel in the stream may start its weight prefetch while this one runs
+    constexpr int NC = kConsumerThreads;
+    const GemvGeom<Q, EPI> G(a);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int rw = a.rw, kw = a.kw, nst = a.nst, pg = a.pg;
-    const int ngrp = a.K / kGroup;
-    const GemvLayout L = gemv_layout(a.K, GB, MT, rw, kw, pg, nst, kInt);
-    const uint32_t sm0 = smem_u32(smem_raw);
-    const uint32_t bars = sm0 + L.off_bars;
-    const uint32_t bar_full = bars, bar_empty = bars + nst * 8, bar_sfull = bars + 2 * nst * 8, bar_sempty = bars + (2 * nst + 2) * 8;
-
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < nst; ++s) { mbar_init(bar_full + s * 8, 1); mbar_init(bar_empty + s * 8, kConsumerWarps); }
-        for (int b = 0; b < 2; ++b) { mbar_init(bar_sfull + b * 8, 1); mbar_init(bar_sempty + b * 8, kConsumerWarps); }
-        mbar_fence_init();
-    }
-    __syncthreads();
-
-    const int rb = Q == Q_I4 ? a.K / 2 : Q == Q_I8 ? a.K : a.K * 2;            // bytes of one weight row
-    const int PT = (rb + L.piece_bytes - 1) / L.piece_bytes;                   // pieces in a full row
-    const int S = (PT + kw - 1) / kw;                                          // ring steps per block
-    const int nblk = (a.nsets + rw - 1) / rw;
-    const int n_b = (int)blockIdx.x < nblk ? (nblk - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-
-    if (warp == kConsumerWarps) {
-        // ------------------------------- producer warp: reads only weights and scales -------------------------------
-        bool failed = false;
-        for (int j = 0; j < n_b; ++j) {
-            const int blk = blockIdx.x + j * gridDim.x;
-            const TileMap<EPI> tm = map_tileset<EPI>(a, blk * rw);
-            if (kInt) {
-                if (!failed && !mbar_wait(bar_sempty + (j & 1) * 8, ((j >> 1) & 1) ^ 1)) { failed = true; if (a.err) atomicExch(a.err, 3u); }
-                const int rows_here = min(L.box_rows, (EPI == EPI_QKV ? 16 : a.rows - tm.row0));
-                const int bytes_m = rows_here * ngrp * 2;
-                const uint32_t dst = sm0 + L.off_scales + (j & 1) * L.scale_block_bytes;
-                if ((bytes_m & 15) == 0) {
-                    if (lane == 0) {
-                        mbar_expect_tx(bar_sfull + (j & 1) * 8, (uint32_t)(bytes_m * MT));
-#pragma unroll
-                        for (int m = 0; m < MT; ++m) bulk_g2s(dst + m * L.box_rows * ngrp * 2, tm.sbase[m], bytes_m, bar_sfull + (j & 1) * 8);
-                    }
-                } else {
-                    // ragged last block: its scale rows are not a whole number of 16-byte units; copy with plain loads
-                    __half* sb = reinterpret_cast<__half*>(smem_raw + L.off_scales + (j & 1) * L.scale_block_bytes);
-                    for (int m = 0; m < MT; ++m)
-                        for (int idx = lane; idx < rows_here * ngrp; idx += 32) sb[m * L.box_rows * ngrp + idx] = tm.sbase[m][idx];
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(bar_sfull + (j & 1) * 8);
-                }
-                __syncwarp();
-            }
-            for (int p = 0; p < S; ++p) {
-                const int i = j * S + p, s = i % nst;
-                if (!failed && !mbar_wait(bar_empty + s * 8, ((i / nst) & 1) ^ 1)) { failed = true; if (a.err) atomicExch(a.err, 4u); }
-                int nparts = PT - p * kw; if (nparts > kw) nparts = kw;        // K-parts that still have a piece at this step
-                if (lane == 0) mbar_expect_tx(bar_full + s * 8, (uint32_t)(nparts * MT * L.box_bytes));   // boxes deliver their full size
-                __syncwarp();
-                if (lane < nparts * MT) {
-                    const int kp = lane / MT, m = lane - kp * MT;
-                    tma_load_2d(sm0 + L.off_stages + s * L.stage_bytes + (kp * MT + m) * L.box_bytes, &a.tmap[tm.mmat[m]],
-                                (kp + p * kw) * L.piece_bytes, tm.mrow[m], bar_full + s * 8);
-                }
-            }
-        }
-        return;
-    }
-
-    // ------------------------------------------- consumer warps ---------------------------------------------------
     const int g = lane >> 2, t = lane & 3;
-    const int rwi = warp % rw, kwi = warp / rw;
-    uint4* xs = reinterpret_cast<uint4*>(smem_raw);
-    int* corr = reinterpret_cast<int*>(smem_raw + L.off_corr);
-    float* xscale = reinterpret_cast<float*>(smem_raw + L.off_xscale);
-    float* red = reinterpret_cast<float*>(smem_raw + L.off_red);
+    const int rw = a.rw, kw = a.kw, gw = a.gw, pg = a.pg, ngrp = G.ngrp;
+    const int rwi = warp % rw, kwi = (warp / rw) % kw, gwi = warp / (rw * kw);     // warp = rwi + rw * (kwi + kw * gwi)
+    const int n_b = cta < G.nblk ? (G.nblk - cta + ncta - 1) / ncta : 0;
+    uint4* xs = reinterpret_cast<uint4*>(R.base);
+    int* corr = reinterpret_cast<int*>(R.base + R.off_corr);
+    float* xscale = reinterpret_cast<float*>(R.base + R.off_xscale);
+    float* red = reinterpret_cast<float*>(R.base + R.off_red);
 
-    pdl_wait();                 // the activation vector comes from the previous kernel
-    if constexpr (kInt) stage_x_digits<Q>(a.x, a.norm_w, a.eps, a.K, smem_raw, corr, xscale, red, NC);
-    else stage_x_f16(a.x, a.norm_w, a.eps, a.K, xs, red, NC);
+    stage_x<Q>(a.x, a.norm_w, a.eps, a.K, R.base, R.off_corr, corr, xscale, red, NC);
+    if (R.stamp && threadIdx.x == 0) *R.stamp = global_ns();
 
-    bool failed = false;
     for (int j = 0; j < n_b; ++j) {
-        const int blk = blockIdx.x + j * gridDim.x;
+        const int blk = cta + j * ncta;
         const int ts = blk * rw + rwi;
-        const bool live = ts < a.nsets && kwi < kw;       // spare warps (rw * kw < 8) only keep the barriers moving
+        const bool live = ts < a.nsets && gwi < gw;       // spare warps (rw * kw * gw < 16) only keep the barriers moving
         const TileMap<EPI> tm = map_tileset<EPI>(a, live ? ts : 0);
         float tot[MT][2];
         float cf[MT][2][4];
-        int ci[MT][2][4];
 #pragma unroll
         for (int m = 0; m < MT; ++m) {
             tot[m][0] = tot[m][1] = 0.f;
 #pragma unroll
-            for (int q = 0; q < 4; ++q) { cf[m][0][q] = cf[m][1][q] = 0.f; ci[m][0][q] = ci[m][1][q] = 0; }
+            for (int q = 0; q < 4; ++q) cf[m][0][q] = cf[m][1][q] = 0.f;
         }
+        const bool merged = kw * gw > 1;                 // K-parts meet in shared memory; lanes 0-15 of the first part finish the rows
+        float preA[2] = {0.f, 0.f}, preB[2] = {0.f, 0.f};
+        if (merged) { if (kwi == 0 && gwi == 0 && lane < 16 && live) epilogue_fetch<EPI>(a, tm.row0, tm.mat, lane, preA); }
+        else if (t == 0 && live) { epilogue_fetch<EPI>(a, tm.row0, tm.mat, g, preA); epilogue_fetch<EPI>(a, tm.row0, tm.mat, g + 8, preB); }
         uint32_t sbuf = 0;
+        const int sb = R.sj & 1;
         if (kInt) {
-            if (!failed && !mbar_wait(bar_sfull + (j & 1) * 8, (j >> 1) & 1)) { failed = true; if (a.err) atomicExch(a.err, 2u); }
-            sbuf = sm0 + L.off_scales + (j & 1) * L.scale_block_bytes + (rwi * 16 + g) * ngrp * 2;     // this lane's row g of tile 0
+            R.wait(R.bar_sfull + sb * 8, (R.sj >> 1) & 1, 2u);
+            sbuf = R.sm0 + R.off_scales + sb * R.scale_block_bytes + (rwi * 16 + g) * ngrp * 2;     // this lane's row g of tile 0
         }
-        for (int p = 0; p < S; ++p) {
-            const int i = j * S + p, s = i % nst;
-            if (!failed && !mbar_wait(bar_full + s * 8, (i / nst) & 1)) { failed = true; if (a.err) atomicExch(a.err, 1u); }
+        for (int p = 0; p < G.S; ++p) {
+            const int s = R.slot;
+            R.wait(R.bar_full + s * 8, R.par, 1u);
             const int c = kwi + p * kw;
-            if (live && c < PT) {
+            if (live && c < G.PT && !R.skip_math) {
                 const int grp0 = c * pg;
                 const int ngp = ngrp - grp0 < pg ? ngrp - grp0 : pg;
-                const uint32_t wrow = sm0 + L.off_stages + s * L.stage_bytes + kwi * MT * L.box_bytes + (rwi * 16 + g) * L.piece_bytes;
-                for (int gi = 0; gi < ngp; ++gi) {
-                    const int grp = grp0 + gi;
-                    if constexpr (kInt) {
-                        compute_group_int<Q, MT>(wrow + gi * GB, L.piece_bytes, L.box_bytes, g, t, sm0 + grp * 256, ci);
+                const int cstride = G.box_rows * kChunkBytes;        // chunk-major box: [chunk][row][64 bytes]
+                const uint32_t wrow = R.sm0 + R.off_stages + s * R.slot_bytes + kwi * MT * G.box_bytes + (rwi * 16 + g) * kChunkBytes + t * 16;
+                if constexpr (kInt) {
+                    constexpr int NI = QT<Q>::NI;
+                    for (int gi = gwi; gi < ngp; gi += gw) {
+                        const int grp = grp0 + gi;
+                        uint4 w[MT][2][NI], xv[2];
+                        load_group_w<Q, MT>(wrow + gi * (GB / kChunkBytes) * cstride, cstride, G.box_bytes, w);
+                        load_group_x(R.sm0 + grp * 256, g, t, xv);
                         const int cr = corr[grp];
                         const float xsc = xscale[grp];
+                        float sc[MT][2];
 #pragma unroll
                         for (int m = 0; m < MT; ++m) {
-                            const uint32_t sa = sbuf + (m * L.box_rows * ngrp + grp) * 2;
-                            const float s0 = lds_h(sa) * xsc, s1 = lds_h(sa + 8 * ngrp * 2) * xsc;
+                            const uint32_t sa = sbuf + (m * G.box_rows * ngrp + grp) * 2;
+                            sc[m][0] = lds_h(sa) * xsc; sc[m][1] = lds_h(sa + 8 * ngrp * 2) * xsc;
+                        }
+                        int ci[MT][2][4];
+#pragma unroll
+                        for (int m = 0; m < MT; ++m)
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) ci[m][0][q] = ci[m][1][q] = 0;
+                        mma_group_int<Q, MT>(w, xv, ci);
+#pragma unroll
+                        for (int m = 0; m < MT; ++m) {
                             // columns 0 and 1 (lanes with t == 0) hold sum q*d0 and sum q*d1
                             const int v0 = (ci[m][0][0] + ci[m][1][0]) + ((ci[m][0][1] + ci[m][1][1]) << 8) - cr;
                             const int v1 = (ci[m][0][2] + ci[m][1][2]) + ((ci[m][0][3] + ci[m][1][3]) << 8) - cr;
-                            tot[m][0] = fmaf((float)v0, s0, tot[m][0]);
-                            tot[m][1] = fmaf((float)v1, s1, tot[m][1]);
-#pragma unroll
-                            for (int q = 0; q < 4; ++q) ci[m][0][q] = ci[m][1][q] = 0;
+                            tot[m][0] = fmaf((float)v0, sc[m][0], tot[m][0]);
+                            tot[m][1] = fmaf((float)v1, sc[m][1], tot[m][1]);
                         }
-                    } else {
-                        compute_group_f16<MT>(wrow + gi * GB, L.piece_bytes, L.box_bytes, t, xs + grp * 16, cf);
                     }
+                } else {
+                    for (int gi = gwi; gi < ngp; gi += gw)
+                        compute_group_f16<MT>(wrow + gi * (GB / kChunkBytes) * cstride, cstride, G.box_bytes, t, xs + (grp0 + gi) * 16, cf);
                 }
             }
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar_empty + s * 8);       // this warp is done with the stage
+            if (lane == 0) mbar_arrive(R.bar_empty + s * 8);       // this warp is done with the stage
+            R.advance();
         }
-        if (kInt) { __syncwarp(); if (lane == 0) mbar_arrive(bar_sempty + (j & 1) * 8); }
+        if (kInt) { __syncwarp(); if (lane == 0) mbar_arrive(R.bar_sempty + sb * 8); ++R.sj; }
         if constexpr (!kInt) {
 #pragma unroll
             for (int m = 0; m < MT; ++m) { tot[m][0] = cf[m][0][0] + cf[m][1][0]; tot[m][1] = cf[m][0][2] + cf[m][1][2]; }
         }
-        if (kw > 1) {
+        if (merged) {
             if (t == 0) {
 #pragma unroll
                 for (int m = 0; m < MT; ++m) { red[warp * 32 + m * 16 + g] = tot[m][0]; red[warp * 32 + m * 16 + g + 8] = tot[m][1]; }
             }
             consumer_sync(NC);
-            if (kwi == 0 && lane < 16 && live) {
+            if (kwi == 0 && gwi == 0 && lane < 16 && live) {
                 float v0 = 0.f, v1 = 0.f;
-                for (int kp = 0; kp < kw; ++kp) { v0 += red[(kp * rw + rwi) * 32 + lane]; if (MT == 2) v1 += red[(kp * rw + rwi) * 32 + 16 + lane]; }
-                epilogue<EPI>(a, tm.row0, tm.mat, lane, v0, v1);
+                for (int kp = 0; kp < kw * gw; ++kp) { v0 += red[(kp * rw + rwi) * 32 + lane]; if (MT == 2) v1 += red[(kp * rw + rwi) * 32 + 16 + lane]; }
+                epilogue<EPI>(a, tm.row0, tm.mat, lane, v0, v1, preA);
             }
             consumer_sync(NC);         // `red` is free again
         } else if (t == 0 && live) {
-            epilogue<EPI>(a, tm.row0, tm.mat, g, tot[0][0], MT == 2 ? tot[MT - 1][0] : 0.f);
-            epilogue<EPI>(a, tm.row0, tm.mat, g + 8, tot[0][1], MT == 2 ? tot[MT - 1][1] : 0.f);
+            epilogue<EPI>(a, tm.row0, tm.mat, g, tot[0][0], MT == 2 ? tot[MT - 1][0] : 0.f, preA);
+            epilogue<EPI>(a, tm.row0, tm.mat, g + 8, tot[0][1], MT == 2 ? tot[MT - 1][1] : 0.f, preB);
         }
     }
+}
+
+// Ring context of a stand-alone launch: the layout gemv_layout computed for this matrix, an empty ring.
+template <int Q, int EPI>
+__device__ __forceinline__ RingCtx gemv_ring(const GemvArgs& a, unsigned char* smem) {
+    const GemvLayout L = gemv_layout(a.K, QT<Q>::GB, EpiMT<EPI>::MT, a.rw, a.kw, a.pg, a.nst, Q != Q_F16);
+    RingCtx R;
+    R.sm0 = smem_u32(smem); R.base = smem;
+    R.off_corr = L.off_corr; R.off_xscale = L.off_xscale; R.off_red = L.off_red; R.off_scales = L.off_scales;
+    R.scale_block_bytes = L.scale_block_bytes; R.off_stages = L.off_stages; R.slot_bytes = L.stage_bytes; R.nslots = a.nst;
+    R.bar_full = R.sm0 + L.off_bars; R.bar_empty = R.bar_full + a.nst * 8; R.bar_sfull = R.bar_empty + a.nst * 8; R.bar_sempty = R.bar_sfull + 16;
+    R.slot = 0; R.par = 0; R.sj = 0; R.err = a.err; R.failed = false; R.skip_math = false; R.stamp = nullptr;
+    return R;
+}
+
+template <int Q, int EPI>
+__global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const __grid_constant__ GemvArgs a) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    pdl_launch_dependents();    // the next kernel in the stream may start its weight prefetch while this one runs
+    RingCtx R = gemv_ring<Q, EPI>(a, smem_raw);
+    if (threadIdx.x == 0) ring_init_barriers(R);
+    __syncthreads();
+    if ((threadIdx.x >> 5) == kConsumerWarps) {
+        gemv_produce<Q, EPI>(a, R, blockIdx.x, gridDim.x);
+        return;
+    }
+    pdl_wait();                 // the activation vector comes from the previous kernel
+    gemv_consume<Q, EPI>(a, R, blockIdx.x, gridDim.x);
 }
 
 }  // namespace cq

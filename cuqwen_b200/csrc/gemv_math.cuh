@@ -17,6 +17,8 @@
 
 namespace cq {
 
+constexpr int kChunkBytes = 64;   // a staged box is chunk-major: [64-byte chunk][row][64 bytes] (see make_weight_map)
+
 template <int Q> struct QT;
 template <> struct QT<Q_I4> { static constexpr int NI = 1, GB = 64; };    // 16-byte loads per row-group per lane, bytes per row-group
 template <> struct QT<Q_I8> { static constexpr int NI = 2, GB = 128; };
@@ -36,11 +38,11 @@ __device__ __forceinline__ void imma_s8s8(int (&c)[4], uint32_t a0, uint32_t a1,
 // four packed nibbles -> four bytes holding q+8: (v & 0x0f0f0f0f) ^ 0x08080808 in one LOP3
 __device__ __forceinline__ uint32_t nib4(uint32_t v) { return and_xor(v, 0x0f0f0f0fu, 0x08080808u); }
 
-// Integer path, one 128-column group for the MT tiles of a warp.  wbase: shared address of this lane's row g of tile 0
-// at this group; tile m starts mstride bytes further.  xd: shared address of the group's digit block, laid out [half (2)][t (4)][digit plane (2)][16 bytes];
+// Integer path, one 128-column group for the MT tiles of a warp.  wbase: shared address of this lane's 16 bytes (column
+// t) of row g of tile 0 in the group's first chunk; the group's next chunk is cstride bytes further, tile m mstride bytes.  xd: shared address of the group's digit block, laid out [half (2)][t (4)][digit plane (2)][16 bytes];
 // lanes with g >= 2 feed zero columns.  Two accumulator sets alternate to shorten the dependent chain.
 template <int Q, int MT>
-__device__ __forceinline__ void compute_group_int(uint32_t wbase, int row_stride, int mstride, int g, int t, uint32_t xd, int (&c)[MT][2][4]) {
+__device__ __forceinline__ void compute_group_int(uint32_t wbase, int cstride, int mstride, int g, int t, uint32_t xd, int (&c)[MT][2][4]) {
     constexpr int NI = QT<Q>::NI;
     uint4 w[MT][2][NI];
 #pragma unroll
@@ -48,7 +50,7 @@ __device__ __forceinline__ void compute_group_int(uint32_t wbase, int row_stride
 #pragma unroll
         for (int h = 0; h < 2; ++h)
 #pragma unroll
-            for (int i = 0; i < NI; ++i) w[m][h][i] = lds128(wbase + m * mstride + h * 8 * row_stride + (i * 4 + t) * 16);
+            for (int i = 0; i < NI; ++i) w[m][h][i] = lds128(wbase + m * mstride + h * 8 * kChunkBytes + i * cstride);
 #pragma unroll
     for (int jj = 0; jj < 2; ++jj) {
         uint4 xv = make_uint4(0u, 0u, 0u, 0u);
@@ -71,16 +73,56 @@ __device__ __forceinline__ void compute_group_int(uint32_t wbase, int row_stride
     }
 }
 
+// The same in two halves, so that a caller can put the loads of several groups in flight before the first MMA:
+// load_group_w fetches the fragments, mma_group_int consumes them.
+template <int Q, int MT>
+__device__ __forceinline__ void load_group_w(uint32_t wbase, int cstride, int mstride, uint4 (&w)[MT][2][QT<Q>::NI]) {
+#pragma unroll
+    for (int m = 0; m < MT; ++m)
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int i = 0; i < QT<Q>::NI; ++i) w[m][h][i] = lds128(wbase + m * mstride + h * 8 * kChunkBytes + i * cstride);
+}
+template <int Q, int MT>
+__device__ __forceinline__ void mma_group_int(const uint4 (&w)[MT][2][QT<Q>::NI], const uint4 (&xv)[2], int (&c)[MT][2][4]) {
+#pragma unroll
+    for (int jj = 0; jj < 2; ++jj) {
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            if (Q == Q_I4) {
+                const uint32_t a0 = u4c(w[m][0][0], 2 * jj), b0 = u4c(w[m][1][0], 2 * jj);
+                const uint32_t a1 = u4c(w[m][0][0], 2 * jj + 1), b1 = u4c(w[m][1][0], 2 * jj + 1);
+                imma_u8s8(c[m][0], nib4(a0), nib4(b0), nib4(a0 >> 4), nib4(b0 >> 4), xv[jj].x, xv[jj].y);
+                imma_u8s8(c[m][1], nib4(a1), nib4(b1), nib4(a1 >> 4), nib4(b1 >> 4), xv[jj].z, xv[jj].w);
+            } else {
+                const uint4& a = w[m][0][jj < QT<Q>::NI ? jj : 0];
+                const uint4& b = w[m][1][jj < QT<Q>::NI ? jj : 0];
+                imma_s8s8(c[m][0], a.x, b.x, a.y, b.y, xv[jj].x, xv[jj].y);
+                imma_s8s8(c[m][1], a.z, b.z, a.w, b.w, xv[jj].z, xv[jj].w);
+            }
+        }
+    }
+}
+// The B operand of a group: the two halves of its digit block (lanes with g >= 2 feed zero columns).
+__device__ __forceinline__ void load_group_x(uint32_t xd, int g, int t, uint4 (&xv)[2]) {
+#pragma unroll
+    for (int jj = 0; jj < 2; ++jj) {
+        xv[jj] = make_uint4(0u, 0u, 0u, 0u);
+        if (g < 2) xv[jj] = lds128(xd + jj * 128 + t * 32 + g * 16);
+    }
+}
+
 // fp16-weight path: x fp16 in natural order (xg = the group's 16 uint4), fp32 accumulators.
 template <int MT>
-__device__ __forceinline__ void compute_group_f16(uint32_t wbase, int row_stride, int mstride, int t, const uint4* __restrict__ xg, float (&c)[MT][2][4]) {
+__device__ __forceinline__ void compute_group_f16(uint32_t wbase, int cstride, int mstride, int t, const uint4* __restrict__ xg, float (&c)[MT][2][4]) {
     uint4 w[MT][2][4];
 #pragma unroll
     for (int m = 0; m < MT; ++m)
 #pragma unroll
         for (int h = 0; h < 2; ++h)
 #pragma unroll
-            for (int i = 0; i < 4; ++i) w[m][h][i] = lds128(wbase + m * mstride + h * 8 * row_stride + (i * 4 + t) * 16);
+            for (int i = 0; i < 4; ++i) w[m][h][i] = lds128(wbase + m * mstride + h * 8 * kChunkBytes + i * cstride);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const uint4 xv = xg[i * 4 + t];

@@ -1,5 +1,11 @@
 // Prologue of the GEMV kernels: bring the activation vector into shared memory in the form the inner loop wants,
 // optionally applying RMSNorm first (reference src/kernels.cu:689-751: out = half(float(x) * inv_rms * float(w))).
+//
+// The vector lives in L2 (another SM wrote it moments ago), so a load costs a full L2 round trip.  Staging is
+// therefore two steps: (1) every thread issues all its loads of x (and of the norm weight) at once and parks the raw
+// fp16 data in shared memory, summing squares on the way; (2) after one barrier the data is converted in place from
+// shared memory (normalise, then either leave fp16 or rewrite as integer digits), one chunk per lane per turn, with
+// short latencies and small register needs.
 #pragma once
 #include "gemv_math.cuh"
 
@@ -8,16 +14,9 @@ namespace cq {
 // Barrier among the first `nthreads` threads of the CTA (the consumer warps); a producer warp beyond them does not take part.
 __device__ __forceinline__ void consumer_sync(int nthreads) { asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory"); }
 
-// sum of squares -> 1/rms over the first `nthreads` threads.  `red` holds >= 33 floats.
-__device__ __forceinline__ float consumers_inv_rms(const __half* __restrict__ x, int dim, float eps, float* red, int nthreads) {
-    float ss = 0.f;
-    const uint4* xv = reinterpret_cast<const uint4*>(x);
-    for (int i = threadIdx.x; i < dim / 8; i += nthreads) {
-        const uint4 v = __ldcg(xv + i);
-        const __half2* h = reinterpret_cast<const __half2*>(&v);
-#pragma unroll
-        for (int k = 0; k < 4; ++k) { const float2 f = __half22float2(h[k]); ss += f.x * f.x + f.y * f.y; }
-    }
+// Block-wide sum over the first `nthreads` threads -> rsqrt(sum / dim + eps).  `red` holds >= 33 floats.
+// Contains two barriers; everything written to shared memory before the call is visible after it.
+__device__ __forceinline__ float consumers_rsqrt_mean(float ss, int dim, float eps, float* red, int nthreads) {
     ss = warp_sum(ss);
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
     consumer_sync(nthreads);
@@ -30,95 +29,143 @@ __device__ __forceinline__ float consumers_inv_rms(const __half* __restrict__ x,
     return red[32];
 }
 
-// One 8-element chunk of x, normalised if asked, as fp16 bits.  Coherent (L2) loads: x may have been written by
-// another SM moments ago.
-__device__ __forceinline__ uint4 load_x_chunk(const __half* x, const __half* norm_w, float inv, int c8) {
-    uint4 v = __ldcg(reinterpret_cast<const uint4*>(x) + c8);
-    if (norm_w) {
-        const uint4 wv = __ldg(reinterpret_cast<const uint4*>(norm_w) + c8);
-        __half2* xh = reinterpret_cast<__half2*>(&v);
-        const __half2* wh = reinterpret_cast<const __half2*>(&wv);
+__device__ __forceinline__ float chunk_sumsq(const uint4& v) {
+    const __half2* h = reinterpret_cast<const __half2*>(&v);
+    float ss = 0.f;
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            const float2 xf = __half22float2(xh[k]), wf = __half22float2(wh[k]);
-            xh[k] = __floats2half2_rn(xf.x * inv * wf.x, xf.y * inv * wf.y);
-        }
+    for (int k = 0; k < 4; ++k) { const float2 f = __half22float2(h[k]); ss += f.x * f.x + f.y * f.y; }
+    return ss;
+}
+
+__device__ __forceinline__ uint4 apply_norm(uint4 v, const uint4& wv, float inv) {
+    __half2* xh = reinterpret_cast<__half2*>(&v);
+    const __half2* wh = reinterpret_cast<const __half2*>(&wv);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float2 xf = __half22float2(xh[k]), wf = __half22float2(wh[k]);
+        xh[k] = __floats2half2_rn(xf.x * inv * wf.x, xf.y * inv * wf.y);
     }
     return v;
 }
 
-// fp16 weights: x in natural order.
-__device__ __forceinline__ void stage_x_f16(const __half* x, const __half* norm_w, float eps, int K, uint4* xs, float* red, int nthreads) {
-    float inv = 0.f;
-    if (norm_w) inv = consumers_inv_rms(x, K, eps, red, nthreads);
-    for (int c8 = threadIdx.x; c8 < K / 8; c8 += nthreads) xs[c8] = load_x_chunk(x, norm_w, inv, c8);
-    consumer_sync(nthreads);
+// Step 1 for NB chunks per thread per turn: chunk i of a turn is c8 = base + i * nthreads + threadIdx.x.  x through L2
+// (coherent), the norm weight through the read-only path; all loads of a turn are issued before the first store.
+template <int NB, bool NORM, bool PARKW>
+__device__ __forceinline__ float park_raw(const __half* x, const __half* norm_w, int nchunk, uint4* raw, uint4* wraw, int nthreads) {
+    float ss = 0.f;
+    for (int base = 0; base < nchunk; base += nthreads * NB) {
+        uint4 v[NB], w[NB];
+#pragma unroll
+        for (int i = 0; i < NB; ++i) {
+            const int c8 = base + i * nthreads + threadIdx.x;
+            if (c8 < nchunk) {
+                v[i] = __ldcg(reinterpret_cast<const uint4*>(x) + c8);
+                if (PARKW) w[i] = __ldg(reinterpret_cast<const uint4*>(norm_w) + c8);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < NB; ++i) {
+            const int c8 = base + i * nthreads + threadIdx.x;
+            if (c8 < nchunk) {
+                raw[c8] = v[i];
+                if (PARKW) wraw[c8] = w[i];
+                if (NORM) ss += chunk_sumsq(v[i]);
+            }
+        }
+    }
+    return ss;
 }
 
 // Quantised weights: per 128-column group, integers X = rint(x * 2^e) with |X| < 2^14, as two signed byte digits in
-// the order the B operand wants (see compute_group_int), plus per group  corr = 8 * sum(X)  (int4 only, else 0) and
+// the order the B operand wants (see mma_group_int), plus per group  corr = 8 * sum(X)  (int4 only, else 0) and
 // xscale = 2^-e.  Digit block of a group: [half jj (2)][t (4)][plane (2)][16 bytes]; the 16 bytes are two 8-byte
 // units, each the eight elements of one 32-bit weight word: int4 order e0,e2,e4,e6,e1,e3,e5,e7, int8 natural order.
+// Sixteen consecutive lanes hold the sixteen chunks of one group; whole warps call this together (full shuffles).
+// The digit block of a group occupies the very 256 bytes its fp16 values came from: the shuffles below sit between a
+// lane's read of its chunk and anybody's write, so the rewrite in place is safe within the warp.
 template <int Q>
-__device__ __forceinline__ void stage_x_digits(const __half* x, const __half* norm_w, float eps, int K, unsigned char* xd, int* corr, float* xscale, float* red, int nthreads) {
-    float inv = 0.f;
-    if (norm_w) inv = consumers_inv_rms(x, K, eps, red, nthreads);
+__device__ __forceinline__ void digits_of_chunk(uint4 v, int c8, bool live, unsigned char* xd, int* corr, float* xscale) {
+    float f[8];
+    {
+        const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) { const float2 p = __half22float2(h[k]); f[2 * k] = p.x; f[2 * k + 1] = p.y; }
+    }
+    float m = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) m = fmaxf(m, fabsf(f[k]));
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    // m in [2^p, 2^(p+1))  ->  e = 13 - p  ->  |X| < 2^14
+    int e = 0;
+    if (m > 0.f) e = 13 - ((int)((__float_as_uint(m) >> 23) & 0xff) - 127);
+    const float up = __uint_as_float((uint32_t)(e + 127) << 23);
+    int X[8], sum = 0;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) { X[k] = __float2int_rn(f[k] * up); sum += X[k]; }
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    __syncwarp();
+    if (!live) return;
+    uint32_t d0[8], d1[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const int lo = (int)(signed char)(X[k] & 0xff);
+        d0[k] = (uint32_t)lo & 0xffu;
+        d1[k] = (uint32_t)((X[k] - lo) >> 8) & 0xffu;
+    }
+    const int grp = c8 >> 4, r = c8 & 15;
+    uint2 p0, p1;
+    int off;
+    if (Q == Q_I4) {
+        const int t = r >> 2, j = r & 3;
+        off = grp * 256 + (j >> 1) * 128 + t * 32 + (j & 1) * 8;
+        p0.x = d0[0] | d0[2] << 8 | d0[4] << 16 | d0[6] << 24; p0.y = d0[1] | d0[3] << 8 | d0[5] << 16 | d0[7] << 24;
+        p1.x = d1[0] | d1[2] << 8 | d1[4] << 16 | d1[6] << 24; p1.y = d1[1] | d1[3] << 8 | d1[5] << 16 | d1[7] << 24;
+    } else {
+        const int i = r >> 3, t = (r >> 1) & 3;
+        off = grp * 256 + i * 128 + t * 32 + (r & 1) * 8;
+        p0.x = d0[0] | d0[1] << 8 | d0[2] << 16 | d0[3] << 24; p0.y = d0[4] | d0[5] << 8 | d0[6] << 16 | d0[7] << 24;
+        p1.x = d1[0] | d1[1] << 8 | d1[2] << 16 | d1[3] << 24; p1.y = d1[4] | d1[5] << 8 | d1[6] << 16 | d1[7] << 24;
+    }
+    *reinterpret_cast<uint2*>(xd + off) = p0;          // plane 0
+    *reinterpret_cast<uint2*>(xd + off + 16) = p1;     // plane 1
+    if (r == 0) {
+        corr[grp] = Q == Q_I4 ? 8 * sum : 0;
+        xscale[grp] = __uint_as_float((uint32_t)(127 - e) << 23);
+    }
+}
+
+// Stage x for the kernel of quantisation Q: digits (int4 / int8, into xd + corr + xscale) or plain fp16 (xd as uint4[]).
+// xarea_bytes: shared memory available from xd on; the norm weight is parked at xd + 2K when 4K bytes fit (else it
+// is re-read from global memory during the conversion).
+template <int Q>
+__device__ __forceinline__ void stage_x(const __half* x, const __half* norm_w, float eps, int K, unsigned char* xd, int xarea_bytes, int* corr, float* xscale,
+                                        float* red, int nthreads) {
     const int nchunk = K / 8, lane = threadIdx.x & 31;
-    // sixteen consecutive lanes hold the sixteen chunks of one group; whole warps iterate together so the shuffles are full
-    for (int base = (threadIdx.x & ~31); base < nchunk; base += nthreads) {
+    uint4* raw = reinterpret_cast<uint4*>(xd);
+    uint4* wraw = raw + nchunk;
+    const bool w_parked = norm_w && 4 * K <= xarea_bytes;
+    float inv = 0.f;
+    if (norm_w) {
+        const float ss = w_parked ? park_raw<4, true, true>(x, norm_w, nchunk, raw, wraw, nthreads) : park_raw<4, true, false>(x, norm_w, nchunk, raw, wraw, nthreads);
+        inv = consumers_rsqrt_mean(ss, K, eps, red, nthreads);
+    } else {
+        park_raw<5, false, false>(x, nullptr, nchunk, raw, nullptr, nthreads);
+        consumer_sync(nthreads);
+    }
+    if (Q == Q_F16 && !norm_w) return;                 // raw fp16 is what the fp16 kernel wants
+#pragma unroll 1
+    for (int base = threadIdx.x & ~31; base < nchunk; base += nthreads) {
         const int c8 = base + lane;
         const bool live = c8 < nchunk;
-        uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (live) v = load_x_chunk(x, norm_w, inv, c8);
-        float f[8];
-        {
-            const __half2* h = reinterpret_cast<const __half2*>(&v);
-#pragma unroll
-            for (int k = 0; k < 4; ++k) { const float2 p = __half22float2(h[k]); f[2 * k] = p.x; f[2 * k + 1] = p.y; }
-        }
-        float m = 0.f;
-#pragma unroll
-        for (int k = 0; k < 8; ++k) m = fmaxf(m, fabsf(f[k]));
-#pragma unroll
-        for (int o = 8; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-        // m in [2^p, 2^(p+1))  ->  e = 13 - p  ->  |X| < 2^14
-        int e = 0;
-        if (m > 0.f) e = 13 - ((int)((__float_as_uint(m) >> 23) & 0xff) - 127);
-        const float up = __uint_as_float((uint32_t)(e + 127) << 23);
-        int X[8], sum = 0;
-#pragma unroll
-        for (int k = 0; k < 8; ++k) { X[k] = __float2int_rn(f[k] * up); sum += X[k]; }
-#pragma unroll
-        for (int o = 8; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        uint4 xv = make_uint4(0u, 0u, 0u, 0u);
         if (live) {
-            uint32_t d0[8], d1[8];
-#pragma unroll
-            for (int k = 0; k < 8; ++k) {
-                const int lo = (int)(signed char)(X[k] & 0xff);
-                d0[k] = (uint32_t)lo & 0xffu;
-                d1[k] = (uint32_t)((X[k] - lo) >> 8) & 0xffu;
-            }
-            const int grp = c8 >> 4, r = c8 & 15;
-            uint2 p0, p1;
-            int off;
-            if (Q == Q_I4) {
-                const int t = r >> 2, j = r & 3;
-                off = grp * 256 + (j >> 1) * 128 + t * 32 + (j & 1) * 8;
-                p0.x = d0[0] | d0[2] << 8 | d0[4] << 16 | d0[6] << 24; p0.y = d0[1] | d0[3] << 8 | d0[5] << 16 | d0[7] << 24;
-                p1.x = d1[0] | d1[2] << 8 | d1[4] << 16 | d1[6] << 24; p1.y = d1[1] | d1[3] << 8 | d1[5] << 16 | d1[7] << 24;
-            } else {
-                const int i = r >> 3, t = (r >> 1) & 3;
-                off = grp * 256 + i * 128 + t * 32 + (r & 1) * 8;
-                p0.x = d0[0] | d0[1] << 8 | d0[2] << 16 | d0[3] << 24; p0.y = d0[4] | d0[5] << 8 | d0[6] << 16 | d0[7] << 24;
-                p1.x = d1[0] | d1[1] << 8 | d1[2] << 16 | d1[3] << 24; p1.y = d1[4] | d1[5] << 8 | d1[6] << 16 | d1[7] << 24;
-            }
-            *reinterpret_cast<uint2*>(xd + off) = p0;          // plane 0
-            *reinterpret_cast<uint2*>(xd + off + 16) = p1;     // plane 1
-            if (r == 0) {
-                corr[grp] = Q == Q_I4 ? 8 * sum : 0;
-                xscale[grp] = __uint_as_float((uint32_t)(127 - e) << 23);
-            }
+            xv = raw[c8];
+            if (norm_w) xv = apply_norm(xv, w_parked ? wraw[c8] : __ldg(reinterpret_cast<const uint4*>(norm_w) + c8), inv);
         }
+        if (Q == Q_F16) { if (live) raw[c8] = xv; }
+        else digits_of_chunk<Q>(xv, c8, live, xd, corr, xscale);
     }
     consumer_sync(nthreads);
 }

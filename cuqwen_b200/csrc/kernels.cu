@@ -3,6 +3,7 @@
 // the launch wrappers for the attention kernel.
 #include "attn.cuh"
 #include "gemv.cuh"
+#include "gemv_math.cuh"
 #include "launch.h"
 #include "rng.cuh"
 
@@ -258,13 +259,18 @@ static EncodeTiledFn encode_tiled() {
     }();
     return fn;
 }
-// Byte-typed 2-D map of a row-major matrix: dims {row_bytes, rows}, box {piece_bytes, box_rows}, zero fill out of bounds.
-static int make_weight_map(CUtensorMap* m, const void* w, size_t row_bytes, size_t rows, int piece_bytes, int box_rows) {
+// Byte-typed 3-D map of a row-major matrix seen as [rows][64-byte chunks]: dims {64, rows, row_bytes / 64}, box
+// {64, box_rows, piece_bytes / 64}, zero fill out of bounds.  A box therefore lands in shared memory chunk-major,
+// [chunk][row][64 bytes]: consecutive rows of one chunk are 64 bytes apart, so the 16-byte fragment loads of an MMA
+// operand (eight rows x four 16-byte columns per quarter-warp) touch every bank once.  In a row-major box the rows
+// would be piece_bytes (a multiple of 128) apart and pairs of rows would collide on the same banks.
+int make_weight_map(CUtensorMap* m, const void* w, size_t row_bytes, size_t rows, int piece_bytes, int box_rows) {
     EncodeTiledFn fn = encode_tiled();
     if (!fn) return (int)cudaErrorNotSupported;
-    const cuuint64_t dims[2] = {row_bytes, rows}, strides[1] = {row_bytes};
-    const cuuint32_t box[2] = {(cuuint32_t)piece_bytes, (cuuint32_t)box_rows}, estr[2] = {1, 1};
-    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(w), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+    if (row_bytes % kChunkBytes || piece_bytes % kChunkBytes) return (int)cudaErrorInvalidValue;
+    const cuuint64_t dims[3] = {kChunkBytes, rows, row_bytes / kChunkBytes}, strides[2] = {row_bytes, kChunkBytes};
+    const cuuint32_t box[3] = {kChunkBytes, (cuuint32_t)box_rows, (cuuint32_t)(piece_bytes / kChunkBytes)}, estr[3] = {1, 1, 1};
+    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(w), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                     CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
 }
@@ -321,7 +327,9 @@ int launch_gemv(int quant, int epi, GemvArgs& a, const LaunchCfg& cfg) {
     }
     if (!nst) return (int)cudaErrorInvalidValue;
     if (epi == EPI_QKV && rw != 1) return (int)cudaErrorInvalidValue;
-    a.rw = rw; a.kw = kw; a.pg = pg; a.nst = nst;
+    int gw = kConsumerWarps / (rw * kw);              // warps left over share cells, group by group
+    while (gw > 1 && gw > pg) gw /= 2;
+    a.rw = rw; a.kw = kw; a.gw = gw; a.pg = pg; a.nst = nst;
     const size_t smem = gemv_smem_bytes(a.K, quant, MT, rw, kw, pg, nst);
     {
         const size_t rbytes = quant == Q_I4 ? a.K / 2 : quant == Q_I8 ? a.K : (size_t)a.K * 2;

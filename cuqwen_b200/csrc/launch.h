@@ -1,5 +1,6 @@
 // Host-side launch interface shared by the engine and the C ABI.
 #pragma once
+#include <cuda.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -8,6 +9,8 @@ namespace cq {
 
 struct GemvArgs;
 struct AttnArgs;
+struct StepPhase;
+struct StepArgs;
 
 // Device-resident control block of one decode step.  The graph reads token /
 // pos / hist_len from here; with auto_advance set the sampler feeds its result
@@ -31,6 +34,16 @@ struct LaunchCfg {
 // GEMV family.  quant: 0 fp16, 1 int8, 2 int4.  epi: cq::Epi.  Fills nsets /
 // ksplit itself.  Returns a cudaError_t value.
 int launch_gemv(int quant, int epi, GemvArgs& a, const LaunchCfg& cfg);
+
+// Byte-typed 2-D tensor map of a row-major matrix: dims {row_bytes, rows}, box {piece_bytes, box_rows}.
+int make_weight_map(CUtensorMap* m, const void* w, size_t row_bytes, size_t rows, int piece_bytes, int box_rows);
+
+// Persistent decode-step kernel (step_kernel.cuh).  plan_step_gemv fills the work split and tensor maps of one GEMV
+// phase; plan_step_smem lays out shared memory for a planned table; launch_decode_step launches `grid` CTAs
+// cooperatively (grid <= SM count).  `sa.bar` must be zero when the kernel starts.
+int plan_step_gemv(int quant, int epi, GemvArgs& a, int ncta, int slot_bytes);
+int plan_step_smem(StepArgs& sa, const StepPhase* phases, int n, int head_dim, int slot_bytes, int max_smem);
+int launch_decode_step(int quant, const StepArgs& sa, int grid, const LaunchCfg& cfg);
 
 int launch_attn(int head_dim, const AttnArgs& a, const LaunchCfg& cfg);
 size_t attn_scratch_floats_o(int n_kv, int nsplit, int head_dim);

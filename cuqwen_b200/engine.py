@@ -18,10 +18,10 @@ from ._abi import Params, check
 FP16, INT8, INT4 = 0, 1, 2
 QUANT_ID = {"fp16": FP16, "int8": INT8, "int4": INT4}
 MODEL_ID = {"0.5b": 0, "1.5b": 1, "3b": 2, "7b": 3, "14b": 4}
-FLAG_ACCURATE_ROPE, FLAG_NO_PDL, FLAG_NO_GRAPH = 1, 2, 4
+FLAG_ACCURATE_ROPE, FLAG_NO_PDL, FLAG_NO_GRAPH, FLAG_FUSED_STEP, FLAG_STEP_TRACE = 1, 2, 4, 8, 16
 
 # cuqwen_get_ptr ids (include/cuqwen_b200.h)
-PTR = dict(X=0, XN=1, Q=2, K=3, V=4, ATT=5, GATE=6, LOGITS=7, KEY_CACHE=8, VALUE_CACHE=9, HISTORY=10,
+PTR = dict(X=0, XN=1, Q=2, K=3, V=4, ATT=5, GATE=6, LOGITS=7, KEY_CACHE=8, VALUE_CACHE=9, HISTORY=10, STEP_TRACE=11,
            EMBED=32, NORM=33, LM_HEAD=34, LM_HEAD_SCALE=35,
            IN_NORM=64, WQ=65, SQ=66, BQ=67, WK=68, SK=69, BK=70, WV=71, SV=72, BV=73, WO=74, SO=75, POST_NORM=76,
            WGATE=77, SGATE=78, WUP=79, SUP=80, WDOWN=81, SDOWN=82)

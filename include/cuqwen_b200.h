@@ -41,7 +41,10 @@ enum { CUQWEN_MODEL_0_5B = 0, CUQWEN_MODEL_1_5B = 1, CUQWEN_MODEL_3B = 2, CUQWEN
 enum {
     CUQWEN_FLAG_ACCURATE_ROPE = 1,  /* accurate pow/sin/cos instead of the fast-math forms the reference build uses */
     CUQWEN_FLAG_NO_PDL = 2,         /* plain stream order between kernels (no programmatic dependent launch) */
-    CUQWEN_FLAG_NO_GRAPH = 4        /* launch the step kernel by kernel instead of replaying a CUDA graph */
+    CUQWEN_FLAG_NO_GRAPH = 4,       /* launch the step kernel by kernel instead of replaying a CUDA graph */
+    CUQWEN_FLAG_FUSED_STEP = 8,     /* experimental: all matrices and the attention of a step in one persistent kernel (grid barriers between
+                                     * phases) instead of one launch each; single GPU only */
+    CUQWEN_FLAG_STEP_TRACE = 16     /* the step kernel stamps phase entry / exit times per CTA (CUQWEN_PTR_STEP_TRACE) */
 };
 
 /* Mirrors QwenConfig (include/config.h:52-127) as run-time data. */
@@ -95,6 +98,7 @@ int cuqwen_tp_plan(int n_heads, int n_kv_heads, int head_dim, int intermediate_s
 enum {
     CUQWEN_PTR_X = 0, CUQWEN_PTR_XN, CUQWEN_PTR_Q, CUQWEN_PTR_K, CUQWEN_PTR_V, CUQWEN_PTR_ATT, CUQWEN_PTR_GATE,
     CUQWEN_PTR_LOGITS, CUQWEN_PTR_KEY_CACHE, CUQWEN_PTR_VALUE_CACHE, CUQWEN_PTR_HISTORY,
+    CUQWEN_PTR_STEP_TRACE,          /* u64 [phases][CTAs][4] nanosecond stamps of the last step (enter, x staged, leave, spare); phases = 6 per layer + 1 */
     CUQWEN_PTR_EMBED = 32, CUQWEN_PTR_NORM, CUQWEN_PTR_LM_HEAD, CUQWEN_PTR_LM_HEAD_SCALE,
     CUQWEN_PTR_IN_NORM = 64, CUQWEN_PTR_WQ, CUQWEN_PTR_SQ, CUQWEN_PTR_BQ, CUQWEN_PTR_WK, CUQWEN_PTR_SK, CUQWEN_PTR_BK,
     CUQWEN_PTR_WV, CUQWEN_PTR_SV, CUQWEN_PTR_BV, CUQWEN_PTR_WO, CUQWEN_PTR_SO, CUQWEN_PTR_POST_NORM,
