@@ -31,8 +31,9 @@ sys.path.insert(0, str(ROOT))
 METRIC = "B=1 decode tok/s (7B W4A16, 1/2/4/8 B200); GEMV HBM GB/s vs peak"
 SEED = 42
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel from an ncu capture (see profiles/);
-# None until a capture exists for the shape.
-NCU_TRAFFIC_BYTES = {("7b", "int4"): None}
+# None until a capture exists for the shape.  7B int4: 70,071,040 read + 1,322,240 written
+# (profiles/gemv_kernel_int4_swiglu_7b_gateup_ncu.md).
+NCU_TRAFFIC_BYTES = {("7b", "int4"): 71393280}
 
 
 def peaks():
@@ -227,7 +228,7 @@ def run_ours(a):
         alg, sec = dominant_kernel_roofline(eng, E, K, cfg, qid)
         ach = alg / sec / 1e9
         out["roofline"] = {"bound": "hbm", "kernel": "gemv_kernel<int4, SWIGLU> (gate/up GEMV + SwiGLU)", "achieved": round(ach, 1), "peak": peak,
-                           "unit": "GB/s", "frac": round(ach / peak, 4), "peak_source": peak_src, "bytes_per_launch": alg,
+                           "unit": "GB/s", "frac": round(ach / peak, 4), "peak_source": peak_src, "frac_of_nominal_8tbs": round(ach / 8000.0, 4), "bytes_per_launch": alg,
                            "us_per_launch": round(sec * 1e6, 3), "traffic": NCU_TRAFFIC_BYTES.get((a.model, a.quant))}
     eng.close()
     if rank == 0 and world == 1 and not a.no_cpu_baseline:
