@@ -162,6 +162,11 @@ struct cuqwen_engine {
     int* d_hist = nullptr; unsigned* bitmap = nullptr; unsigned long long* best = nullptr; unsigned* ticket = nullptr;
     int* out_ring = nullptr; int ring_cap = 65536; int* h_out = nullptr;   // h_out holds ring_cap + 1 ints
     float* tp_partial = nullptr; unsigned long long* tp_keys = nullptr;
+    // peer exchange (tensor parallel without collective calls): one receive block per rank, mapped into every peer
+    unsigned char* tp_rx = nullptr; size_t tp_rx_bytes = 0; unsigned char* peer_rx[8] = {}; bool tp_peer = false;
+    __half* x2 = nullptr;
+    int steps_done = 0;                          // mirrors the device-side step counter (StepCtl::pad[1])
+    std::vector<cudaEvent_t>* prof = nullptr;    // cuqwen_step_profile: an event is recorded after every launch of the step
     // persistent step kernel (single GPU): phase table on the device, its shared-memory map, the grid barrier word
     StepPhase* d_phases = nullptr; StepArgs step_args{}; unsigned* step_bar = nullptr; bool fused = false; int fused_grid = 0;
     unsigned long long* step_trace = nullptr; size_t step_trace_bytes = 0;
@@ -237,9 +242,11 @@ extern "C" void cuqwen_destroy(cuqwen_engine* e) {
     cudaStreamSynchronize(e->stream);
     if (e->gexec) cudaGraphExecDestroy(e->gexec);
     if (e->graph) cudaGraphDestroy(e->graph);
+    for (int r = 0; r < 8; ++r) if (e->peer_rx[r] && e->peer_rx[r] != e->tp_rx) cudaIpcCloseMemHandle(e->peer_rx[r]);
+    if (e->tp_rx) cudaFree(e->tp_rx);
     if (e->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(e->comm);
     void* bufs[] = {e->x, e->xn, e->q, e->k, e->v, e->att, e->gate, e->logits, e->kc, e->vc, e->part_o, e->part_ml, e->counters, e->ctl, e->d_hist,
-                    e->bitmap, e->best, e->ticket, e->out_ring, e->tp_partial, e->tp_keys, e->warena, e->d_phases, e->step_bar, e->step_trace};
+                    e->bitmap, e->best, e->ticket, e->out_ring, e->tp_partial, e->tp_keys, e->warena, e->d_phases, e->step_bar, e->step_trace, e->x2};
     for (void* b : bufs) if (b) cudaFree(b);
     if (e->h_ctl) cudaFreeHost(e->h_ctl);
     if (e->h_out) cudaFreeHost(e->h_out);
@@ -393,10 +400,32 @@ static void describe_step(cuqwen_engine* e, std::vector<HostPhase>& out, int nsp
         h.ph.kind = PH_GEMV; h.ph.quant = quant; h.ph.epi = epi; h.ph.g = a; h.reduce = reduce;
         out.push_back(h);
     };
+    // Peer-exchange bookkeeping (tensor parallel): `cur` is the buffer that holds the residual stream, `pending` the
+    // exchange whose partials still have to be added to it by the next kernel that reads it.
+    const bool peer = e->tp > 1 && e->tp_peer;
+    __half* cur = e->x;
+    int pending = -1, next_xi = 0;
+    auto take_x = [&](GemvArgs& a) {                                        // a normed GEMV reads the residual stream
+        a.x = cur;
+        if (peer && pending >= 0) {
+            const int slot = pending & 1;
+            __half* other = cur == e->x ? e->x2 : e->x;
+            a.ngather = e->tp; a.gather = reinterpret_cast<const uint2*>(e->tp_rx) + (size_t)slot * e->tp * p.dim;
+            a.x_next = other; a.step_no = &e->ctl->pad[1]; a.seq_index = pending;
+            cur = other; pending = -1;
+        }
+    };
+    auto push_to = [&](GemvArgs& a) {                                       // a row-parallel matrix hands its partial to every rank
+        const int slot = next_xi & 1;
+        a.npush = e->tp; a.step_no = &e->ctl->pad[1]; a.seq_index = next_xi;
+        for (int d = 0; d < e->tp; ++d) a.push[d] = reinterpret_cast<uint2*>(e->peer_rx[d]) + ((size_t)slot * e->tp + e->rank) * p.dim;
+        pending = next_xi++;
+    };
     for (int l = 0; l < p.n_layers; ++l) {
         const Layer& L = e->layers[l];
         {   // RMSNorm + QKV + bias + RoPE + KV store
             GemvArgs a = gv(e->x, p.dim);
+            take_x(a);
             a.norm_w = L.in_norm; a.eps = eps;
             a.w[0] = L.q.w; a.w[1] = L.k.w; a.w[2] = L.v.w; a.s[0] = L.q.s; a.s[1] = L.k.s; a.s[2] = L.v.s;
             a.bias[0] = L.bq; a.bias[1] = L.bk; a.bias[2] = L.bv;
@@ -421,10 +450,12 @@ static void describe_step(cuqwen_engine* e, std::vector<HostPhase>& out, int nsp
             GemvArgs a = gv(e->att, e->q_dim_l);
             a.w[0] = L.o.w; a.s[0] = L.o.s; a.rows = p.dim;
             if (e->tp == 1) { a.out_h = e->x; gemv_phase(p.quant, EPI_RESID, a, false); }
+            else if (peer) { push_to(a); gemv_phase(p.quant, EPI_PUSH, a, false); }
             else { a.out_f = e->tp_partial; gemv_phase(p.quant, EPI_F32, a, true); }
         }
         {   // RMSNorm + gate/up + SwiGLU
             GemvArgs a = gv(e->x, p.dim);
+            take_x(a);
             a.norm_w = L.post_norm; a.eps = eps;
             a.w[0] = L.gate.w; a.w[1] = L.up.w; a.s[0] = L.gate.s; a.s[1] = L.up.s; a.rows = e->inter_l; a.out_h = e->gate;
             gemv_phase(p.quant, EPI_SWIGLU, a, false);
@@ -433,11 +464,13 @@ static void describe_step(cuqwen_engine* e, std::vector<HostPhase>& out, int nsp
             GemvArgs a = gv(e->gate, e->inter_l);
             a.w[0] = L.down.w; a.s[0] = L.down.s; a.rows = p.dim;
             if (e->tp == 1) { a.out_h = e->x; gemv_phase(p.quant, EPI_RESID, a, false); }
+            else if (peer) { push_to(a); gemv_phase(p.quant, EPI_PUSH, a, false); }
             else { a.out_f = e->tp_partial; gemv_phase(p.quant, EPI_F32, a, true); }
         }
     }
     {   // final RMSNorm + lm_head
         GemvArgs a = gv(e->x, p.dim);
+        take_x(a);
         a.norm_w = e->norm; a.eps = eps; a.w[0] = e->lm.w; a.s[0] = e->lm.s; a.rows = e->vocab_l; a.out_h = e->logits;
         gemv_phase(e->lm_quant, EPI_F16, a, false);
     }
@@ -487,7 +520,9 @@ static int record_step(cuqwen_engine* e, cudaStream_t s, bool pdl) {
     t_err = reinterpret_cast<unsigned*>(&e->ctl->pad[0]);
     int n = 0;
     const float pen = __half2float(__float2half(p.repetition_penalty));
-#define LK(call) do { int r_ = (call); if (r_) return fail(CUQWEN_ERR_CUDA, "%s: %s", #call, cudaGetErrorString((cudaError_t)r_)); ++n; } while (0)
+#define MARK() do { if (e->prof) { cudaEvent_t ev_; CK(cudaEventCreate(&ev_)); CK(cudaEventRecord(ev_, s)); e->prof->push_back(ev_); } } while (0)
+#define LK(call) do { int r_ = (call); if (r_) return fail(CUQWEN_ERR_CUDA, "%s: %s", #call, cudaGetErrorString((cudaError_t)r_)); ++n; MARK(); } while (0)
+    MARK();
     LK(launch_embed(e->embed, &e->ctl->token, e->x, p.dim, cfg_plain));
     if (e->fused) {
         CK(cudaMemsetAsync(e->step_bar, 0, 4, s));
@@ -499,7 +534,7 @@ static int record_step(cuqwen_engine* e, cudaStream_t s, bool pdl) {
             if (h.ph.kind == PH_ATTN) { LK(launch_attn(p.head_dim, h.ph.at, cfg)); continue; }
             LK(launch_gemv(h.ph.quant, h.ph.epi, h.ph.g, cfg));
             if (h.reduce) {
-                if (int r = tp_allreduce(e, e->tp_partial, p.dim, s)) return r; ++n;
+                if (int r = tp_allreduce(e, e->tp_partial, p.dim, s)) return r; ++n; MARK();
                 LK(launch_resid_sum(e->x, e->tp_partial, 1, 0, p.dim, cfg_plain));
             }
         }
@@ -509,10 +544,11 @@ static int record_step(cuqwen_engine* e, cudaStream_t s, bool pdl) {
         LK(launch_argmax(e->logits, e->vocab_l, 0, e->ctl, e->out_ring, e->ring_cap, e->d_hist, e->bitmap, e->best, e->ticket, nullptr, nullptr, cfg));
     } else {
         LK(launch_argmax(e->logits, e->vocab_l, e->plan.v0, e->ctl, e->out_ring, e->ring_cap, e->d_hist, e->bitmap, e->best, e->ticket, e->tp_keys + e->tp, nullptr, cfg));
-        NK(g_nccl.AllGather(e->tp_keys + e->tp, e->tp_keys, 1, ncclUint64, e->comm, s)); ++n;
+        NK(g_nccl.AllGather(e->tp_keys + e->tp, e->tp_keys, 1, ncclUint64, e->comm, s)); ++n; MARK();
         LK(launch_merge_keys(e->tp_keys, e->tp, e->ctl, e->out_ring, e->ring_cap, cfg_plain));
     }
 #undef LK
+#undef MARK
     e->launches = n;
     return CUQWEN_OK;
 }
@@ -546,11 +582,12 @@ extern "C" int cuqwen_step(cuqwen_engine* e, int token, int pos, const int* hist
         return fail(CUQWEN_ERR_ARG, "token %d / pos %d / history_len %d out of range", token, pos, history_len);
     CK(cudaSetDevice(e->p.device));
     if (int r = ensure_graph(e)) return r;
-    StepCtl c{}; c.token = token; c.pos = pos; c.hist_len = (history && history_len > 0) ? history_len : 0;
+    StepCtl c{}; c.token = token; c.pos = pos; c.hist_len = (history && history_len > 0) ? history_len : 0; c.pad[1] = e->steps_done;
     *e->h_ctl = c;
     CK(cudaMemcpyAsync(e->ctl, e->h_ctl, sizeof(StepCtl), cudaMemcpyHostToDevice, e->stream));
     if (c.hist_len) CK(cudaMemcpyAsync(e->d_hist, history, (size_t)c.hist_len * 4, cudaMemcpyHostToDevice, e->stream));
     if (int r = run_step(e)) return r;
+    e->steps_done += 1;
     CK(cudaMemcpyAsync(e->h_out, &e->ctl->sampled, 8, cudaMemcpyDeviceToHost, e->stream));   // sampled token + wait-expired word
     CK(cudaStreamSynchronize(e->stream));
     if (e->h_out[1]) return fail(CUQWEN_ERR_TIMEOUT, "a bounded device-side wait expired (code %d)", e->h_out[1]);
@@ -566,11 +603,12 @@ extern "C" int cuqwen_decode_n(cuqwen_engine* e, int first_token, int start_pos,
         return fail(CUQWEN_ERR_ARG, "decode_n arguments out of range");
     CK(cudaSetDevice(e->p.device));
     if (int r = ensure_graph(e)) return r;
-    StepCtl c{}; c.token = first_token; c.pos = start_pos; c.auto_advance = 1;
+    StepCtl c{}; c.token = first_token; c.pos = start_pos; c.auto_advance = 1; c.pad[1] = e->steps_done;
     *e->h_ctl = c;
     CK(cudaMemcpyAsync(e->ctl, e->h_ctl, sizeof(StepCtl), cudaMemcpyHostToDevice, e->stream));
     CK(cudaEventRecord(e->ev0, e->stream));
     for (int i = 0; i < n; ++i) if (int r = run_step(e)) return r;
+    e->steps_done += n;
     CK(cudaEventRecord(e->ev1, e->stream));
     CK(cudaMemcpyAsync(e->h_out, e->out_ring, (size_t)n * 4, cudaMemcpyDeviceToHost, e->stream));
     CK(cudaMemcpyAsync(e->h_out + n, &e->ctl->pad[0], 4, cudaMemcpyDeviceToHost, e->stream));
@@ -582,6 +620,31 @@ extern "C" int cuqwen_decode_n(cuqwen_engine* e, int first_token, int start_pos,
 }
 
 extern "C" float cuqwen_last_decode_ms(const cuqwen_engine* e) { return e ? e->last_ms : 0.f; }
+
+extern "C" int cuqwen_step_profile(cuqwen_engine* e, int token, int pos, float* us, int cap, int* n_out) {
+    if (!e || !us || cap < 1) return fail(CUQWEN_ERR_ARG, "null argument");
+    if (!e->loaded) return fail(CUQWEN_ERR_STATE, "cuqwen_step_profile before cuqwen_load");
+    if (e->tp > 1 && !e->comm) return fail(CUQWEN_ERR_STATE, "cuqwen_step_profile before cuqwen_tp_init");
+    if (token < 0 || token >= e->p.vocab_size || pos < 0 || pos >= e->p.max_seq_len) return fail(CUQWEN_ERR_ARG, "token / pos out of range");
+    CK(cudaSetDevice(e->p.device));
+    StepCtl c{}; c.token = token; c.pos = pos; c.pad[1] = e->steps_done;
+    *e->h_ctl = c;
+    CK(cudaMemcpyAsync(e->ctl, e->h_ctl, sizeof(StepCtl), cudaMemcpyHostToDevice, e->stream));
+    std::vector<cudaEvent_t> evs;
+    e->prof = &evs;
+    int r = record_step(e, e->stream, false);      // launch by launch, no graph, plain stream order
+    e->prof = nullptr;
+    e->steps_done += 1;
+    cudaError_t ce = cudaStreamSynchronize(e->stream);
+    int n = 0;
+    if (!r && ce == cudaSuccess)
+        for (size_t i = 1; i < evs.size() && n < cap; ++i, ++n) { float ms = 0.f; cudaEventElapsedTime(&ms, evs[i - 1], evs[i]); us[n] = ms * 1e3f; }
+    for (cudaEvent_t ev : evs) cudaEventDestroy(ev);
+    if (r) return r;
+    CK(ce);
+    if (n_out) *n_out = n;
+    return CUQWEN_OK;
+}
 
 extern "C" int cuqwen_kv_fill_normal(cuqwen_engine* e, int ctx_len, uint64_t seed) {
     if (!e || ctx_len < 0 || ctx_len > e->p.max_seq_len) return fail(CUQWEN_ERR_ARG, "ctx_len out of range");
@@ -615,6 +678,47 @@ extern "C" int cuqwen_tp_init(cuqwen_engine* e, const void* id_bytes, size_t n) 
     CK(cudaSetDevice(e->p.device));
     ncclUniqueId id; memcpy(&id, id_bytes, sizeof id);
     NK(g_nccl.CommInitRank(&e->comm, e->tp, id, e->rank));
+    if (e->p.flags & CUQWEN_FLAG_TP_NCCL) return CUQWEN_OK;          // keep the collective-call path (baseline)
+    // Receive block of this rank: [2 slots][tp][dim] words of {fp32 partial, sequence number}.  Every rank
+    // maps every other rank's block (CUDA IPC; the 64-byte handles travel through one NCCL all-gather), so that the
+    // row-parallel GEMVs can store their partial outputs straight into their consumers' memory.
+    if (e->tp > 8) return CUQWEN_OK;
+    const cuqwen_params& p = e->p;
+    e->tp_rx_bytes = (size_t)2 * e->tp * p.dim * 8;
+    CK(cudaMalloc((void**)&e->tp_rx, e->tp_rx_bytes));
+    CK(cudaMemset(e->tp_rx, 0, e->tp_rx_bytes));
+    CK(cudaMalloc((void**)&e->x2, (size_t)p.dim * 2)); CK(cudaMemset(e->x2, 0, (size_t)p.dim * 2));
+    cudaIpcMemHandle_t mine, all[8];
+    CK(cudaIpcGetMemHandle(&mine, e->tp_rx));
+    unsigned char* d_h = nullptr;
+    CK(cudaMalloc((void**)&d_h, sizeof(all)));
+    CK(cudaMemcpy(d_h + (size_t)e->rank * sizeof(mine), &mine, sizeof(mine), cudaMemcpyHostToDevice));
+    ncclResult_t nr = g_nccl.AllGather(d_h + (size_t)e->rank * sizeof(mine), d_h, sizeof(mine), ncclChar, e->comm, e->stream);
+    cudaError_t ce = cudaStreamSynchronize(e->stream);
+    if (nr == ncclSuccess && ce == cudaSuccess) ce = cudaMemcpy(all, d_h, sizeof(mine) * e->tp, cudaMemcpyDeviceToHost);
+    cudaFree(d_h);
+    if (nr != ncclSuccess) return fail(CUQWEN_ERR_NCCL, "all-gather of IPC handles: %s", g_nccl.GetErrorString(nr));
+    CK(ce);
+    bool ok = true;
+    for (int r = 0; r < e->tp && ok; ++r) {
+        if (r == e->rank) { e->peer_rx[r] = e->tp_rx; continue; }
+        void* ptr = nullptr;
+        if (cudaIpcOpenMemHandle(&ptr, all[r], cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) { cudaGetLastError(); ok = false; break; }
+        e->peer_rx[r] = (unsigned char*)ptr;
+    }
+    // all ranks must agree on the path: a rank that could not map a peer makes everybody fall back to the collective calls
+    int* d_ok = nullptr;
+    CK(cudaMalloc((void**)&d_ok, 8));
+    const int mine_ok = ok ? 1 : 0;
+    CK(cudaMemcpy(d_ok, &mine_ok, 4, cudaMemcpyHostToDevice));
+    nr = g_nccl.AllReduce(d_ok, d_ok + 1, 1, ncclInt32, ncclMin, e->comm, e->stream);
+    ce = cudaStreamSynchronize(e->stream);
+    int all_ok = 0;
+    if (nr == ncclSuccess && ce == cudaSuccess) ce = cudaMemcpy(&all_ok, d_ok + 1, 4, cudaMemcpyDeviceToHost);
+    cudaFree(d_ok);
+    if (nr != ncclSuccess) return fail(CUQWEN_ERR_NCCL, "all-reduce of the peer-mapping status: %s", g_nccl.GetErrorString(nr));
+    CK(ce);
+    e->tp_peer = all_ok == 1;
     return CUQWEN_OK;
 }
 

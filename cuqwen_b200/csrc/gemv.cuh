@@ -20,7 +20,7 @@
 
 namespace cq {
 
-enum Epi : int { EPI_F16 = 0, EPI_F32 = 1, EPI_RESID = 2, EPI_SWIGLU = 3, EPI_QKV = 4 };
+enum Epi : int { EPI_F16 = 0, EPI_F32 = 1, EPI_RESID = 2, EPI_SWIGLU = 3, EPI_QKV = 4, EPI_PUSH = 5 };
 
 struct alignas(64) GemvArgs {
     CUtensorMap tmap[3];      // one 2-D byte map per weight matrix: dims {row bytes, rows}, box {piece bytes, 16}
@@ -47,6 +47,20 @@ struct alignas(64) GemvArgs {
     int n_heads, n_kv, hd, max_seq;
     float theta;
     int rope_fast;
+    // Tensor-parallel exchange of a row-parallel matrix (o_proj, down): no collective call, no fence, no flag word.
+    // EPI_PUSH stores each fp32 partial output, paired with the exchange's sequence number in one 8-byte word, straight
+    // into every rank's receive slot over NVLink peer stores.  The kernel that consumes the vector next (always a GEMV
+    // with fused RMSNorm) reads the words until every one carries the expected sequence number and forms
+    // x_next = half(float(x) + sum_r partial_r) while it stages x ("gather").  An 8-byte store is single-copy atomic,
+    // so a word is either old (wrong number) or complete.  Reference: single-GPU only; the sum replaces
+    // src/kernels.cu:670-671 / :620-621 across ranks.
+    uint2* push[8];                // EPI_PUSH: start of this rank's slot inside rank d's receive buffer, {value bits, sequence}
+    int npush;
+    int ngather;                   // consumer: number of slots to add to x (0 = plain x)
+    const uint2* gather;           // this rank's receive slots, [ngather][K] words
+    __half* x_next;                // where CTA 0 stores the summed vector (never the buffer x points at)
+    const int* step_no;            // sequence number of an exchange = *step_no * 128 + seq_index + 1
+    int seq_index;
 };
 
 template <int EPI> struct EpiMT { static constexpr int MT = (EPI == EPI_SWIGLU || EPI == EPI_QKV) ? 2 : 1; };
@@ -136,6 +150,8 @@ __device__ __forceinline__ void epilogue_fetch(const GemvArgs& a, int row0, int 
         const int ra = row0 + r;
         pre[0] = __half2float(a.bias[mat][ra]);
         pre[1] = __half2float(a.bias[mat][ra + a.hd / 2]);
+    } else if (EPI == EPI_PUSH) {
+        pre[1] = __uint_as_float((unsigned)(*a.step_no) * 128u + (unsigned)a.seq_index + 1u);     // the exchange's sequence number, as bits
     }
 }
 
@@ -148,6 +164,13 @@ __device__ __forceinline__ void epilogue(const GemvArgs& a, int row0, int mat, i
     } else if (EPI == EPI_F32) {
         const int row = row0 + r;
         if (row < a.rows) a.out_f[row] = v0;
+    } else if (EPI == EPI_PUSH) {
+        const int row = row0 + r;
+        if (row < a.rows) {
+            const unsigned vb = __float_as_uint(v0), seq = __float_as_uint(pre[1]);
+            for (int d = 0; d < a.npush; ++d)                            // peer stores (one of them local), value and number together
+                asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(a.push[d] + row), "r"(vb), "r"(seq) : "memory");
+        }
     } else if (EPI == EPI_RESID) {
         // reference src/kernels.cu:670-671 and :620-621
         const int row = row0 + r;

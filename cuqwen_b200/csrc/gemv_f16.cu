@@ -26,6 +26,7 @@ int launch_gemv_f16(int epi, const GemvArgs& a, dim3 grid, dim3 block, size_t sm
         case EPI_RESID: return go<EPI_RESID>(a, grid, block, smem, cfg);
         case EPI_SWIGLU: return go<EPI_SWIGLU>(a, grid, block, smem, cfg);
         case EPI_QKV: return go<EPI_QKV>(a, grid, block, smem, cfg);
+        case EPI_PUSH: return go<EPI_PUSH>(a, grid, block, smem, cfg);
     }
     return (int)cudaErrorInvalidValue;
 }

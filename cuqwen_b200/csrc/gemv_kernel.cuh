@@ -129,7 +129,9 @@ __device__ __forceinline__ void gemv_consume(const GemvArgs& a, RingCtx& R, int 
     float* xscale = reinterpret_cast<float*>(R.base + R.off_xscale);
     float* red = reinterpret_cast<float*>(R.base + R.off_red);
 
-    stage_x<Q>(a.x, a.norm_w, a.eps, a.K, R.base, R.off_corr, corr, xscale, red, NC);
+    GatherSrc gs{a.gather, a.ngather, 0u, a.x_next, cta == 0, R.err};
+    if (a.ngather > 0) gs.seq = (unsigned)(*a.step_no) * 128u + (unsigned)a.seq_index + 1u;     // tensor parallel: x plus the partials the ranks pushed
+    stage_x<Q>(a.x, a.norm_w, a.eps, a.K, R.base, R.off_corr, corr, xscale, red, NC, a.ngather > 0 ? &gs : nullptr);
     if (R.stamp && threadIdx.x == 0) *R.stamp = global_ns();
 
     for (int j = 0; j < n_b; ++j) {

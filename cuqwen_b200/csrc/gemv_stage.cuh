@@ -76,6 +76,78 @@ __device__ __forceinline__ float park_raw(const __half* x, const __half* norm_w,
     return ss;
 }
 
+// Tensor-parallel consumer side of an exchange (see GemvArgs): what park_raw does, for x_new = half(float(x) + sum over
+// ranks of the fp32 partials in this rank's receive slots), summed in rank order so every rank forms the same bits.
+// A slot word is {value bits, sequence number}; a word whose number is not `seq` yet has not arrived and is read again
+// (bounded: after about two seconds *err is set and the stale value is used).
+// store_next: this CTA also writes x_new to global memory for the kernels after this one.
+struct GatherSrc {
+    const uint2* slots;      // [n][K] words
+    int n;
+    unsigned seq;
+    __half* x_next;          // written when store_next
+    bool store_next;
+    unsigned* err;
+};
+__device__ __forceinline__ uint4 ld_volatile16(const void* p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+template <bool PARKW>
+__device__ __forceinline__ float park_gather(const __half* x, const __half* norm_w, const GatherSrc& gs, int K, int nchunk, uint4* raw, uint4* wraw, int nthreads) {
+    constexpr int RB = 2;                                  // source ranks whose loads are in flight together
+    float ss = 0.f;
+    bool gave_up = false;
+    for (int c8 = threadIdx.x; c8 < nchunk; c8 += nthreads) {
+        const uint4 xo = __ldcg(reinterpret_cast<const uint4*>(x) + c8);
+        uint4 wv = make_uint4(0u, 0u, 0u, 0u);
+        if (PARKW) wv = __ldg(reinterpret_cast<const uint4*>(norm_w) + c8);
+        float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int r0 = 0; r0 < gs.n; r0 += RB) {
+            uint4 q[RB][4];
+            unsigned long long t0 = 0ull;
+            for (;;) {
+                bool ok = true;
+#pragma unroll
+                for (int j = 0; j < RB; ++j)
+                    if (r0 + j < gs.n) {
+                        const uint4* p = reinterpret_cast<const uint4*>(gs.slots + (size_t)(r0 + j) * K + (size_t)c8 * 8);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) q[j][i] = ld_volatile16(p + i);
+                    }
+#pragma unroll
+                for (int j = 0; j < RB; ++j)
+                    if (r0 + j < gs.n) {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) ok = ok && q[j][i].y == gs.seq && q[j][i].w == gs.seq;
+                    }
+                if (ok || gave_up) break;
+                if (t0 == 0ull) t0 = global_ns();
+                else if (global_ns() - t0 > 2000000000ull) { gave_up = true; if (gs.err) atomicExch(gs.err, 8u); break; }
+            }
+#pragma unroll
+            for (int j = 0; j < RB; ++j)
+                if (r0 + j < gs.n) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) { s[2 * i] += __uint_as_float(q[j][i].x); s[2 * i + 1] += __uint_as_float(q[j][i].z); }
+                }
+        }
+        uint4 xn;
+        {
+            const __half2* h = reinterpret_cast<const __half2*>(&xo);
+            __half2* o = reinterpret_cast<__half2*>(&xn);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) { const float2 f = __half22float2(h[k]); o[k] = __floats2half2_rn(f.x + s[2 * k], f.y + s[2 * k + 1]); }
+        }
+        raw[c8] = xn;
+        if (PARKW) wraw[c8] = wv;
+        if (gs.store_next) reinterpret_cast<uint4*>(gs.x_next)[c8] = xn;
+        ss += chunk_sumsq(xn);
+    }
+    return ss;
+}
+
 // Quantised weights: per 128-column group, integers X = rint(x * 2^e) with |X| < 2^14, as two signed byte digits in
 // the order the B operand wants (see mma_group_int), plus per group  corr = 8 * sum(X)  (int4 only, else 0) and
 // xscale = 2^-e.  Digit block of a group: [half jj (2)][t (4)][plane (2)][16 bytes]; the 16 bytes are two 8-byte
@@ -141,14 +213,16 @@ __device__ __forceinline__ void digits_of_chunk(uint4 v, int c8, bool live, unsi
 // is re-read from global memory during the conversion).
 template <int Q>
 __device__ __forceinline__ void stage_x(const __half* x, const __half* norm_w, float eps, int K, unsigned char* xd, int xarea_bytes, int* corr, float* xscale,
-                                        float* red, int nthreads) {
+                                        float* red, int nthreads, const GatherSrc* gs = nullptr) {
     const int nchunk = K / 8, lane = threadIdx.x & 31;
     uint4* raw = reinterpret_cast<uint4*>(xd);
     uint4* wraw = raw + nchunk;
     const bool w_parked = norm_w && 4 * K <= xarea_bytes;
     float inv = 0.f;
     if (norm_w) {
-        const float ss = w_parked ? park_raw<4, true, true>(x, norm_w, nchunk, raw, wraw, nthreads) : park_raw<4, true, false>(x, norm_w, nchunk, raw, wraw, nthreads);
+        float ss;
+        if (gs && gs->n > 0) ss = w_parked ? park_gather<true>(x, norm_w, *gs, K, nchunk, raw, wraw, nthreads) : park_gather<false>(x, norm_w, *gs, K, nchunk, raw, wraw, nthreads);
+        else ss = w_parked ? park_raw<4, true, true>(x, norm_w, nchunk, raw, wraw, nthreads) : park_raw<4, true, false>(x, norm_w, nchunk, raw, wraw, nthreads);
         inv = consumers_rsqrt_mean(ss, K, eps, red, nthreads);
     } else {
         park_raw<5, false, false>(x, nullptr, nchunk, raw, nullptr, nthreads);

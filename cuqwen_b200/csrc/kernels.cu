@@ -118,6 +118,7 @@ __device__ __forceinline__ unsigned long long argmax_pack(float v, int idx) {
 }
 __device__ __forceinline__ void finish_step(StepCtl* ctl, int token, int* out_ring, int ring_cap) {
     ctl->sampled = token;
+    ctl->pad[1] += 1;                  // steps completed: sequence numbers of the tensor-parallel exchanges derive from it
     if (ctl->auto_advance) {
         ctl->token = token;
         ctl->pos += 1;

@@ -44,7 +44,8 @@ enum {
     CUQWEN_FLAG_NO_GRAPH = 4,       /* launch the step kernel by kernel instead of replaying a CUDA graph */
     CUQWEN_FLAG_FUSED_STEP = 8,     /* experimental: all matrices and the attention of a step in one persistent kernel (grid barriers between
                                      * phases) instead of one launch each; single GPU only */
-    CUQWEN_FLAG_STEP_TRACE = 16     /* the step kernel stamps phase entry / exit times per CTA (CUQWEN_PTR_STEP_TRACE) */
+    CUQWEN_FLAG_STEP_TRACE = 16,    /* the step kernel stamps phase entry / exit times per CTA (CUQWEN_PTR_STEP_TRACE) */
+    CUQWEN_FLAG_TP_NCCL = 32        /* tensor parallel: sum the row-parallel partials with NCCL all-reduce calls instead of peer stores */
 };
 
 /* Mirrors QwenConfig (include/config.h:52-127) as run-time data. */
@@ -113,6 +114,11 @@ int cuqwen_get_params(const cuqwen_engine* e, cuqwen_params* out);
 uint64_t cuqwen_step_bytes(const cuqwen_engine* e, int ctx);
 /* Kernel launches in one decode step. */
 int cuqwen_step_launches(const cuqwen_engine* e);
+/* Tracing aid (no counterpart in the reference, whose benchmark/kernel_profile.cu times kernels in isolation): run ONE
+ * step launch by launch with a CUDA event after every launch and return the microseconds between consecutive events,
+ * in launch order (embedding, then per layer qkv / attention / o_proj / gate-up / down, lm_head, penalty, sampler;
+ * tensor-parallel runs add their exchange launches).  Times include launch gaps.  Every rank must call it together. */
+int cuqwen_step_profile(cuqwen_engine* e, int token, int pos, float* us, int cap, int* n_out);
 
 /* ---- raw device memory helpers (so a host language needs no CUDA binding of its own) ---- */
 int cuqwen_dev_alloc(int device, size_t bytes, void** dev_ptr);
