@@ -164,7 +164,7 @@ struct cuqwen_engine {
     float* tp_partial = nullptr; unsigned long long* tp_keys = nullptr;
     // peer exchange (tensor parallel without collective calls): one receive block per rank, mapped into every peer
     unsigned char* tp_rx = nullptr; size_t tp_rx_bytes = 0; unsigned char* peer_rx[8] = {}; bool tp_peer = false;
-    __half* x2 = nullptr;
+    __half* x2 = nullptr; bool tp_sum_separate = false;
     int steps_done = 0;                          // mirrors the device-side step counter (StepCtl::pad[1])
     std::vector<cudaEvent_t>* prof = nullptr;    // cuqwen_step_profile: an event is recorded after every launch of the step
     // persistent step kernel (single GPU): phase table on the device, its shared-memory map, the grid barrier word
@@ -389,7 +389,11 @@ static int tp_allreduce(cuqwen_engine* e, float* buf, int n, cudaStream_t s) {
 
 // The matrix and attention work of one step, in order.  `reduce`: a row-parallel matrix whose fp32 partial must be
 // summed over the tensor-parallel ranks and added to the residual stream afterwards.
-struct HostPhase { StepPhase ph; bool reduce; };
+struct HostPhase {
+    StepPhase ph; bool reduce;
+    // peer exchange with many ranks: after this (pushing) matrix a small kernel sums the slots once into sum_dst
+    bool sum_after; const __half* sum_src; __half* sum_dst; const void* sum_slots; int sum_seq;
+};
 
 static void describe_step(cuqwen_engine* e, std::vector<HostPhase>& out, int nsplit, bool with_fold) {
     const cuqwen_params& p = e->p;
@@ -407,7 +411,7 @@ static void describe_step(cuqwen_engine* e, std::vector<HostPhase>& out, int nsp
     int pending = -1, next_xi = 0;
     auto take_x = [&](GemvArgs& a) {                                        // a normed GEMV reads the residual stream
         a.x = cur;
-        if (peer && pending >= 0) {
+        if (peer && pending >= 0 && !e->tp_sum_separate) {
             const int slot = pending & 1;
             __half* other = cur == e->x ? e->x2 : e->x;
             a.ngather = e->tp; a.gather = reinterpret_cast<const uint2*>(e->tp_rx) + (size_t)slot * e->tp * p.dim;
@@ -420,6 +424,14 @@ static void describe_step(cuqwen_engine* e, std::vector<HostPhase>& out, int nsp
         a.npush = e->tp; a.step_no = &e->ctl->pad[1]; a.seq_index = next_xi;
         for (int d = 0; d < e->tp; ++d) a.push[d] = reinterpret_cast<uint2*>(e->peer_rx[d]) + ((size_t)slot * e->tp + e->rank) * p.dim;
         pending = next_xi++;
+    };
+    auto sum_after_push = [&]() {                                           // many ranks: one kernel sums the slots, the next GEMV reads x plainly
+        if (!(peer && e->tp_sum_separate)) return;
+        HostPhase& h = out.back();
+        __half* other = cur == e->x ? e->x2 : e->x;
+        h.sum_after = true; h.sum_src = cur; h.sum_dst = other; h.sum_seq = pending;
+        h.sum_slots = reinterpret_cast<const uint2*>(e->tp_rx) + (size_t)(pending & 1) * e->tp * p.dim;
+        cur = other; pending = -1;
     };
     for (int l = 0; l < p.n_layers; ++l) {
         const Layer& L = e->layers[l];
@@ -450,7 +462,7 @@ static void describe_step(cuqwen_engine* e, std::vector<HostPhase>& out, int nsp
             GemvArgs a = gv(e->att, e->q_dim_l);
             a.w[0] = L.o.w; a.s[0] = L.o.s; a.rows = p.dim;
             if (e->tp == 1) { a.out_h = e->x; gemv_phase(p.quant, EPI_RESID, a, false); }
-            else if (peer) { push_to(a); gemv_phase(p.quant, EPI_PUSH, a, false); }
+            else if (peer) { push_to(a); gemv_phase(p.quant, EPI_PUSH, a, false); sum_after_push(); }
             else { a.out_f = e->tp_partial; gemv_phase(p.quant, EPI_F32, a, true); }
         }
         {   // RMSNorm + gate/up + SwiGLU
@@ -464,7 +476,7 @@ static void describe_step(cuqwen_engine* e, std::vector<HostPhase>& out, int nsp
             GemvArgs a = gv(e->gate, e->inter_l);
             a.w[0] = L.down.w; a.s[0] = L.down.s; a.rows = p.dim;
             if (e->tp == 1) { a.out_h = e->x; gemv_phase(p.quant, EPI_RESID, a, false); }
-            else if (peer) { push_to(a); gemv_phase(p.quant, EPI_PUSH, a, false); }
+            else if (peer) { push_to(a); gemv_phase(p.quant, EPI_PUSH, a, false); sum_after_push(); }
             else { a.out_f = e->tp_partial; gemv_phase(p.quant, EPI_F32, a, true); }
         }
     }
@@ -533,6 +545,7 @@ static int record_step(cuqwen_engine* e, cudaStream_t s, bool pdl) {
         for (HostPhase& h : hp) {
             if (h.ph.kind == PH_ATTN) { LK(launch_attn(p.head_dim, h.ph.at, cfg)); continue; }
             LK(launch_gemv(h.ph.quant, h.ph.epi, h.ph.g, cfg));
+            if (h.sum_after) LK(launch_tp_sum(h.sum_src, h.sum_dst, h.sum_slots, e->tp, p.dim, &e->ctl->pad[1], h.sum_seq, t_err, cfg_plain));
             if (h.reduce) {
                 if (int r = tp_allreduce(e, e->tp_partial, p.dim, s)) return r; ++n; MARK();
                 LK(launch_resid_sum(e->x, e->tp_partial, 1, 0, p.dim, cfg_plain));
@@ -719,6 +732,8 @@ extern "C" int cuqwen_tp_init(cuqwen_engine* e, const void* id_bytes, size_t n) 
     if (nr != ncclSuccess) return fail(CUQWEN_ERR_NCCL, "all-reduce of the peer-mapping status: %s", g_nccl.GetErrorString(nr));
     CK(ce);
     e->tp_peer = all_ok == 1;
+    e->tp_sum_separate = true;                      // the slots are summed once by a small kernel; 0 = every CTA of the next GEMV sums them while staging x (measured slower)
+    if (const char* v = getenv("CUQWEN_TP_SUM_KERNEL")) e->tp_sum_separate = atoi(v) != 0;       // development aid
     return CUQWEN_OK;
 }
 

@@ -4,6 +4,7 @@
 #include "attn.cuh"
 #include "gemv.cuh"
 #include "gemv_math.cuh"
+#include "gemv_stage.cuh"
 #include "launch.h"
 #include "rng.cuh"
 
@@ -178,6 +179,57 @@ __global__ void merge_keys_kernel(const unsigned long long* __restrict__ keys, i
 }
 int launch_merge_keys(const unsigned long long* keys, int n, StepCtl* ctl, int* out_ring, int ring_cap, const LaunchCfg& cfg) {
     return launch_k(merge_keys_kernel, dim3(1), dim3(32), 0, cfg, keys, n, ctl, out_ring, ring_cap);
+}
+
+// ---- tensor-parallel residual from pushed slots: x_next = half(float(x) + sum_r slot_r), one thread per 8 columns ----
+// Used instead of the gather inside the consuming GEMV when there are many ranks: there every CTA would read all
+// ranks' slots again; here they are read once.  Same words, same bounded re-read, same rank order as park_gather.
+__global__ void tp_sum_kernel(const __half* __restrict__ x, __half* __restrict__ x_next, const uint2* slots, int n, int K, const int* step_no, int seq_index, unsigned* err) {
+    pdl_launch_dependents(); pdl_wait();
+    const int c8 = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c8 >= K / 8) return;
+    const unsigned seq = (unsigned)(*step_no) * 128u + (unsigned)seq_index + 1u;
+    const uint4 xo = __ldcg(reinterpret_cast<const uint4*>(x) + c8);
+    float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    bool gave_up = false;
+    for (int r0 = 0; r0 < n; r0 += 4) {
+        uint4 q[4][4];
+        unsigned long long t0 = 0ull;
+        for (;;) {
+            bool ok = true;
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (r0 + j < n) {
+                    const uint4* p = reinterpret_cast<const uint4*>(slots + (size_t)(r0 + j) * K + (size_t)c8 * 8);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) q[j][i] = ld_volatile16(p + i);
+                }
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (r0 + j < n) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) ok = ok && q[j][i].y == seq && q[j][i].w == seq;
+                }
+            if (ok || gave_up) break;
+            if (t0 == 0ull) t0 = global_ns();
+            else if (global_ns() - t0 > 2000000000ull) { gave_up = true; if (err) atomicExch(err, 8u); break; }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            if (r0 + j < n) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) { s[2 * i] += __uint_as_float(q[j][i].x); s[2 * i + 1] += __uint_as_float(q[j][i].z); }
+            }
+    }
+    uint4 xn;
+    const __half2* h = reinterpret_cast<const __half2*>(&xo);
+    __half2* o = reinterpret_cast<__half2*>(&xn);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) { const float2 f = __half22float2(h[k]); o[k] = __floats2half2_rn(f.x + s[2 * k], f.y + s[2 * k + 1]); }
+    reinterpret_cast<uint4*>(x_next)[c8] = xn;
+}
+int launch_tp_sum(const __half* x, __half* x_next, const void* slots, int n, int K, const int* step_no, int seq_index, unsigned* err, const LaunchCfg& cfg) {
+    return launch_k(tp_sum_kernel, dim3((K / 8 + 31) / 32), dim3(32), 0, cfg, x, x_next, (const uint2*)slots, n, K, step_no, seq_index, err);
 }
 
 // ---- tensor-parallel residual: x = half(float(x) + sum_r partial_r) --------

@@ -68,6 +68,8 @@ int launch_argmax(const __half* logits, int vocab, int vocab_base, StepCtl* ctl,
 int launch_merge_keys(const unsigned long long* keys, int n, StepCtl* ctl, int* out_ring, int ring_cap, const LaunchCfg& cfg);
 // x = half(float(x) + sum_r partial[r][:])   (row-parallel layers under tensor parallelism)
 int launch_resid_sum(__half* x, const float* partial, int n_parts, size_t part_stride, int dim, const LaunchCfg& cfg);
+// Tensor parallel, many ranks: x_next = half(float(x) + sum over n ranks of the pushed {value, sequence} slots [n][K]).
+int launch_tp_sum(const __half* x, __half* x_next, const void* slots, int n, int K, const int* step_no, int seq_index, unsigned* err, const LaunchCfg& cfg);
 // out = half(float(q) * float(scale)) for every weight; quant 1 or 2.
 int launch_dequant(int quant, const void* w, const __half* s, __half* out, long rows, long cols, const LaunchCfg& cfg);
 // Deterministic N(0,1) fp16 fill: element i gets a value that depends only on (seed, base + i).

@@ -26,14 +26,15 @@ def gpu_count() -> int:
         return 0
 
 
-@pytest.mark.parametrize("flags", [0, E.FLAG_TP_NCCL], ids=["peer_stores", "nccl_allreduce"])
+@pytest.mark.parametrize("flags,sum_kernel", [(0, 0), (0, 1), (E.FLAG_TP_NCCL, 0)], ids=["peer_stores", "peer_stores_sum_kernel", "nccl_allreduce"])
 @pytest.mark.parametrize("quant", [2, 0])
-def test_two_ranks_match_one_gpu(built, tmp_path, quant, flags):
+def test_two_ranks_match_one_gpu(built, tmp_path, monkeypatch, quant, flags, sum_kernel):
     if gpu_count() < 2:
         pytest.skip("needs two GPUs")
     path = tmp_path / "m.bin"
     binfmt.write_model(path, CFG, quant, binfmt.random_tensors(CFG, 4))
     (tmp_path / "cfg.json").write_text(json.dumps(CFG))
+    monkeypatch.setenv("CUQWEN_TP_SUM_KERNEL", str(sum_kernel))      # 1: the many-rank variant (slots summed once by a small kernel)
     worker = Path(__file__).with_name("tp_worker.py")
     procs = [subprocess.Popen([sys.executable, str(worker), str(r), "2", str(tmp_path), str(path), str(quant), str(flags)],
                               stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(2)]
@@ -51,7 +52,7 @@ def test_two_ranks_match_one_gpu(built, tmp_path, quant, flags):
 
     r0, r1 = np.load(tmp_path / "rank0.npz"), np.load(tmp_path / "rank1.npz")
     assert r0["toks"].tolist() == r1["toks"].tolist()                       # every rank learns the same token
-    per_layer = 5 if flags == 0 else 9                                        # the NCCL path adds an all-reduce and a residual kernel twice per layer
+    per_layer = 9 if flags else 7 if sum_kernel else 5                        # NCCL: + all-reduce and residual kernel twice per layer; sum kernel: + 2
     assert int(r0["launches"]) == 1 + per_layer * CFG["layers"] + 3 + 2       # ... + key all-gather and merge
     got = np.concatenate([r0["logits"], r1["logits"]])
     assert close(got, want), report(got, want)
