@@ -1,0 +1,26 @@
+// Compile-and-link probe for include/cuqwen_compat.hpp: a program shaped like the reference's own main loop
+// (load_weights -> malloc_qwen_state -> qwen_forward -> free_*) and a few launch_* calls must build unchanged.
+// With no argument it only checks static facts and exits; given a model file it would run on a GPU.
+#include "cuqwen_compat.hpp"
+
+static_assert(QwenConfig::magic == 0x5157454E, "magic");
+static_assert(QwenConfig::dim % QUANT_GROUP_SIZE == 0, "dim");
+
+int main(int argc, char** argv) {
+    printf("%s %s %s dim=%d layers=%d quant=%d stride=%d\n", QwenConfig::model_name, MODEL_TAG, QwenConfig::bin_path, QwenConfig::dim, QwenConfig::n_layers,
+           QwenConfig::quant_type, (int)WEIGHT_ROW_STRIDE(QwenConfig::dim));
+    if (argc < 2) return 0;
+    QwenWeights weights;
+    QwenConfig config = load_weights(argv[1], weights);
+    QwenState state;
+    malloc_qwen_state(config, state);
+    int tok = 1;
+    for (int pos = 0; pos < 4; ++pos) tok = qwen_forward(tok, pos, config, state, weights);
+    launch_rmsnorm(state.x, weights.norm_weight, state.att, config.dim, __float2half(config.norm_eps));
+    launch_gemv_add_fp16(weights.layers[0].o_proj_weight, weights.layers[0].o_proj_scale, state.xb, state.x, config.dim, config.n_heads * config.head_dim);
+    launch_argmax(state.logits, nullptr, config.vocab_size);
+    printf("%d\n", tok);
+    free_qwen_state(state);
+    free_weights(weights, config);
+    return 0;
+}

@@ -1,0 +1,49 @@
+"""include/cuqwen_compat.hpp: a program written against CuQwen's C++ host API builds against the shim unchanged
+(CPU check: compile, link, static facts) and produces the engine's own tokens when run on a GPU."""
+import subprocess
+from pathlib import Path
+
+import pytest
+
+from cuqwen_b200 import build
+from cuqwen_b200 import engine as E
+
+ROOT = Path(__file__).resolve().parent.parent
+PROBE = ROOT / "tests" / "compat_probe.cpp"
+
+
+def compile_probe(out: Path, model: str, quant: str) -> Path:
+    exe = out / f"probe_{model}_{quant}"
+    cmd = ["g++", "-std=c++17", f"-DQWEN_MODEL_{model}", f"-DQUANT_{quant}", f"-I{ROOT / 'include'}", "-I/usr/local/cuda/include", str(PROBE), "-o", str(exe),
+           f"-L{ROOT / 'cuqwen_b200'}", "-lcuqwen_b200", "-L/usr/local/cuda/lib64", "-lcudart", f"-Wl,-rpath,{ROOT / 'cuqwen_b200'}"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    return exe
+
+
+@pytest.mark.parametrize("model,quant,want", [
+    ("0_5B", "INT4", "0.5B 0_5b weights/model_int4_0_5b.bin dim=896 layers=24 quant=2 stride=448"),
+    ("7B", "INT8", "7B 7b weights/model_int8_7b.bin dim=3584 layers=28 quant=1 stride=3584"),
+    ("14B", "FP16", "14B 14b weights/model_fp16_14b.bin dim=5120 layers=48 quant=0 stride=5120"),
+])
+def test_reference_style_program_builds_against_the_shim(built, tmp_path, model, quant, want):
+    exe = compile_probe(tmp_path, model, quant)
+    r = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert r.returncode == 0 and r.stdout.strip() == want
+
+
+@pytest.mark.gpu
+def test_reference_style_program_runs(built, tmpdir_big):
+    path = tmpdir_big / "m05_int4_compat.bin"
+    subprocess.run([str(build.GEN_BIN), "--out", str(path), "--model", "0.5b", "--quant", "int4", "--seed", "7"], check=True)
+    exe = compile_probe(tmpdir_big, "0_5B", "INT4")
+    r = subprocess.run([str(exe), str(path)], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    eng = E.Engine(E.model_params("0.5b", 2))
+    eng.load(str(path))
+    tok = 1
+    for pos in range(4):
+        tok = eng.step(tok, pos)
+    eng.close()
+    path.unlink()
+    assert int(r.stdout.strip().splitlines()[-1]) == tok
