@@ -38,6 +38,7 @@ struct AttnArgs {
     float* part_ml;
     unsigned* counters;
     unsigned* err;          // receives a non-zero code when a bounded wait expires (may be null)
+    int stages;             // two-launch variant: ring depth (0 = its default)
 };
 
 inline size_t attn_smem_bytes(int hd) { return (size_t)kAttnStages * 2 * kAttnStageKeys * hd * 2 + 128; }

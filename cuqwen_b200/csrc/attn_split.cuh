@@ -1,0 +1,154 @@
+// Split-KV decode attention as two launches: attn_partial_kernel (grid n_kv x nsplit) streams a contiguous key range
+// per CTA and writes an un-normalised partial (O, m, l) per query head; attn_fold_kernel (one CTA per query head)
+// merges the non-empty partials of its head and writes fp16.  Reference stages: src/kernels.cu:105-219 and :222-288.
+//
+// Compared with the single-launch variant in attn.cuh (partials merged by a ticket tree inside the same kernel) this
+// trades one small extra launch - started early through programmatic dependent launch, so it is already resident when
+// the partials land - for two fence + atomic + reload round trips on the critical path of the last CTAs, and it puts
+// eight consumer warps on the key stream instead of four (warps 0-3 take the even stages, warps 4-7 the odd ones).
+#pragma once
+#include "attn.cuh"
+
+namespace cq {
+
+constexpr int kSplitWarps = 8;                                  // consumer warps of the partial kernel
+constexpr int kSplitThreads = (kSplitWarps + 1) * 32;
+constexpr int kSplitStages = 4;
+constexpr int kFoldWarps = 16;
+
+inline size_t attn_split_smem_bytes(int hd, int stages) { return (size_t)stages * 2 * kAttnStageKeys * hd * 2 + 128; }
+
+template <int HD>
+__global__ void __launch_bounds__(kSplitThreads) attn_partial_kernel(const AttnArgs a) {
+    constexpr int NCH = HD / 32, ROWB = HD * 2, HALF = kAttnStageKeys * ROWB, NCT = kSplitWarps * 32;
+    extern __shared__ __align__(128) unsigned char dyn[];
+    __shared__ float sm_o[kSplitWarps][kMaxGroup][HD];
+    __shared__ float sm_ml[kSplitWarps][kMaxGroup][2];
+    __shared__ __align__(8) unsigned long long sm_bar[2 * kSplitStages];
+
+    pdl_launch_dependents();
+    const int kvh = blockIdx.x, split = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int nst = a.stages >= 2 && a.stages <= kSplitStages ? a.stages : kSplitStages;      // ring depth of this launch
+    const uint32_t stage0 = smem_u32(dyn), bar_full = smem_u32(sm_bar), bar_empty = bar_full + kSplitStages * 8;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < nst; ++s) { mbar_init(bar_full + s * 8, 1); mbar_init(bar_empty + s * 8, kSplitWarps); }
+        mbar_fence_init();
+    }
+    __syncthreads();
+    pdl_wait();                 // K/V row `pos` and q come from the previous kernel
+
+    const int len = *a.d_pos + 1;
+    int chunk = (len + a.nsplit - 1) / a.nsplit;
+    chunk = (chunk + 15) & ~15;
+    const int t0 = split * chunk;
+    const int t1 = min(t0 + chunk, len);
+    if (t0 >= len) return;                                       // an empty split publishes nothing; the fold skips it
+    const int nstage = (t1 - t0 + kAttnStageKeys - 1) / kAttnStageKeys;
+
+    if (warp == kSplitWarps) {
+        if (lane == 0) {
+            const unsigned char* kb = reinterpret_cast<const unsigned char*>(a.kc) + ((size_t)kvh * a.max_seq + t0) * ROWB;
+            const unsigned char* vb = reinterpret_cast<const unsigned char*>(a.vc) + ((size_t)kvh * a.max_seq + t0) * ROWB;
+            bool failed = false;
+            for (int sn = 0; sn < nstage; ++sn) {
+                const int s = sn % nst;
+                if (!failed && !mbar_wait(bar_empty + s * 8, ((sn / nst) & 1) ^ 1)) { failed = true; if (a.err) atomicExch(a.err, 5u); }
+                const int n = min(kAttnStageKeys, t1 - t0 - sn * kAttnStageKeys);
+                const uint32_t bytes = (uint32_t)n * ROWB;
+                mbar_expect_tx(bar_full + s * 8, 2 * bytes);
+                bulk_g2s(stage0 + s * 2 * HALF, kb + (size_t)sn * HALF, bytes, bar_full + s * 8);
+                bulk_g2s(stage0 + s * 2 * HALF + HALF, vb + (size_t)sn * HALF, bytes, bar_full + s * 8);
+            }
+        }
+        return;
+    }
+    const int half_id = warp >> 2, wq = warp & 3;
+    uint32_t qa[NCH][4];
+    attn_load_q<HD>(qa, a.q + (size_t)kvh * a.grp * HD, a.grp, g, t);
+    AttnState<HD> st;
+    st.reset();
+    bool failed = false;
+    for (int sn = 0; sn < nstage; ++sn) {
+        const int s = sn % nst;
+        if (!failed && !mbar_wait(bar_full + s * 8, (sn / nst) & 1)) { failed = true; if (a.err) atomicExch(a.err, 6u); }
+        const int kb = t0 + sn * kAttnStageKeys + 16 * wq;       // first key of this warp's tile
+        if ((sn & 1) == half_id && kb < t1) {
+            const unsigned char* sK = dyn + s * 2 * HALF + 16 * wq * ROWB;
+            attn_tile<HD, false>(st, qa, sK, sK + HALF, t1 - kb, a.scale_log2, g, t);
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_empty + s * 8);
+    }
+    attn_state_to_smem<HD>(st, &sm_o[warp][0][0], &sm_ml[warp][0][0], g, t);
+    asm volatile("bar.sync 1, %0;" ::"r"(NCT) : "memory");
+    float* po = a.part_o + ((size_t)(kvh * a.nsplit + split) * kMaxGroup) * HD;
+    float* pml = a.part_ml + ((size_t)(kvh * a.nsplit + split) * kMaxGroup) * 2;
+    attn_merge_warps<HD>(&sm_o[0][0][0], &sm_ml[0][0][0], kSplitWarps, a.grp, po, pml, threadIdx.x, NCT);
+}
+
+// One CTA per query head; warp w takes splits w, w + 16, ...; lane = 4-float column of the head.
+template <int HD>
+__global__ void __launch_bounds__(kFoldWarps * 32) attn_fold_kernel(const AttnArgs a) {
+    constexpr int NCOL = HD / 4;
+    __shared__ float4 o_w[kFoldWarps][NCOL];
+    __shared__ float ml_w[kFoldWarps][2];
+    pdl_launch_dependents();
+    pdl_wait();                 // the partials come from the kernel before this one
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int head = blockIdx.x, kvh = head / a.grp, h = head - kvh * a.grp;
+    const int len = *a.d_pos + 1;
+    int chunk = (len + a.nsplit - 1) / a.nsplit;
+    chunk = (chunk + 15) & ~15;
+    const int nne = (len + chunk - 1) / chunk;                   // non-empty splits: 0 .. nne-1
+    float M = -INFINITY, L = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    constexpr int NB = 4;                                        // splits in flight per warp
+    for (int s0 = warp; s0 < nne; s0 += kFoldWarps * NB) {
+        float mm[NB], ll[NB];
+        float4 vv[NB];
+#pragma unroll
+        for (int i = 0; i < NB; ++i) {
+            const int s = s0 + i * kFoldWarps;
+            mm[i] = -INFINITY; ll[i] = 0.f; vv[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (s < nne) {
+                const size_t slot = (size_t)(kvh * a.nsplit + s) * kMaxGroup + h;
+                mm[i] = __ldcg(a.part_ml + slot * 2); ll[i] = __ldcg(a.part_ml + slot * 2 + 1);
+                if (lane < NCOL) vv[i] = __ldcg(reinterpret_cast<const float4*>(a.part_o + slot * HD) + lane);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < NB; ++i) {
+            const float Mn = fmaxf(M, mm[i]);
+            if (Mn == -INFINITY) continue;
+            const float fo = M == -INFINITY ? 0.f : ex2(M - Mn), fn = mm[i] == -INFINITY ? 0.f : ex2(mm[i] - Mn);
+            acc.x = acc.x * fo + vv[i].x * fn; acc.y = acc.y * fo + vv[i].y * fn; acc.z = acc.z * fo + vv[i].z * fn; acc.w = acc.w * fo + vv[i].w * fn;
+            L = L * fo + ll[i] * fn; M = Mn;
+        }
+    }
+    if (lane < NCOL) o_w[warp][lane] = acc;
+    if (lane == 0) { ml_w[warp][0] = M; ml_w[warp][1] = L; }
+    __syncthreads();
+    if (warp == 0) {
+        float Mx = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kFoldWarps; ++w) Mx = fmaxf(Mx, ml_w[w][0]);
+        float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+        float Ls = 0.f;
+#pragma unroll
+        for (int w = 0; w < kFoldWarps; ++w) {
+            const float mw = ml_w[w][0];
+            const float f = mw == -INFINITY ? 0.f : ex2(mw - Mx);
+            if (lane < NCOL) { const float4 v = o_w[w][lane]; o.x += v.x * f; o.y += v.y * f; o.z += v.z * f; o.w += v.w * f; }
+            Ls += ml_w[w][1] * f;
+        }
+        if (lane < NCOL) {
+            const float inv = 1.0f / Ls;
+            __half2* dst = reinterpret_cast<__half2*>(a.out + (size_t)head * HD + lane * 4);
+            dst[0] = __floats2half2_rn(o.x * inv, o.y * inv);
+            dst[1] = __floats2half2_rn(o.z * inv, o.w * inv);
+        }
+    }
+}
+
+}  // namespace cq

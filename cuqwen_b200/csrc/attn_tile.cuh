@@ -4,6 +4,7 @@
 // Reference arithmetic being replaced: src/kernels.cu:105-219 (there: fp16 scores and probabilities, WMMA).
 #pragma once
 #include "attn_combine.cuh"
+#include "tma.cuh"
 
 namespace cq {
 
@@ -33,7 +34,7 @@ __device__ __forceinline__ void attn_load_q(uint32_t (&qa)[HD / 32][4], const __
 template <bool FROM_GLOBAL>
 __device__ __forceinline__ uint4 attn_ld16(const unsigned char* p) {
     if (FROM_GLOBAL) return __ldcg(reinterpret_cast<const uint4*>(p));
-    return *reinterpret_cast<const uint4*>(p);
+    return lds128(smem_u32(p));        // explicit shared-window load: stays ld.shared even where the pointer's origin is not visible
 }
 
 // sK / sV: rows [key][HD] fp16 of the tile's 16 keys; nvalid >= 1 of them exist (the rest are never read).

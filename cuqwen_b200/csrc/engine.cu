@@ -486,6 +486,22 @@ static void describe_step(cuqwen_engine* e, std::vector<HostPhase>& out, int nsp
         a.norm_w = e->norm; a.eps = eps; a.w[0] = e->lm.w; a.s[0] = e->lm.s; a.rows = e->vocab_l; a.out_h = e->logits;
         gemv_phase(e->lm_quant, EPI_F16, a, false);
     }
+    // Each GEMV warms L2 with the small tensors of the next GEMV that normalises its input: its RMSNorm weight and, for
+    // the q/k/v kernel, the biases.
+    for (size_t i = 0; i < out.size(); ++i) {
+        if (out[i].ph.kind != PH_GEMV) continue;
+        for (size_t j = i + 1; j < out.size(); ++j) {
+            if (out[j].ph.kind != PH_GEMV) continue;
+            const GemvArgs& nx = out[j].ph.g;
+            GemvArgs& me = out[i].ph.g;
+            if (nx.norm_w) { me.warm[0] = nx.norm_w; me.warm_bytes[0] = nx.K * 2; }
+            if (out[j].ph.epi == EPI_QKV) {
+                me.warm[1] = nx.bias[0]; me.warm_bytes[1] = nx.n_heads * nx.hd * 2;
+                me.warm[2] = nx.bias[1]; me.warm_bytes[2] = nx.n_kv * nx.hd * 2;           // (the v bias, as small, is left to its first use)
+            }
+            break;
+        }
+    }
 }
 
 // Plans the persistent step kernel for this engine (single GPU only) and uploads its phase table.  Leaves
@@ -543,7 +559,7 @@ static int record_step(cuqwen_engine* e, cudaStream_t s, bool pdl) {
         std::vector<HostPhase> hp;
         describe_step(e, hp, e->nsplit, false);
         for (HostPhase& h : hp) {
-            if (h.ph.kind == PH_ATTN) { LK(launch_attn(p.head_dim, h.ph.at, cfg)); continue; }
+            if (h.ph.kind == PH_ATTN) { LK(launch_attn(p.head_dim, h.ph.at, cfg)); ++n; continue; }      // two launches: partials, fold
             LK(launch_gemv(h.ph.quant, h.ph.epi, h.ph.g, cfg));
             if (h.sum_after) LK(launch_tp_sum(h.sum_src, h.sum_dst, h.sum_slots, e->tp, p.dim, &e->ctl->pad[1], h.sum_seq, t_err, cfg_plain));
             if (h.reduce) {

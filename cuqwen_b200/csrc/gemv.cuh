@@ -5,11 +5,11 @@
 // on-disk layout of the reference, export_weights.py:123-205).  The reference computes, per 8-wide chunk,
 // "p = sum float(q)*float(x); acc += p*scale" (src/kernels.cu:11-57).
 //
-// Data path.  Every warp owns 16 output rows (x MT matrices) at a time and a private ring of shared-memory stages.
-// One lane issues a 2-D TMA tile copy (cp.async.bulk.tensor.2d: a box of 16 rows x up to 256 bytes of the row-major
-// weight matrix) per stage; the box lands in the ring and signals an mbarrier, so the HBM stream is decoupled from
-// the register file and the scoreboards.  Rows past the end of the matrix are zero-filled by the TMA unit.  The lanes
-// then read their fragments from the stage and run the tensor-core inner product described in gemv_math.cuh.
+// Data path.  A producer warp issues TMA tile copies (cp.async.bulk.tensor.3d: boxes of 16*rw rows x up to 256 bytes
+// of the row-major weight matrix, delivered chunk-major) into a CTA-wide ring of shared-memory stages; each box signals
+// an mbarrier, so the HBM stream is decoupled from the register file and the scoreboards.  Rows past the end of the
+// matrix are zero-filled by the TMA unit.  Eight consumer warps, each owning 16 output rows (x MT matrices) of a block
+// and a share of K, read their fragments from the stages and run the tensor-core inner product of gemv_math.cuh.
 //
 // Every wait on an mbarrier is bounded (about two seconds of wall time); when it expires the kernel records a code
 // in *err, stops waiting and finishes with meaningless numbers rather than hanging.
@@ -23,7 +23,7 @@ namespace cq {
 enum Epi : int { EPI_F16 = 0, EPI_F32 = 1, EPI_RESID = 2, EPI_SWIGLU = 3, EPI_QKV = 4, EPI_PUSH = 5 };
 
 struct alignas(64) GemvArgs {
-    CUtensorMap tmap[3];      // one 2-D byte map per weight matrix: dims {row bytes, rows}, box {piece bytes, 16}
+    CUtensorMap tmap[3];      // one 3-D byte map per weight matrix: dims {64, rows, row bytes / 64}, box {64, 16*rw, piece bytes / 64}
     const uint8_t* w[3];      // matrices: [0] generic / gate / q, [1] up / k, [2] v
     const __half* s[3];       // their group scales (null for fp16 weights)
     const __half* x;          // input vector [K]
@@ -61,6 +61,10 @@ struct alignas(64) GemvArgs {
     __half* x_next;                // where CTA 0 stores the summed vector (never the buffer x points at)
     const int* step_no;            // sequence number of an exchange = *step_no * 128 + seq_index + 1
     int seq_index;
+    // Small read-only tensors that the NEXT kernels of the step will want at once (RMSNorm weight, biases): the producer
+    // warp asks L2 for them while this kernel streams, so that their first use is an L2 hit instead of an HBM miss.
+    const void* warm[3];
+    int warm_bytes[3];
 };
 
 template <int EPI> struct EpiMT { static constexpr int MT = (EPI == EPI_SWIGLU || EPI == EPI_QKV) ? 2 : 1; };
@@ -68,7 +72,8 @@ template <int EPI> struct EpiMT { static constexpr int MT = (EPI == EPI_SWIGLU |
 // Shared-memory carve-up, computed the same way by the host (for the launch size) and the kernel.
 //   [x: K*2 bytes (fp16 vector, or the two digit planes)] [per-group corr (int) and xscale (float)] [reduction buffer]
 //   [2 scale blocks] [ring of stages] [mbarriers]
-// A stage holds, for each K-part kp and tile m, one TMA box of (16*rw rows) x piece_bytes:  [kp][m][row][piece_bytes].
+// A stage holds, for each K-part kp and tile m, one TMA box of (16*rw rows) x piece_bytes, chunk-major:
+// [kp][m][64-byte chunk][row][64 bytes].
 constexpr int kConsumerWarps = 8;
 struct GemvLayout {
     int piece_bytes, box_rows, box_bytes, stage_bytes, scale_block_bytes;

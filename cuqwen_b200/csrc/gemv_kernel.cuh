@@ -173,8 +173,8 @@ __device__ __forceinline__ void gemv_consume(const GemvArgs& a, RingCtx& R, int 
                         uint4 w[MT][2][NI], xv[2];
                         load_group_w<Q, MT>(wrow + gi * (GB / kChunkBytes) * cstride, cstride, G.box_bytes, w);
                         load_group_x(R.sm0 + grp * 256, g, t, xv);
-                        const int cr = corr[grp];
-                        const float xsc = xscale[grp];
+                        const int cr = (int)lds32(R.sm0 + R.off_corr + grp * 4);
+                        const float xsc = __uint_as_float(lds32(R.sm0 + R.off_xscale + grp * 4));
                         float sc[MT][2];
 #pragma unroll
                         for (int m = 0; m < MT; ++m) {
@@ -250,6 +250,12 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const __grid_cons
     if (threadIdx.x == 0) ring_init_barriers(R);
     __syncthreads();
     if ((threadIdx.x >> 5) == kConsumerWarps) {
+        if (blockIdx.x == 0) {
+#pragma unroll
+            for (int i = 0; i < 3; ++i)
+                for (int off = (threadIdx.x & 31) * 128; off < a.warm_bytes[i]; off += 32 * 128)
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(a.warm[i]) + off));
+        }
         gemv_produce<Q, EPI>(a, R, blockIdx.x, gridDim.x);
         return;
     }

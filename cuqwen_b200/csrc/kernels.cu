@@ -1,7 +1,7 @@
 // Small kernels of the decode step (embedding row, stand-alone RMSNorm / RoPE /
 // KV store, repetition penalty, greedy sampler, tensor-parallel helpers) and
 // the launch wrappers for the attention kernel.
-#include "attn.cuh"
+#include "attn_split.cuh"
 #include "gemv.cuh"
 #include "gemv_math.cuh"
 #include "gemv_stage.cuh"
@@ -278,20 +278,23 @@ size_t attn_scratch_floats_o(int n_kv, int nsplit, int head_dim) { return attn_s
 size_t attn_scratch_floats_ml(int n_kv, int nsplit) { return attn_slots(n_kv, nsplit) * kMaxGroup * 2; }
 size_t attn_scratch_counters(int n_kv, int nsplit) { return attn_counters(n_kv, nsplit); }
 
+static int env_int(const char* name, int dflt);
+// Two launches: partials, then the fold (attn_split.cuh).  Returns the first error.
+template <int HD>
+static int launch_attn_split(const AttnArgs& a, const LaunchCfg& cfg) {
+    AttnArgs b = a;
+    b.stages = env_int("CUQWEN_ATTN_STAGES", kSplitStages);      // tuning override (development aid)
+    if (b.stages < 2 || b.stages > kSplitStages) b.stages = kSplitStages;
+    const size_t smem = attn_split_smem_bytes(HD, b.stages);
+    cudaError_t e = cudaFuncSetAttribute(attn_partial_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_split_smem_bytes(HD, kSplitStages));
+    if (e != cudaSuccess) return (int)e;
+    if (int r = launch_k(attn_partial_kernel<HD>, dim3(b.n_kv, b.nsplit), dim3(kSplitThreads), smem, cfg, b)) return r;
+    return launch_k(attn_fold_kernel<HD>, dim3(b.n_kv * b.grp), dim3(kFoldWarps * 32), 0, cfg, b);
+}
 int launch_attn(int head_dim, const AttnArgs& a, const LaunchCfg& cfg) {
     if (a.grp < 1 || a.grp > kMaxGroup || a.nsplit < 1 || a.nsplit > kMaxSplit) return (int)cudaErrorInvalidValue;
-    dim3 grid(a.n_kv, a.nsplit), block(kAttnThreads);
-    const size_t smem = attn_smem_bytes(head_dim);
-    if (head_dim == 128) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-        return launch_k(attn_decode_kernel<128>, grid, block, smem, cfg, a);
-    }
-    if (head_dim == 64) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-        return launch_k(attn_decode_kernel<64>, grid, block, smem, cfg, a);
-    }
+    if (head_dim == 128) return launch_attn_split<128>(a, cfg);
+    if (head_dim == 64) return launch_attn_split<64>(a, cfg);
     return (int)cudaErrorInvalidValue;
 }
 

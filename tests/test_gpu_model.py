@@ -58,7 +58,7 @@ def test_small_model_step_vs_oracle(built, tmp_path, name, quant, fused):
     Kc = eng.read("KEY_CACHE").reshape(cfg["layers"], cfg["kv"], 128, cfg["hd"])
     Ko, _ = orc.kv_views()
     assert close(Kc[:, :, :40], Ko[:, :, :40]) and not Kc[:, :, 40:].any()
-    assert eng.step_launches == (4 if fused else 1 + 5 * cfg["layers"] + 3)   # embed, (step kernel | 5 per layer + lm_head), penalty, argmax
+    assert eng.step_launches == (4 if fused else 1 + 6 * cfg["layers"] + 3)   # embed, (step kernel | 6 per layer + lm_head), penalty, argmax
     eng.close(); orc.close()
 
 

@@ -52,7 +52,7 @@ def test_two_ranks_match_one_gpu(built, tmp_path, monkeypatch, quant, flags, sum
 
     r0, r1 = np.load(tmp_path / "rank0.npz"), np.load(tmp_path / "rank1.npz")
     assert r0["toks"].tolist() == r1["toks"].tolist()                       # every rank learns the same token
-    per_layer = 9 if flags else 7 if sum_kernel else 5                        # NCCL: + all-reduce and residual kernel twice per layer; sum kernel: + 2
+    per_layer = 10 if flags else 8 if sum_kernel else 6                       # 6 = qkv, attention x2, o_proj, gate/up, down; NCCL adds an all-reduce and a residual kernel twice, the sum kernel adds 2
     assert int(r0["launches"]) == 1 + per_layer * CFG["layers"] + 3 + 2       # ... + key all-gather and merge
     got = np.concatenate([r0["logits"], r1["logits"]])
     assert close(got, want), report(got, want)
