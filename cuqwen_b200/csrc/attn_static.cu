@@ -19,11 +19,13 @@
 // There is ONE scratch block per device: two calls that may overlap on the device (different streams, or different
 // host threads without ordering between their streams) race on it.  Calls on one stream are ordered and safe.
 //
-// The kernel is the body of attn.cuh compiled under another name, so cuqwen_k_attention and the engine keep their
-// own instantiation untouched.
-#define attn_decode_kernel attn_decode_static_kernel
-#include "attn.cuh"
-#undef attn_decode_kernel
+// The kernels are the bodies of attn_split.cuh (partials, then the per-head fold) compiled under other names, so
+// cuqwen_k_attention and the engine keep their own instantiations untouched and both entries compute the same bits.
+#define attn_partial_kernel attn_partial_static_kernel
+#define attn_fold_kernel attn_fold_static_kernel
+#include "attn_split.cuh"
+#undef attn_partial_kernel
+#undef attn_fold_kernel
 
 #include <mutex>
 
@@ -58,8 +60,8 @@ int scratch_base(int device, unsigned char** out) {
         unsigned char* p = nullptr;
         cudaError_t e = cudaGetSymbolAddress((void**)&p, g_scratch);
         if (e != cudaSuccess || !p) return report_error(CUQWEN_ERR_CUDA, "cudaGetSymbolAddress(attention scratch): %s", cudaGetErrorString(e));
-        e = cudaFuncSetAttribute(attn_decode_static_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_smem_bytes(128));
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_decode_static_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_smem_bytes(64));
+        e = cudaFuncSetAttribute(attn_partial_static_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_split_smem_bytes(128, kSplitStages));
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_partial_static_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_split_smem_bytes(64, kSplitStages));
         if (e != cudaSuccess) return report_error(CUQWEN_ERR_CUDA, "cudaFuncSetAttribute(attention): %s", cudaGetErrorString(e));
         g_base[device] = p;
     }
@@ -70,9 +72,12 @@ int scratch_base(int device, unsigned char** out) {
 template <int HD>
 cudaError_t launch(const AttnArgs& a, cudaStream_t stream) {
     cudaLaunchConfig_t lc = {};
-    lc.gridDim = dim3(a.n_kv, a.nsplit); lc.blockDim = dim3(kAttnThreads);
-    lc.dynamicSmemBytes = attn_smem_bytes(HD); lc.stream = stream;
-    return cudaLaunchKernelEx(&lc, attn_decode_static_kernel<HD>, a);
+    lc.gridDim = dim3(a.n_kv, a.nsplit); lc.blockDim = dim3(kSplitThreads);
+    lc.dynamicSmemBytes = attn_split_smem_bytes(HD, kSplitStages); lc.stream = stream;
+    cudaError_t e = cudaLaunchKernelEx(&lc, attn_partial_static_kernel<HD>, a);
+    if (e != cudaSuccess) return e;
+    lc.gridDim = dim3(a.n_kv * a.grp); lc.blockDim = dim3(kFoldWarps * 32); lc.dynamicSmemBytes = 0;
+    return cudaLaunchKernelEx(&lc, attn_fold_static_kernel<HD>, a);
 }
 
 }  // namespace
@@ -96,7 +101,7 @@ extern "C" int cuqwen_k_attention_static(int device, void* stream, const void* q
     AttnArgs a{};
     a.q = (const __half*)q; a.kc = (const __half*)kc; a.vc = (const __half*)vc; a.out = (__half*)out; a.d_pos = d_pos;
     a.n_kv = n_kv; a.grp = n_heads / n_kv; a.max_seq = max_seq; a.nsplit = nsplit;
-    a.scale_log2 = (1.0f / sqrtf((float)hd)) * 1.4426950408889634f;
+    a.scale_log2 = (1.0f / sqrtf((float)hd)) * 1.4426950408889634f; a.stages = kSplitStages;
     a.part_o = reinterpret_cast<float*>(base + kOffO);
     a.part_ml = reinterpret_cast<float*>(base + kOffMl);
     a.counters = reinterpret_cast<unsigned*>(base + kOffCounters);
