@@ -165,6 +165,7 @@ struct cuqwen_engine {
     // peer exchange (tensor parallel without collective calls): one receive block per rank, mapped into every peer
     unsigned char* tp_rx = nullptr; size_t tp_rx_bytes = 0; unsigned char* peer_rx[8] = {}; bool tp_peer = false;
     __half* x2 = nullptr; bool tp_sum_separate = false;
+    unsigned char* gate_xd = nullptr; int* gate_corr = nullptr; float* gate_xscale = nullptr;    // SwiGLU output in staged form (see GemvArgs::xd_out)
     int steps_done = 0;                          // mirrors the device-side step counter (StepCtl::pad[1])
     std::vector<cudaEvent_t>* prof = nullptr;    // cuqwen_step_profile: an event is recorded after every launch of the step
     // persistent step kernel (single GPU): phase table on the device, its shared-memory map, the grid barrier word
@@ -221,7 +222,8 @@ extern "C" int cuqwen_create(const cuqwen_params* pin, cuqwen_engine** out) {
     const size_t kvn = (size_t)p.n_layers * e->n_kv_l * p.max_seq_len * p.head_dim;
     CK(dalloc((void**)&e->x, p.dim * 2)); CK(dalloc((void**)&e->xn, p.dim * 2));
     CK(dalloc((void**)&e->q, e->q_dim_l * 2)); CK(dalloc((void**)&e->k, e->kv_dim_l * 2)); CK(dalloc((void**)&e->v, e->kv_dim_l * 2));
-    CK(dalloc((void**)&e->att, e->q_dim_l * 2)); CK(dalloc((void**)&e->gate, e->inter_l * 2)); CK(dalloc((void**)&e->logits, e->vocab_l * 2));
+    CK(dalloc((void**)&e->att, e->q_dim_l * 2)); CK(dalloc((void**)&e->gate, e->inter_l * 2));
+    { const size_t cb = ((size_t)(e->inter_l / kGroup) * 4 + 15) / 16 * 16; CK(dalloc((void**)&e->gate_xd, (size_t)e->inter_l * 2)); CK(dalloc((void**)&e->gate_corr, cb)); CK(dalloc((void**)&e->gate_xscale, cb)); } CK(dalloc((void**)&e->logits, e->vocab_l * 2));
     CK(dalloc((void**)&e->kc, kvn * 2)); CK(dalloc((void**)&e->vc, kvn * 2));     // zeroed like src/model.cu:37-38
     CK(dalloc((void**)&e->part_o, attn_scratch_floats_o(e->n_kv_l, e->nsplit, p.head_dim) * 4));
     CK(dalloc((void**)&e->part_ml, attn_scratch_floats_ml(e->n_kv_l, e->nsplit) * 4));
@@ -246,7 +248,7 @@ extern "C" void cuqwen_destroy(cuqwen_engine* e) {
     if (e->tp_rx) cudaFree(e->tp_rx);
     if (e->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(e->comm);
     void* bufs[] = {e->x, e->xn, e->q, e->k, e->v, e->att, e->gate, e->logits, e->kc, e->vc, e->part_o, e->part_ml, e->counters, e->ctl, e->d_hist,
-                    e->bitmap, e->best, e->ticket, e->out_ring, e->tp_partial, e->tp_keys, e->warena, e->d_phases, e->step_bar, e->step_trace, e->x2};
+                    e->bitmap, e->best, e->ticket, e->out_ring, e->tp_partial, e->tp_keys, e->warena, e->d_phases, e->step_bar, e->step_trace, e->x2, e->gate_xd, e->gate_corr, e->gate_xscale};
     for (void* b : bufs) if (b) cudaFree(b);
     if (e->h_ctl) cudaFreeHost(e->h_ctl);
     if (e->h_out) cudaFreeHost(e->h_out);
@@ -407,6 +409,9 @@ static void describe_step(cuqwen_engine* e, std::vector<HostPhase>& out, int nsp
     // Peer-exchange bookkeeping (tensor parallel): `cur` is the buffer that holds the residual stream, `pending` the
     // exchange whose partials still have to be added to it by the next kernel that reads it.
     const bool peer = e->tp > 1 && e->tp_peer;
+    // SwiGLU output handed to the down projection in staged form: only when the separate gate/up launch will work on
+    // whole 128-row groups (eight tile sets per block), which the launcher decides from the tile-set count
+    const bool hand_over = !with_fold && p.quant != 0 && gemv_tile_sets_per_block((e->inter_l + 15) / 16, e->sms, EPI_SWIGLU) == 8;
     __half* cur = e->x;
     int pending = -1, next_xi = 0;
     auto take_x = [&](GemvArgs& a) {                                        // a normed GEMV reads the residual stream
@@ -470,11 +475,13 @@ static void describe_step(cuqwen_engine* e, std::vector<HostPhase>& out, int nsp
             take_x(a);
             a.norm_w = L.post_norm; a.eps = eps;
             a.w[0] = L.gate.w; a.w[1] = L.up.w; a.s[0] = L.gate.s; a.s[1] = L.up.s; a.rows = e->inter_l; a.out_h = e->gate;
+            if (hand_over) { a.xd_out = e->gate_xd; a.corr_out = e->gate_corr; a.xscale_out = e->gate_xscale; }
             gemv_phase(p.quant, EPI_SWIGLU, a, false);
         }
         {   // down + residual
             GemvArgs a = gv(e->gate, e->inter_l);
             a.w[0] = L.down.w; a.s[0] = L.down.s; a.rows = p.dim;
+            if (hand_over) { a.xd_in = e->gate_xd; a.corr_in = e->gate_corr; a.xscale_in = e->gate_xscale; }
             if (e->tp == 1) { a.out_h = e->x; gemv_phase(p.quant, EPI_RESID, a, false); }
             else if (peer) { push_to(a); gemv_phase(p.quant, EPI_PUSH, a, false); sum_after_push(); }
             else { a.out_f = e->tp_partial; gemv_phase(p.quant, EPI_F32, a, true); }

@@ -61,6 +61,12 @@ struct alignas(64) GemvArgs {
     __half* x_next;                // where CTA 0 stores the summed vector (never the buffer x points at)
     const int* step_no;            // sequence number of an exchange = *step_no * 128 + seq_index + 1
     int seq_index;
+    // Hand-over of an activation vector in staged form.  A SwiGLU kernel whose blocks are whole 128-row groups (rw = 8,
+    // no K split) also writes its outputs as the digit blocks, corrections and scales that a quantised GEMV's inner loop
+    // reads (gemv_stage.cuh), once; the GEMV that consumes the vector then fetches them with three bulk copies
+    // instead of converting the whole vector again in every one of its CTAs.
+    unsigned char* xd_out; int* corr_out; float* xscale_out;                 // producer side (EPI_SWIGLU), may be null
+    const unsigned char* xd_in; const int* corr_in; const float* xscale_in;  // consumer side, may be null
     // Small read-only tensors that the NEXT kernels of the step will want at once (RMSNorm weight, biases): the producer
     // warp asks L2 for them while this kernel streams, so that their first use is an L2 hit instead of an HBM miss.
     const void* warm[3];
@@ -95,7 +101,7 @@ __host__ __device__ inline GemvLayout gemv_layout(int K, int group_bytes, int MT
     L.off_scales = o; o += 2 * L.scale_block_bytes;
     o = (o + 127) / 128 * 128;               // TMA destinations are 128-byte aligned
     L.off_stages = o; o += nst * L.stage_bytes;
-    L.off_bars = o; o += (2 * nst + 4) * 8;  // full[nst], empty[nst], scale full[2], scale empty[2]
+    L.off_bars = o; o += (2 * nst + 5) * 8;  // full[nst], empty[nst], scale full[2], scale empty[2], x staged[1]
     L.total = o;
     return L;
 }
@@ -162,7 +168,7 @@ __device__ __forceinline__ void epilogue_fetch(const GemvArgs& a, int row0, int 
 
 // Finish one output row (pair).  r = row slot 0..15 inside the tile set; pre = what epilogue_fetch returned for it.
 template <int EPI>
-__device__ __forceinline__ void epilogue(const GemvArgs& a, int row0, int mat, int r, float v0, float v1, const float (&pre)[2]) {
+__device__ __forceinline__ void epilogue(const GemvArgs& a, int row0, int mat, int r, float v0, float v1, const float (&pre)[2], __half* hbuf = nullptr) {
     if (EPI == EPI_F16) {
         const int row = row0 + r;
         if (row < a.rows) a.out_h[row] = __float2half(v0);
@@ -185,7 +191,9 @@ __device__ __forceinline__ void epilogue(const GemvArgs& a, int row0, int mat, i
         const int row = row0 + r;
         if (row < a.rows) {
             const float sig = __fdividef(1.0f, 1.0f + __expf(-v0));
-            a.out_h[row] = __float2half(v0 * sig * v1);
+            const __half h = __float2half(v0 * sig * v1);
+            a.out_h[row] = h;
+            if (hbuf) hbuf[r] = h;              // the block's 128 outputs meet in shared memory for the digit hand-over
         }
     } else {
         // bias in fp32, one rounding to fp16 (src/kernels.cu:468-472); rotate-half RoPE on q and k from the rounded

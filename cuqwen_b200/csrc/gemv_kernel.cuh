@@ -25,6 +25,7 @@ struct RingCtx {
     unsigned char* base;          // generic pointer to offset 0
     int off_corr, off_xscale, off_red, off_scales, scale_block_bytes, off_stages, slot_bytes, nslots;
     uint32_t bar_full, bar_empty, bar_sfull, bar_sempty;
+    uint32_t bar_x, xpar;         // barrier of the bulk-copied activation vector and its parity
     int slot;                     // next ring slot
     uint32_t par;                 // its parity: number of completed laps, mod 2
     uint32_t sj;                  // scale blocks used so far
@@ -42,6 +43,7 @@ struct RingCtx {
 __device__ __forceinline__ void ring_init_barriers(const RingCtx& R) {
     for (int s = 0; s < R.nslots; ++s) { mbar_init(R.bar_full + s * 8, 1); mbar_init(R.bar_empty + s * 8, kConsumerWarps); }
     for (int b = 0; b < 2; ++b) { mbar_init(R.bar_sfull + b * 8, 1); mbar_init(R.bar_sempty + b * 8, kConsumerWarps); }
+    mbar_init(R.bar_x, 1);
     mbar_fence_init();
 }
 
@@ -131,7 +133,22 @@ __device__ __forceinline__ void gemv_consume(const GemvArgs& a, RingCtx& R, int 
 
     GatherSrc gs{a.gather, a.ngather, 0u, a.x_next, cta == 0, R.err};
     if (a.ngather > 0) gs.seq = (unsigned)(*a.step_no) * 128u + (unsigned)a.seq_index + 1u;     // tensor parallel: x plus the partials the ranks pushed
-    stage_x<Q>(a.x, a.norm_w, a.eps, a.K, R.base, R.off_corr, corr, xscale, red, NC, a.ngather > 0 ? &gs : nullptr);
+    if (kInt && a.xd_in) {
+        // the vector arrives already staged (digit blocks, corrections, scales written by the kernel that produced it)
+        const uint32_t cbytes = (uint32_t)((ngrp * 4 + 15) / 16 * 16);
+        if (threadIdx.x == 0) {
+            fence_async_smem();
+            mbar_expect_tx(R.bar_x, (uint32_t)(a.K * 2) + 2u * cbytes);
+            bulk_g2s(R.sm0, a.xd_in, (uint32_t)(a.K * 2), R.bar_x);
+            bulk_g2s(R.sm0 + R.off_corr, a.corr_in, cbytes, R.bar_x);
+            bulk_g2s(R.sm0 + R.off_xscale, a.xscale_in, cbytes, R.bar_x);
+        }
+        R.wait(R.bar_x, R.xpar, 9u);
+        R.xpar ^= 1u;
+    } else if (stage_x<Q>(a.x, a.norm_w, a.eps, a.K, R.base, R.off_corr, corr, xscale, red, NC, a.ngather > 0 ? &gs : nullptr, R.bar_x, R.xpar)) R.xpar ^= 1u;
+    // a SwiGLU kernel whose block is a whole 128-row group hands its outputs over in staged form as well
+    const bool emit = EPI == EPI_SWIGLU && kInt && a.xd_out != nullptr && rw == 8 && kw == 1 && gw == 1;
+    __half* hbuf = reinterpret_cast<__half*>(red);
     if (R.stamp && threadIdx.x == 0) *R.stamp = global_ns();
 
     for (int j = 0; j < n_b; ++j) {
@@ -223,8 +240,19 @@ __device__ __forceinline__ void gemv_consume(const GemvArgs& a, RingCtx& R, int 
             }
             consumer_sync(NC);         // `red` is free again
         } else if (t == 0 && live) {
-            epilogue<EPI>(a, tm.row0, tm.mat, g, tot[0][0], MT == 2 ? tot[MT - 1][0] : 0.f, preA);
-            epilogue<EPI>(a, tm.row0, tm.mat, g + 8, tot[0][1], MT == 2 ? tot[MT - 1][1] : 0.f, preB);
+            epilogue<EPI>(a, tm.row0, tm.mat, g, tot[0][0], MT == 2 ? tot[MT - 1][0] : 0.f, preA, emit ? hbuf + rwi * 16 : nullptr);
+            epilogue<EPI>(a, tm.row0, tm.mat, g + 8, tot[0][1], MT == 2 ? tot[MT - 1][1] : 0.f, preB, emit ? hbuf + rwi * 16 : nullptr);
+        }
+        if constexpr (EPI == EPI_SWIGLU && kInt) {
+            if (emit && blk * 8 + 7 < a.nsets) {           // (uniform over the CTA)
+                consumer_sync(NC);
+                if (warp == 0) {
+                    const int c = lane & 15;
+                    const uint4 v = reinterpret_cast<const uint4*>(hbuf)[c];
+                    digits_of_chunk<Q>(v, blk * 16 + c, lane < 16, a.xd_out, a.corr_out, a.xscale_out);
+                }
+                consumer_sync(NC);                         // hbuf is free for the next block
+            }
         }
     }
 }
@@ -238,6 +266,7 @@ __device__ __forceinline__ RingCtx gemv_ring(const GemvArgs& a, unsigned char* s
     R.off_corr = L.off_corr; R.off_xscale = L.off_xscale; R.off_red = L.off_red; R.off_scales = L.off_scales;
     R.scale_block_bytes = L.scale_block_bytes; R.off_stages = L.off_stages; R.slot_bytes = L.stage_bytes; R.nslots = a.nst;
     R.bar_full = R.sm0 + L.off_bars; R.bar_empty = R.bar_full + a.nst * 8; R.bar_sfull = R.bar_empty + a.nst * 8; R.bar_sempty = R.bar_sfull + 16;
+    R.bar_x = R.bar_sempty + 16; R.xpar = 0u;
     R.slot = 0; R.par = 0; R.sj = 0; R.err = a.err; R.failed = false; R.skip_math = false; R.stamp = nullptr;
     return R;
 }

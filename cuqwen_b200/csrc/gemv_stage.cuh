@@ -211,24 +211,43 @@ __device__ __forceinline__ void digits_of_chunk(uint4 v, int c8, bool live, unsi
 // Stage x for the kernel of quantisation Q: digits (int4 / int8, into xd + corr + xscale) or plain fp16 (xd as uint4[]).
 // xarea_bytes: shared memory available from xd on; the norm weight is parked at xd + 2K when 4K bytes fit (else it
 // is re-read from global memory during the conversion).
+// bar_x / xpar: an mbarrier (shared-window address) and its current parity; when given and the sources are 16-byte
+// aligned, step 1 is two bulk copies issued by one thread (x through L2, the norm weight beside it) instead of
+// per-thread loads: one instruction, no registers, the whole vector in flight at once.  Returns whether the barrier
+// was used (the caller then flips the parity).
 template <int Q>
-__device__ __forceinline__ void stage_x(const __half* x, const __half* norm_w, float eps, int K, unsigned char* xd, int xarea_bytes, int* corr, float* xscale,
-                                        float* red, int nthreads, const GatherSrc* gs = nullptr) {
+__device__ __forceinline__ bool stage_x(const __half* x, const __half* norm_w, float eps, int K, unsigned char* xd, int xarea_bytes, int* corr, float* xscale,
+                                        float* red, int nthreads, const GatherSrc* gs = nullptr, uint32_t bar_x = 0u, uint32_t xpar = 0u) {
     const int nchunk = K / 8, lane = threadIdx.x & 31;
     uint4* raw = reinterpret_cast<uint4*>(xd);
     uint4* wraw = raw + nchunk;
     const bool w_parked = norm_w && 4 * K <= xarea_bytes;
+    const bool gather = gs && gs->n > 0;
+    const bool bulk = bar_x != 0u && !gather && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (!norm_w || (w_parked && (reinterpret_cast<uintptr_t>(norm_w) & 15) == 0));
     float inv = 0.f;
-    if (norm_w) {
+    if (bulk) {
+        if (threadIdx.x == 0) {
+            fence_async_smem();                        // earlier generic-proxy accesses to this area come before the copy's writes
+            mbar_expect_tx(bar_x, (uint32_t)(K * 2) * (norm_w ? 2u : 1u));
+            bulk_g2s(smem_u32(raw), x, (uint32_t)(K * 2), bar_x);
+            if (norm_w) bulk_g2s(smem_u32(wraw), norm_w, (uint32_t)(K * 2), bar_x);
+        }
+        mbar_wait(bar_x, xpar);                        // bounded; on expiry the vector is garbage and the ring waits report it
+        if (norm_w) {
+            float ss = 0.f;
+            for (int c8 = threadIdx.x; c8 < nchunk; c8 += nthreads) ss += chunk_sumsq(raw[c8]);
+            inv = consumers_rsqrt_mean(ss, K, eps, red, nthreads);
+        }
+    } else if (norm_w) {
         float ss;
-        if (gs && gs->n > 0) ss = w_parked ? park_gather<true>(x, norm_w, *gs, K, nchunk, raw, wraw, nthreads) : park_gather<false>(x, norm_w, *gs, K, nchunk, raw, wraw, nthreads);
+        if (gather) ss = w_parked ? park_gather<true>(x, norm_w, *gs, K, nchunk, raw, wraw, nthreads) : park_gather<false>(x, norm_w, *gs, K, nchunk, raw, wraw, nthreads);
         else ss = w_parked ? park_raw<4, true, true>(x, norm_w, nchunk, raw, wraw, nthreads) : park_raw<4, true, false>(x, norm_w, nchunk, raw, wraw, nthreads);
         inv = consumers_rsqrt_mean(ss, K, eps, red, nthreads);
     } else {
         park_raw<5, false, false>(x, nullptr, nchunk, raw, nullptr, nthreads);
         consumer_sync(nthreads);
     }
-    if (Q == Q_F16 && !norm_w) return;                 // raw fp16 is what the fp16 kernel wants
+    if (Q == Q_F16 && !norm_w) return bulk;            // raw fp16 is what the fp16 kernel wants
 #pragma unroll 1
     for (int base = threadIdx.x & ~31; base < nchunk; base += nthreads) {
         const int c8 = base + lane;
@@ -242,6 +261,7 @@ __device__ __forceinline__ void stage_x(const __half* x, const __half* norm_w, f
         else digits_of_chunk<Q>(xv, c8, live, xd, corr, xscale);
     }
     consumer_sync(nthreads);
+    return bulk;                                       // true: the barrier completed a phase, its parity flips
 }
 
 }  // namespace cq

@@ -338,6 +338,13 @@ static int env_int(const char* name, int dflt) {
     return v && *v ? atoi(v) : dflt;
 }
 
+// Tile sets (16 rows each) per CTA block of a stand-alone launch: as many as keep at least one block per SM.
+int gemv_tile_sets_per_block(int nsets, int sm_count, int epi) {
+    int rw = 1;
+    if (epi != EPI_QKV) while (rw < 8 && nsets / (rw * 2) >= sm_count) rw *= 2;
+    return rw;
+}
+
 // Picks the work split (rw row-warps x kw K-parts), the staged piece size and the ring depth for one GEMV launch.
 //   many tile sets: blocks of up to 8 tile sets (128 rows), every consumer warp walks the whole K of its 16 rows;
 //   few tile sets: one tile set per CTA, its K split over the eight consumer warps.
@@ -357,8 +364,7 @@ int launch_gemv(int quant, int epi, GemvArgs& a, const LaunchCfg& cfg) {
     const int gb = quant == Q_I4 ? 64 : quant == Q_I8 ? 128 : 256;
     const int pg_max = 256 / gb;                     // row pieces of at most 256 bytes (TMA box limit for byte elements)
     const int kMaxSmem = 225 * 1024;
-    int rw = 1;
-    if (epi != EPI_QKV) while (rw < 8 && a.nsets / (rw * 2) >= cfg.sm_count) rw *= 2;
+    int rw = gemv_tile_sets_per_block(a.nsets, cfg.sm_count, epi);
     int kw = 8 / rw;                                 // rw * kw may end up below 8 when a row has few pieces: the spare warps idle
     const int nblk = (a.nsets + rw - 1) / rw;
     const int grid = nblk;                            // CTAs loop when there are more blocks than fit at once

@@ -34,6 +34,8 @@ struct LaunchCfg {
 // GEMV family.  quant: 0 fp16, 1 int8, 2 int4.  epi: cq::Epi.  Fills nsets /
 // ksplit itself.  Returns a cudaError_t value.
 int launch_gemv(int quant, int epi, GemvArgs& a, const LaunchCfg& cfg);
+// Tile sets (16 rows each) per CTA block that launch_gemv will choose for `nsets` tile sets.
+int gemv_tile_sets_per_block(int nsets, int sm_count, int epi);
 
 // Byte-typed 2-D tensor map of a row-major matrix: dims {row_bytes, rows}, box {piece_bytes, box_rows}.
 int make_weight_map(CUtensorMap* m, const void* w, size_t row_bytes, size_t rows, int piece_bytes, int box_rows);

@@ -79,7 +79,7 @@ int plan_step_smem(StepArgs& sa, const StepPhase* ph, int n, int hd, int slot_by
     if (nslots > 12) nslots = 12;
     if (nslots < 3) return (int)cudaErrorInvalidValue;
     sa.nslots = nslots; o += nslots * slot_bytes;
-    sa.off_bars = o; o += (2 * nslots + 4) * 8;
+    sa.off_bars = o; o += (2 * nslots + 5) * 8;
     sa.smem_bytes = o;
     sa.hd = hd;
     return 0;

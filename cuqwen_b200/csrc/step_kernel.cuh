@@ -258,6 +258,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) decode_step_kernel(const __gr
     R.off_corr = sa.off_corr; R.off_xscale = sa.off_xscale; R.off_red = sa.off_red; R.off_scales = sa.off_scales;
     R.scale_block_bytes = sa.scale_block_bytes; R.off_stages = sa.off_stages; R.slot_bytes = sa.slot_bytes; R.nslots = sa.nslots;
     R.bar_full = R.sm0 + sa.off_bars; R.bar_empty = R.bar_full + sa.nslots * 8; R.bar_sfull = R.bar_empty + sa.nslots * 8; R.bar_sempty = R.bar_sfull + 16;
+    R.bar_x = R.bar_sempty + 16; R.xpar = 0u;
     R.slot = 0; R.par = 0; R.sj = 0; R.err = sa.err; R.failed = false; R.skip_math = (sa.debug & 1) != 0; R.stamp = nullptr;
     if (threadIdx.x == 0) ring_init_barriers(R);
     __syncthreads();
