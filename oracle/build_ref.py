@@ -8,7 +8,7 @@ path never calls); only ``ref_wrap.cu`` of this repository is added.  Flags
 follow the reference's CMakeLists.txt:105 (``-O3 --use_fast_math``), the
 architecture is sm_100a.
 
-Usage: python oracle/build_ref.py [--ref /root/reference] [--only 7b:int4,0.5b:fp16]
+Usage: python oracle/build_ref.py [--ref <CuQwen checkout>] [--only 7b:int4,0.5b:fp16]
 """
 from __future__ import annotations
 

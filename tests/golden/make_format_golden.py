@@ -1,6 +1,6 @@
 """Generate tests/golden/format_golden.npz by importing the reference's own export_weights.py.
 
-Run where the CuQwen checkout is available:  python tests/golden/make_format_golden.py [/root/reference]
+Run where the CuQwen checkout is available:  python tests/golden/make_format_golden.py [<CuQwen checkout>]
 The fixture pins the quantiser and the serialised byte layout (write_fp16 / write_int8 / write_int4) on small
 seeded matrices, including an all-zero group, exact half-way cases and values that clip.
 """
