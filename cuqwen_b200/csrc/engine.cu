@@ -411,7 +411,8 @@ static void describe_step(cuqwen_engine* e, std::vector<HostPhase>& out, int nsp
     const bool peer = e->tp > 1 && e->tp_peer;
     // SwiGLU output handed to the down projection in staged form: only when the separate gate/up launch will work on
     // whole 128-row groups (eight tile sets per block), which the launcher decides from the tile-set count
-    const bool hand_over = !with_fold && p.quant != 0 && gemv_tile_sets_per_block((e->inter_l + 15) / 16, e->sms, EPI_SWIGLU) == 8;
+    const bool hand_over = !with_fold && p.quant != 0 && !(p.flags & CUQWEN_FLAG_NO_HANDOVER) &&
+                           gemv_tile_sets_per_block((e->inter_l + 15) / 16, e->sms, EPI_SWIGLU) == 8;
     __half* cur = e->x;
     int pending = -1, next_xi = 0;
     auto take_x = [&](GemvArgs& a) {                                        // a normed GEMV reads the residual stream

@@ -45,7 +45,8 @@ enum {
     CUQWEN_FLAG_FUSED_STEP = 8,     /* experimental: all matrices and the attention of a step in one persistent kernel (grid barriers between
                                      * phases) instead of one launch each; single GPU only */
     CUQWEN_FLAG_STEP_TRACE = 16,    /* the step kernel stamps phase entry / exit times per CTA (CUQWEN_PTR_STEP_TRACE) */
-    CUQWEN_FLAG_TP_NCCL = 32        /* tensor parallel: sum the row-parallel partials with NCCL all-reduce calls instead of peer stores */
+    CUQWEN_FLAG_TP_NCCL = 32,       /* tensor parallel: sum the row-parallel partials with NCCL all-reduce calls instead of peer stores */
+    CUQWEN_FLAG_NO_HANDOVER = 64    /* the down projection converts its input itself instead of taking it staged from the SwiGLU kernel */
 };
 
 /* Mirrors QwenConfig (include/config.h:52-127) as run-time data. */

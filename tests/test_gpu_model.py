@@ -19,6 +19,11 @@ SMALL = {
 }
 
 
+# wide MLP: 18944 = 148 x 128 columns, the smallest width at which (on a 148-SM GPU) the gate/up launch works on whole
+# 128-row groups and hands its output to the down projection in staged form
+SMALL["wide_mlp"] = dict(vocab=1024, dim=256, inter=18944, layers=2, heads=4, kv=2, hd=64, tied=True)
+
+
 def write_small(tmp_path, name, quant, seed=1):
     cfg = SMALL[name]
     p = tmp_path / f"{name}_{quant}.bin"
@@ -60,6 +65,21 @@ def test_small_model_step_vs_oracle(built, tmp_path, name, quant, fused):
     assert close(Kc[:, :, :40], Ko[:, :, :40]) and not Kc[:, :, 40:].any()
     assert eng.step_launches == (4 if fused else 1 + 6 * cfg["layers"] + 3)   # embed, (step kernel | 6 per layer + lm_head), penalty, argmax
     eng.close(); orc.close()
+
+
+@pytest.mark.parametrize("quant", [1, 2])
+def test_staged_handover_of_the_mlp_activation(built, tmp_path, quant):
+    """The SwiGLU kernel's staged output (digits, corrections, scales) must be exactly what the down projection would
+    have derived from the fp16 vector itself: both paths give the same bits, and both agree with the oracle."""
+    cfg, path = write_small(tmp_path, "wide_mlp", quant)
+    a, b = make_engine(cfg, quant, path, flags=E.FLAG_ACCURATE_ROPE), make_engine(cfg, quant, path, flags=E.FLAG_ACCURATE_ROPE | E.FLAG_NO_HANDOVER)
+    orc = O.OracleModel(str(path), 128)
+    for pos, t in enumerate([5, 900, 17, 333, 64, 2]):
+        a.step(t, pos); b.step(t, pos); orc.step(t, pos)
+        la, lb = a.read("LOGITS"), b.read("LOGITS")
+        assert np.array_equal(la.view(np.uint16), lb.view(np.uint16)), f"pos {pos}: staged hand-over changes the result"
+        assert close(la, orc.logits), f"pos {pos}: " + report(la, orc.logits)
+    a.close(); b.close(); orc.close()
 
 
 def test_step_kernel_agrees_with_launch_per_matrix(built, tmp_path):
