@@ -102,7 +102,10 @@ static int dev_ctx(int device, DevCtx** out) {
     *out = &d;
     return CUQWEN_OK;
 }
-#define DEV(device) DevCtx* dc; { int r_ = dev_ctx(device, &dc); if (r_) return r_; } t_err = dc->err; LaunchCfg cfg{dc->stream, dc->sms, false}
+// The per-kernel entry points launch the way the engine's graph does: with programmatic dependent launch, so that a
+// kernel's prologue may overlap the tail of the call before it (every kernel waits for its predecessor before it
+// touches data).
+#define DEV(device) DevCtx* dc; { int r_ = dev_ctx(device, &dc); if (r_) return r_; } t_err = dc->err; LaunchCfg cfg{dc->stream, dc->sms, true}
 
 // ---------------------------------------------------------------------------
 // NCCL through dlopen (no link-time dependency; single-GPU use never loads it)
