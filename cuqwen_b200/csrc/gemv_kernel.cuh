@@ -199,10 +199,6 @@ __device__ __forceinline__ void gemv_consume(const GemvArgs& a, RingCtx& R, int 
                             sc[m][0] = lds_h(sa) * xsc; sc[m][1] = lds_h(sa + 8 * ngrp * 2) * xsc;
                         }
                         int ci[MT][2][4];
-#pragma unroll
-                        for (int m = 0; m < MT; ++m)
-#pragma unroll
-                            for (int q = 0; q < 4; ++q) ci[m][0][q] = ci[m][1][q] = 0;
                         mma_group_int<Q, MT>(w, xv, ci);
 #pragma unroll
                         for (int m = 0; m < MT; ++m) {
@@ -268,6 +264,9 @@ __device__ __forceinline__ RingCtx gemv_ring(const GemvArgs& a, unsigned char* s
     R.bar_full = R.sm0 + L.off_bars; R.bar_empty = R.bar_full + a.nst * 8; R.bar_sfull = R.bar_empty + a.nst * 8; R.bar_sempty = R.bar_sfull + 16;
     R.bar_x = R.bar_sempty + 16; R.xpar = 0u;
     R.slot = 0; R.par = 0; R.sj = 0; R.err = a.err; R.failed = false; R.skip_math = false; R.stamp = nullptr;
+#ifdef CQ_SKIP_MATH
+    R.skip_math = true;      // development build: consume the ring without arithmetic (measures the copy path)
+#endif
     return R;
 }
 

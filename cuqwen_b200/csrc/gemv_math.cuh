@@ -35,46 +35,24 @@ __device__ __forceinline__ void imma_s8s8(int (&c)[4], uint32_t a0, uint32_t a1,
     asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+// The same with a zero accumulator on input (the first MMA of a chain): no registers need clearing beforehand.
+__device__ __forceinline__ void imma_u8s8_z(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                 : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+__device__ __forceinline__ void imma_s8s8_z(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                 : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
 // four packed nibbles -> four bytes holding q+8: (v & 0x0f0f0f0f) ^ 0x08080808 in one LOP3
 __device__ __forceinline__ uint32_t nib4(uint32_t v) { return and_xor(v, 0x0f0f0f0fu, 0x08080808u); }
 
-// Integer path, one 128-column group for the MT tiles of a warp.  wbase: shared address of this lane's 16 bytes (column
-// t) of row g of tile 0 in the group's first chunk; the group's next chunk is cstride bytes further, tile m mstride bytes.  xd: shared address of the group's digit block, laid out [half (2)][t (4)][digit plane (2)][16 bytes];
-// lanes with g >= 2 feed zero columns.  Two accumulator sets alternate to shorten the dependent chain.
-template <int Q, int MT>
-__device__ __forceinline__ void compute_group_int(uint32_t wbase, int cstride, int mstride, int g, int t, uint32_t xd, int (&c)[MT][2][4]) {
-    constexpr int NI = QT<Q>::NI;
-    uint4 w[MT][2][NI];
-#pragma unroll
-    for (int m = 0; m < MT; ++m)
-#pragma unroll
-        for (int h = 0; h < 2; ++h)
-#pragma unroll
-            for (int i = 0; i < NI; ++i) w[m][h][i] = lds128(wbase + m * mstride + h * 8 * kChunkBytes + i * cstride);
-#pragma unroll
-    for (int jj = 0; jj < 2; ++jj) {
-        uint4 xv = make_uint4(0u, 0u, 0u, 0u);
-        if (g < 2) xv = lds128(xd + jj * 128 + t * 32 + g * 16);
-#pragma unroll
-        for (int m = 0; m < MT; ++m) {
-            if (Q == Q_I4) {
-                // the lane's 16 bytes are 32 consecutive weights; word j carries elements 8j..8j+7, low nibble first
-                const uint32_t a0 = u4c(w[m][0][0], 2 * jj), b0 = u4c(w[m][1][0], 2 * jj);
-                const uint32_t a1 = u4c(w[m][0][0], 2 * jj + 1), b1 = u4c(w[m][1][0], 2 * jj + 1);
-                imma_u8s8(c[m][0], nib4(a0), nib4(b0), nib4(a0 >> 4), nib4(b0 >> 4), xv.x, xv.y);
-                imma_u8s8(c[m][1], nib4(a1), nib4(b1), nib4(a1 >> 4), nib4(b1 >> 4), xv.z, xv.w);
-            } else {
-                const uint4& a = w[m][0][jj];
-                const uint4& b = w[m][1][jj];
-                imma_s8s8(c[m][0], a.x, b.x, a.y, b.y, xv.x, xv.y);
-                imma_s8s8(c[m][1], a.z, b.z, a.w, b.w, xv.z, xv.w);
-            }
-        }
-    }
-}
-
-// The same in two halves, so that a caller can put the loads of several groups in flight before the first MMA:
-// load_group_w fetches the fragments, mma_group_int consumes them.
+// Integer path, one 128-column group for the MT tiles of a warp, in two halves so that a caller can put the loads of
+// a group in flight before the first MMA.  wbase: shared address of this lane's 16 bytes (column t) of row g of tile 0
+// in the group's first chunk; the group's next chunk is cstride bytes further, tile m mstride bytes.  The B operand is
+// the group's digit block, laid out [half (2)][t (4)][digit plane (2)][16 bytes]; lanes with g >= 2 feed zero columns.
+// Two accumulator sets per tile alternate to shorten the dependent chain.
+// load_group_w fetches the fragments, mma_group_int consumes them (c need not be cleared: it is overwritten).
 template <int Q, int MT>
 __device__ __forceinline__ void load_group_w(uint32_t wbase, int cstride, int mstride, uint4 (&w)[MT][2][QT<Q>::NI]) {
 #pragma unroll
@@ -93,13 +71,23 @@ __device__ __forceinline__ void mma_group_int(const uint4 (&w)[MT][2][QT<Q>::NI]
             if (Q == Q_I4) {
                 const uint32_t a0 = u4c(w[m][0][0], 2 * jj), b0 = u4c(w[m][1][0], 2 * jj);
                 const uint32_t a1 = u4c(w[m][0][0], 2 * jj + 1), b1 = u4c(w[m][1][0], 2 * jj + 1);
-                imma_u8s8(c[m][0], nib4(a0), nib4(b0), nib4(a0 >> 4), nib4(b0 >> 4), xv[jj].x, xv[jj].y);
-                imma_u8s8(c[m][1], nib4(a1), nib4(b1), nib4(a1 >> 4), nib4(b1 >> 4), xv[jj].z, xv[jj].w);
+                if (jj == 0) {      // first MMA of each accumulator chain: c comes in undefined and leaves initialised
+                    imma_u8s8_z(c[m][0], nib4(a0), nib4(b0), nib4(a0 >> 4), nib4(b0 >> 4), xv[jj].x, xv[jj].y);
+                    imma_u8s8_z(c[m][1], nib4(a1), nib4(b1), nib4(a1 >> 4), nib4(b1 >> 4), xv[jj].z, xv[jj].w);
+                } else {
+                    imma_u8s8(c[m][0], nib4(a0), nib4(b0), nib4(a0 >> 4), nib4(b0 >> 4), xv[jj].x, xv[jj].y);
+                    imma_u8s8(c[m][1], nib4(a1), nib4(b1), nib4(a1 >> 4), nib4(b1 >> 4), xv[jj].z, xv[jj].w);
+                }
             } else {
                 const uint4& a = w[m][0][jj < QT<Q>::NI ? jj : 0];
                 const uint4& b = w[m][1][jj < QT<Q>::NI ? jj : 0];
-                imma_s8s8(c[m][0], a.x, b.x, a.y, b.y, xv[jj].x, xv[jj].y);
-                imma_s8s8(c[m][1], a.z, b.z, a.w, b.w, xv[jj].z, xv[jj].w);
+                if (jj == 0) {
+                    imma_s8s8_z(c[m][0], a.x, b.x, a.y, b.y, xv[jj].x, xv[jj].y);
+                    imma_s8s8_z(c[m][1], a.z, b.z, a.w, b.w, xv[jj].z, xv[jj].w);
+                } else {
+                    imma_s8s8(c[m][0], a.x, b.x, a.y, b.y, xv[jj].x, xv[jj].y);
+                    imma_s8s8(c[m][1], a.z, b.z, a.w, b.w, xv[jj].z, xv[jj].w);
+                }
             }
         }
     }
