@@ -7,6 +7,7 @@ the bytes really come from HBM rather than from the 126 MB L2, and the result is
 kernel has to move.
 
     python -m cuqwen_b200.microbench --model 7b --quant int4 --pos 8192 [--kernels gateup,down] [--iters 50] [--json]
+    python -m cuqwen_b200.microbench --quant int4 --gemv 4864x896        # one GEMV, HBM-cold and L2-warm
 """
 from __future__ import annotations
 
@@ -141,6 +142,33 @@ def run(model: str, quant: str, pos: int, which, iters: int, device: int = 0, ro
     return results
 
 
+def single_gemv(rows: int, cols: int, quant: str, iters: int, device: int = 0) -> list:
+    """One W.x GEMV (fp16 out), HBM-cold (rotating over copies worth three L2 sizes) and L2-warm (one copy).
+    With rows=4864, cols=896, quant=int4 this is the single W4A16 GEMV of the benchmark configurations:
+    integers uniform in [-8, 7], scales U(0.002, 0.02), x ~ N(0, 1); bytes = weights + scales + x + y."""
+    q = E.QUANT_ID[quant]
+    rng = np.random.default_rng(1234)
+    x = E.DevBuf.from_numpy(rng.standard_normal(cols).astype(np.float16), device)
+    y = E.DevBuf(rows * 2, device)
+    out = []
+    for label, rot in (("HBM-cold", 3 * L2_BYTES), ("L2-warm", 0)):
+        c = Copies(rng, rows, cols, q, rot, device)
+
+        def f():
+            w, s = c.next()
+            K.gemv(q, w, s, x, y, rows, cols, device=device)
+        for _ in range(10):
+            f()
+        E.sync(device)
+        K.bench_begin(device)
+        for _ in range(iters):
+            f()
+        us = K.bench_end(device) * 1e3 / iters
+        alg = c.bytes + cols * 2 + rows * 2
+        out.append({"kernel": f"gemv {rows}x{cols} {quant} ({label})", "us": round(us, 3), "bytes": int(alg), "gbs": round(alg / us / 1e3, 1)})
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--model", default="7b")
@@ -151,7 +179,17 @@ def main():
     ap.add_argument("--device", type=int, default=0)
     ap.add_argument("--rotate-mb", type=int, default=3 * 126)
     ap.add_argument("--json", action="store_true")
+    ap.add_argument("--gemv", default="", help="ROWSxCOLS: time one GEMV of that shape instead (e.g. 4864x896), cold and L2-warm")
     a = ap.parse_args()
+    if a.gemv:
+        rows, cols = (int(v) for v in a.gemv.lower().split("x"))
+        res = single_gemv(rows, cols, a.quant, max(a.iters, 200), a.device)
+        if a.json:
+            print(json.dumps({"quant": a.quant, "kernels": res}))
+        else:
+            for r in res:
+                print(f"  {r['kernel']:<44} {r['us']:>9.2f} us  {r['bytes'] / 1e6:>9.3f} MB  {r['gbs']:>8.1f} GB/s")
+        return
     res = run(a.model, a.quant, a.pos, set(a.kernels.split(",")), a.iters, a.device, a.rotate_mb << 20)
     if a.json:
         print(json.dumps({"model": a.model, "quant": a.quant, "pos": a.pos, "kernels": res}))
