@@ -216,6 +216,7 @@ extern "C" int cuqwen_create(const cuqwen_params* pin, cuqwen_engine** out) {
     e->q_dim_l = e->n_heads_l * p.head_dim; e->kv_dim_l = e->n_kv_l * p.head_dim;
     e->inter_l = plan.i1 - plan.i0; e->vocab_l = plan.v1 - plan.v0;
     CK(cudaDeviceGetAttribute(&e->sms, cudaDevAttrMultiProcessorCount, p.device));
+    if (const char* v = getenv("CUQWEN_ATTN_SPLITS")) { if (atoi(v) > 0) p.attn_splits = atoi(v); }      // tuning override (development aid)
     e->nsplit = p.attn_splits > 0 ? p.attn_splits : (e->sms + e->n_kv_l - 1) / e->n_kv_l;
     if (e->nsplit > kMaxSplit) e->nsplit = kMaxSplit;
     CK(cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking));
