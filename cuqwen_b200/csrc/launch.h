@@ -31,13 +31,14 @@ struct LaunchCfg {
     bool pdl;         // launch with programmatic stream serialization
 };
 
-// GEMV family.  quant: 0 fp16, 1 int8, 2 int4.  epi: cq::Epi.  Fills nsets /
-// ksplit itself.  Returns a cudaError_t value.
+// GEMV family.  quant: 0 fp16, 1 int8, 2 int4.  epi: cq::Epi.  Chooses the work split (rw, kw, gw), the staged piece
+// size and the ring depth, builds the tensor maps and launches.  Returns a cudaError_t value.
 int launch_gemv(int quant, int epi, GemvArgs& a, const LaunchCfg& cfg);
 // Tile sets (16 rows each) per CTA block that launch_gemv will choose for `nsets` tile sets.
 int gemv_tile_sets_per_block(int nsets, int sm_count, int epi);
 
-// Byte-typed 2-D tensor map of a row-major matrix: dims {row_bytes, rows}, box {piece_bytes, box_rows}.
+// Byte-typed 3-D tensor map of a row-major matrix seen as [rows][64-byte chunks]: a box of box_rows rows x piece_bytes
+// lands in shared memory chunk-major, [chunk][row][64 bytes].
 int make_weight_map(CUtensorMap* m, const void* w, size_t row_bytes, size_t rows, int piece_bytes, int box_rows);
 
 // Persistent decode-step kernel (step_kernel.cuh).  plan_step_gemv fills the work split and tensor maps of one GEMV
