@@ -112,3 +112,25 @@ def test_argmax_key_orders_like_the_sampler():
     assert keys == sorted(keys) and len({k >> 32 for k in keys[2:]}) == 4
     assert tp.pack_argmax_key(1.0, 3) > tp.pack_argmax_key(1.0, 4)           # ties go to the smaller index
     assert tp.unpack_argmax_index(tp.pack_argmax_key(1.0, 151935)) == 151935
+
+
+@pytest.mark.parametrize("size", [2, 4, 8])
+def test_shards_of_all_ranks_tile_the_model(built, size):
+    """More ranks than KV heads: ranks that share a KV head split its query heads and each keeps that head's K and V.
+    Whatever the split, the column slices of o_proj and down tile their matrices exactly once, the row slices of
+    q / gate / up / lm_head do too, and every query head sits on a rank that also holds its KV head."""
+    cfg = dict(dim=512, inter=2048, vocab=640, layers=1, heads=8, kv=2, hd=128, tied=False)
+    t = {k: v for k, v in binfmt.random_tensors(cfg, seed=11).items()}
+    pfx, hd, grp = "model.layers.0", cfg["hd"], cfg["heads"] // cfg["kv"]
+    plans = [tp.plan(cfg, r, size) for r in range(size)]
+    shards = [tp.shard_tensors(t, cfg, p) for p in plans]
+    cat = lambda name, axis: np.concatenate([s[name] for s in shards], axis=axis)
+    for name, axis in ((f"{pfx}.self_attn.q_proj.weight", 0), (f"{pfx}.self_attn.q_proj.bias", 0), (f"{pfx}.self_attn.o_proj.weight", 1),
+                       (f"{pfx}.mlp.gate_proj.weight", 0), (f"{pfx}.mlp.up_proj.weight", 0), (f"{pfx}.mlp.down_proj.weight", 1), ("lm_head.weight", 0)):
+        assert np.array_equal(cat(name, axis), t[name]), name
+    for p, s in zip(plans, shards):
+        assert p.q0 // grp >= p.kv0 and (p.q1 - 1) // grp < p.kv1                      # its query heads find their KV head locally
+        assert np.array_equal(s[f"{pfx}.self_attn.k_proj.weight"], t[f"{pfx}.self_attn.k_proj.weight"][p.kv0 * hd:p.kv1 * hd])
+        assert np.array_equal(s["model.norm.weight"], t["model.norm.weight"])          # replicated
+    kv_copies = sum(p.kv1 - p.kv0 for p in plans)
+    assert kv_copies == max(cfg["kv"], size)                                           # KV heads are replicated only when ranks outnumber them
