@@ -1,7 +1,8 @@
 """In-tree build of the CUDA library (sm_100a) and of the CPU oracle.
 
 ``build_all()`` compiles every ``csrc/*.cu`` with nvcc for ``sm_100a`` and links
-``cuqwen_b200/libcuqwen_b200.so``; it also builds ``oracle/liboracle.so`` (the
+``cuqwen_b200/libcuqwen_b200.so`` and the host-only tokenizer into
+``cuqwen_b200/libcuqwen_tok.so``; it also builds ``oracle/liboracle.so`` (the
 scalar C checker) and, when the CuQwen sources are present on this machine, the
 reference's own CUDA kernels into ``oracle/_ref/`` (see ``oracle/build_ref.py``).
 Objects go to ``build/`` and are rebuilt only when a source or header is newer.
@@ -20,6 +21,8 @@ OBJ = ROOT / "build" / "obj"
 LIB = ROOT / "cuqwen_b200" / "libcuqwen_b200.so"
 ORACLE_SRC = ROOT / "oracle" / "oracle.c"
 ORACLE_LIB = ROOT / "oracle" / "liboracle.so"
+TOK_SRC = CSRC / "tokenizer.cpp"
+TOK_LIB = ROOT / "cuqwen_b200" / "libcuqwen_tok.so"
 GEN_SRC = CSRC / "gen_random_bin.cpp"
 GEN_BIN = ROOT / "cuqwen_b200" / "gen_random_bin"
 
@@ -48,7 +51,7 @@ def _run(cmd, log: Path | None = None):
 
 def build_cuda(verbose: bool = False) -> Path:
     OBJ.mkdir(parents=True, exist_ok=True)
-    headers = list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")) + [ROOT / "include" / "cuqwen_b200.h"]
+    headers = list(CSRC.glob("*.cuh")) + [h for h in CSRC.glob("*.h") if h.name != "unicode_tables.h"] + [ROOT / "include" / "cuqwen_b200.h"]
     srcs = sorted(CSRC.glob("*.cu"))
     jobs = []
     for s in srcs:
@@ -77,6 +80,14 @@ def build_oracle() -> Path:
     return ORACLE_LIB
 
 
+def build_tokenizer() -> Path:
+    """The tokenizer is host code with no CUDA in it: a library of its own (include/cuqwen_tokenizer.h)."""
+    deps = [TOK_SRC, CSRC / "unicode_tables.h", ROOT / "include" / "cuqwen_tokenizer.h"]
+    if _newer(TOK_LIB, deps):
+        _run(["g++", "-O2", "-std=c++17", "-Wall", "-shared", "-fPIC", str(TOK_SRC), "-o", str(TOK_LIB)])
+    return TOK_LIB
+
+
 def build_gen() -> Path:
     if GEN_SRC.exists() and _newer(GEN_BIN, [GEN_SRC]):
         _run(["g++", "-O3", "-std=c++17", "-pthread", str(GEN_SRC), "-o", str(GEN_BIN)])
@@ -86,6 +97,7 @@ def build_gen() -> Path:
 def build_all(verbose: bool = False) -> None:
     build_cuda(verbose)
     build_gen()
+    build_tokenizer()
     build_oracle()
     ref = ROOT / "oracle" / "build_ref.py"
     if ref.exists() and Path("/root/reference/src/kernels.cu").exists():

@@ -1,0 +1,303 @@
+"""The tokenizer (libcuqwen_tok.so, include/cuqwen_tokenizer.h) against the step-by-step restatement of the
+reference's QwenTokenizer in oracle/tokenizer_py.py, on a synthetic vocabulary: the real ranks file is produced from a
+downloaded checkpoint and is not available offline.  Ids are bit-exact or the test fails."""
+import collections
+import ctypes as C
+import json
+import re
+import subprocess
+import unicodedata
+from pathlib import Path
+
+import pytest
+from hypothesis import HealthCheck, given, settings
+from hypothesis import strategies as st
+
+from cuqwen_b200 import build
+from cuqwen_b200 import tokenizer as T
+from oracle import tokenizer_py as O
+
+ROOT = Path(__file__).resolve().parent.parent
+HEADER = (ROOT / "include" / "cuqwen_tokenizer.h").read_text()
+
+# Made-up text that exercises every branch of the pre-tokenising pattern.
+CORPUS = [
+    "The quick brown fox doesn't jump; it's 12345 o'clock and we'll see, they've said, I'm sure he'd go. You're right",
+    "UPPER'S CASE'LL WE'VE I'M HE'D CAN'T YOU'RE",
+    "tabs\tand\t\tmore\ttabs, trailing spaces   \nnew line\r\nCRLF line\n\n\nthree blank    \n   indented",
+    "   leading spaces and a trailing one ",
+    "punctuation!!! ... (brackets) [square] {curly} <angle> #hash $dollar %percent ^caret &amp *star",
+    " !lead-space-punct\n\n ?again\r\n",
+    "日本語のテキストと漢字、かな、カナ。数字は１２３と٤٥٦と789。",
+    "Ελληνικά Кириллица עברית العربية हिन्दी ไทย 한국어",
+    "mixed émigré naïve façade Ærøskøbing ſtraße 'ſ",
+    "emoji 🎉🎊 and flags 🇯🇵 and zwj 👩‍👩‍👧 ok",
+    "no-break space, ideographic　space, thin space, line sep, para sep, nel\u0085x, mvs᠎x",
+    "x = y**2 + 3.14159*z - 1e-9; // comment\n\tif (a != b) { return a <= b ? a : b; }\n",
+    "a", " ", "\n", "'", "''s", "1", " 1", "  1", "a1b2", "'s", " 's", "x's", "\r", "\r\r\n", " \r\n \r\n", "\n \n a",
+    "²³ superscripts ½ fraction Ⅻ roman ① circled",
+    "control\x01chars\x1f\x7fhere\x00end",
+]
+
+
+def assigned(cp: int) -> bool:
+    return unicodedata.category(chr(cp)) not in ("Cn", "Cs")
+
+
+def train_vocab(texts, n_merges: int) -> dict:
+    """A small byte-level BPE vocabulary in the ranks file's convention: ids 0..255 are the byte symbols, every
+    merge after that takes the next id (so rank == id)."""
+    alpha = O.byte_alphabet()
+    vocab = {alpha[b]: i for i, b in enumerate(sorted(alpha))}
+    words = collections.Counter()
+    for t in texts:
+        for piece in O.pretokenize(t.encode("utf-8")):
+            words[tuple(alpha[b] for b in piece)] += 1
+    for _ in range(n_merges):
+        pairs = collections.Counter()
+        for w, c in words.items():
+            for a, b in zip(w, w[1:]):
+                pairs[(a, b)] += c
+        if not pairs:
+            break
+        (a, b), _cnt = max(pairs.items(), key=lambda kv: (kv[1], kv[0]))
+        if a + b in vocab:
+            break
+        vocab[a + b] = len(vocab)
+        merged = collections.Counter()
+        for w, c in words.items():
+            out, i = [], 0
+            while i < len(w):
+                if i + 1 < len(w) and w[i] == a and w[i + 1] == b:
+                    out.append(a + b)
+                    i += 2
+                else:
+                    out.append(w[i])
+                    i += 1
+            merged[tuple(out)] += c
+        words = merged
+    return vocab
+
+
+@pytest.fixture(scope="module")
+def ranks(tmp_path_factory):
+    build.build_tokenizer()
+    vocab = train_vocab(CORPUS, 400)
+    n = len(vocab)
+    # "<|endoftext|>" is also given a vocabulary entry (then decode returns the literal); the others are not,
+    # as in the exported Qwen2.5 files (then decode returns nothing for them)
+    vocab["<|endoftext|>"] = n
+    added = {str(n): "<|endoftext|>", str(n + 1): "<|im_start|>", str(n + 2): "<|im_end|>", str(n + 3): "<|fim|>", str(n + 4): "<|fim|><|pad|>"}
+    path = tmp_path_factory.mktemp("tok") / "ranks.json"
+    with open(path, "w", encoding="utf-8") as f:
+        json.dump({"vocab": vocab, "special_tokens": {"eos_token": "<|endoftext|>"}, "added_tokens": added}, f, ensure_ascii=False, indent=2)
+    return path
+
+
+@pytest.fixture(scope="module")
+def toks(ranks):
+    t = T.QwenTokenizer(ranks)
+    yield t, O.OracleTokenizer(ranks)
+    t.close()
+
+
+def declared_symbols():
+    return sorted(set(re.findall(r"\b(cuqwen_tok_[a-z0-9_]+)\s*\(", HEADER)))
+
+
+def test_library_exports_what_the_header_declares(ranks):
+    assert declared_symbols() == sorted(T.SIGNATURES)
+    raw = C.CDLL(str(T.LIB_PATH))
+    for name in declared_symbols():
+        assert hasattr(raw, name), name
+
+
+def test_entry_points_cite_the_reference():
+    for name in ("cuqwen_tok_open", "cuqwen_tok_encode", "cuqwen_tok_decode", "cuqwen_tok_chat_template", "cuqwen_tok_pretokenize"):
+        idx = HEADER.index(name + "(")
+        assert re.search(r"src/tokenizer\.cpp:\d+", HEADER[max(0, idx - 700):idx]), name
+
+
+@pytest.mark.parametrize("text", CORPUS)
+def test_pretokenizer_matches_the_pattern(ranks, text):
+    assert T.pretokenize(text) == O.pretokenize(text.encode("utf-8"))
+
+
+def test_pretokenizer_known_splits(ranks):
+    # worked out by hand from the pattern's alternatives
+    assert T.pretokenize("Hello, world!  It's 42.\n\n  x") == [b"Hello", b",", b" world", b"!", b" ", b" It", b"'s", b" ", b"4", b"2", b".\n\n", b" ", b" x"]
+    assert T.pretokenize("a  \n  b") == [b"a", b"  \n", b" ", b" b"]
+    assert T.pretokenize("end   ") == [b"end", b"   "]
+    assert T.pretokenize("I'LL") == [b"I", b"'LL"]
+    assert T.pretokenize("\tfoo") == [b"\tfoo"]
+    assert T.pretokenize("\nfoo") == [b"\n", b"foo"]
+    assert T.pretokenize(" ...\r\nx") == [b" ...\r\n", b"x"]
+    assert T.pretokenize("") == []
+
+
+def test_every_assigned_code_point_is_classified_like_the_pattern(ranks):
+    # one probe string per code point: "a" + c + "a" splits differently for letters, numbers, white space and the rest
+    bad = []
+    for cp in range(0x110000):
+        if not assigned(cp):
+            continue
+        s = "a" + chr(cp) + "a"
+        if T.pretokenize(s) != O.pretokenize(s.encode("utf-8")):
+            bad.append(hex(cp))
+    # the tables here are Unicode 15.0; the `regex` module may know a later version that reclassified a few characters
+    assert len(bad) <= 32, bad[:50]
+
+
+def test_pretokenizer_agrees_with_the_tokenizers_package(ranks):
+    tk = pytest.importorskip("tokenizers")
+    pat = r"(?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\r\n\p{L}\p{N}]?\p{L}+|\p{N}| ?[^\s\p{L}\p{N}]+[\r\n]*|\s*[\r\n]+|\s+(?!\S)|\s+"
+    split = tk.pre_tokenizers.Split(tk.Regex(pat), behavior="isolated", invert=False)
+    for text in CORPUS:
+        if "᠎" in text or "\x1f" in text:
+            continue       # that engine's \s differs from PCRE2's on U+180E and on the C0 separators
+        want = [p.encode("utf-8") for p, _ in split.pre_tokenize_str(text)]
+        assert T.pretokenize(text) == want, text
+
+
+@pytest.mark.parametrize("raw", [b"ab\xffcd", b"\xc0\xaf", b"\xed\xa0\x80", b"\xf4\x90\x80\x80", b"abc\xe3\x81", b"\xf8\x88\x80\x80\x80"])
+def test_invalid_utf8_yields_nothing(toks, raw):
+    t, o = toks
+    assert T.pretokenize(raw) == [] == O.pretokenize(raw)
+    assert t.encode(raw) == [] == o.encode(raw)
+    # a special token still cuts the text, and the valid stretch after it is encoded
+    both = raw + b"<|im_end|>ok"
+    assert t.encode(both) == o.encode(both) and len(t.encode(both)) >= 2
+
+
+@pytest.mark.parametrize("text", CORPUS)
+def test_encode_matches_the_restatement(toks, text):
+    t, o = toks
+    ids = t.encode(text)
+    assert ids == o.encode(text.encode("utf-8"))
+    assert t.decode_bytes(ids) == text.encode("utf-8") == o.decode(ids)
+
+
+def test_merges_shorten_the_corpus(toks):
+    t, _ = toks
+    text = " ".join(CORPUS[:3])
+    assert len(t.encode(text)) < 0.7 * len(text.encode("utf-8"))
+
+
+def test_special_tokens(toks, ranks):
+    t, o = toks
+    n = t.vocab_size - 1      # id of <|endoftext|>
+    assert t.special_count == 5
+    cases = [
+        "<|im_start|>user\nhi<|im_end|>\n<|im_start|>assistant\n",
+        "<|fim|><|pad|><|fim|>x<|fim|><|pad|>",         # the longer literal wins where both start
+        "<|endoftext|><|endoftext|>", "a<|im_end|", "<|im_start|", "<<|im_end|>>", "<|im_end|><|unknown|>",
+    ]
+    for c in cases:
+        assert t.encode(c) == o.encode(c.encode()), c
+    assert t.encode("<|fim|><|pad|><|fim|>") == [n + 4, n + 3]
+    assert t.encode("<|endoftext|>") == [n]
+    # decode: a special token that has a vocabulary entry comes back literally, one without contributes nothing
+    assert t.decode_single(n) == b"<|endoftext|>" == o.decode_single(n)
+    assert t.decode_single(n + 1) == b"" == o.decode_single(n + 1)
+    assert t.decode_single(10**6) == b"" and t.decode_single(-5) == b""
+
+
+def test_chat_template(toks):
+    t, _ = toks
+    msgs = [T.Message("system", "You are a helpful assistant."), T.Message("user", "Hi ✓\nthere")]
+    want = O.chat_template([(m.role, m.content) for m in msgs], True)
+    assert t.apply_chat_template(msgs) == want
+    assert want.endswith("<|im_end|>\n<|im_start|>assistant\n")
+    assert T.apply_chat_template(msgs, False) == O.chat_template([(m.role, m.content) for m in msgs], False)
+    assert T.apply_chat_template([], True) == "<|im_start|>assistant\n" and T.apply_chat_template([], False) == ""
+
+
+_text = st.text(alphabet=st.one_of(
+    st.sampled_from(list(" \t\n\r'.,!?-_()[]0123456789sStTmMdDlLrReEvV 　 \u0085")),
+    st.characters(min_codepoint=0x20, max_codepoint=0x2FFF, exclude_categories=("Cn", "Cs")),
+    st.characters(min_codepoint=0x3000, max_codepoint=0x1FAFF, exclude_categories=("Cn", "Cs", "Co")),
+), max_size=48)
+
+
+@settings(max_examples=300, deadline=None, suppress_health_check=[HealthCheck.function_scoped_fixture, HealthCheck.too_slow])
+@given(text=_text)
+def test_random_text(toks, text):
+    t, o = toks
+    raw = text.encode("utf-8")
+    assert T.pretokenize(raw) == O.pretokenize(raw)
+    ids = t.encode(raw)
+    assert ids == o.encode(raw)
+    assert t.decode_bytes(ids) == raw
+
+
+def test_long_runs_finish_quickly(toks):
+    t, _ = toks
+    text = "=" * 20000 + " " * 20000 + "word " * 20000 + "9" * 20000
+    ids = t.encode(text)
+    assert t.decode_bytes(ids) == text.encode()
+
+
+def test_open_errors(tmp_path, ranks):
+    with pytest.raises(T.TokenizerError) as e:
+        T.QwenTokenizer(tmp_path / "absent.json")
+    assert e.value.code == T.E_IO and "Cannot open JSON file: " in str(e.value)
+    for i, text in enumerate(['{"vocab": {"a": 1,}}', '{"vocab": {"a": "x"}}', '{"vocab": {"a": 1}', '[1, 2]', '{"vocab": {"\\ud800": 1}}', '{"added_tokens": {"x": "<|a|>"}}', ""]):
+        p = tmp_path / f"bad{i}.json"
+        p.write_text(text)
+        with pytest.raises(T.TokenizerError) as e:
+            T.QwenTokenizer(p)
+        assert e.value.code == T.E_PARSE, text
+
+
+def test_json_escapes_and_other_keys(tmp_path):
+    alpha = O.byte_alphabet()
+    vocab = {alpha[b]: b for b in range(256)}
+    p = tmp_path / "esc.json"
+    # ASCII-only JSON (every non-ASCII symbol as \uXXXX), a surrogate pair, nested values under an ignored key
+    doc = {"ignored": [1, 2.5e3, True, None, {"deep": ["x", {}]}], "vocab": dict(vocab, **{"\U0001F600": 300, "q\"\\\n": 301}), "added_tokens": {"302": "<|té|>"}}
+    p.write_text(json.dumps(doc, ensure_ascii=True))
+    with T.QwenTokenizer(p) as t:
+        o = O.OracleTokenizer(p)
+        assert t.vocab_size == 258 and t.special_count == 1
+        for text in ("héllo <|té|> \x00\xff", "abc"):
+            assert t.encode(text) == o.encode(text.encode("utf-8"))
+        assert t.encode("<|té|>") == [302]
+        assert t.decode_single(300) == "\U0001F600".encode("utf-8") == o.decode_single(300)
+
+
+def test_small_buffers_report_the_size_needed(ranks):
+    lib = T.lib()
+    h = C.c_void_p()
+    assert lib.cuqwen_tok_open(str(ranks).encode(), C.byref(h)) == 0
+    text = b"hello world, hello"
+    n = C.c_size_t(0)
+    ids = (C.c_int * 64)()
+    assert lib.cuqwen_tok_encode(h, text, len(text), ids, 1, C.byref(n)) == T.E_SPACE and n.value > 1
+    need = n.value
+    assert lib.cuqwen_tok_encode(h, text, len(text), ids, need, C.byref(n)) == 0 and n.value == need
+    out = C.create_string_buffer(64)
+    assert lib.cuqwen_tok_decode(h, ids, need, out, 3, C.byref(n)) == T.E_SPACE and n.value == len(text)
+    assert lib.cuqwen_tok_decode(h, ids, need, out, 64, C.byref(n)) == 0 and out.raw[:n.value] == text
+    assert lib.cuqwen_tok_encode(None, text, len(text), ids, 64, C.byref(n)) == T.E_ARG
+    assert lib.cuqwen_tok_encode(h, b"", 0, ids, 64, C.byref(n)) == 0 and n.value == 0
+    lib.cuqwen_tok_close(h)
+    lib.cuqwen_tok_close(None)
+
+
+def test_reference_style_program_builds_against_the_compat_header(toks, ranks, tmp_path):
+    t, _ = toks
+    exe = tmp_path / "tokenizer_probe"
+    cmd = ["g++", "-std=c++17", f"-I{ROOT / 'include' / 'compat'}", str(ROOT / "tests" / "tokenizer_probe.cpp"), "-o", str(exe),
+           f"-L{ROOT / 'cuqwen_b200'}", "-lcuqwen_tok", f"-Wl,-rpath,{ROOT / 'cuqwen_b200'}"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    user = "What's 2+2?\nThanks <|endoftext|>"
+    r = subprocess.run([str(exe), str(ranks), user], capture_output=True)
+    assert r.returncode == 0, r.stderr
+    first, rest = r.stdout.split(b"\n", 1)
+    prompt = T.apply_chat_template([T.Message("system", "You are a helpful assistant."), T.Message("user", user)], True)
+    want = t.encode(prompt)
+    assert [int(x) for x in first.split()] == want
+    assert rest == t.decode_bytes(want)
+    r = subprocess.run([str(exe), str(tmp_path / "nope.json")], capture_output=True, text=True)
+    assert r.returncode == 3 and r.stdout.startswith("Cannot open JSON file: ")
