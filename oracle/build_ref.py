@@ -8,7 +8,15 @@ path never calls); only ``ref_wrap.cu`` of this repository is added.  Flags
 follow the reference's CMakeLists.txt:105 (``-O3 --use_fast_math``), the
 architecture is sm_100a.
 
-Usage: python oracle/build_ref.py [--ref <CuQwen checkout>] [--only 7b:int4,0.5b:fp16]
+It also builds the reference's own PROGRAMS into oracle/_ref/apps/, each from its unmodified source file:
+  chat_b200_<m>_<q>, benchmark_b200_<m>_<q>, kernel_profile_b200_<m>_<q>
+      src/main.cu, benchmark/cuqwen_benchmark.cu, benchmark/kernel_profile.cu compiled against this repository's
+      source-compatible headers (include/compat) and linked to libcuqwen_b200.so / libcuqwen_tok.so: the drop-in check;
+  benchmark_ref_<m>_<q>
+      benchmark/cuqwen_benchmark.cu with the reference's own kernels.cu, model.cu, load_weights.cpp: the stock
+      program, for a like-for-like run under the reference's own measuring protocol.
+
+Usage: python oracle/build_ref.py [--ref <CuQwen checkout>] [--only 7b:int4,0.5b:fp16] [--no-apps]
 """
 from __future__ import annotations
 
@@ -48,10 +56,52 @@ def build_one(ref: Path, model: str, quant: str) -> Path:
     return out
 
 
+APPS = [("0.5b", "int4"), ("7b", "int4")]
+ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
+
+
+def app_path(kind: str, model: str, quant: str) -> Path:
+    return OUT / "apps" / f"{kind}_{model.replace('.', '_')}_{quant}"
+
+
+def _nvcc(cmd, what: str) -> None:
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        sys.stderr.write(r.stdout + r.stderr)
+        raise RuntimeError(f"reference program build failed: {what}")
+
+
+def build_apps(ref: Path, model: str, quant: str) -> list[Path]:
+    """The reference's programs for one (model, quant); skipped when this repository's libraries are not built yet."""
+    libdir = ROOT / "cuqwen_b200"
+    if not (libdir / "libcuqwen_b200.so").exists() or not (libdir / "libcuqwen_tok.so").exists():
+        return []
+    (OUT / "apps").mkdir(parents=True, exist_ok=True)
+    defs = [f"-D{MODEL_DEF[model]}"] + ([f"-D{QUANT_DEF[quant]}"] if QUANT_DEF[quant] else [])
+    compat = [ROOT / "include" / "cuqwen_compat.hpp", ROOT / "include" / "cuqwen_b200.h", ROOT / "include" / "cuqwen_tokenizer.h",
+              ROOT / "include" / "compat" / "tokenizer.h"]
+    built = []
+    ours = {"chat_b200": ref / "src" / "main.cu", "benchmark_b200": ref / "benchmark" / "cuqwen_benchmark.cu",
+            "kernel_profile_b200": ref / "benchmark" / "kernel_profile.cu"}
+    for kind, src in ours.items():
+        out = app_path(kind, model, quant)
+        if not (out.exists() and all(out.stat().st_mtime > d.stat().st_mtime for d in [src, *compat])):
+            _nvcc(["nvcc", "-O2", "-std=c++17", *ARCH, "-diag-suppress", "177", *defs, "-I", str(ROOT / "include" / "compat"), str(src), "-o", str(out),
+                   "-L", str(libdir), "-lcuqwen_b200", "-lcuqwen_tok", "-Xlinker", "-rpath=$ORIGIN/../../../cuqwen_b200"], out.name)
+        built.append(out)
+    out = app_path("benchmark_ref", model, quant)
+    srcs = [ref / "src" / "kernels.cu", ref / "src" / "model.cu", ref / "src" / "load_weights.cpp", ref / "benchmark" / "cuqwen_benchmark.cu"]
+    if not (out.exists() and all(out.stat().st_mtime > d.stat().st_mtime for d in srcs)):
+        _nvcc(["nvcc", "-O3", "--use_fast_math", "-std=c++17", *ARCH, "-x", "cu", *defs, "-I", str(ref / "include"), *map(str, srcs), "-o", str(out)], out.name)
+    built.append(out)
+    return built
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", default="/root/reference")
     ap.add_argument("--only", default="")
+    ap.add_argument("--no-apps", action="store_true")
     a = ap.parse_args()
     ref = Path(a.ref)
     if not (ref / "src" / "kernels.cu").exists():
@@ -62,6 +112,10 @@ def main() -> None:
     with ThreadPoolExecutor(max_workers=4) as ex:
         for p in ex.map(lambda mq: build_one(ref, *mq), todo):
             print("built", p.name)
+        if not a.no_apps:
+            for ps in ex.map(lambda mq: build_apps(ref, *mq), APPS):
+                for p in ps:
+                    print("built", p.name)
 
 
 if __name__ == "__main__":

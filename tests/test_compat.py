@@ -47,3 +47,23 @@ def test_reference_style_program_runs(built, tmpdir_big):
     eng.close()
     path.unlink()
     assert int(r.stdout.strip().splitlines()[-1]) == tok
+
+
+def test_the_references_own_programs_build_against_the_compat_headers(built, tmp_path):
+    """src/main.cu, benchmark/cuqwen_benchmark.cu and benchmark/kernel_profile.cu, unmodified, with -Iinclude/compat
+    (forwarding headers config.h / load_weights.h / model.cuh / kernels.cuh / tokenizer.h).  Needs the CuQwen
+    checkout, so it is skipped where that is absent."""
+    import importlib.util
+    import shutil
+    spec = importlib.util.spec_from_file_location("build_ref", ROOT / "oracle" / "build_ref.py")
+    build_ref = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(build_ref)
+    ref = Path("/root/reference")
+    if not (ref / "src" / "main.cu").exists() or shutil.which("nvcc") is None:
+        pytest.skip("no CuQwen checkout on this machine")
+    build.build_tokenizer()
+    apps = build_ref.build_apps(ref, "0.5b", "int4")
+    assert {p.name for p in apps} == {"chat_b200_0_5b_int4", "benchmark_b200_0_5b_int4", "kernel_profile_b200_0_5b_int4", "benchmark_ref_0_5b_int4"}
+    # the chat program starts, and without its ranks file stops with the reference's message
+    r = subprocess.run([str(build_ref.app_path("chat_b200", "0.5b", "int4"))], capture_output=True, text=True, cwd=tmp_path, stdin=subprocess.DEVNULL)
+    assert r.returncode != 0 and "Cannot open JSON file: weights/qwen25_bpe_ranks.json" in r.stderr
