@@ -301,3 +301,47 @@ def test_reference_style_program_builds_against_the_compat_header(toks, ranks, t
     assert rest == t.decode_bytes(want)
     r = subprocess.run([str(exe), str(tmp_path / "nope.json")], capture_output=True, text=True)
     assert r.returncode == 3 and r.stdout.startswith("Cannot open JSON file: ")
+
+
+_key = st.text(alphabet=st.one_of(st.sampled_from(list("ab<>|\"\\/\n\t é😀")), st.characters(min_codepoint=1, max_codepoint=0x2FF, exclude_categories=("Cs",))), min_size=1, max_size=6)
+
+
+@settings(max_examples=100, deadline=None, suppress_health_check=[HealthCheck.function_scoped_fixture, HealthCheck.too_slow])
+@given(keys=st.lists(_key, unique=True, max_size=12), ascii_only=st.booleans(), indent=st.sampled_from([None, 0, 2]),
+       junk=st.recursive(st.one_of(st.none(), st.booleans(), st.integers(-10**6, 10**6), st.floats(allow_nan=False, allow_infinity=False), st.text(max_size=5)),
+                         lambda c: st.one_of(st.lists(c, max_size=3), st.dictionaries(st.text(max_size=4), c, max_size=3)), max_leaves=8))
+def test_json_reader_agrees_with_pythons_on_generated_ranks_files(tmp_path_factory, keys, ascii_only, indent, junk):
+    # whatever the JSON writer's escaping and layout, the same vocabulary comes out: checked through decode
+    alpha = O.byte_alphabet()
+    vocab = {alpha[b]: b for b in range(256)}
+    for i, k in enumerate(keys):
+        vocab.setdefault(k, 256 + i)
+    p = tmp_path_factory.mktemp("j") / "r.json"
+    p.write_text(json.dumps({"other": junk, "vocab": vocab, "added_tokens": {"999": "<|x|>"}, "more": [junk]}, ensure_ascii=ascii_only, indent=indent), encoding="utf-8")
+    with T.QwenTokenizer(p) as t:
+        o = O.OracleTokenizer(p)
+        assert t.vocab_size == len(vocab) and t.special_count == 1
+        ids = sorted(set(vocab.values()))
+        assert [t.decode_single(i) for i in ids] == [o.decode_single(i) for i in ids]
+        text = "ab<|x|>" + "".join(keys)
+        assert t.encode(text) == o.encode(text.encode("utf-8"))
+
+
+def test_one_tokenizer_serves_several_threads(toks):
+    import threading
+    t, _ = toks
+    texts = [c * 50 for c in CORPUS[:8]]
+    want = [t.encode(x) for x in texts]
+    errors = []
+
+    def work(k):
+        for _ in range(20):
+            if t.encode(texts[k]) != want[k] or t.decode_bytes(want[k]) != texts[k].encode("utf-8"):
+                errors.append(k)
+
+    threads = [threading.Thread(target=work, args=(k,)) for k in range(len(texts))]
+    for th in threads:
+        th.start()
+    for th in threads:
+        th.join()
+    assert not errors
