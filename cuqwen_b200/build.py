@@ -70,7 +70,9 @@ def build_cuda(verbose: bool = False) -> Path:
                 print("compiled", name)
     objs = [OBJ / (s.stem + ".o") for s in srcs]
     if _newer(LIB, objs):
-        _run(["nvcc", "-shared", "-o", str(LIB), *map(str, objs), "-lcudart", "-ldl"])
+        tmp = LIB.with_suffix(".so.tmp")     # link aside and rename: a reader never sees a half-written library
+        _run(["nvcc", "-shared", "-o", str(tmp), *map(str, objs), "-lcudart", "-ldl"])
+        os.replace(tmp, LIB)
     return LIB
 
 
