@@ -13,7 +13,7 @@ namespace cq {
 
 constexpr int kSplitWarps = 8;                                  // consumer warps of the partial kernel
 constexpr int kSplitThreads = (kSplitWarps + 1) * 32;
-constexpr int kSplitStages = 4;
+constexpr int kSplitStages = 4;    // six stages (they fit) measured no faster: the consumers, not the copies, set the pace
 constexpr int kFoldWarps = 16;
 
 inline size_t attn_split_smem_bytes(int hd, int stages) { return (size_t)stages * 2 * kAttnStageKeys * hd * 2 + 128; }

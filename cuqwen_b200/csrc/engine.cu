@@ -82,7 +82,7 @@ extern "C" int cuqwen_model_params(int model_id, int quant, cuqwen_params* p) {
 // ---------------------------------------------------------------------------
 // per-device context for the stand-alone kernel entry points
 // ---------------------------------------------------------------------------
-struct DevCtx { bool init = false; cudaStream_t stream = nullptr; int sms = 0; cudaEvent_t ev0 = nullptr, ev1 = nullptr; unsigned* err = nullptr; unsigned* h_err = nullptr; };
+struct DevCtx { bool init = false; cudaStream_t stream = nullptr; int sms = 0; cudaEvent_t ev0 = nullptr, ev1 = nullptr, ev_join = nullptr; unsigned* err = nullptr; unsigned* h_err = nullptr; };
 // device word that kernels launched by the calling thread report an expired bounded wait to
 static thread_local unsigned* t_err = nullptr;
 static DevCtx g_dev[64];
@@ -96,6 +96,7 @@ static int dev_ctx(int device, DevCtx** out) {
         CK(cudaStreamCreateWithFlags(&d.stream, cudaStreamNonBlocking));
         CK(cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, device));
         CK(cudaEventCreate(&d.ev0)); CK(cudaEventCreate(&d.ev1));
+        CK(cudaEventCreateWithFlags(&d.ev_join, cudaEventDisableTiming));
         CK(cudaMalloc((void**)&d.err, 4)); CK(cudaMemset(d.err, 0, 4)); CK(cudaMallocHost((void**)&d.h_err, 4));
         d.init = true;
     }
@@ -857,6 +858,17 @@ extern "C" int cuqwen_dev_sync(int device) {
     CK(cudaMemcpyAsync(dc->h_err, dc->err, 4, cudaMemcpyDeviceToHost, dc->stream));
     CK(cudaStreamSynchronize(dc->stream)); CK(cudaGetLastError());
     if (*dc->h_err) { unsigned c = *dc->h_err; CK(cudaMemset(dc->err, 0, 4)); return fail(CUQWEN_ERR_TIMEOUT, "a bounded device-side wait expired (code %u)", c); }
+    return CUQWEN_OK;
+}
+// Orders the library's per-device stream against a caller's stream (0 = the legacy default stream):
+// leave == 0: work queued from now on through cuqwen_k_* waits for what the caller's stream holds so far;
+// leave != 0: what the caller queues on its stream from now on waits for the cuqwen_k_* work queued so far.
+extern "C" int cuqwen_dev_join(int device, void* caller_stream, int leave) {
+    DEV(device); (void)cfg;
+    cudaStream_t from = leave ? dc->stream : (cudaStream_t)caller_stream;
+    cudaStream_t to = leave ? (cudaStream_t)caller_stream : dc->stream;
+    CK(cudaEventRecord(dc->ev_join, from));
+    CK(cudaStreamWaitEvent(to, dc->ev_join, 0));
     return CUQWEN_OK;
 }
 extern "C" int cuqwen_bench_begin(int device) { DEV(device); (void)cfg; CK(cudaEventRecord(dc->ev0, dc->stream)); return CUQWEN_OK; }

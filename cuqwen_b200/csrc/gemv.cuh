@@ -11,7 +11,7 @@
 // matrix are zero-filled by the TMA unit.  Eight consumer warps, each owning 16 output rows (x MT matrices) of a block
 // and a share of K, read their fragments from the stages and run the tensor-core inner product of gemv_math.cuh.
 //
-// Every wait on an mbarrier is bounded (about two seconds of wall time); when it expires the kernel records a code
+// Every wait on an mbarrier is bounded (4e9 SM cycles, two to four seconds); when it expires the kernel records a code
 // in *err, stops waiting and finishes with meaningless numbers rather than hanging.
 #pragma once
 #include <cuda.h>

@@ -79,7 +79,7 @@ __device__ __forceinline__ float park_raw(const __half* x, const __half* norm_w,
 // Tensor-parallel consumer side of an exchange (see GemvArgs): what park_raw does, for x_new = half(float(x) + sum over
 // ranks of the fp32 partials in this rank's receive slots), summed in rank order so every rank forms the same bits.
 // A slot word is {value bits, sequence number}; a word whose number is not `seq` yet has not arrived and is read again
-// (bounded: after about two seconds *err is set and the stale value is used).
+// (bounded: after 4e9 SM cycles, two to four seconds, *err is set and the stale value is used).
 // store_next: this CTA also writes x_new to global memory for the kernels after this one.
 struct GatherSrc {
     const uint2* slots;      // [n][K] words
@@ -123,8 +123,9 @@ __device__ __forceinline__ float park_gather(const __half* x, const __half* norm
                         for (int i = 0; i < 4; ++i) ok = ok && q[j][i].y == gs.seq && q[j][i].w == gs.seq;
                     }
                 if (ok || gave_up) break;
-                if (t0 == 0ull) t0 = global_ns();
-                else if (global_ns() - t0 > 2000000000ull) { gave_up = true; if (gs.err) atomicExch(gs.err, 8u); break; }
+                const unsigned long long now = (unsigned long long)sm_cycles();      // the SM's cycle counter: cheap to read
+                if (t0 == 0ull) t0 = now | 1ull;
+                else if (now - t0 > 4000000000ull) { gave_up = true; if (gs.err) atomicExch(gs.err, 8u); break; }
             }
 #pragma unroll
             for (int j = 0; j < RB; ++j)

@@ -211,8 +211,9 @@ __global__ void tp_sum_kernel(const __half* __restrict__ x, __half* __restrict__
                     for (int i = 0; i < 4; ++i) ok = ok && q[j][i].y == seq && q[j][i].w == seq;
                 }
             if (ok || gave_up) break;
-            if (t0 == 0ull) t0 = global_ns();
-            else if (global_ns() - t0 > 2000000000ull) { gave_up = true; if (err) atomicExch(err, 8u); break; }
+            const unsigned long long now = (unsigned long long)sm_cycles();      // the SM's cycle counter: cheap to read
+            if (t0 == 0ull) t0 = now | 1ull;
+            else if (now - t0 > 4000000000ull) { gave_up = true; if (err) atomicExch(err, 8u); break; }
         }
 #pragma unroll
         for (int j = 0; j < 4; ++j)

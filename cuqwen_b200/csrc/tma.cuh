@@ -20,14 +20,19 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
     return ok;
 }
 __device__ __forceinline__ unsigned long long global_ns() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
-// Bounded wait: false when the phase did not complete within ~2 s.
+__device__ __forceinline__ long long sm_cycles() { long long t; asm volatile("mov.u64 %0, %clock64;" : "=l"(t)); return t; }
+// Bounded wait: false when the phase did not complete within about 4e9 SM cycles (2 to 4 s at the clocks this part
+// runs at).  The bound is kept on the SM's own cycle counter: a %globaltimer read is a long-latency operation, and
+// one on every wait that does not succeed at once delays the moment the waiting warp sees the phase complete.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     if (mbar_try_wait(bar, parity)) return true;
-    const unsigned long long t0 = global_ns();
+    long long t0 = 0;
     for (;;) {
 #pragma unroll 1
         for (int i = 0; i < 64; ++i) if (mbar_try_wait(bar, parity)) return true;
-        if (global_ns() - t0 > 2000000000ull) return false;
+        const long long now = sm_cycles();
+        if (t0 == 0) t0 = now;
+        else if (now - t0 > 4000000000ll) return false;
     }
 }
 // global -> shared bulk copy; completion is signalled on `bar` with the byte count.  dst, src and bytes are multiples of 16.

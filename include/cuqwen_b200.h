@@ -128,6 +128,12 @@ int cuqwen_dev_upload(int device, void* dev_dst, const void* host_src, size_t by
 int cuqwen_dev_download(int device, void* host_dst, const void* dev_src, size_t bytes);
 int cuqwen_dev_memset(int device, void* dev_ptr, int value, size_t bytes);
 int cuqwen_dev_sync(int device);
+/* Stream ordering between a caller's CUDA stream (a cudaStream_t; NULL = the legacy default stream) and the
+ * library's per-device stream that the cuqwen_k_* calls queue on.  leave == 0: later cuqwen_k_* work waits for what
+ * the caller's stream holds now; leave != 0: later work on the caller's stream waits for the cuqwen_k_* work queued
+ * so far.  The reference's launch_* take the stream as an argument (include/kernels.cuh:19-160); a binding that
+ * wraps each call in join(0) ... join(1) keeps that meaning. */
+int cuqwen_dev_join(int device, void* caller_stream, int leave);
 /* CUDA events on the library's per-device stream, to time a sequence of cuqwen_k_* calls from a host language. */
 int cuqwen_bench_begin(int device);
 int cuqwen_bench_end(int device, float* ms);

@@ -5,7 +5,8 @@
 //
 // What is kept: type, field, macro and function names and argument meaning; print-and-exit error behaviour.
 // What differs: the engine owns every device buffer, so the structs hold BORROWED pointers (free_* release the engine,
-// not individual tensors); `stream` arguments are ignored (the engine has its own stream and CUDA graph); the knobs
+// not individual tensors); the engine has its own stream and CUDA graph: qwen_forward is synchronous and ignores its
+// `stream` argument, the launch_* wrappers order their work against the stream they are given (StreamScope); the knobs
 // that tuned the reference kernels (ATTN_PARTITIONS, ...) exist as constants for harnesses that print them but tune nothing.
 #pragma once
 #include <cuda_fp16.h>
@@ -190,40 +191,59 @@ inline int qwen_forward(int token, int pos, const QwenConfig&, QwenState& s, con
 // ---- the launch_* operators (device pointers in the reference's layouts; work is queued on the library's stream of
 // device 0, cuqwen_dev_sync(0) waits for it; `stream` arguments are ignored) ----
 #define CUQWEN_K(call) do { if (call) cuqwen_compat::die(#call); } while (0)
-inline void launch_embedding_lookup(const half* table, const int* d_token_id, half* out, int dim, cudaStream_t = 0) {
+// The reference's launch_* are ordered on the stream they are given.  The library queues on a stream of its own, so
+// every wrapper below brackets its call: on entry the library's stream waits for what the caller's stream holds, on
+// exit the caller's stream waits for the work just queued (cuqwen_dev_join).  Events, copies and synchronisation on
+// the caller's stream then mean what they mean with the reference.
+namespace cuqwen_compat {
+struct StreamScope {
+    cudaStream_t s;
+    explicit StreamScope(cudaStream_t st) : s(st) { if (cuqwen_dev_join(0, (void*)s, 0)) die("cuqwen_dev_join"); }
+    ~StreamScope() { cuqwen_dev_join(0, (void*)s, 1); }
+};
+}  // namespace cuqwen_compat
+inline void launch_embedding_lookup(const half* table, const int* d_token_id, half* out, int dim, cudaStream_t stream = 0) {
+    cuqwen_compat::StreamScope scope_(stream);
     CUQWEN_K(cuqwen_k_embedding(0, table, d_token_id, out, dim));
 }
-inline void launch_rmsnorm(const half* x, const half* norm_weight, half* out, int dim, half eps, cudaStream_t = 0) {
+inline void launch_rmsnorm(const half* x, const half* norm_weight, half* out, int dim, half eps, cudaStream_t stream = 0) {
+    cuqwen_compat::StreamScope scope_(stream);
     CUQWEN_K(cuqwen_k_rmsnorm(0, x, norm_weight, out, dim, __half2float(eps)));
 }
 inline void launch_kv_cache_store(const half* k, const half* v, half* kcache, half* vcache, const int* d_pos, int n_kv_heads, int max_seq, int head_dim,
-                                  cudaStream_t = 0) {
+                                  cudaStream_t stream = 0) {
+    cuqwen_compat::StreamScope scope_(stream);
     CUQWEN_K(cuqwen_k_kv_store(0, k, v, kcache, vcache, d_pos, n_kv_heads, max_seq, head_dim));
 }
-inline void launch_gemv_add_fp16(const qweight_t* w, const half* scale, const half* in, half* x_inout, int rows, int cols, cudaStream_t = 0) {
+inline void launch_gemv_add_fp16(const qweight_t* w, const half* scale, const half* in, half* x_inout, int rows, int cols, cudaStream_t stream = 0) {
+    cuqwen_compat::StreamScope scope_(stream);
     CUQWEN_K(cuqwen_k_gemv_add(0, QUANT_TYPE_ID, w, scale, in, x_inout, rows, cols));
 }
 inline void launch_fused_mlp_stage2(half* x, const qweight_t* down_weight, const half* down_scale, const half* intermediate_in, int dim, int inter_dim,
-                                    cudaStream_t = 0) {
+                                    cudaStream_t stream = 0) {
+    cuqwen_compat::StreamScope scope_(stream);
     CUQWEN_K(cuqwen_k_gemv_add(0, QUANT_TYPE_ID, down_weight, down_scale, intermediate_in, x, dim, inter_dim));
 }
 // norm_weight / eps are accepted and, as in the reference (src/kernels.cu:578), ignored: x arrives normalised
 inline void launch_fused_mlp_stage1(const half* x, const half* /*norm_weight*/, const qweight_t* gate_weight, const qweight_t* up_weight, const half* gate_scale,
-                                    const half* up_scale, half* intermediate_out, int dim, int inter_dim, half /*eps*/, cudaStream_t = 0) {
+                                    const half* up_scale, half* intermediate_out, int dim, int inter_dim, half /*eps*/, cudaStream_t stream = 0) {
+    cuqwen_compat::StreamScope scope_(stream);
     CUQWEN_K(cuqwen_k_mlp1(0, QUANT_TYPE_ID, x, nullptr, 0.f, gate_weight, up_weight, gate_scale, up_scale, intermediate_out, dim, inter_dim));
 }
 // q/k/v projections + bias + RoPE; norm_weight / eps ignored as in the reference (src/kernels.cu:502)
 inline void launch_fused_attn_block(const half* x, const half* /*norm_weight*/, const qweight_t* W_q, const qweight_t* W_k, const qweight_t* W_v,
                                     const half* W_q_scale, const half* W_k_scale, const half* W_v_scale, const half* b_q, const half* b_k, const half* b_v,
                                     half* q_out, half* k_out, half* v_out, int dim, int /*q_dim*/, int /*kv_dim*/, int n_heads, int n_kv_heads, int head_dim,
-                                    const int* d_pos, float rope_theta, half /*eps*/, cudaStream_t = 0) {
+                                    const int* d_pos, float rope_theta, half /*eps*/, cudaStream_t stream = 0) {
+    cuqwen_compat::StreamScope scope_(stream);
     CUQWEN_K(cuqwen_k_qkv(0, QUANT_TYPE_ID, x, nullptr, 0.f, W_q, W_k, W_v, W_q_scale, W_k_scale, W_v_scale, b_q, b_k, b_v, q_out, k_out, v_out, nullptr, nullptr,
                           dim, n_heads, n_kv_heads, head_dim, QwenConfig::max_seq_len, d_pos, rope_theta, 1));
 }
 // The partial buffers of the reference are not used: this library keeps its own scratch per (device, shape).
 inline void launch_gqa_attention_decode(const half* q, const half* key_cache, const half* value_cache, half* attn_out, const int* d_pos, int n_heads,
                                         int n_kv_heads, int head_dim, int max_seq_len, float* /*d_partial_out*/, float* /*d_partial_max*/,
-                                        float* /*d_partial_sum*/, cudaStream_t = 0) {
+                                        float* /*d_partial_sum*/, cudaStream_t stream = 0) {
+    cuqwen_compat::StreamScope scope_(stream);
     static void *so = nullptr, *sml = nullptr, *cnt = nullptr;
     static size_t have[3] = {0, 0, 0};
     const int splits = 148 / n_kv_heads > 128 ? 128 : 148 / n_kv_heads;
@@ -237,7 +257,8 @@ inline void launch_gqa_attention_decode(const half* q, const half* key_cache, co
     }
     CUQWEN_K(cuqwen_k_attention(0, q, key_cache, value_cache, attn_out, d_pos, n_heads, n_kv_heads, head_dim, max_seq_len, splits, so, sml, cnt));
 }
-inline void launch_apply_repetition_penalty(half* logits, const int* d_history, const int* d_history_len, int vocab_size, half penalty, cudaStream_t = 0) {
+inline void launch_apply_repetition_penalty(half* logits, const int* d_history, const int* d_history_len, int vocab_size, half penalty, cudaStream_t stream = 0) {
+    cuqwen_compat::StreamScope scope_(stream);
     static void* bitmap = nullptr;
     static int have = 0;
     if (vocab_size > have) {
@@ -248,16 +269,19 @@ inline void launch_apply_repetition_penalty(half* logits, const int* d_history, 
     }
     CUQWEN_K(cuqwen_k_penalty(0, logits, d_history, d_history_len, vocab_size, __half2float(penalty), bitmap));
 }
-inline void launch_argmax(const half* logits, int* d_sampled_token, int vocab_size, cudaStream_t = 0) {
+inline void launch_argmax(const half* logits, int* d_sampled_token, int vocab_size, cudaStream_t stream = 0) {
+    cuqwen_compat::StreamScope scope_(stream);
     static void* scratch = nullptr;
     if (!scratch) { CUQWEN_K(cuqwen_dev_alloc(0, 16, &scratch)); CUQWEN_K(cuqwen_dev_memset(0, scratch, 0, 16)); }
     CUQWEN_K(cuqwen_k_argmax(0, logits, d_sampled_token, vocab_size, scratch));
 }
-inline void launch_compute_logits(const half* x_normed, const half* lm_head_weight, half* logits, int vocab_size, int dim, cudaStream_t = 0) {
+inline void launch_compute_logits(const half* x_normed, const half* lm_head_weight, half* logits, int vocab_size, int dim, cudaStream_t stream = 0) {
+    cuqwen_compat::StreamScope scope_(stream);
     CUQWEN_K(cuqwen_k_gemv(0, CUQWEN_FP16, lm_head_weight, nullptr, x_normed, nullptr, 0.f, logits, vocab_size, dim));
 }
 inline void launch_compute_logits_int8(const half* x_normed, const int8_t* lm_head_w, const half* lm_head_scale, half* logits, int vocab_size, int dim,
-                                       cudaStream_t = 0) {
+                                       cudaStream_t stream = 0) {
+    cuqwen_compat::StreamScope scope_(stream);
     CUQWEN_K(cuqwen_k_gemv(0, CUQWEN_INT8, lm_head_w, lm_head_scale, x_normed, nullptr, 0.f, logits, vocab_size, dim));
 }
 #undef CUQWEN_K
