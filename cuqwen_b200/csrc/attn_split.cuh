@@ -5,7 +5,8 @@
 // Compared with the single-launch variant in attn.cuh (partials merged by a ticket tree inside the same kernel) this
 // trades one small extra launch - started early through programmatic dependent launch, so it is already resident when
 // the partials land - for two fence + atomic + reload round trips on the critical path of the last CTAs, and it puts
-// eight consumer warps on the key stream instead of four (warps 0-3 take the even stages, warps 4-7 the odd ones).
+// eight consumer warps on the key stream instead of four (warp pair p takes the stages sn with sn % 4 == p, each
+// warp 32 of the stage's 64 keys).
 #pragma once
 #include "attn.cuh"
 
@@ -13,7 +14,7 @@ namespace cq {
 
 constexpr int kSplitWarps = 8;                                  // consumer warps of the partial kernel
 constexpr int kSplitThreads = (kSplitWarps + 1) * 32;
-constexpr int kSplitStages = 4;    // six stages (they fit) measured no faster: the consumers, not the copies, set the pace
+constexpr int kSplitStages = 6;    // four stages being worked on by the four warp pairs, two on their way
 constexpr int kFoldWarps = 16;
 
 inline size_t attn_split_smem_bytes(int hd, int stages) { return (size_t)stages * 2 * kAttnStageKeys * hd * 2 + 128; }
@@ -63,7 +64,7 @@ __global__ void __launch_bounds__(kSplitThreads) attn_partial_kernel(const AttnA
         }
         return;
     }
-    const int half_id = warp >> 2, wq = warp & 3;
+    const int pair = warp >> 1, wh = warp & 1;                  // stage sn belongs to the warp pair sn % 4; each warp takes 32 of its keys
     uint32_t qa[NCH][4];
     attn_load_q<HD>(qa, a.q + (size_t)kvh * a.grp * HD, a.grp, g, t);
     AttnState<HD> st;
@@ -72,10 +73,10 @@ __global__ void __launch_bounds__(kSplitThreads) attn_partial_kernel(const AttnA
     for (int sn = 0; sn < nstage; ++sn) {
         const int s = sn % nst;
         if (!failed && !mbar_wait(bar_full + s * 8, (sn / nst) & 1)) { failed = true; if (a.err) atomicExch(a.err, 6u); }
-        const int kb = t0 + sn * kAttnStageKeys + 16 * wq;       // first key of this warp's tile
-        if ((sn & 1) == half_id && kb < t1) {
-            const unsigned char* sK = dyn + s * 2 * HALF + 16 * wq * ROWB;
-            attn_tile<HD, false>(st, qa, sK, sK + HALF, t1 - kb, a.scale_log2, g, t);
+        const int kb = t0 + sn * kAttnStageKeys + 32 * wh;       // first key of this warp's 32
+        if ((sn & 3) == pair && kb < t1) {
+            const unsigned char* sK = dyn + s * 2 * HALF + 32 * wh * ROWB;
+            attn_tile32<HD>(st, qa, sK, sK + HALF, t1 - kb, a.scale_log2, g, t);
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_empty + s * 8);
