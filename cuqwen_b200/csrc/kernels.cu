@@ -369,7 +369,11 @@ int launch_gemv(int quant, int epi, GemvArgs& a, const LaunchCfg& cfg) {
     int kw = 8 / rw;                                 // rw * kw may end up below 8 when a row has few pieces: the spare warps idle
     const int nblk = (a.nsets + rw - 1) / rw;
     const int grid = nblk;                            // CTAs loop when there are more blocks than fit at once
-    int cap = env_int("CUQWEN_GEMV_CAP_KB", nblk > cfg.sm_count ? 110 : 220) * 1024;
+    // Shared-memory budget of a CTA.  int4 weights with more blocks than SMs: 110 KB, so that two CTAs share an SM and
+    // one streams while the other is in its prologue or epilogue.  int8 / fp16 weights move two to four times the
+    // bytes per row piece, and a ring cut to 110 KB is too shallow for them (measured on the 14B int8 matrices:
+    // gate/up 37.5 us at 110 KB against 28.2 us at 220 KB, lm_head 139 against 119 us): they take the whole SM.
+    int cap = env_int("CUQWEN_GEMV_CAP_KB", (nblk > cfg.sm_count && quant == Q_I4) ? 110 : 220) * 1024;
     const int env_pg = env_int("CUQWEN_GEMV_PG", 0), env_nst = env_int("CUQWEN_GEMV_NST", 0);
     int pg = 0, nst = 0;
     for (int pass = 0; pass < 2 && !nst; ++pass) {
