@@ -4,9 +4,8 @@
 // Reference behaviour being replaced: src/kernels.cu:105-219 (stage 1, 64 fixed partitions, WMMA) and :222-288
 // (stage 2 combine).  Here scores and the softmax stay in fp32 (the reference rounds scores to fp16).
 //
-// This header holds what the attention variants share: the argument block and the stage geometry.  The kernels are in
-// attn_split.cuh (two launches: partials, then a per-head fold) and step_kernel.cuh (a phase of the persistent step
-// kernel); the arithmetic of a 16-key tile is in attn_tile.cuh.
+// This header holds the argument block and the stage geometry.  The kernels are in attn_split.cuh (two launches:
+// partials, then a per-head fold); the arithmetic of a key tile is in attn_tile.cuh.
 //
 // Scratch (sizes from attn_slots / attn_counters in attn_combine.cuh): part_o [slots][8][hd] fp32, part_ml
 // [slots][8][2] fp32; slot [kvh][split] receives the partial of one key range.  `counters` is kept in the interface
@@ -32,6 +31,7 @@ struct AttnArgs {
     unsigned* counters;
     unsigned* err;          // receives a non-zero code when a bounded wait expires (may be null)
     int stages;             // ring depth of the partial kernel (0 = its default)
+    unsigned long long* trace;       // optional: timeline words of the partial launch (8) and of the fold launch (8), else null
 };
 
 }  // namespace cq

@@ -33,12 +33,15 @@ __global__ void __launch_bounds__(kSplitThreads) attn_partial_kernel(const AttnA
     const int nst = a.stages >= 2 && a.stages <= kSplitStages ? a.stages : kSplitStages;      // ring depth of this launch
     const uint32_t stage0 = smem_u32(dyn), bar_full = smem_u32(sm_bar), bar_empty = bar_full + kSplitStages * 8;
     if (threadIdx.x == 0) {
+        trace_first(a.trace, 0); trace_last(a.trace, 1);
         for (int s = 0; s < nst; ++s) { mbar_init(bar_full + s * 8, 1); mbar_init(bar_empty + s * 8, kSplitWarps); }
         mbar_fence_init();
     }
     __syncthreads();
-    pdl_wait();                 // K/V row `pos` and q come from the previous kernel
 
+    // The position is stable for the whole step (the step's first kernel is not launched early), and cache rows before
+    // it were written by earlier steps: the split's key range and every stage below row `pos` need not wait for the
+    // kernel before this one.  Row `pos` itself and q come from that kernel.
     const int len = *a.d_pos + 1;
     int chunk = (len + a.nsplit - 1) / a.nsplit;
     chunk = (chunk + 15) & ~15;
@@ -51,11 +54,12 @@ __global__ void __launch_bounds__(kSplitThreads) attn_partial_kernel(const AttnA
         if (lane == 0) {
             const unsigned char* kb = reinterpret_cast<const unsigned char*>(a.kc) + ((size_t)kvh * a.max_seq + t0) * ROWB;
             const unsigned char* vb = reinterpret_cast<const unsigned char*>(a.vc) + ((size_t)kvh * a.max_seq + t0) * ROWB;
-            bool failed = false;
+            bool failed = false, waited = false;
             for (int sn = 0; sn < nstage; ++sn) {
                 const int s = sn % nst;
                 if (!failed && !mbar_wait(bar_empty + s * 8, ((sn / nst) & 1) ^ 1)) { failed = true; if (a.err) atomicExch(a.err, 5u); }
                 const int n = min(kAttnStageKeys, t1 - t0 - sn * kAttnStageKeys);
+                if (!waited && t0 + sn * kAttnStageKeys + n == len) { pdl_wait(); waited = true; }      // the stage that holds row `pos`
                 const uint32_t bytes = (uint32_t)n * ROWB;
                 mbar_expect_tx(bar_full + s * 8, 2 * bytes);
                 bulk_g2s(stage0 + s * 2 * HALF, kb + (size_t)sn * HALF, bytes, bar_full + s * 8);
@@ -64,9 +68,12 @@ __global__ void __launch_bounds__(kSplitThreads) attn_partial_kernel(const AttnA
         }
         return;
     }
+    pdl_wait();                 // q comes from the previous kernel
+    if (threadIdx.x == 0) trace_first(a.trace, 2);
     const int pair = warp >> 1, wh = warp & 1;                  // stage sn belongs to the warp pair sn % 4; each warp takes 32 of its keys
     uint32_t qa[NCH][4];
     attn_load_q<HD>(qa, a.q + (size_t)kvh * a.grp * HD, a.grp, g, t);
+    if (threadIdx.x == 0) trace_last(a.trace, 3);
     AttnState<HD> st;
     st.reset();
     bool failed = false;
@@ -81,11 +88,13 @@ __global__ void __launch_bounds__(kSplitThreads) attn_partial_kernel(const AttnA
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_empty + s * 8);
     }
+    if (threadIdx.x == 0) trace_last(a.trace, 4);
     attn_state_to_smem<HD>(st, &sm_o[warp][0][0], &sm_ml[warp][0][0], g, t);
     asm volatile("bar.sync 1, %0;" ::"r"(NCT) : "memory");
     float* po = a.part_o + ((size_t)(kvh * a.nsplit + split) * kMaxGroup) * HD;
     float* pml = a.part_ml + ((size_t)(kvh * a.nsplit + split) * kMaxGroup) * 2;
     attn_merge_warps<HD>(&sm_o[0][0][0], &sm_ml[0][0][0], kSplitWarps, a.grp, po, pml, threadIdx.x, NCT);
+    if (threadIdx.x == 0) trace_last(a.trace, 5);
 }
 
 // One CTA per query head; warp w takes splits w, w + 16, ...; lane = 4-float column of the head.
@@ -95,7 +104,10 @@ __global__ void __launch_bounds__(kFoldWarps * 32) attn_fold_kernel(const AttnAr
     __shared__ float4 o_w[kFoldWarps][NCOL];
     __shared__ float ml_w[kFoldWarps][2];
     pdl_launch_dependents();
+    unsigned long long* tr = a.trace ? a.trace + 8 : nullptr;
+    if (threadIdx.x == 0) { trace_first(tr, 0); trace_last(tr, 1); }
     pdl_wait();                 // the partials come from the kernel before this one
+    if (threadIdx.x == 0) trace_first(tr, 2);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int head = blockIdx.x, kvh = head / a.grp, h = head - kvh * a.grp;
     const int len = *a.d_pos + 1;
@@ -149,6 +161,7 @@ __global__ void __launch_bounds__(kFoldWarps * 32) attn_fold_kernel(const AttnAr
             dst[0] = __floats2half2_rn(o.x * inv, o.y * inv);
             dst[1] = __floats2half2_rn(o.z * inv, o.w * inv);
         }
+        if (lane == 0) trace_last(tr, 5);
     }
 }
 

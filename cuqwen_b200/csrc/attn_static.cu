@@ -11,9 +11,15 @@
 // e.g. 4 KV heads x 74 splits or 8 KV heads x 42 splits.  The array is 1,598,720 bytes per device.  Larger shapes are
 // rejected with CUQWEN_ERR_ARG.
 //
+// Status: every wait inside the kernels is bounded; when one runs out the kernel finishes with meaningless numbers and
+// leaves a non-zero code in a status word of the block.  That word is NOT part of what a call clears, so it survives
+// until the host asks: cuqwen_k_attention_static_status copies it out (into the caller's own variable, no allocation),
+// clears it, and answers CUQWEN_ERR_TIMEOUT when it was set.  Ask after the work has been queued and before trusting
+// `out`; the query waits for `stream`.
+//
 // Set-up: the first call for a device (with that device current) looks the array's address up with
 // cudaGetSymbolAddress and raises the kernel's dynamic shared-memory limit; make that first call before any stream
-// capture begins.  Later calls only queue a 1.25 KB memset of the tickets and status word and the kernel launch.
+// capture begins.  Later calls only queue a 1 KB memset of the tickets and the kernel launch.
 // Nothing here calls cudaMalloc, cudaFree or any routine that allocates.
 //
 // There is ONE scratch block per device: two calls that may overlap on the device (different streams, or different
@@ -41,11 +47,11 @@ constexpr int kStaticCounters = 256;
 constexpr int kStaticMaxHd = 128;
 
 constexpr size_t kOffCounters = 0;                                   // u32 [kStaticCounters], zero between launches
-constexpr size_t kOffErr = kOffCounters + kStaticCounters * 4;       // u32 status word (+ padding to 256 B)
+constexpr size_t kClearBytes = kStaticCounters * 4;                  // what every call clears: the tickets, nothing else
+constexpr size_t kOffErr = kClearBytes;                              // u32 status word (+ padding to 256 B); cleared only by the status query
 constexpr size_t kOffMl = kOffErr + 256;                             // float [kStaticSlots][8][2]
 constexpr size_t kOffO = kOffMl + (size_t)kStaticSlots * kMaxGroup * 2 * 4;   // float [kStaticSlots][8][hd]
 constexpr size_t kScratchBytes = kOffO + (size_t)kStaticSlots * kMaxGroup * kStaticMaxHd * 4;
-constexpr size_t kClearBytes = kOffMl;                               // tickets + status word
 
 static __device__ __align__(256) unsigned char g_scratch[kScratchBytes];
 
@@ -109,4 +115,25 @@ extern "C" int cuqwen_k_attention_static(int device, void* stream, const void* q
     e = hd == 128 ? launch<128>(a, st) : launch<64>(a, st);
     if (e != cudaSuccess) return report_error(CUQWEN_ERR_CUDA, "attention launch: %s", cudaGetErrorString(e));
     return CUQWEN_OK;
+}
+
+// Reads and clears the status word of the device's scratch block (see the file comment).  `code_out` receives the
+// word (0 = no wait ran out since the last query).  Waits for `stream`; allocates nothing.
+extern "C" int cuqwen_k_attention_static_status(int device, void* stream, unsigned* code_out) {
+    if (device < 0 || device >= kMaxDevices) return report_error(CUQWEN_ERR_ARG, "device %d out of range", device);
+    if (!code_out) return report_error(CUQWEN_ERR_ARG, "null argument");
+    cudaError_t e = cudaSetDevice(device);
+    if (e != cudaSuccess) return report_error(CUQWEN_ERR_CUDA, "cudaSetDevice(%d): %s", device, cudaGetErrorString(e));
+    unsigned char* base = nullptr;
+    if (int r = scratch_base(device, &base)) return r;
+    cudaStream_t st = (cudaStream_t)stream;
+    *code_out = 0u;
+    e = cudaMemcpyAsync(code_out, base + kOffErr, 4, cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return report_error(CUQWEN_ERR_CUDA, "reading the attention status word: %s", cudaGetErrorString(e));
+    if (*code_out == 0u) return CUQWEN_OK;
+    e = cudaMemsetAsync(base + kOffErr, 0, 4, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return report_error(CUQWEN_ERR_CUDA, "clearing the attention status word: %s", cudaGetErrorString(e));
+    return report_error(CUQWEN_ERR_TIMEOUT, "a bounded device-side wait expired in cuqwen_k_attention_static (code %u)", *code_out);
 }

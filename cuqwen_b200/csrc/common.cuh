@@ -10,6 +10,24 @@ constexpr int kGroup = 128;  // weights per fp16 scale along the input dim (refe
 
 enum Quant : int { Q_F16 = 0, Q_I8 = 1, Q_I4 = 2 };
 
+// Tensor-parallel exchanges are numbered  step * kSeqPerStep + index + 1  (index < kSeqPerStep: two per layer and a few
+// per token), so that a receive word left over from an earlier exchange can never carry the number a reader expects.
+constexpr unsigned kSeqPerStep = 512u;
+constexpr long long kWaitCyclesDefault = 4000000000ll;     // bound of every device-side wait, in SM cycles (two to four seconds)
+
+// One exchange word = {fp32 value bits (low half), sequence number (high half)} moved as ONE 64-bit access, so that the
+// pair is written and read indivisibly by the memory model (a vector access of two 32-bit elements would not be).
+__device__ __forceinline__ void st_pair(void* p, unsigned value_bits, unsigned seq) {
+    const unsigned long long w = ((unsigned long long)seq << 32) | value_bits;
+    asm volatile("st.volatile.global.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
+}
+// Two adjacent exchange words (16 bytes) as two 64-bit elements.
+__device__ __forceinline__ void ld_pair2(const void* p, unsigned long long& a, unsigned long long& b) {
+    asm volatile("ld.volatile.global.v2.u64 {%0,%1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
+}
+__device__ __forceinline__ unsigned pair_seq(unsigned long long w) { return (unsigned)(w >> 32); }
+__device__ __forceinline__ float pair_val(unsigned long long w) { return __uint_as_float((unsigned)(w & 0xffffffffull)); }
+
 // Streaming 128-bit read of data that is touched once per step (weights, KV):
 // read-only path, do not keep it in L1.
 __device__ __forceinline__ uint4 ldg_stream(const void* p) {

@@ -21,7 +21,6 @@
 #include "errors.h"
 #include "gemv.cuh"
 #include "launch.h"
-#include "step_kernel.cuh"
 #include "tp_plan.h"
 
 using namespace cq;
@@ -172,9 +171,7 @@ struct cuqwen_engine {
     unsigned char* gate_xd = nullptr; int* gate_corr = nullptr; float* gate_xscale = nullptr;    // SwiGLU output in staged form (see GemvArgs::xd_out)
     int steps_done = 0;                          // mirrors the device-side step counter (StepCtl::pad[1])
     std::vector<cudaEvent_t>* prof = nullptr;    // cuqwen_step_profile: an event is recorded after every launch of the step
-    // persistent step kernel (single GPU): phase table on the device, its shared-memory map, the grid barrier word
-    StepPhase* d_phases = nullptr; StepArgs step_args{}; unsigned* step_bar = nullptr; bool fused = false; int fused_grid = 0;
-    unsigned long long* step_trace = nullptr; size_t step_trace_bytes = 0;
+    unsigned long long* step_trace = nullptr; size_t step_trace_bytes = 0;     // CUQWEN_FLAG_STEP_TRACE: eight timeline words per launch (tma.cuh)
     // graph
     cudaGraph_t graph = nullptr; cudaGraphExec_t gexec = nullptr; bool graph_ready = false;
     int launches = 0;
@@ -206,6 +203,9 @@ extern "C" int cuqwen_create(const cuqwen_params* pin, cuqwen_engine** out) {
         (p.n_heads * p.head_dim) % 128 || p.n_heads / p.n_kv_heads > kMaxGroup)
         return fail(CUQWEN_ERR_ARG, "unsupported dims: dim %d inter %d vocab %d layers %d heads %d/%d hd %d", p.dim, p.intermediate_size, p.vocab_size,
                     p.n_layers, p.n_heads, p.n_kv_heads, p.head_dim);
+    // exchanges of a step are numbered 0 .. 2 * n_layers + 1 inside a window of kSeqPerStep numbers (common.cuh)
+    if (p.tp_size > 1 && 2 * p.n_layers + 2 > (int)kSeqPerStep)
+        return fail(CUQWEN_ERR_ARG, "tensor parallelism supports at most %d layers (this model has %d)", (int)kSeqPerStep / 2 - 1, p.n_layers);
     TpPlan plan;
     if (int r = tp_plan(p.n_heads, p.n_kv_heads, p.head_dim, p.intermediate_size, p.vocab_size, p.tp_rank, p.tp_size, &plan))
         return fail(CUQWEN_ERR_ARG, "model cannot be split over tp_size %d (rule %d)", p.tp_size, r);
@@ -253,7 +253,7 @@ extern "C" void cuqwen_destroy(cuqwen_engine* e) {
     if (e->tp_rx) cudaFree(e->tp_rx);
     if (e->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(e->comm);
     void* bufs[] = {e->x, e->xn, e->q, e->k, e->v, e->att, e->gate, e->logits, e->kc, e->vc, e->part_o, e->part_ml, e->counters, e->ctl, e->d_hist,
-                    e->bitmap, e->best, e->ticket, e->out_ring, e->tp_partial, e->tp_keys, e->warena, e->d_phases, e->step_bar, e->step_trace, e->x2, e->gate_xd, e->gate_corr, e->gate_xscale};
+                    e->bitmap, e->best, e->ticket, e->out_ring, e->tp_partial, e->tp_keys, e->warena, e->step_trace, e->x2, e->gate_xd, e->gate_corr, e->gate_xscale};
     for (void* b : bufs) if (b) cudaFree(b);
     if (e->h_ctl) cudaFreeHost(e->h_ctl);
     if (e->h_out) cudaFreeHost(e->h_out);
@@ -347,8 +347,6 @@ static int walk_file(cuqwen_engine* e, Cursor cur, Arena& ar, int lm_fmt) {
     return CUQWEN_OK;
 }
 
-static int build_fused_step(cuqwen_engine* e);
-
 extern "C" int cuqwen_load(cuqwen_engine* e, const char* path) {
     if (!e || !path) return fail(CUQWEN_ERR_ARG, "null argument");
     if (e->loaded) return fail(CUQWEN_ERR_STATE, "weights already loaded");
@@ -379,7 +377,11 @@ extern "C" int cuqwen_load(cuqwen_engine* e, const char* path) {
     r = walk_file(e, cur, real, h[10]);
     if (r) { cudaFree(e->warena); e->warena = nullptr; return fail(r, "copying weights to the device failed: %s", cudaGetErrorString(cudaGetLastError())); }
     CK(cudaDeviceSynchronize());
-    if (int fr = build_fused_step(e)) return fr;
+    if (e->p.flags & CUQWEN_FLAG_STEP_TRACE) {      // eight timeline words per launch, zeroed by the reader between steps
+        e->step_trace_bytes = (size_t)(1 + 8 * e->p.n_layers + 8) * 64;
+        CK(cudaMalloc((void**)&e->step_trace, e->step_trace_bytes));
+        CK(cudaMemset(e->step_trace, 0, e->step_trace_bytes));
+    }
     e->loaded = true;
     return CUQWEN_OK;
 }
@@ -396,13 +398,15 @@ static int tp_allreduce(cuqwen_engine* e, float* buf, int n, cudaStream_t s) {
 
 // The matrix and attention work of one step, in order.  `reduce`: a row-parallel matrix whose fp32 partial must be
 // summed over the tensor-parallel ranks and added to the residual stream afterwards.
+enum PhaseKind : int { PH_GEMV = 0, PH_ATTN = 1 };
+struct Phase { GemvArgs g; AttnArgs at; int kind, quant, epi; };
 struct HostPhase {
-    StepPhase ph; bool reduce;
+    Phase ph; bool reduce;
     // peer exchange with many ranks: after this (pushing) matrix a small kernel sums the slots once into sum_dst
     bool sum_after; const __half* sum_src; __half* sum_dst; const void* sum_slots; int sum_seq;
 };
 
-static void describe_step(cuqwen_engine* e, std::vector<HostPhase>& out, int nsplit, bool with_fold) {
+static void describe_step(cuqwen_engine* e, std::vector<HostPhase>& out, int nsplit) {
     const cuqwen_params& p = e->p;
     const size_t kv_layer = (size_t)e->n_kv_l * p.max_seq_len * p.head_dim;
     const float eps = __half2float(__float2half(p.norm_eps));   // the reference narrows eps to fp16 (src/model.cu:96)
@@ -416,7 +420,7 @@ static void describe_step(cuqwen_engine* e, std::vector<HostPhase>& out, int nsp
     const bool peer = e->tp > 1 && e->tp_peer;
     // SwiGLU output handed to the down projection in staged form: only when the separate gate/up launch will work on
     // whole 128-row groups (eight tile sets per block), which the launcher decides from the tile-set count
-    const bool hand_over = !with_fold && p.quant != 0 && !(p.flags & CUQWEN_FLAG_NO_HANDOVER) &&
+    const bool hand_over = p.quant != 0 && !(p.flags & CUQWEN_FLAG_NO_HANDOVER) &&
                            gemv_tile_sets_per_block((e->inter_l + 15) / 16, e->sms, EPI_SWIGLU) == 8;
     __half* cur = e->x;
     int pending = -1, next_xi = 0;
@@ -465,9 +469,8 @@ static void describe_step(cuqwen_engine* e, std::vector<HostPhase>& out, int nsp
             a.n_kv = e->n_kv_l; a.grp = e->plan.grp; a.max_seq = p.max_seq_len; a.nsplit = nsplit;
             a.scale_log2 = (1.0f / sqrtf((float)p.head_dim)) * 1.4426950408889634f;
             a.part_o = e->part_o; a.part_ml = e->part_ml; a.counters = e->counters; a.err = t_err;
-            h.ph.kind = PH_ATTN; h.ph.k_cur = e->k; h.ph.v_cur = e->v;
+            h.ph.kind = PH_ATTN;
             out.push_back(h);
-            if (with_fold) { h.ph.kind = PH_FOLD; out.push_back(h); }      // the step kernel merges the splits in a phase of its own
         }
         {   // o_proj + residual
             GemvArgs a = gv(e->att, e->q_dim_l);
@@ -517,43 +520,6 @@ static void describe_step(cuqwen_engine* e, std::vector<HostPhase>& out, int nsp
     }
 }
 
-// Plans the persistent step kernel for this engine (single GPU only) and uploads its phase table.  Leaves
-// e->fused false when the shapes do not fit the kernel's shared-memory budget; the step then runs as separate launches.
-static int build_fused_step(cuqwen_engine* e) {
-    e->fused = false;
-    if (e->tp != 1 || !(e->p.flags & CUQWEN_FLAG_FUSED_STEP)) return CUQWEN_OK;
-    const int grid = e->sms;
-    if (e->n_kv_l > grid || e->plan.grp > kMaxGroup) return CUQWEN_OK;
-    int nsplit = grid / e->n_kv_l;
-    if (nsplit > e->nsplit) nsplit = e->nsplit;
-    t_err = reinterpret_cast<unsigned*>(&e->ctl->pad[0]);
-    std::vector<HostPhase> hp;
-    describe_step(e, hp, nsplit, true);
-    const int slot_bytes = 32 * 1024;
-    std::vector<StepPhase> ph(hp.size());
-    for (size_t i = 0; i < hp.size(); ++i) {
-        ph[i] = hp[i].ph;
-        if (ph[i].kind == PH_GEMV && plan_step_gemv(ph[i].quant, ph[i].epi, ph[i].g, grid, slot_bytes)) return CUQWEN_OK;
-    }
-    int max_smem = 0;
-    CK(cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, e->p.device));
-    StepArgs sa{};
-    if (plan_step_smem(sa, ph.data(), (int)ph.size(), e->p.head_dim, slot_bytes, max_smem)) return CUQWEN_OK;
-    CK(cudaMalloc((void**)&e->d_phases, ph.size() * sizeof(StepPhase)));
-    CK(cudaMemcpy(e->d_phases, ph.data(), ph.size() * sizeof(StepPhase), cudaMemcpyHostToDevice));
-    CK(cudaMalloc((void**)&e->step_bar, 256));
-    CK(cudaMemset(e->step_bar, 0, 256));
-    if (e->p.flags & CUQWEN_FLAG_STEP_TRACE) {
-        e->step_trace_bytes = ph.size() * (size_t)grid * 4 * sizeof(unsigned long long);
-        CK(cudaMalloc((void**)&e->step_trace, e->step_trace_bytes));
-        CK(cudaMemset(e->step_trace, 0, e->step_trace_bytes));
-    }
-    sa.phases = e->d_phases; sa.nphases = (int)ph.size(); sa.bar = e->step_bar; sa.err = t_err; sa.trace = e->step_trace;
-    if (const char* d = getenv("CUQWEN_STEP_DEBUG")) sa.debug = atoi(d);
-    e->step_args = sa; e->fused_grid = grid; e->fused = true;
-    return CUQWEN_OK;
-}
-
 static int record_step(cuqwen_engine* e, cudaStream_t s, bool pdl) {
     const cuqwen_params& p = e->p;
     LaunchCfg cfg{s, e->sms, pdl};
@@ -565,16 +531,15 @@ static int record_step(cuqwen_engine* e, cudaStream_t s, bool pdl) {
 #define LK(call) do { int r_ = (call); if (r_) return fail(CUQWEN_ERR_CUDA, "%s: %s", #call, cudaGetErrorString((cudaError_t)r_)); ++n; MARK(); } while (0)
     MARK();
     LK(launch_embed(e->embed, &e->ctl->token, e->x, p.dim, cfg_plain));
-    if (e->fused) {
-        CK(cudaMemsetAsync(e->step_bar, 0, 4, s));
-        LK(launch_decode_step(p.quant, e->step_args, e->fused_grid, cfg_plain));
-    } else {
+    {
         std::vector<HostPhase> hp;
-        describe_step(e, hp, e->nsplit, false);
+        describe_step(e, hp, e->nsplit);
         for (HostPhase& h : hp) {
-            if (h.ph.kind == PH_ATTN) { LK(launch_attn(p.head_dim, h.ph.at, cfg)); ++n; continue; }      // two launches: partials, fold
+            unsigned long long* tr = e->step_trace && (size_t)(n + 2) * 64 <= e->step_trace_bytes ? e->step_trace + (size_t)n * 8 : nullptr;
+            if (h.ph.kind == PH_ATTN) { h.ph.at.trace = tr; LK(launch_attn(p.head_dim, h.ph.at, cfg)); ++n; continue; }      // two launches: partials, fold
+            h.ph.g.trace = tr;
             LK(launch_gemv(h.ph.quant, h.ph.epi, h.ph.g, cfg));
-            if (h.sum_after) LK(launch_tp_sum(h.sum_src, h.sum_dst, h.sum_slots, e->tp, p.dim, &e->ctl->pad[1], h.sum_seq, t_err, cfg_plain));
+            if (h.sum_after) LK(launch_tp_sum(h.sum_src, h.sum_dst, h.sum_slots, e->tp, p.dim, &e->ctl->pad[1], h.sum_seq, t_err, 0, cfg_plain));
             if (h.reduce) {
                 if (int r = tp_allreduce(e, e->tp_partial, p.dim, s)) return r; ++n; MARK();
                 LK(launch_resid_sum(e->x, e->tp_partial, 1, 0, p.dim, cfg_plain));
@@ -879,13 +844,19 @@ extern "C" int cuqwen_bench_end(int device, float* ms) { DEV(device); (void)cfg;
 // ---------------------------------------------------------------------------
 #define KK(call) do { int r_ = (call); if (r_) return fail(r_ == (int)cudaErrorInvalidValue ? CUQWEN_ERR_ARG : CUQWEN_ERR_CUDA, "%s: %s", #call, cudaGetErrorString((cudaError_t)r_)); } while (0)
 static bool bad_q(int q) { return q < 0 || q > 2; }
+// A null pointer handed to a kernel is a device fault, not an error code: every entry point checks the pointers it
+// will dereference first.  Scales are required exactly when the weights are quantised.
+#define NOT_NULL(...) do { const void* ps_[] = {__VA_ARGS__}; for (const void* p_ : ps_) if (!p_) return fail(CUQWEN_ERR_ARG, "%s: null pointer argument", __func__); } while (0)
+#define SCALES_OK(quant, ...) do { if (quant) NOT_NULL(__VA_ARGS__); } while (0)
 
 extern "C" int cuqwen_k_embedding(int device, const void* table, const int* d_token, void* out, int dim) {
     DEV(device); if (dim <= 0 || dim % 8) return fail(CUQWEN_ERR_ARG, "dim must be a positive multiple of 8");
+    NOT_NULL(table, d_token, out);
     KK(launch_embed((const __half*)table, d_token, (__half*)out, dim, cfg)); return CUQWEN_OK;
 }
 extern "C" int cuqwen_k_rmsnorm(int device, const void* x, const void* w, void* out, int dim, float eps) {
     DEV(device); if (dim <= 0) return fail(CUQWEN_ERR_ARG, "dim must be positive");
+    NOT_NULL(x, w, out);
     KK(launch_rmsnorm((const __half*)x, (const __half*)w, (__half*)out, dim, eps, cfg)); return CUQWEN_OK;
 }
 extern "C" int cuqwen_k_qkv(int device, int quant, const void* x, const void* norm_w, float eps, const void* wq, const void* wk, const void* wv,
@@ -893,6 +864,9 @@ extern "C" int cuqwen_k_qkv(int device, int quant, const void* x, const void* no
                             void* v_out, void* kcache, void* vcache, int dim, int n_heads, int n_kv, int hd, int max_seq, const int* d_pos, float theta, int fast) {
     DEV(device);
     if (bad_q(quant) || dim <= 0 || dim % kGroup || (hd != 64 && hd != 128) || n_heads < 1 || n_kv < 1) return fail(CUQWEN_ERR_ARG, "unsupported qkv shape");
+    NOT_NULL(x, wq, wk, wv, bq, bk, bv, d_pos);          // the biases are required (every Qwen2.5 q/k/v projection has one); outputs may be null one by one
+    SCALES_OK(quant, sq, sk, sv);
+    if ((kcache || vcache) && max_seq < 1) return fail(CUQWEN_ERR_ARG, "max_seq_len must be positive when a cache is given");
     GemvArgs a = gv((const __half*)x, dim);
     a.norm_w = (const __half*)norm_w; a.eps = eps;
     a.w[0] = (const uint8_t*)wq; a.w[1] = (const uint8_t*)wk; a.w[2] = (const uint8_t*)wv;
@@ -903,10 +877,10 @@ extern "C" int cuqwen_k_qkv(int device, int quant, const void* x, const void* no
     KK(launch_gemv(quant, EPI_QKV, a, cfg)); return CUQWEN_OK;
 }
 extern "C" int cuqwen_k_rope(int device, void* q, void* k, int n_heads, int n_kv, int hd, const int* d_pos, float theta, int fast) {
-    DEV(device); KK(launch_rope((__half*)q, (__half*)k, n_heads, n_kv, hd, d_pos, theta, fast, cfg)); return CUQWEN_OK;
+    DEV(device); NOT_NULL(q, k, d_pos); KK(launch_rope((__half*)q, (__half*)k, n_heads, n_kv, hd, d_pos, theta, fast, cfg)); return CUQWEN_OK;
 }
 extern "C" int cuqwen_k_kv_store(int device, const void* k, const void* v, void* kc, void* vc, const int* d_pos, int n_kv, int max_seq, int hd) {
-    DEV(device); KK(launch_kv_store((const __half*)k, (const __half*)v, (__half*)kc, (__half*)vc, d_pos, n_kv, max_seq, hd, cfg)); return CUQWEN_OK;
+    DEV(device); NOT_NULL(k, v, kc, vc, d_pos); KK(launch_kv_store((const __half*)k, (const __half*)v, (__half*)kc, (__half*)vc, d_pos, n_kv, max_seq, hd, cfg)); return CUQWEN_OK;
 }
 extern "C" int cuqwen_attn_scratch_bytes(int n_kv, int hd, int nsplit, size_t* bo, size_t* bml, size_t* bc) {
     if (n_kv < 1 || nsplit < 1 || nsplit > kMaxSplit || (hd != 64 && hd != 128)) return fail(CUQWEN_ERR_ARG, "unsupported attention shape");
@@ -920,6 +894,7 @@ extern "C" int cuqwen_k_attention(int device, const void* q, const void* kc, con
     DEV(device);
     if (n_kv < 1 || n_heads % n_kv || n_heads / n_kv > kMaxGroup || (hd != 64 && hd != 128) || nsplit < 1 || nsplit > kMaxSplit)
         return fail(CUQWEN_ERR_ARG, "unsupported attention shape (heads %d/%d, head_dim %d, splits %d)", n_heads, n_kv, hd, nsplit);
+    NOT_NULL(q, kc, vc, out, d_pos, so, sml);
     AttnArgs a{};
     a.q = (const __half*)q; a.kc = (const __half*)kc; a.vc = (const __half*)vc; a.out = (__half*)out; a.d_pos = d_pos;
     a.n_kv = n_kv; a.grp = n_heads / n_kv; a.max_seq = max_seq; a.nsplit = nsplit;
@@ -929,39 +904,60 @@ extern "C" int cuqwen_k_attention(int device, const void* q, const void* kc, con
 }
 extern "C" int cuqwen_k_gemv_add(int device, int quant, const void* w, const void* s, const void* in, void* x, int rows, int cols) {
     DEV(device); if (bad_q(quant)) return fail(CUQWEN_ERR_ARG, "quant out of range");
+    NOT_NULL(w, in, x); SCALES_OK(quant, s);
     GemvArgs a = gv((const __half*)in, cols); a.w[0] = (const uint8_t*)w; a.s[0] = (const __half*)s; a.rows = rows; a.out_h = (__half*)x;
     KK(launch_gemv(quant, EPI_RESID, a, cfg)); return CUQWEN_OK;
 }
 extern "C" int cuqwen_k_gemv(int device, int quant, const void* w, const void* s, const void* x, const void* norm_w, float eps, void* y, int rows, int cols) {
     DEV(device); if (bad_q(quant)) return fail(CUQWEN_ERR_ARG, "quant out of range");
+    NOT_NULL(w, x, y); SCALES_OK(quant, s);
     GemvArgs a = gv((const __half*)x, cols); a.norm_w = (const __half*)norm_w; a.eps = eps; a.w[0] = (const uint8_t*)w; a.s[0] = (const __half*)s; a.rows = rows; a.out_h = (__half*)y;
     KK(launch_gemv(quant, EPI_F16, a, cfg)); return CUQWEN_OK;
 }
 extern "C" int cuqwen_k_gemv_f32(int device, int quant, const void* w, const void* s, const void* x, float* y, int rows, int cols) {
     DEV(device); if (bad_q(quant)) return fail(CUQWEN_ERR_ARG, "quant out of range");
+    NOT_NULL(w, x, y); SCALES_OK(quant, s);
     GemvArgs a = gv((const __half*)x, cols); a.w[0] = (const uint8_t*)w; a.s[0] = (const __half*)s; a.rows = rows; a.out_f = y;
     KK(launch_gemv(quant, EPI_F32, a, cfg)); return CUQWEN_OK;
 }
 extern "C" int cuqwen_k_mlp1(int device, int quant, const void* x, const void* norm_w, float eps, const void* wg, const void* wu, const void* sg,
                              const void* su, void* out, int dim, int inter) {
     DEV(device); if (bad_q(quant)) return fail(CUQWEN_ERR_ARG, "quant out of range");
+    NOT_NULL(x, wg, wu, out); SCALES_OK(quant, sg, su);
     GemvArgs a = gv((const __half*)x, dim); a.norm_w = (const __half*)norm_w; a.eps = eps;
     a.w[0] = (const uint8_t*)wg; a.w[1] = (const uint8_t*)wu; a.s[0] = (const __half*)sg; a.s[1] = (const __half*)su; a.rows = inter; a.out_h = (__half*)out;
     KK(launch_gemv(quant, EPI_SWIGLU, a, cfg)); return CUQWEN_OK;
 }
 extern "C" int cuqwen_k_penalty(int device, void* logits, const int* hist, const int* d_len, int vocab, float pen, void* bitmap) {
     DEV(device);
+    NOT_NULL(logits, hist, d_len, bitmap);
     KK(launch_penalty((__half*)logits, hist, d_len, vocab, 0, pen, (unsigned*)bitmap, cfg));
     KK(launch_clear_bitmap(hist, d_len, vocab, 0, (unsigned*)bitmap, cfg));
     return CUQWEN_OK;
 }
 extern "C" int cuqwen_k_argmax(int device, const void* logits, int* d_out, int vocab, void* scratch16) {
     DEV(device);
+    NOT_NULL(logits, d_out, scratch16);
     unsigned long long* best = (unsigned long long*)scratch16;
     KK(launch_argmax((const __half*)logits, vocab, 0, nullptr, nullptr, 0, nullptr, nullptr, best, (unsigned*)(best + 1), nullptr, d_out, cfg));
     return CUQWEN_OK;
 }
 extern "C" int cuqwen_k_dequant(int device, int quant, const void* w, const void* s, void* out, long rows, long cols) {
     DEV(device); if (quant != 1 && quant != 2) return fail(CUQWEN_ERR_ARG, "dequant needs quant 1 or 2");
+    NOT_NULL(w, s, out);
     KK(launch_dequant(quant, w, (const __half*)s, (__half*)out, rows, cols, cfg)); return CUQWEN_OK;
+}
+
+// Tensor-parallel helper, stand-alone: x_next = half(float(x) + sum over n_ranks receive slots [n_ranks][dim] of
+// {fp32 partial, sequence} words), waiting (bounded) until every word carries step * 512 + seq_index + 1 with the step
+// read from *d_step_no.  wait_cycles bounds the wait in SM cycles (0 = the default, two to four seconds); when it runs
+// out the kernel returns, and the next cuqwen_dev_sync reports CUQWEN_ERR_TIMEOUT.
+extern "C" int cuqwen_k_tp_sum(int device, const void* x, void* x_next, const void* slots, int n_ranks, int dim, const int* d_step_no, int seq_index,
+                               long long wait_cycles) {
+    DEV(device);
+    if (n_ranks < 1 || n_ranks > 8 || dim <= 0 || dim % 8 || seq_index < 0 || seq_index >= (int)kSeqPerStep || wait_cycles < 0)
+        return fail(CUQWEN_ERR_ARG, "unsupported tp_sum arguments");
+    NOT_NULL(x, x_next, slots, d_step_no);
+    KK(launch_tp_sum((const __half*)x, (__half*)x_next, slots, n_ranks, dim, d_step_no, seq_index, t_err, wait_cycles, cfg));
+    return CUQWEN_OK;
 }

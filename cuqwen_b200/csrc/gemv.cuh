@@ -51,16 +51,17 @@ struct alignas(64) GemvArgs {
     // EPI_PUSH stores each fp32 partial output, paired with the exchange's sequence number in one 8-byte word, straight
     // into every rank's receive slot over NVLink peer stores.  The kernel that consumes the vector next (always a GEMV
     // with fused RMSNorm) reads the words until every one carries the expected sequence number and forms
-    // x_next = half(float(x) + sum_r partial_r) while it stages x ("gather").  An 8-byte store is single-copy atomic,
-    // so a word is either old (wrong number) or complete.  Reference: single-GPU only; the sum replaces
+    // x_next = half(float(x) + sum_r partial_r) while it stages x ("gather").  A word travels as one 64-bit scalar
+    // store and is read as one 64-bit element, so it is either old (wrong number) or complete.  Reference: single-GPU only; the sum replaces
     // src/kernels.cu:670-671 / :620-621 across ranks.
     uint2* push[8];                // EPI_PUSH: start of this rank's slot inside rank d's receive buffer, {value bits, sequence}
     int npush;
     int ngather;                   // consumer: number of slots to add to x (0 = plain x)
     const uint2* gather;           // this rank's receive slots, [ngather][K] words
     __half* x_next;                // where CTA 0 stores the summed vector (never the buffer x points at)
-    const int* step_no;            // sequence number of an exchange = *step_no * 128 + seq_index + 1
+    const int* step_no;            // sequence number of an exchange = *step_no * kSeqPerStep + seq_index + 1
     int seq_index;
+    long long wait_cycles;         // bound of the gather's re-read loop in SM cycles (0 = kWaitCyclesDefault)
     // Hand-over of an activation vector in staged form.  A SwiGLU kernel whose blocks are whole 128-row groups (rw = 8,
     // no K split) also writes its outputs as the digit blocks, corrections and scales that a quantised GEMV's inner loop
     // reads (gemv_stage.cuh), once; the GEMV that consumes the vector then fetches them with three bulk copies
@@ -71,6 +72,7 @@ struct alignas(64) GemvArgs {
     // warp asks L2 for them while this kernel streams, so that their first use is an L2 hit instead of an HBM miss.
     const void* warm[3];
     int warm_bytes[3];
+    unsigned long long* trace;     // optional: this launch's eight timeline words (tma.cuh), else null
 };
 
 template <int EPI> struct EpiMT { static constexpr int MT = (EPI == EPI_SWIGLU || EPI == EPI_QKV) ? 2 : 1; };
@@ -162,7 +164,7 @@ __device__ __forceinline__ void epilogue_fetch(const GemvArgs& a, int row0, int 
         pre[0] = __half2float(a.bias[mat][ra]);
         pre[1] = __half2float(a.bias[mat][ra + a.hd / 2]);
     } else if (EPI == EPI_PUSH) {
-        pre[1] = __uint_as_float((unsigned)(*a.step_no) * 128u + (unsigned)a.seq_index + 1u);     // the exchange's sequence number, as bits
+        pre[1] = __uint_as_float((unsigned)(*a.step_no) * kSeqPerStep + (unsigned)a.seq_index + 1u);     // the exchange's sequence number, as bits
     }
 }
 
@@ -179,8 +181,7 @@ __device__ __forceinline__ void epilogue(const GemvArgs& a, int row0, int mat, i
         const int row = row0 + r;
         if (row < a.rows) {
             const unsigned vb = __float_as_uint(v0), seq = __float_as_uint(pre[1]);
-            for (int d = 0; d < a.npush; ++d)                            // peer stores (one of them local), value and number together
-                asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(a.push[d] + row), "r"(vb), "r"(seq) : "memory");
+            for (int d = 0; d < a.npush; ++d) st_pair(a.push[d] + row, vb, seq);      // peer stores (one of them local), value and number in one 64-bit word
         }
     } else if (EPI == EPI_RESID) {
         // reference src/kernels.cu:670-671 and :620-621

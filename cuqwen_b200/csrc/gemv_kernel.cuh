@@ -131,8 +131,8 @@ __device__ __forceinline__ void gemv_consume(const GemvArgs& a, RingCtx& R, int 
     float* xscale = reinterpret_cast<float*>(R.base + R.off_xscale);
     float* red = reinterpret_cast<float*>(R.base + R.off_red);
 
-    GatherSrc gs{a.gather, a.ngather, 0u, a.x_next, cta == 0, R.err};
-    if (a.ngather > 0) gs.seq = (unsigned)(*a.step_no) * 128u + (unsigned)a.seq_index + 1u;     // tensor parallel: x plus the partials the ranks pushed
+    GatherSrc gs{a.gather, a.ngather, 0u, a.x_next, cta == 0, R.err, a.wait_cycles > 0 ? a.wait_cycles : kWaitCyclesDefault};
+    if (a.ngather > 0) gs.seq = (unsigned)(*a.step_no) * kSeqPerStep + (unsigned)a.seq_index + 1u;     // tensor parallel: x plus the partials the ranks pushed
     if (kInt && a.xd_in) {
         // the vector arrives already staged (digit blocks, corrections, scales written by the kernel that produced it)
         const uint32_t cbytes = (uint32_t)((ngrp * 4 + 15) / 16 * 16);
@@ -150,6 +150,7 @@ __device__ __forceinline__ void gemv_consume(const GemvArgs& a, RingCtx& R, int 
     const bool emit = EPI == EPI_SWIGLU && kInt && a.xd_out != nullptr && rw == 8 && kw == 1 && gw == 1;
     __half* hbuf = reinterpret_cast<__half*>(red);
     if (R.stamp && threadIdx.x == 0) *R.stamp = global_ns();
+    if (threadIdx.x == 0) trace_last(a.trace, 3);
 
     for (int j = 0; j < n_b; ++j) {
         const int blk = cta + j * ncta;
@@ -219,6 +220,7 @@ __device__ __forceinline__ void gemv_consume(const GemvArgs& a, RingCtx& R, int 
             R.advance();
         }
         if (kInt) { __syncwarp(); if (lane == 0) mbar_arrive(R.bar_sempty + sb * 8); ++R.sj; }
+        if (threadIdx.x == 0 && j == n_b - 1) trace_last(a.trace, 4);
         if constexpr (!kInt) {
 #pragma unroll
             for (int m = 0; m < MT; ++m) { tot[m][0] = cf[m][0][0] + cf[m][1][0]; tot[m][1] = cf[m][0][2] + cf[m][1][2]; }
@@ -275,7 +277,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const __grid_cons
     extern __shared__ __align__(128) unsigned char smem_raw[];
     pdl_launch_dependents();    // the next kernel in the stream may start its weight prefetch while this one runs
     RingCtx R = gemv_ring<Q, EPI>(a, smem_raw);
-    if (threadIdx.x == 0) ring_init_barriers(R);
+    if (threadIdx.x == 0) { trace_first(a.trace, 0); trace_last(a.trace, 1); ring_init_barriers(R); }
     __syncthreads();
     if ((threadIdx.x >> 5) == kConsumerWarps) {
         if (blockIdx.x == 0) {
@@ -288,7 +290,9 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const __grid_cons
         return;
     }
     pdl_wait();                 // the activation vector comes from the previous kernel
+    if (threadIdx.x == 0) trace_first(a.trace, 2);
     gemv_consume<Q, EPI>(a, R, blockIdx.x, gridDim.x);
+    if (threadIdx.x == 0) trace_last(a.trace, 5);
 }
 
 }  // namespace cq

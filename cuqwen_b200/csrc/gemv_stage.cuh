@@ -79,7 +79,7 @@ __device__ __forceinline__ float park_raw(const __half* x, const __half* norm_w,
 // Tensor-parallel consumer side of an exchange (see GemvArgs): what park_raw does, for x_new = half(float(x) + sum over
 // ranks of the fp32 partials in this rank's receive slots), summed in rank order so every rank forms the same bits.
 // A slot word is {value bits, sequence number}; a word whose number is not `seq` yet has not arrived and is read again
-// (bounded: after 4e9 SM cycles, two to four seconds, *err is set and the stale value is used).
+// (bounded: after `limit` SM cycles, by default 4e9 = two to four seconds, *err is set and the stale value is used).
 // store_next: this CTA also writes x_new to global memory for the kernels after this one.
 struct GatherSrc {
     const uint2* slots;      // [n][K] words
@@ -88,12 +88,8 @@ struct GatherSrc {
     __half* x_next;          // written when store_next
     bool store_next;
     unsigned* err;
+    long long limit;         // SM cycles after which the re-read loop gives up
 };
-__device__ __forceinline__ uint4 ld_volatile16(const void* p) {
-    uint4 v;
-    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
-    return v;
-}
 template <bool PARKW>
 __device__ __forceinline__ float park_gather(const __half* x, const __half* norm_w, const GatherSrc& gs, int K, int nchunk, uint4* raw, uint4* wraw, int nthreads) {
     constexpr int RB = 2;                                  // source ranks whose loads are in flight together
@@ -105,33 +101,33 @@ __device__ __forceinline__ float park_gather(const __half* x, const __half* norm
         if (PARKW) wv = __ldg(reinterpret_cast<const uint4*>(norm_w) + c8);
         float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
         for (int r0 = 0; r0 < gs.n; r0 += RB) {
-            uint4 q[RB][4];
+            unsigned long long q[RB][8];
             unsigned long long t0 = 0ull;
             for (;;) {
                 bool ok = true;
 #pragma unroll
                 for (int j = 0; j < RB; ++j)
                     if (r0 + j < gs.n) {
-                        const uint4* p = reinterpret_cast<const uint4*>(gs.slots + (size_t)(r0 + j) * K + (size_t)c8 * 8);
+                        const uint2* p = gs.slots + (size_t)(r0 + j) * K + (size_t)c8 * 8;
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) q[j][i] = ld_volatile16(p + i);
+                        for (int i = 0; i < 4; ++i) ld_pair2(p + 2 * i, q[j][2 * i], q[j][2 * i + 1]);
                     }
 #pragma unroll
                 for (int j = 0; j < RB; ++j)
                     if (r0 + j < gs.n) {
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) ok = ok && q[j][i].y == gs.seq && q[j][i].w == gs.seq;
+                        for (int i = 0; i < 8; ++i) ok = ok && pair_seq(q[j][i]) == gs.seq;
                     }
                 if (ok || gave_up) break;
                 const unsigned long long now = (unsigned long long)sm_cycles();      // the SM's cycle counter: cheap to read
                 if (t0 == 0ull) t0 = now | 1ull;
-                else if (now - t0 > 4000000000ull) { gave_up = true; if (gs.err) atomicExch(gs.err, 8u); break; }
+                else if (now - t0 > (unsigned long long)gs.limit) { gave_up = true; if (gs.err) atomicExch(gs.err, 8u); break; }
             }
 #pragma unroll
             for (int j = 0; j < RB; ++j)
                 if (r0 + j < gs.n) {
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) { s[2 * i] += __uint_as_float(q[j][i].x); s[2 * i + 1] += __uint_as_float(q[j][i].z); }
+                    for (int i = 0; i < 8; ++i) s[i] += pair_val(q[j][i]);
                 }
         }
         uint4 xn;

@@ -184,42 +184,43 @@ int launch_merge_keys(const unsigned long long* keys, int n, StepCtl* ctl, int* 
 // ---- tensor-parallel residual from pushed slots: x_next = half(float(x) + sum_r slot_r), one thread per 8 columns ----
 // Used instead of the gather inside the consuming GEMV when there are many ranks: there every CTA would read all
 // ranks' slots again; here they are read once.  Same words, same bounded re-read, same rank order as park_gather.
-__global__ void tp_sum_kernel(const __half* __restrict__ x, __half* __restrict__ x_next, const uint2* slots, int n, int K, const int* step_no, int seq_index, unsigned* err) {
+__global__ void tp_sum_kernel(const __half* __restrict__ x, __half* __restrict__ x_next, const uint2* slots, int n, int K, const int* step_no, int seq_index,
+                              unsigned* err, long long limit) {
     pdl_launch_dependents(); pdl_wait();
     const int c8 = blockIdx.x * blockDim.x + threadIdx.x;
     if (c8 >= K / 8) return;
-    const unsigned seq = (unsigned)(*step_no) * 128u + (unsigned)seq_index + 1u;
+    const unsigned seq = (unsigned)(*step_no) * kSeqPerStep + (unsigned)seq_index + 1u;
     const uint4 xo = __ldcg(reinterpret_cast<const uint4*>(x) + c8);
     float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     bool gave_up = false;
     for (int r0 = 0; r0 < n; r0 += 4) {
-        uint4 q[4][4];
+        unsigned long long q[4][8];
         unsigned long long t0 = 0ull;
         for (;;) {
             bool ok = true;
 #pragma unroll
             for (int j = 0; j < 4; ++j)
                 if (r0 + j < n) {
-                    const uint4* p = reinterpret_cast<const uint4*>(slots + (size_t)(r0 + j) * K + (size_t)c8 * 8);
+                    const uint2* p = slots + (size_t)(r0 + j) * K + (size_t)c8 * 8;
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) q[j][i] = ld_volatile16(p + i);
+                    for (int i = 0; i < 4; ++i) ld_pair2(p + 2 * i, q[j][2 * i], q[j][2 * i + 1]);
                 }
 #pragma unroll
             for (int j = 0; j < 4; ++j)
                 if (r0 + j < n) {
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) ok = ok && q[j][i].y == seq && q[j][i].w == seq;
+                    for (int i = 0; i < 8; ++i) ok = ok && pair_seq(q[j][i]) == seq;
                 }
             if (ok || gave_up) break;
             const unsigned long long now = (unsigned long long)sm_cycles();      // the SM's cycle counter: cheap to read
             if (t0 == 0ull) t0 = now | 1ull;
-            else if (now - t0 > 4000000000ull) { gave_up = true; if (err) atomicExch(err, 8u); break; }
+            else if (now - t0 > (unsigned long long)limit) { gave_up = true; if (err) atomicExch(err, 8u); break; }
         }
 #pragma unroll
         for (int j = 0; j < 4; ++j)
             if (r0 + j < n) {
 #pragma unroll
-                for (int i = 0; i < 4; ++i) { s[2 * i] += __uint_as_float(q[j][i].x); s[2 * i + 1] += __uint_as_float(q[j][i].z); }
+                for (int i = 0; i < 8; ++i) s[i] += pair_val(q[j][i]);
             }
     }
     uint4 xn;
@@ -229,8 +230,10 @@ __global__ void tp_sum_kernel(const __half* __restrict__ x, __half* __restrict__
     for (int k = 0; k < 4; ++k) { const float2 f = __half22float2(h[k]); o[k] = __floats2half2_rn(f.x + s[2 * k], f.y + s[2 * k + 1]); }
     reinterpret_cast<uint4*>(x_next)[c8] = xn;
 }
-int launch_tp_sum(const __half* x, __half* x_next, const void* slots, int n, int K, const int* step_no, int seq_index, unsigned* err, const LaunchCfg& cfg) {
-    return launch_k(tp_sum_kernel, dim3((K / 8 + 31) / 32), dim3(32), 0, cfg, x, x_next, (const uint2*)slots, n, K, step_no, seq_index, err);
+int launch_tp_sum(const __half* x, __half* x_next, const void* slots, int n, int K, const int* step_no, int seq_index, unsigned* err, long long wait_cycles,
+                  const LaunchCfg& cfg) {
+    return launch_k(tp_sum_kernel, dim3((K / 8 + 31) / 32), dim3(32), 0, cfg, x, x_next, (const uint2*)slots, n, K, step_no, seq_index, err,
+                    wait_cycles > 0 ? wait_cycles : kWaitCyclesDefault);
 }
 
 // ---- tensor-parallel residual: x = half(float(x) + sum_r partial_r) --------

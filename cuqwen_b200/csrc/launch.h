@@ -9,8 +9,6 @@ namespace cq {
 
 struct GemvArgs;
 struct AttnArgs;
-struct StepPhase;
-struct StepArgs;
 
 // Device-resident control block of one decode step.  The graph reads token /
 // pos / hist_len from here; with auto_advance set the sampler feeds its result
@@ -41,13 +39,6 @@ int gemv_tile_sets_per_block(int nsets, int sm_count, int epi);
 // lands in shared memory chunk-major, [chunk][row][64 bytes].
 int make_weight_map(CUtensorMap* m, const void* w, size_t row_bytes, size_t rows, int piece_bytes, int box_rows);
 
-// Persistent decode-step kernel (step_kernel.cuh).  plan_step_gemv fills the work split and tensor maps of one GEMV
-// phase; plan_step_smem lays out shared memory for a planned table; launch_decode_step launches `grid` CTAs
-// cooperatively (grid <= SM count).  `sa.bar` must be zero when the kernel starts.
-int plan_step_gemv(int quant, int epi, GemvArgs& a, int ncta, int slot_bytes);
-int plan_step_smem(StepArgs& sa, const StepPhase* phases, int n, int head_dim, int slot_bytes, int max_smem);
-int launch_decode_step(int quant, const StepArgs& sa, int grid, const LaunchCfg& cfg);
-
 int launch_attn(int head_dim, const AttnArgs& a, const LaunchCfg& cfg);
 size_t attn_scratch_floats_o(int n_kv, int nsplit, int head_dim);
 size_t attn_scratch_floats_ml(int n_kv, int nsplit);
@@ -72,7 +63,9 @@ int launch_merge_keys(const unsigned long long* keys, int n, StepCtl* ctl, int* 
 // x = half(float(x) + sum_r partial[r][:])   (row-parallel layers under tensor parallelism)
 int launch_resid_sum(__half* x, const float* partial, int n_parts, size_t part_stride, int dim, const LaunchCfg& cfg);
 // Tensor parallel, many ranks: x_next = half(float(x) + sum over n ranks of the pushed {value, sequence} slots [n][K]).
-int launch_tp_sum(const __half* x, __half* x_next, const void* slots, int n, int K, const int* step_no, int seq_index, unsigned* err, const LaunchCfg& cfg);
+// wait_cycles: bound of the re-read loop in SM cycles (0 = the default of about two to four seconds).
+int launch_tp_sum(const __half* x, __half* x_next, const void* slots, int n, int K, const int* step_no, int seq_index, unsigned* err, long long wait_cycles,
+                  const LaunchCfg& cfg);
 // out = half(float(q) * float(scale)) for every weight; quant 1 or 2.
 int launch_dequant(int quant, const void* w, const __half* s, __half* out, long rows, long cols, const LaunchCfg& cfg);
 // Deterministic N(0,1) fp16 fill: element i gets a value that depends only on (seed, base + i).

@@ -4,9 +4,10 @@
 
 * launch by launch (``cuqwen_step_profile``): the default path run eagerly with a CUDA event after every launch, averaged
   per kind of kernel (times include launch gaps, so they bound the graph replay from above);
-* phase by phase (``CUQWEN_FLAG_FUSED_STEP | CUQWEN_FLAG_STEP_TRACE``): the persistent step kernel's own stamps - for
-  every phase the span from the first CTA entering it to the first CTA entering the next, the mean and longest time a
-  CTA's consumers were busy in it, the time spent staging the activation vector, and the barrier that follows.
+* inside the graph (``CUQWEN_FLAG_STEP_TRACE``): every GEMV / attention launch stamps its own timeline while the step
+  replays as a CUDA graph with programmatic dependent launch - relative to the moment the launch before it finished:
+  when its first / last CTA started, when the dependency wait returned, when the input vector was staged, when the
+  main loop and the kernel ended.  The last column is what the launch adds to the step.
 
 The reference's counterpart is benchmark/kernel_profile.cu, which times each kernel in isolation.
 """
@@ -19,7 +20,7 @@ from pathlib import Path
 
 import numpy as np
 
-from . import binfmt, build
+from . import _abi, binfmt, build
 from . import engine as E
 
 
@@ -54,35 +55,35 @@ def launches(model: str, quant: str, ctx: int, reps: int = 5) -> dict:
     return out
 
 
-def phases(model: str, quant: str, ctx: int) -> dict:
+def timeline(model: str, quant: str, ctx: int, reps: int = 8) -> dict:
     prm = E.model_params(model, quant)
-    prm.flags = E.FLAG_FUSED_STEP | E.FLAG_STEP_TRACE
+    prm.flags = E.FLAG_STEP_TRACE
     eng = E.Engine(prm)
     eng.load(str(model_file(model, quant)))
     eng.kv_fill_normal(ctx, 42)
     eng.decode_n(1234, ctx, 64)
     ms = eng.last_decode_ms / 64
-    eng.step(5, ctx + 64)
-    _, nbytes = eng.ptr("STEP_TRACE")
-    if nbytes == 0:
-        eng.close()
-        return {"ms_per_step": ms, "phases": {}}
     L = binfmt.MODELS[model]["layers"]
-    nph = 6 * L + 1
-    tr = eng.read("STEP_TRACE", dtype=np.uint64).astype(np.int64).reshape(nph, -1, 4)
+    ptr, nbytes = eng.ptr("STEP_TRACE")
+    acc = None
+    for r in range(reps):
+        _abi.check(_abi.lib().cuqwen_dev_memset(eng.device, ptr, 0, nbytes))
+        E.sync(eng.device)
+        eng.step(5, ctx + 64 + r)                               # one graph replay
+        t = eng.read("STEP_TRACE", dtype=np.uint64).reshape(-1, 8).copy()
+        for c in (0, 2):
+            t[:, c] = ~t[:, c]                                  # "first" stamps are stored complemented
+        t = t.astype(np.int64)[1:1 + 6 * L + 1]                 # launch 0 is the embedding copy (no stamps)
+        prev_end = np.concatenate([[t[0, 0]], t[:-1, 5]])
+        rel = (t[:, :6] - prev_end[:, None]) / 1e3
+        acc = rel if acc is None else acc + rel
     eng.close()
+    rel = acc / reps
+    body = rel[:6 * L].reshape(L, 6, 6)[1:].mean(0)             # skip the first layer (it follows the embedding copy)
     names = ["qkv", "attn partials", "attn fold", "o_proj", "gate/up", "down"]
-    agg: dict = {}
-    for p in range(nph):
-        name = names[p % 6] if p < nph - 1 else "lm_head"
-        ent, stg, ext = tr[p, :, 0], tr[p, :, 1], tr[p, :, 2]
-        nxt = tr[p + 1, :, 0].min() if p + 1 < nph else ext.max()
-        staged = [(s - e) for s, e in zip(stg, ent) if s > 0]
-        d = dict(span=(nxt - ent.min()) / 1e3, busy_mean=float((ext - ent).mean()) / 1e3, busy_max=float((ext - ent).max()) / 1e3,
-                 stage=float(np.mean(staged)) / 1e3 if staged else 0.0, barrier=(nxt - ext.max()) / 1e3)
-        if p >= 6 or name == "lm_head":          # skip the first layer (cold)
-            agg.setdefault(name, []).append(d)
-    return {"ms_per_step": ms, "phases": {n: {k: float(np.mean([d[k] for d in lst])) for k in lst[0]} for n, lst in agg.items()}}
+    rows = {n: body[i].tolist() for i, n in enumerate(names)}
+    rows["lm_head"] = rel[6 * L].tolist()
+    return {"ms_per_step": ms, "rows": rows, "layer_us": float(body[:, 5].sum())}
 
 
 def main():
@@ -99,11 +100,12 @@ def main():
         print(f"  {n:<22s} {v:7.2f} us per layer")
     for n, v in la["tail"].items():
         print(f"  {n:<22s} {v:7.2f} us")
-    ph = phases(a.model, a.quant, a.ctx)
-    print(f"persistent step kernel: {ph['ms_per_step']:.3f} ms per step")
-    print(f"  {'phase':<14s} {'span':>7s} {'busy':>7s} {'longest':>7s} {'staging':>7s} {'barrier':>7s}   (us)")
-    for n, d in ph["phases"].items():
-        print(f"  {n:<14s} {d['span']:7.2f} {d['busy_mean']:7.2f} {d['busy_max']:7.2f} {d['stage']:7.2f} {d['barrier']:7.2f}")
+    tl = timeline(a.model, a.quant, a.ctx)
+    print(f"inside the graph ({tl['ms_per_step']:.3f} ms per step with the stamps on), us after the previous launch ended:")
+    print(f"  {'launch':<14s} {'1st CTA':>8s} {'last CTA':>8s} {'wait ret':>8s} {'staged':>8s} {'loop end':>8s} {'end':>8s}")
+    for n, v in tl["rows"].items():
+        print(f"  {n:<14s} " + " ".join(f"{x:8.2f}" if abs(x) < 1e6 else f"{'-':>8s}" for x in v))
+    print(f"  one layer: {tl['layer_us']:.2f} us")
 
 
 if __name__ == "__main__":

@@ -42,9 +42,8 @@ enum {
     CUQWEN_FLAG_ACCURATE_ROPE = 1,  /* accurate pow/sin/cos instead of the fast-math forms the reference build uses */
     CUQWEN_FLAG_NO_PDL = 2,         /* plain stream order between kernels (no programmatic dependent launch) */
     CUQWEN_FLAG_NO_GRAPH = 4,       /* launch the step kernel by kernel instead of replaying a CUDA graph */
-    CUQWEN_FLAG_FUSED_STEP = 8,     /* experimental: all matrices and the attention of a step in one persistent kernel (grid barriers between
-                                     * phases) instead of one launch each; single GPU only */
-    CUQWEN_FLAG_STEP_TRACE = 16,    /* the step kernel stamps phase entry / exit times per CTA (CUQWEN_PTR_STEP_TRACE) */
+    /* 8 is unused (it selected a persistent one-launch step kernel that was removed: it never beat the launch chain) */
+    CUQWEN_FLAG_STEP_TRACE = 16,    /* profiling: every GEMV / attention launch of a step stamps its timeline (CUQWEN_PTR_STEP_TRACE) */
     CUQWEN_FLAG_TP_NCCL = 32,       /* tensor parallel: sum the row-parallel partials with NCCL all-reduce calls instead of peer stores */
     CUQWEN_FLAG_NO_HANDOVER = 64    /* the down projection converts its input itself instead of taking it staged from the SwiGLU kernel */
 };
@@ -100,7 +99,10 @@ int cuqwen_tp_plan(int n_heads, int n_kv_heads, int head_dim, int intermediate_s
 enum {
     CUQWEN_PTR_X = 0, CUQWEN_PTR_XN, CUQWEN_PTR_Q, CUQWEN_PTR_K, CUQWEN_PTR_V, CUQWEN_PTR_ATT, CUQWEN_PTR_GATE,
     CUQWEN_PTR_LOGITS, CUQWEN_PTR_KEY_CACHE, CUQWEN_PTR_VALUE_CACHE, CUQWEN_PTR_HISTORY,
-    CUQWEN_PTR_STEP_TRACE,          /* u64 [phases][CTAs][4] nanosecond stamps of the last step (enter, x staged, leave, spare); phases = 6 per layer + 1 */
+    CUQWEN_PTR_STEP_TRACE,          /* u64 [launch][8] nanosecond stamps merged over CTAs with atomic max, launch = position in the step (0 = the
+                                     * embedding copy, then 6 per layer, then the lm_head): ~first CTA start, last CTA start, ~first dependency
+                                     * wait returned, last input staged, last main loop done, last exit, 2 spare ("~" = stored complemented).
+                                     * Stamps accumulate: zero the block between steps. */
     CUQWEN_PTR_EMBED = 32, CUQWEN_PTR_NORM, CUQWEN_PTR_LM_HEAD, CUQWEN_PTR_LM_HEAD_SCALE,
     CUQWEN_PTR_IN_NORM = 64, CUQWEN_PTR_WQ, CUQWEN_PTR_SQ, CUQWEN_PTR_BQ, CUQWEN_PTR_WK, CUQWEN_PTR_SK, CUQWEN_PTR_BK,
     CUQWEN_PTR_WV, CUQWEN_PTR_SV, CUQWEN_PTR_BV, CUQWEN_PTR_WO, CUQWEN_PTR_SO, CUQWEN_PTR_POST_NORM,
@@ -147,7 +149,9 @@ int cuqwen_k_embedding(int device, const void* embed_table, const int* d_token, 
 /* launch_rmsnorm (kernels.cuh:132-139); eps as the fp16-rounded value the reference passes. */
 int cuqwen_k_rmsnorm(int device, const void* x, const void* weight, void* out, int dim, float eps);
 /* launch_fused_attn_block (kernels.cuh:69-94): q/k/v = W.x + b, then RoPE on q and k.  norm_weight non-null
- * fuses the RMSNorm of x; kcache/vcache non-null also stores k, v at row *d_pos (launch_kv_cache_store, :37-47). */
+ * fuses the RMSNorm of x; kcache/vcache non-null also stores k, v at row *d_pos (launch_kv_cache_store, :37-47).
+ * x, the three weights, the three biases and d_pos are required (and the scales when quant != 0); q_out / k_out / v_out
+ * and the caches may be null one by one.  Like every cuqwen_k_* entry, a null required pointer is CUQWEN_ERR_ARG. */
 int cuqwen_k_qkv(int device, int quant, const void* x, const void* norm_weight, float eps,
                  const void* wq, const void* wk, const void* wv, const void* sq, const void* sk, const void* sv,
                  const void* bq, const void* bk, const void* bv, void* q_out, void* k_out, void* v_out,
@@ -158,7 +162,7 @@ int cuqwen_k_rope(int device, void* q, void* k, int n_heads, int n_kv_heads, int
 /* launch_kv_cache_store (kernels.cuh:37-47) */
 int cuqwen_k_kv_store(int device, const void* k, const void* v, void* kcache, void* vcache, const int* d_pos, int n_kv_heads, int max_seq_len, int head_dim);
 /* launch_gqa_attention_decode (kernels.cuh:21-36).  scratch_o / scratch_ml / counters sized by
- * cuqwen_attn_scratch_bytes; counters must be zero on first use. */
+ * cuqwen_attn_scratch_bytes; `counters` is kept in the signature for callers that size it and is never touched. */
 int cuqwen_k_attention(int device, const void* q, const void* kcache, const void* vcache, void* out, const int* d_pos,
                        int n_heads, int n_kv_heads, int head_dim, int max_seq_len, int n_splits,
                        void* scratch_o, void* scratch_ml, void* counters);
@@ -172,6 +176,11 @@ int cuqwen_attn_scratch_bytes(int n_kv_heads, int head_dim, int n_splits, size_t
  * capture.  Calls that can overlap on one device (different unordered streams) race on the single scratch block. */
 int cuqwen_k_attention_static(int device, void* stream, const void* q, const void* kcache, const void* vcache, void* out,
                               const int* d_pos, int n_heads, int n_kv_heads, int head_dim, int max_seq_len, int n_splits);
+/* No counterpart in the reference.  How a caller of cuqwen_k_attention_static learns that a bounded wait inside its
+ * kernels ran out (the output is then meaningless): the kernels leave a code in a status word of the fixed array, which
+ * no call clears.  This query waits for `stream`, copies the word into *code_out (the caller's own variable; nothing is
+ * allocated), clears it, and returns CUQWEN_ERR_TIMEOUT when it was non-zero, CUQWEN_OK otherwise. */
+int cuqwen_k_attention_static_status(int device, void* stream, unsigned* code_out);
 /* launch_gemv_add_fp16 / launch_fused_mlp_stage2 (kernels.cuh:122-130, :110-120): x_inout += W . input */
 int cuqwen_k_gemv_add(int device, int quant, const void* w, const void* scale, const void* input, void* x_inout, int rows, int cols);
 /* Plain GEMV y = W . x (fp16 out), optional fused RMSNorm of x.  launch_compute_logits(_int8) (kernels.cuh:141-160). */
@@ -187,6 +196,14 @@ int cuqwen_k_penalty(int device, void* logits, const int* d_history, const int* 
 int cuqwen_k_argmax(int device, const void* logits, int* d_token_out, int vocab, void* scratch16);
 /* Dequantised fp16 weights half(float(q) * float(scale)) (the value dot8 multiplies by, src/kernels.cu:27-42). */
 int cuqwen_k_dequant(int device, int quant, const void* w, const void* scale, void* out_fp16, long rows, long cols);
+
+/* No counterpart in the reference (it is single-GPU).  The residual update after a row-parallel matrix under tensor
+ * parallelism, stand-alone: x_next = half(float(x) + sum over n_ranks receive slots), slots = [n_ranks][dim] 8-byte words
+ * {fp32 partial, sequence number}.  The kernel re-reads a word until it carries  *d_step_no * 512 + seq_index + 1, for
+ * at most wait_cycles SM cycles (0 = the default of about 4e9); when the wait runs out it returns with whatever the
+ * slots hold and the next cuqwen_dev_sync reports CUQWEN_ERR_TIMEOUT. */
+int cuqwen_k_tp_sum(int device, const void* x, void* x_next, const void* slots, int n_ranks, int dim, const int* d_step_no, int seq_index,
+                    long long wait_cycles);
 
 const char* cuqwen_strerror(int code);
 const char* cuqwen_last_error(void);

@@ -96,3 +96,15 @@ def test_tp_plan_rejects_impossible_splits(built):
     assert plan(14, 2, 64, 4864, 151936, 0, 3)[0] == 1      # 3 ranks, 2 KV heads
     assert plan(14, 2, 64, 4864, 151936, 1, 2)[0] == 1      # 7 heads x 64 = 448 columns: not whole scale groups
     assert plan(28, 4, 128, 18944, 152064, 9, 8)[0] == 1    # rank out of range
+
+
+def test_tensor_parallel_layer_bound(built):
+    """Exchange sequence numbers are step * 512 + index + 1 with two exchanges per layer: a tensor-parallel engine with
+    more layers than that window holds is refused at creation (single-GPU engines have no exchange and no bound)."""
+    from cuqwen_b200 import engine as E
+    from cuqwen_b200._abi import CuQwenError
+    prm = E.custom_params(1024, 256, 512, 300, 4, 2, 64, "int4", max_seq_len=64)
+    prm.tp_size, prm.tp_rank = 2, 0
+    with pytest.raises(CuQwenError) as err:
+        E.Engine(prm)
+    assert err.value.code == 1 and "layers" in str(err.value)

@@ -5,6 +5,7 @@ Tolerance for fp16 outputs: 2e-3 relative or 1e-2 absolute; integer / bit-patter
 import numpy as np
 import pytest
 
+from cuqwen_b200 import _abi
 from cuqwen_b200 import kernels as K
 from oracle import oracle_py as O
 from tests.gpu_util import ATOL, EPS_H, QNAME, RTOL, DevBuf, Pool, close, dev, dint, quant_mats, report, sync
@@ -331,3 +332,59 @@ def test_embedding_lookup(built):
     out = DevBuf(896 * 2)
     K.embedding_lookup(dev(table), dint(777), out, 896)
     assert np.array_equal(d2h(out), table[777])
+
+
+def test_bounded_wait_runs_out_and_is_reported(built):
+    """The failure-detection path, made to happen on purpose and safely: the tensor-parallel sum waits for exchange
+    words that carry an expected sequence number.  One rank's words never get it, the wait is given a bound of two
+    million cycles (about a millisecond), so the kernel gives up, returns normally and leaves a code in the device's
+    status word; cuqwen_dev_sync reports CUQWEN_ERR_TIMEOUT once, the word is clear afterwards and the next call works."""
+    from cuqwen_b200._abi import CuQwenError
+    lib = _abi.lib()
+    dim, n, step, idx = 1024, 2, 7, 3
+    rng = np.random.default_rng(11)
+    x = rng.standard_normal(dim).astype(np.float16)
+    part = rng.standard_normal((n, dim)).astype(np.float32)
+    seq = step * 512 + idx + 1
+    words = np.zeros((n, dim, 2), np.uint32)
+    words[:, :, 0] = part.view(np.uint32)
+    words[0, :, 1] = seq                       # rank 0 delivered; rank 1's words still carry an old number
+    words[1, :, 1] = seq - 512
+    dx, dn, dw, ds = dev(x), DevBuf(dim * 2), dev(words), dint(step)
+    sync()
+    assert lib.cuqwen_k_tp_sum(0, dx.ptr, dn.ptr, dw.ptr, n, dim, ds.ptr, idx, 2_000_000) == 0
+    with pytest.raises(CuQwenError) as err:
+        sync()
+    assert err.value.code == 9
+    sync()                                     # the status word was cleared by the report
+    words[1, :, 1] = seq
+    dw.upload(words)
+    assert lib.cuqwen_k_tp_sum(0, dx.ptr, dn.ptr, dw.ptr, n, dim, ds.ptr, idx, 2_000_000) == 0
+    sync()
+    want = (x.astype(np.float32) + part[0] + part[1]).astype(np.float16)
+    assert np.array_equal(dn.numpy(np.float16).view(np.uint16), want.view(np.uint16))
+
+
+def test_null_pointers_are_argument_errors_not_faults(built):
+    """Every per-kernel entry point answers CUQWEN_ERR_ARG (1) for a missing required pointer and launches nothing."""
+    lib = _abi.lib()
+    b = DevBuf(1 << 16)
+    p = b.ptr
+    assert lib.cuqwen_k_qkv(0, 2, p, None, 0.0, p, p, p, p, p, p, None, p, p, p, p, p, None, None, 128, 2, 1, 64, 64, p, 1e6, 1) == 1      # bq missing
+    assert lib.cuqwen_k_qkv(0, 2, None, None, 0.0, p, p, p, p, p, p, p, p, p, p, p, p, None, None, 128, 2, 1, 64, 64, p, 1e6, 1) == 1   # x missing
+    assert lib.cuqwen_k_qkv(0, 2, p, None, 0.0, p, p, p, None, p, p, p, p, p, p, p, p, None, None, 128, 2, 1, 64, 64, p, 1e6, 1) == 1   # scale missing for int4
+    assert lib.cuqwen_k_qkv(0, 0, p, None, 0.0, p, p, p, None, None, None, p, p, p, p, p, p, None, None, 128, 2, 1, 64, 64, None, 1e6, 1) == 1   # d_pos missing
+    assert lib.cuqwen_k_gemv(0, 1, p, None, p, None, 0.0, p, 16, 128) == 1
+    assert lib.cuqwen_k_gemv_add(0, 0, None, None, p, p, 16, 128) == 1
+    assert lib.cuqwen_k_gemv_f32(0, 0, p, None, p, None, 16, 128) == 1
+    assert lib.cuqwen_k_mlp1(0, 2, p, None, 0.0, p, p, p, None, p, 128, 128) == 1
+    assert lib.cuqwen_k_attention(0, p, p, p, p, None, 4, 2, 64, 64, 4, p, p, p) == 1
+    assert lib.cuqwen_k_embedding(0, p, None, p, 128) == 1
+    assert lib.cuqwen_k_rmsnorm(0, p, None, p, 128, 1e-6) == 1
+    assert lib.cuqwen_k_rope(0, p, None, 2, 1, 64, p, 1e6, 1) == 1
+    assert lib.cuqwen_k_kv_store(0, p, p, p, None, p, 1, 64, 64) == 1
+    assert lib.cuqwen_k_penalty(0, p, p, None, 128, 1.1, p) == 1
+    assert lib.cuqwen_k_argmax(0, p, None, 128, p) == 1
+    assert lib.cuqwen_k_dequant(0, 2, p, None, p, 16, 128) == 1
+    assert lib.cuqwen_k_tp_sum(0, p, p, None, 2, 128, p, 0, 0) == 1
+    sync()

@@ -7,6 +7,7 @@ its scratch block is reused from call to call and must come back clean.
 from __future__ import annotations
 
 import ctypes
+import ctypes.util
 
 import numpy as np
 import pytest
@@ -14,7 +15,8 @@ import pytest
 from cuqwen_b200 import _abi
 from cuqwen_b200 import kernels as K
 from cuqwen_b200.engine import DevBuf, sync
-from gpu_util import dev, dint
+from gpu_util import close, dev, dint, report
+from oracle import oracle_py as O
 
 pytestmark = pytest.mark.gpu
 
@@ -22,8 +24,33 @@ pytestmark = pytest.mark.gpu
 def _device_sync():
     # The static entry point queues on a caller-chosen stream (here the CUDA default stream), which the library's own
     # stream does not order with: wait for the whole device through the runtime the library is linked against.
-    rt = ctypes.CDLL("libcudart.so.12")
+    rt = ctypes.CDLL(_cudart_name())
     assert rt.cudaDeviceSynchronize() == 0
+
+
+def _cudart_name() -> str:
+    """The CUDA runtime the library itself is linked against (its NEEDED entry, resolved by the loader because the
+    library is already mapped), else whatever the system's search path offers."""
+    lib_path = str(_abi.LIB_PATH)
+    with open("/proc/self/maps") as f:
+        for line in f:
+            if "libcudart" in line:
+                return line.split()[-1]
+    _abi.lib()
+    with open("/proc/self/maps") as f:
+        for line in f:
+            if "libcudart" in line:
+                return line.split()[-1]
+    name = ctypes.util.find_library("cudart")
+    assert name, f"no CUDA runtime found for {lib_path}"
+    return name
+
+
+def _status() -> int:
+    code = ctypes.c_uint(123)
+    rc = _abi.lib().cuqwen_k_attention_static_status(0, None, ctypes.byref(code))
+    assert rc == 0, _abi.lib().cuqwen_last_error()
+    return code.value
 
 
 def _case(nh, nkv, hd, length, nsplit, seed):
@@ -47,6 +74,7 @@ def test_static_scratch_attention_matches_the_allocating_entry(built, nh, nkv, h
     K.gqa_attention_decode(dq, dk, dv, want_buf, dp, nh, nkv, hd, max_seq, nsplit, so, sml, cnt)
     want = want_buf.numpy(np.float16)
     assert np.isfinite(want.astype(np.float32)).all()
+    exact = O.attention(q, Kc, Vc, nh, nkv, hd, max_seq, length)          # the CPU oracle: softmax(q K^T / sqrt(hd)) V in fp32
 
     for call in range(2):
         out = DevBuf(nh * hd * 2)                  # zeroed on the library's stream ...
@@ -55,6 +83,8 @@ def test_static_scratch_attention_matches_the_allocating_entry(built, nh, nkv, h
         _device_sync()
         got = out.numpy(np.float16)
         assert np.array_equal(got.view(np.uint16), want.view(np.uint16)), f"call {call}: static-scratch result differs"
+        assert close(got, exact), f"call {call}: " + report(got, exact)
+        assert _status() == 0, "a bounded wait ran out inside the static-scratch kernels"
 
 
 def test_static_scratch_attention_rejects_shapes_beyond_its_block(built):
