@@ -33,7 +33,7 @@ __global__ void __launch_bounds__(kSplitThreads) attn_partial_kernel(const AttnA
     const int nst = a.stages >= 2 && a.stages <= kSplitStages ? a.stages : kSplitStages;      // ring depth of this launch
     const uint32_t stage0 = smem_u32(dyn), bar_full = smem_u32(sm_bar), bar_empty = bar_full + kSplitStages * 8;
     if (threadIdx.x == 0) {
-        trace_first(a.trace, 0); trace_last(a.trace, 1);
+        trace_first(a.trace, 0); trace_last(a.trace, 1); trace_start(a.trace);
         for (int s = 0; s < nst; ++s) { mbar_init(bar_full + s * 8, 1); mbar_init(bar_empty + s * 8, kSplitWarps); }
         mbar_fence_init();
     }
@@ -104,7 +104,7 @@ __global__ void __launch_bounds__(kFoldWarps * 32) attn_fold_kernel(const AttnAr
     __shared__ float4 o_w[kFoldWarps][NCOL];
     __shared__ float ml_w[kFoldWarps][2];
     pdl_launch_dependents();
-    unsigned long long* tr = a.trace ? a.trace + 8 : nullptr;
+    unsigned long long* tr = a.trace ? a.trace + kTraceWords : nullptr;
     if (threadIdx.x == 0) { trace_first(tr, 0); trace_last(tr, 1); }
     pdl_wait();                 // the partials come from the kernel before this one
     if (threadIdx.x == 0) trace_first(tr, 2);

@@ -378,7 +378,7 @@ extern "C" int cuqwen_load(cuqwen_engine* e, const char* path) {
     if (r) { cudaFree(e->warena); e->warena = nullptr; return fail(r, "copying weights to the device failed: %s", cudaGetErrorString(cudaGetLastError())); }
     CK(cudaDeviceSynchronize());
     if (e->p.flags & CUQWEN_FLAG_STEP_TRACE) {      // eight timeline words per launch, zeroed by the reader between steps
-        e->step_trace_bytes = (size_t)(1 + 8 * e->p.n_layers + 8) * 64;
+        e->step_trace_bytes = (size_t)(1 + 8 * e->p.n_layers + 8) * kTraceWords * 8;
         CK(cudaMalloc((void**)&e->step_trace, e->step_trace_bytes));
         CK(cudaMemset(e->step_trace, 0, e->step_trace_bytes));
     }
@@ -535,7 +535,7 @@ static int record_step(cuqwen_engine* e, cudaStream_t s, bool pdl) {
         std::vector<HostPhase> hp;
         describe_step(e, hp, e->nsplit);
         for (HostPhase& h : hp) {
-            unsigned long long* tr = e->step_trace && (size_t)(n + 2) * 64 <= e->step_trace_bytes ? e->step_trace + (size_t)n * 8 : nullptr;
+            unsigned long long* tr = e->step_trace && (size_t)(n + 2) * kTraceWords * 8 <= e->step_trace_bytes ? e->step_trace + (size_t)n * kTraceWords : nullptr;
             if (h.ph.kind == PH_ATTN) { h.ph.at.trace = tr; LK(launch_attn(p.head_dim, h.ph.at, cfg)); ++n; continue; }      // two launches: partials, fold
             h.ph.g.trace = tr;
             LK(launch_gemv(h.ph.quant, h.ph.epi, h.ph.g, cfg));

@@ -36,6 +36,7 @@ struct alignas(64) GemvArgs {
     int gw;                   // warps that share one (row-warp, K-part) cell: they take the 128-column groups of a staged piece in turn
     int pg;                   // 128-column groups per staged row piece
     int nst;                  // stages in the CTA's ring
+    int nsb;                  // scale blocks in shared memory: 2 (the next block's scales arrive while this one computes) or 1 when no CTA has a second block
     unsigned* err;            // device word that receives a non-zero code when a bounded wait expires (may be null)
     __half* out_h;            // EPI_F16 / EPI_RESID (in-out) / EPI_SWIGLU
     float* out_f;             // EPI_F32
@@ -79,7 +80,7 @@ template <int EPI> struct EpiMT { static constexpr int MT = (EPI == EPI_SWIGLU |
 
 // Shared-memory carve-up, computed the same way by the host (for the launch size) and the kernel.
 //   [x: K*2 bytes (fp16 vector, or the two digit planes)] [per-group corr (int) and xscale (float)] [reduction buffer]
-//   [2 scale blocks] [ring of stages] [mbarriers]
+//   [1 or 2 scale blocks] [ring of stages] [mbarriers]
 // A stage holds, for each K-part kp and tile m, one TMA box of (16*rw rows) x piece_bytes, chunk-major:
 // [kp][m][64-byte chunk][row][64 bytes].
 constexpr int kConsumerWarps = 8;
@@ -87,7 +88,7 @@ struct GemvLayout {
     int piece_bytes, box_rows, box_bytes, stage_bytes, scale_block_bytes;
     int off_corr, off_xscale, off_red, off_scales, off_stages, off_bars, total;
 };
-__host__ __device__ inline GemvLayout gemv_layout(int K, int group_bytes, int MT, int rw, int kw, int pg, int nst, bool quantised) {
+__host__ __device__ inline GemvLayout gemv_layout(int K, int group_bytes, int MT, int rw, int kw, int pg, int nst, bool quantised, int nsb) {
     GemvLayout L;
     const int ng = K / kGroup;
     L.piece_bytes = pg * group_bytes;
@@ -95,21 +96,23 @@ __host__ __device__ inline GemvLayout gemv_layout(int K, int group_bytes, int MT
     L.box_bytes = L.box_rows * L.piece_bytes;
     L.stage_bytes = kw * MT * L.box_bytes;
     L.scale_block_bytes = quantised ? MT * L.box_rows * ng * 2 : 0;
-    int o = K <= 8192 ? K * 4 : K * 2;       // x (fp16 or digits), and room for the RMSNorm weight beside it while x is staged
+    // x (fp16 or digits).  Vectors of up to 6144 values are staged from registers (stage_x_regs); longer ones up to
+    // 8192 get room for the RMSNorm weight beside them while x is staged.
+    int o = K <= 6144 ? K * 2 : K <= 8192 ? K * 4 : K * 2;
     L.off_corr = o; o += (ng * 4 + 15) / 16 * 16;
     L.off_xscale = o; o += (ng * 4 + 15) / 16 * 16;
     L.off_red = o; o += kConsumerWarps * 32 * 4 + 16;
     o = (o + 127) / 128 * 128;
-    L.off_scales = o; o += 2 * L.scale_block_bytes;
+    L.off_scales = o; o += nsb * L.scale_block_bytes;
     o = (o + 127) / 128 * 128;               // TMA destinations are 128-byte aligned
     L.off_stages = o; o += nst * L.stage_bytes;
     L.off_bars = o; o += (2 * nst + 5) * 8;  // full[nst], empty[nst], scale full[2], scale empty[2], x staged[1]
     L.total = o;
     return L;
 }
-inline size_t gemv_smem_bytes(int K, int quant, int MT, int rw, int kw, int pg, int nst) {
+inline size_t gemv_smem_bytes(int K, int quant, int MT, int rw, int kw, int pg, int nst, int nsb) {
     const int gb = quant == Q_I4 ? 64 : quant == Q_I8 ? 128 : 256;
-    return (size_t)gemv_layout(K, gb, MT, rw, kw, pg, nst, quant != Q_F16).total;
+    return (size_t)gemv_layout(K, gb, MT, rw, kw, pg, nst, quant != Q_F16, nsb).total;
 }
 
 // Where the 16 x MT rows of tile set `ts` live.  mrow[m] / mmat[m]: first row of tile m inside matrix mmat[m];

@@ -12,9 +12,17 @@ static int go(const GemvArgs& a, dim3 grid, dim3 block, size_t smem, const Launc
     at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     at[0].val.programmaticStreamSerializationAllowed = 1;
     lc.attrs = at; lc.numAttrs = cfg.pdl ? 1 : 0;
-    if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_kernel<Q_F16, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-        if (e != cudaSuccess) return (int)e;
+    {
+        // Every kernel of the step asks for the largest shared-memory carveout: CTAs of two consecutive kernels can only
+        // share an SM (the second one prefetching its weights while the first still runs) when both run under the same
+        // L1 / shared-memory split.
+        static bool once = false;
+        if (!once) {
+            cudaError_t e = cudaFuncSetAttribute(gemv_kernel<Q_F16, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+            if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_kernel<Q_F16, EPI>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+            if (e != cudaSuccess) return (int)e;
+            once = true;
+        }
     }
     return (int)cudaLaunchKernelEx(&lc, gemv_kernel<Q_F16, EPI>, a);
 }

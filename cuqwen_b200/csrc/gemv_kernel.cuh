@@ -29,6 +29,7 @@ struct RingCtx {
     int slot;                     // next ring slot
     uint32_t par;                 // its parity: number of completed laps, mod 2
     uint32_t sj;                  // scale blocks used so far
+    uint32_t nsb;                 // scale blocks in shared memory (1 or 2): block j uses buffer j % nsb in phase (j / nsb) & 1
     unsigned* err;                // device word that receives a code when a bounded wait expires (may be null)
     bool failed;                  // a wait of this thread expired: stop waiting, finish with meaningless numbers
     bool skip_math;               // development aid: consume the ring without doing the arithmetic
@@ -75,8 +76,8 @@ __device__ __forceinline__ void gemv_produce(const GemvArgs& a, RingCtx& R, int 
         const int blk = cta + j * ncta;
         const TileMap<EPI> tm = map_tileset<EPI>(a, blk * a.rw);
         if (kInt) {
-            const int sb = R.sj & 1;
-            R.wait(R.bar_sempty + sb * 8, ((R.sj >> 1) & 1) ^ 1, 3u);
+            const int sb = R.sj % R.nsb;
+            R.wait(R.bar_sempty + sb * 8, ((R.sj / R.nsb) & 1) ^ 1, 3u);
             const int rows_here = min(G.box_rows, (EPI == EPI_QKV ? 16 : a.rows - tm.row0));
             const int bytes_m = rows_here * G.ngrp * 2;
             const uint32_t dst = R.sm0 + R.off_scales + sb * R.scale_block_bytes;
@@ -145,7 +146,7 @@ __device__ __forceinline__ void gemv_consume(const GemvArgs& a, RingCtx& R, int 
         }
         R.wait(R.bar_x, R.xpar, 9u);
         R.xpar ^= 1u;
-    } else if (stage_x<Q>(a.x, a.norm_w, a.eps, a.K, R.base, R.off_corr, corr, xscale, red, NC, a.ngather > 0 ? &gs : nullptr, R.bar_x, R.xpar)) R.xpar ^= 1u;
+    } else if (stage_x<Q>(a.x, a.norm_w, a.eps, a.K, R.base, R.off_corr, corr, xscale, red, NC, a.ngather > 0 ? &gs : nullptr, R.bar_x, R.xpar, a.trace)) R.xpar ^= 1u;
     // a SwiGLU kernel whose block is a whole 128-row group hands its outputs over in staged form as well
     const bool emit = EPI == EPI_SWIGLU && kInt && a.xd_out != nullptr && rw == 8 && kw == 1 && gw == 1;
     __half* hbuf = reinterpret_cast<__half*>(red);
@@ -170,9 +171,9 @@ __device__ __forceinline__ void gemv_consume(const GemvArgs& a, RingCtx& R, int 
         if (merged) { if (kwi == 0 && gwi == 0 && lane < 16 && live) epilogue_fetch<EPI>(a, tm.row0, tm.mat, lane, preA); }
         else if (t == 0 && live) { epilogue_fetch<EPI>(a, tm.row0, tm.mat, g, preA); epilogue_fetch<EPI>(a, tm.row0, tm.mat, g + 8, preB); }
         uint32_t sbuf = 0;
-        const int sb = R.sj & 1;
+        const int sb = R.sj % R.nsb;
         if (kInt) {
-            R.wait(R.bar_sfull + sb * 8, (R.sj >> 1) & 1, 2u);
+            R.wait(R.bar_sfull + sb * 8, (R.sj / R.nsb) & 1, 2u);
             sbuf = R.sm0 + R.off_scales + sb * R.scale_block_bytes + (rwi * 16 + g) * ngrp * 2;     // this lane's row g of tile 0
         }
         for (int p = 0; p < G.S; ++p) {
@@ -258,14 +259,14 @@ __device__ __forceinline__ void gemv_consume(const GemvArgs& a, RingCtx& R, int 
 // Ring context of a stand-alone launch: the layout gemv_layout computed for this matrix, an empty ring.
 template <int Q, int EPI>
 __device__ __forceinline__ RingCtx gemv_ring(const GemvArgs& a, unsigned char* smem) {
-    const GemvLayout L = gemv_layout(a.K, QT<Q>::GB, EpiMT<EPI>::MT, a.rw, a.kw, a.pg, a.nst, Q != Q_F16);
+    const GemvLayout L = gemv_layout(a.K, QT<Q>::GB, EpiMT<EPI>::MT, a.rw, a.kw, a.pg, a.nst, Q != Q_F16, a.nsb);
     RingCtx R;
     R.sm0 = smem_u32(smem); R.base = smem;
     R.off_corr = L.off_corr; R.off_xscale = L.off_xscale; R.off_red = L.off_red; R.off_scales = L.off_scales;
     R.scale_block_bytes = L.scale_block_bytes; R.off_stages = L.off_stages; R.slot_bytes = L.stage_bytes; R.nslots = a.nst;
     R.bar_full = R.sm0 + L.off_bars; R.bar_empty = R.bar_full + a.nst * 8; R.bar_sfull = R.bar_empty + a.nst * 8; R.bar_sempty = R.bar_sfull + 16;
     R.bar_x = R.bar_sempty + 16; R.xpar = 0u;
-    R.slot = 0; R.par = 0; R.sj = 0; R.err = a.err; R.failed = false; R.skip_math = false; R.stamp = nullptr;
+    R.slot = 0; R.par = 0; R.sj = 0; R.nsb = (uint32_t)a.nsb; R.err = a.err; R.failed = false; R.skip_math = false; R.stamp = nullptr;
 #ifdef CQ_SKIP_MATH
     R.skip_math = true;      // development build: consume the ring without arithmetic (measures the copy path)
 #endif
@@ -277,7 +278,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const __grid_cons
     extern __shared__ __align__(128) unsigned char smem_raw[];
     pdl_launch_dependents();    // the next kernel in the stream may start its weight prefetch while this one runs
     RingCtx R = gemv_ring<Q, EPI>(a, smem_raw);
-    if (threadIdx.x == 0) { trace_first(a.trace, 0); trace_last(a.trace, 1); ring_init_barriers(R); }
+    if (threadIdx.x == 0) { trace_first(a.trace, 0); trace_last(a.trace, 1); trace_start(a.trace); ring_init_barriers(R); }
     __syncthreads();
     if ((threadIdx.x >> 5) == kConsumerWarps) {
         if (blockIdx.x == 0) {

@@ -205,6 +205,45 @@ __device__ __forceinline__ void digits_of_chunk(uint4 v, int c8, bool live, unsi
     }
 }
 
+// Short vectors (at most NB * nthreads chunks of eight values): the whole vector fits the consumers' registers, so it
+// is fetched with plain loads - every load of the CTA in flight at once, an L2 hit each - normalised and converted
+// straight from registers, and only the final form touches shared memory.  Same arithmetic, same bits as the staged
+// path below.  Thread tid owns chunks tid, tid + nthreads, ...: a warp's lanes hold consecutive chunks, sixteen lanes
+// one 128-column group, as digits_of_chunk wants.
+template <int Q, int NB>
+__device__ __forceinline__ void stage_x_regs(const __half* x, const __half* norm_w, float eps, int K, unsigned char* xd, int* corr, float* xscale,
+                                             float* red, int nthreads, unsigned long long* trace = nullptr) {
+    const int nchunk = K / 8;
+    uint4 v[NB], w[NB];
+#pragma unroll
+    for (int i = 0; i < NB; ++i) {
+        const int c8 = i * nthreads + threadIdx.x;
+        v[i] = make_uint4(0u, 0u, 0u, 0u); w[i] = v[i];
+        if (c8 < nchunk) {
+            v[i] = __ldcg(reinterpret_cast<const uint4*>(x) + c8);
+            if (norm_w) w[i] = __ldg(reinterpret_cast<const uint4*>(norm_w) + c8);
+        }
+    }
+    if (norm_w) {
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < NB; ++i) ss += chunk_sumsq(v[i]);
+        if (trace && threadIdx.x == 0 && ss >= 0.f) trace_last(trace, 6);
+        const float inv = consumers_rsqrt_mean(ss, K, eps, red, nthreads);
+        if (trace && threadIdx.x == 0 && inv >= 0.f) trace_last(trace, 7);
+#pragma unroll
+        for (int i = 0; i < NB; ++i) v[i] = apply_norm(v[i], w[i], inv);
+    }
+#pragma unroll
+    for (int i = 0; i < NB; ++i) {
+        const int c8 = i * nthreads + threadIdx.x;
+        if ((i * nthreads + (threadIdx.x & ~31)) >= nchunk) break;        // whole warp beyond the vector (uniform)
+        if (Q == Q_F16) { if (c8 < nchunk) reinterpret_cast<uint4*>(xd)[c8] = v[i]; }
+        else digits_of_chunk<Q>(v[i], c8, c8 < nchunk, xd, corr, xscale);
+    }
+    consumer_sync(nthreads);
+}
+
 // Stage x for the kernel of quantisation Q: digits (int4 / int8, into xd + corr + xscale) or plain fp16 (xd as uint4[]).
 // xarea_bytes: shared memory available from xd on; the norm weight is parked at xd + 2K when 4K bytes fit (else it
 // is re-read from global memory during the conversion).
@@ -214,12 +253,17 @@ __device__ __forceinline__ void digits_of_chunk(uint4 v, int c8, bool live, unsi
 // was used (the caller then flips the parity).
 template <int Q>
 __device__ __forceinline__ bool stage_x(const __half* x, const __half* norm_w, float eps, int K, unsigned char* xd, int xarea_bytes, int* corr, float* xscale,
-                                        float* red, int nthreads, const GatherSrc* gs = nullptr, uint32_t bar_x = 0u, uint32_t xpar = 0u) {
+                                        float* red, int nthreads, const GatherSrc* gs = nullptr, uint32_t bar_x = 0u, uint32_t xpar = 0u, unsigned long long* trace = nullptr) {
     const int nchunk = K / 8, lane = threadIdx.x & 31;
     uint4* raw = reinterpret_cast<uint4*>(xd);
     uint4* wraw = raw + nchunk;
     const bool w_parked = norm_w && 4 * K <= xarea_bytes;
     const bool gather = gs && gs->n > 0;
+    if (!gather && nchunk <= 3 * nthreads && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (!norm_w || (reinterpret_cast<uintptr_t>(norm_w) & 15) == 0)) {
+        if (nchunk <= 2 * nthreads) stage_x_regs<Q, 2>(x, norm_w, eps, K, xd, corr, xscale, red, nthreads, trace);
+        else stage_x_regs<Q, 3>(x, norm_w, eps, K, xd, corr, xscale, red, nthreads, trace);
+        return false;
+    }
     const bool bulk = bar_x != 0u && !gather && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (!norm_w || (w_parked && (reinterpret_cast<uintptr_t>(norm_w) & 15) == 0));
     float inv = 0.f;
     if (bulk) {

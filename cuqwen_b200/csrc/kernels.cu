@@ -8,6 +8,7 @@
 #include "launch.h"
 #include "rng.cuh"
 
+#include <cstdio>
 #include <cstdlib>
 
 namespace cq {
@@ -291,6 +292,8 @@ static int launch_attn_split(const AttnArgs& a, const LaunchCfg& cfg) {
     if (b.stages < 2 || b.stages > kSplitStages) b.stages = kSplitStages;
     const size_t smem = attn_split_smem_bytes(HD, b.stages);
     cudaError_t e = cudaFuncSetAttribute(attn_partial_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_split_smem_bytes(HD, kSplitStages));
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_partial_kernel<HD>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_fold_kernel<HD>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     if (e != cudaSuccess) return (int)e;
     if (int r = launch_k(attn_partial_kernel<HD>, dim3(b.n_kv, b.nsplit), dim3(kSplitThreads), smem, cfg, b)) return r;
     return launch_k(attn_fold_kernel<HD>, dim3(b.n_kv * b.grp), dim3(kFoldWarps * 32), 0, cfg, b);
@@ -371,12 +374,19 @@ int launch_gemv(int quant, int epi, GemvArgs& a, const LaunchCfg& cfg) {
     int rw = gemv_tile_sets_per_block(a.nsets, cfg.sm_count, epi);
     int kw = 8 / rw;                                 // rw * kw may end up below 8 when a row has few pieces: the spare warps idle
     const int nblk = (a.nsets + rw - 1) / rw;
-    const int grid = nblk;                            // CTAs loop when there are more blocks than fit at once
-    // Shared-memory budget of a CTA.  int4 weights with more blocks than SMs: 110 KB, so that two CTAs share an SM and
-    // one streams while the other is in its prologue or epilogue.  int8 / fp16 weights move two to four times the
-    // bytes per row piece, and a ring cut to 110 KB is too shallow for them (measured on the 14B int8 matrices:
-    // gate/up 37.5 us at 110 KB against 28.2 us at 220 KB, lm_head 139 against 119 us): they take the whole SM.
-    int cap = env_int("CUQWEN_GEMV_CAP_KB", (nblk > cfg.sm_count && quant == Q_I4) ? 110 : 220) * 1024;
+    // Shared-memory budget of a CTA.  int4 weights with more blocks than SMs: 110 KB and up to two CTAs per SM's worth
+    // of grid, so that a CTA with a second block need not wait for one with a single block.  int8 / fp16 weights move
+    // two to four times the bytes per row piece, and a ring cut to 110 KB is too shallow for them (measured on the 14B
+    // int8 matrices: gate/up 37.5 us at 110 KB against 28.2 us at 220 KB, lm_head 139 against 119 us): they take the
+    // whole SM.  (Two consecutive kernels of the step never share an SM: a CTA of nine warps takes registers for
+    // twelve, which leaves no room for a second one at 96 to 110 registers per thread; capped at 80 registers they do
+    // share, and the step was slower - 574 against 703 tok/s on the 7B int4 model - because the early weight copies
+    // of the next kernel compete with the loads the running kernel is waiting for.)
+    const int cap_kb = (nblk > cfg.sm_count && quant == Q_I4) ? 110 : 220;
+    const int per_sm = cap_kb == 110 ? 2 : 1;
+    const int grid = nblk < per_sm * cfg.sm_count ? nblk : per_sm * cfg.sm_count;
+    const int nsb = nblk <= grid ? 1 : 2;            // a second scale block only when some CTA has a second block
+    int cap = env_int("CUQWEN_GEMV_CAP_KB", cap_kb) * 1024;
     const int env_pg = env_int("CUQWEN_GEMV_PG", 0), env_nst = env_int("CUQWEN_GEMV_NST", 0);
     int pg = 0, nst = 0;
     for (int pass = 0; pass < 2 && !nst; ++pass) {
@@ -386,8 +396,8 @@ int launch_gemv(int quant, int epi, GemvArgs& a, const LaunchCfg& cfg) {
             const int steps = (pt + kwq - 1) / kwq;
             int want = env_nst > 0 ? env_nst : (rw == 8 ? 6 : steps < 6 ? steps : 6);
             int n = want;
-            while (n > 1 && gemv_smem_bytes(a.K, quant, MT, rw, kwq, q, n) > (size_t)cap) --n;
-            if (gemv_smem_bytes(a.K, quant, MT, rw, kwq, q, n) > (size_t)cap) continue;
+            while (n > 1 && gemv_smem_bytes(a.K, quant, MT, rw, kwq, q, n, nsb) > (size_t)cap) --n;
+            if (gemv_smem_bytes(a.K, quant, MT, rw, kwq, q, n, nsb) > (size_t)cap) continue;
             if (n >= (want < 3 ? want : 3) || q == 1 || env_pg > 0) { pg = q; nst = n; kw = kwq; break; }
             if (!nst || n > nst) { pg = q; nst = n; kw = kwq; }
             if (q == 1) break;
@@ -399,8 +409,8 @@ int launch_gemv(int quant, int epi, GemvArgs& a, const LaunchCfg& cfg) {
     if (epi == EPI_QKV && rw != 1) return (int)cudaErrorInvalidValue;
     int gw = kConsumerWarps / (rw * kw);              // warps left over share cells, group by group
     while (gw > 1 && gw > pg) gw /= 2;
-    a.rw = rw; a.kw = kw; a.gw = gw; a.pg = pg; a.nst = nst;
-    const size_t smem = gemv_smem_bytes(a.K, quant, MT, rw, kw, pg, nst);
+    a.rw = rw; a.kw = kw; a.gw = gw; a.pg = pg; a.nst = nst; a.nsb = nsb;
+    const size_t smem = gemv_smem_bytes(a.K, quant, MT, rw, kw, pg, nst, nsb);
     {
         const size_t rbytes = quant == Q_I4 ? a.K / 2 : quant == Q_I8 ? a.K : (size_t)a.K * 2;
         const int nmat = epi == EPI_QKV ? 3 : epi == EPI_SWIGLU ? 2 : 1;
@@ -409,10 +419,8 @@ int launch_gemv(int quant, int epi, GemvArgs& a, const LaunchCfg& cfg) {
             if (int r = make_weight_map(&a.tmap[m], a.w[m], rbytes, rows_m, pg * gb, 16 * rw)) return r;
         }
     }
-    const int blocks = (a.nsets + rw - 1) / rw;
-    const int per_sm = smem <= 110 * 1024 ? 2 : 1;
-    const dim3 gridd(blocks < per_sm * cfg.sm_count ? blocks : per_sm * cfg.sm_count), block(kGemvThreadsHost);
-    (void)grid;
+    const dim3 gridd(grid), block(kGemvThreadsHost);
+    if (env_int("CUQWEN_GEMV_SHOW", 0)) fprintf(stderr, "gemv q%d epi%d K%d nsets%d: rw%d kw%d gw%d pg%d nst%d nsb%d grid%d smem %zu\n", quant, epi, a.K, a.nsets, rw, kw, gw, pg, nst, nsb, grid, smem);
     if (quant == Q_I4) return launch_gemv_i4(epi, a, gridd, block, smem, cfg);
     if (quant == Q_I8) return launch_gemv_i8(epi, a, gridd, block, smem, cfg);
     return launch_gemv_f16(epi, a, gridd, block, smem, cfg);

@@ -21,10 +21,13 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 }
 __device__ __forceinline__ unsigned long long global_ns() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
 __device__ __forceinline__ long long sm_cycles() { long long t; asm volatile("mov.u64 %0, %clock64;" : "=l"(t)); return t; }
-// Per-launch timeline (profiling aid, CUQWEN_FLAG_STEP_TRACE): a launch owns eight u64 words that its CTAs merge with
+// Per-launch timeline (profiling aid, CUQWEN_FLAG_STEP_TRACE): a launch owns sixteen u64 words that its CTAs merge with
 // atomic max - "earliest" stamps are stored complemented, so one memset to zero resets them all.  One thread per CTA calls.
 //   0 first CTA started (~)   1 last CTA started   2 first consumer past the dependency wait (~)   3 last CTA had its
 //   input vector staged   4 last CTA left its main loop   5 last CTA finished
+//   6, 7 stamps inside the staging of the input vector   8 sum of the CTAs' start times (low 32 bits of each)   9 number of CTAs
+constexpr int kTraceWords = 16;
+__device__ __forceinline__ void trace_start(unsigned long long* t) { if (t) { atomicAdd(t + 8, global_ns() & 0xffffffffull); atomicAdd(t + 9, 1ull); } }
 __device__ __forceinline__ void trace_first(unsigned long long* t, int i) { if (t) atomicMax(t + i, ~global_ns()); }
 __device__ __forceinline__ void trace_last(unsigned long long* t, int i) { if (t) atomicMax(t + i, global_ns()); }
 // Bounded wait: false when the phase did not complete within about 4e9 SM cycles (2 to 4 s at the clocks this part

@@ -70,7 +70,7 @@ def timeline(model: str, quant: str, ctx: int, reps: int = 8) -> dict:
         _abi.check(_abi.lib().cuqwen_dev_memset(eng.device, ptr, 0, nbytes))
         E.sync(eng.device)
         eng.step(5, ctx + 64 + r)                               # one graph replay
-        t = eng.read("STEP_TRACE", dtype=np.uint64).reshape(-1, 8).copy()
+        t = eng.read("STEP_TRACE", dtype=np.uint64).reshape(-1, 16).copy()
         for c in (0, 2):
             t[:, c] = ~t[:, c]                                  # "first" stamps are stored complemented
         t = t.astype(np.int64)[1:1 + 6 * L + 1]                 # launch 0 is the embedding copy (no stamps)
