@@ -41,6 +41,7 @@ SIGNATURES = {
     "cuqwen_step_launches": (_i, [_vp]),
     "cuqwen_step_profile": (_i, [_vp, _i, _i, C.POINTER(C.c_float), _i, C.POINTER(_i)]),
     "cuqwen_dev_alloc": (_i, [_i, _sz, C.POINTER(_vp)]),
+    "cuqwen_dev_sm_count": (_i, [_i, _pi]),
     "cuqwen_dev_free": (_i, [_i, _vp]),
     "cuqwen_dev_upload": (_i, [_i, _vp, _vp, _sz]),
     "cuqwen_dev_download": (_i, [_i, _vp, _vp, _sz]),

@@ -26,6 +26,24 @@ TOK_LIB = ROOT / "cuqwen_b200" / "libcuqwen_tok.so"
 GEN_SRC = CSRC / "gen_random_bin.cpp"
 GEN_BIN = ROOT / "cuqwen_b200" / "gen_random_bin"
 
+def reference_dir() -> Path:
+    """Where a checkout of the reference (CuQwen) lies: $CUQWEN_REFERENCE_DIR, else a directory named `reference`
+    beside this repository.  Only build-time and test-time tooling looks there; nothing at run time does."""
+    return Path(os.environ.get("CUQWEN_REFERENCE_DIR") or ROOT.parent / "reference")
+
+
+def cuda_home() -> Path:
+    """The CUDA toolkit root: $CUDA_HOME / $CUDA_PATH, else the directory two levels above the nvcc on PATH."""
+    for var in ("CUDA_HOME", "CUDA_PATH"):
+        if os.environ.get(var):
+            return Path(os.environ[var])
+    import shutil
+    nvcc = shutil.which("nvcc")
+    if nvcc:
+        return Path(nvcc).resolve().parent.parent
+    raise RuntimeError("CUDA toolkit not found: set CUDA_HOME")
+
+
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xptxas", "-v",
@@ -102,8 +120,8 @@ def build_all(verbose: bool = False) -> None:
     build_tokenizer()
     build_oracle()
     ref = ROOT / "oracle" / "build_ref.py"
-    if ref.exists() and Path("/root/reference/src/kernels.cu").exists():
-        subprocess.run([sys.executable, str(ref)], check=True)
+    if ref.exists() and (reference_dir() / "src" / "kernels.cu").exists():
+        subprocess.run([sys.executable, str(ref), "--ref", str(reference_dir())], check=True)
 
 
 if __name__ == "__main__":

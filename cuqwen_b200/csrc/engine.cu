@@ -160,6 +160,7 @@ struct cuqwen_engine {
     // state
     __half *x = nullptr, *xn = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *att = nullptr, *gate = nullptr, *logits = nullptr;
     __half *kc = nullptr, *vc = nullptr;
+    __half *spare_up = nullptr, *spare_out = nullptr;     // QwenState::up / mlp_out of the source-compatible layer (never read by the step)
     float *part_o = nullptr, *part_ml = nullptr; unsigned* counters = nullptr;
     StepCtl* ctl = nullptr; StepCtl* h_ctl = nullptr;
     int* d_hist = nullptr; unsigned* bitmap = nullptr; unsigned long long* best = nullptr; unsigned* ticket = nullptr;
@@ -229,6 +230,7 @@ extern "C" int cuqwen_create(const cuqwen_params* pin, cuqwen_engine** out) {
     CK(dalloc((void**)&e->q, e->q_dim_l * 2)); CK(dalloc((void**)&e->k, e->kv_dim_l * 2)); CK(dalloc((void**)&e->v, e->kv_dim_l * 2));
     CK(dalloc((void**)&e->att, e->q_dim_l * 2)); CK(dalloc((void**)&e->gate, e->inter_l * 2));
     { const size_t cb = ((size_t)(e->inter_l / kGroup) * 4 + 15) / 16 * 16; CK(dalloc((void**)&e->gate_xd, (size_t)e->inter_l * 2)); CK(dalloc((void**)&e->gate_corr, cb)); CK(dalloc((void**)&e->gate_xscale, cb)); } CK(dalloc((void**)&e->logits, e->vocab_l * 2));
+    CK(dalloc((void**)&e->spare_up, (size_t)e->inter_l * 2)); CK(dalloc((void**)&e->spare_out, (size_t)p.dim * 2));
     CK(dalloc((void**)&e->kc, kvn * 2)); CK(dalloc((void**)&e->vc, kvn * 2));     // zeroed like src/model.cu:37-38
     CK(dalloc((void**)&e->part_o, attn_scratch_floats_o(e->n_kv_l, e->nsplit, p.head_dim) * 4));
     CK(dalloc((void**)&e->part_ml, attn_scratch_floats_ml(e->n_kv_l, e->nsplit) * 4));
@@ -253,7 +255,7 @@ extern "C" void cuqwen_destroy(cuqwen_engine* e) {
     if (e->tp_rx) cudaFree(e->tp_rx);
     if (e->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(e->comm);
     void* bufs[] = {e->x, e->xn, e->q, e->k, e->v, e->att, e->gate, e->logits, e->kc, e->vc, e->part_o, e->part_ml, e->counters, e->ctl, e->d_hist,
-                    e->bitmap, e->best, e->ticket, e->out_ring, e->tp_partial, e->tp_keys, e->warena, e->step_trace, e->x2, e->gate_xd, e->gate_corr, e->gate_xscale};
+                    e->bitmap, e->best, e->ticket, e->out_ring, e->tp_partial, e->tp_keys, e->warena, e->step_trace, e->spare_up, e->spare_out, e->x2, e->gate_xd, e->gate_corr, e->gate_xscale};
     for (void* b : bufs) if (b) cudaFree(b);
     if (e->h_ctl) cudaFreeHost(e->h_ctl);
     if (e->h_out) cudaFreeHost(e->h_out);
@@ -549,6 +551,13 @@ static int record_step(cuqwen_engine* e, cudaStream_t s, bool pdl) {
     LK(launch_penalty(e->logits, e->d_hist, &e->ctl->hist_len, e->vocab_l, e->plan.v0, pen, e->bitmap, cfg));
     if (e->tp == 1) {
         LK(launch_argmax(e->logits, e->vocab_l, 0, e->ctl, e->out_ring, e->ring_cap, e->d_hist, e->bitmap, e->best, e->ticket, nullptr, nullptr, cfg));
+    } else if (e->tp_peer) {
+        // every rank stores its best (value, index) key straight into every rank's key slots; no collective call
+        unsigned long long* slots[8];
+        const size_t keys_off = (size_t)2 * e->tp * p.dim * 8;          // the key words follow the partial-sum slots in the receive block
+        for (int d = 0; d < e->tp; ++d) slots[d] = reinterpret_cast<unsigned long long*>(e->peer_rx[d] + keys_off) + e->rank;
+        LK(launch_argmax(e->logits, e->vocab_l, e->plan.v0, e->ctl, e->out_ring, e->ring_cap, e->d_hist, e->bitmap, e->best, e->ticket, nullptr, nullptr, cfg, slots, e->tp));
+        LK(launch_merge_pushed_keys(reinterpret_cast<const unsigned long long*>(e->tp_rx + keys_off), e->tp, e->ctl, e->out_ring, e->ring_cap, t_err, 0, cfg));
     } else {
         LK(launch_argmax(e->logits, e->vocab_l, e->plan.v0, e->ctl, e->out_ring, e->ring_cap, e->d_hist, e->bitmap, e->best, e->ticket, e->tp_keys + e->tp, nullptr, cfg));
         NK(g_nccl.AllGather(e->tp_keys + e->tp, e->tp_keys, 1, ncclUint64, e->comm, s)); ++n; MARK();
@@ -691,7 +700,7 @@ extern "C" int cuqwen_tp_init(cuqwen_engine* e, const void* id_bytes, size_t n) 
     // row-parallel GEMVs can store their partial outputs straight into their consumers' memory.
     if (e->tp > 8) return CUQWEN_OK;
     const cuqwen_params& p = e->p;
-    e->tp_rx_bytes = (size_t)2 * e->tp * p.dim * 8;
+    e->tp_rx_bytes = (size_t)2 * e->tp * p.dim * 8 + (size_t)2 * e->tp * 8;      // partial-sum slots [2][tp][dim], then the samplers' key words [2][tp]
     CK(cudaMalloc((void**)&e->tp_rx, e->tp_rx_bytes));
     CK(cudaMemset(e->tp_rx, 0, e->tp_rx_bytes));
     CK(cudaMalloc((void**)&e->x2, (size_t)p.dim * 2)); CK(cudaMemset(e->x2, 0, (size_t)p.dim * 2));
@@ -803,6 +812,15 @@ extern "C" int cuqwen_get_ptr(cuqwen_engine* e, int which, int layer, void** ptr
             case CUQWEN_PTR_VALUE_CACHE: r = e->vc; b = kvb; break;
             case CUQWEN_PTR_HISTORY: r = e->d_hist; b = (size_t)p.max_seq_len * 4; break;
             case CUQWEN_PTR_STEP_TRACE: r = e->step_trace; b = e->step_trace_bytes; break;
+            case CUQWEN_PTR_TOKEN: r = &e->ctl->token; b = 4; break;
+            case CUQWEN_PTR_POS: r = &e->ctl->pos; b = 4; break;
+            case CUQWEN_PTR_HISTORY_LEN: r = &e->ctl->hist_len; b = 4; break;
+            case CUQWEN_PTR_SAMPLED: r = &e->ctl->sampled; b = 4; break;
+            case CUQWEN_PTR_PARTIAL_O: r = e->part_o; b = attn_scratch_floats_o(e->n_kv_l, e->nsplit, p.head_dim) * 4; break;
+            case CUQWEN_PTR_PARTIAL_ML: r = e->part_ml; b = attn_scratch_floats_ml(e->n_kv_l, e->nsplit) * 4; break;
+            case CUQWEN_PTR_UP: r = e->spare_up; b = (size_t)e->inter_l * 2; break;
+            case CUQWEN_PTR_MLP_OUT: r = e->spare_out; b = (size_t)p.dim * 2; break;
+            case CUQWEN_PTR_STREAM: r = (void*)e->stream; b = 0; break;
             default: return fail(CUQWEN_ERR_ARG, "unknown pointer id %d", which);
         }
     }
@@ -814,6 +832,7 @@ extern "C" int cuqwen_get_ptr(cuqwen_engine* e, int which, int layer, void** ptr
 // raw device helpers
 // ---------------------------------------------------------------------------
 extern "C" int cuqwen_dev_alloc(int device, size_t bytes, void** p) { DEV(device); (void)cfg; CK(cudaMalloc(p, bytes ? bytes : 1)); return CUQWEN_OK; }
+extern "C" int cuqwen_dev_sm_count(int device, int* n) { DEV(device); (void)cfg; if (!n) return fail(CUQWEN_ERR_ARG, "null argument"); *n = dc->sms; return CUQWEN_OK; }
 extern "C" int cuqwen_dev_free(int device, void* p) { DEV(device); (void)cfg; CK(cudaStreamSynchronize(dc->stream)); CK(cudaFree(p)); return CUQWEN_OK; }
 extern "C" int cuqwen_dev_upload(int device, void* d, const void* h, size_t n) { DEV(device); (void)cfg; CK(cudaMemcpyAsync(d, h, n, cudaMemcpyHostToDevice, dc->stream)); CK(cudaStreamSynchronize(dc->stream)); return CUQWEN_OK; }
 extern "C" int cuqwen_dev_download(int device, void* h, const void* d, size_t n) { DEV(device); (void)cfg; CK(cudaMemcpyAsync(h, d, n, cudaMemcpyDeviceToHost, dc->stream)); CK(cudaStreamSynchronize(dc->stream)); return CUQWEN_OK; }

@@ -129,9 +129,22 @@ __device__ __forceinline__ void finish_step(StepCtl* ctl, int token, int* out_ri
         ctl->out_idx = o + 1;
     }
 }
+// Tensor parallel: where a rank's best (value, index) goes.  Every rank stores ONE 64-bit word into every rank's key
+// slots (plain peer stores, like the partial sums of the row-parallel matrices): bits 63..32 the order-preserving key
+// of the fp32 value, 31..14 the complemented global index (vocabularies below 2^18 entries), 13..0 the step's number.
+// Slots are double-buffered by step parity; a reader knows a word is this step's by its low 14 bits.
+struct KeyPush {
+    unsigned long long* slot[8];   // rank d's receive words [2][n]: slot[d] points at word [0][this rank]
+    int n;                         // ranks (0 = no push)
+};
+__device__ __forceinline__ unsigned long long key_word(unsigned long long packed, unsigned step) {
+    const unsigned long long hi = packed >> 32, nidx = packed & 0x3ffffull;      // ~index keeps its low 18 bits
+    return (hi << 32) | (nidx << 14) | (unsigned long long)((step + 1u) & 0x3fffu);
+}
+
 __global__ void argmax_kernel(const __half* __restrict__ logits, int vocab, int vocab_base, StepCtl* ctl, int* out_ring, int ring_cap,
                               const int* __restrict__ hist, unsigned* bitmap, unsigned long long* best, unsigned* ticket,
-                              unsigned long long* key_out, int* token_out) {
+                              unsigned long long* key_out, int* token_out, const KeyPush kp) {
     __shared__ unsigned long long sbest[8];
     pdl_launch_dependents(); pdl_wait();
     // undo the penalty pass's marks (idempotent stores of zero)
@@ -160,16 +173,55 @@ __global__ void argmax_kernel(const __half* __restrict__ logits, int vocab, int 
             const unsigned long long fin = atomicExch(best, 0ull);
             *ticket = 0u;
             const int token = (int)(~((unsigned)(fin & 0xffffffffu)));
-            if (key_out) *key_out = fin;
+            if (kp.n > 0) {
+                const unsigned step = (unsigned)ctl->pad[1];
+                const unsigned long long w = key_word(fin, step);
+                for (int d = 0; d < kp.n; ++d)
+                    asm volatile("st.volatile.global.u64 [%0], %1;" ::"l"(kp.slot[d] + (size_t)(step & 1u) * kp.n), "l"(w) : "memory");
+            } else if (key_out) *key_out = fin;
             else if (ctl) finish_step(ctl, token, out_ring, ring_cap);
             if (token_out) *token_out = token;
         }
     }
 }
 int launch_argmax(const __half* logits, int vocab, int vocab_base, StepCtl* ctl, int* out_ring, int ring_cap, const int* hist, unsigned* bitmap,
-                  unsigned long long* best, unsigned* ticket, unsigned long long* key_out, int* token_out, const LaunchCfg& cfg) {
+                  unsigned long long* best, unsigned* ticket, unsigned long long* key_out, int* token_out, const LaunchCfg& cfg,
+                  unsigned long long* const* push_slots, int n_push) {
     int blocks = cfg.sm_count > 16 ? cfg.sm_count : 16;   // >= 16 blocks x 256 threads cover the 4096 history slots
-    return launch_k(argmax_kernel, dim3(blocks), dim3(256), 0, cfg, logits, vocab, vocab_base, ctl, out_ring, ring_cap, hist, bitmap, best, ticket, key_out, token_out);
+    KeyPush kp{};
+    if (push_slots && n_push > 0) {
+        if (n_push > 8 || vocab_base + vocab > (1 << 18) || !ctl) return (int)cudaErrorInvalidValue;
+        kp.n = n_push;
+        for (int d = 0; d < n_push; ++d) kp.slot[d] = push_slots[d];
+    }
+    return launch_k(argmax_kernel, dim3(blocks), dim3(256), 0, cfg, logits, vocab, vocab_base, ctl, out_ring, ring_cap, hist, bitmap, best, ticket, key_out, token_out, kp);
+}
+// Tensor parallel: waits (bounded) until the n key words of this step have arrived in this rank's slots, takes their
+// maximum and finishes the step like the single-GPU sampler does.  One warp; lane r watches rank r's word.
+__global__ void merge_pushed_keys_kernel(const unsigned long long* slots, int n, StepCtl* ctl, int* out_ring, int ring_cap, unsigned* err, long long limit) {
+    pdl_launch_dependents(); pdl_wait();
+    const int lane = threadIdx.x;
+    const unsigned step = (unsigned)ctl->pad[1];
+    const unsigned want = (step + 1u) & 0x3fffu;
+    unsigned long long w = 0ull;
+    if (lane < n) {
+        const unsigned long long* p = slots + (size_t)(step & 1u) * n + lane;
+        unsigned long long t0 = 0ull;
+        for (;;) {
+            asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+            if ((unsigned)(w & 0x3fffull) == want) break;
+            const unsigned long long now = (unsigned long long)sm_cycles();
+            if (t0 == 0ull) t0 = now | 1ull;
+            else if (now - t0 > (unsigned long long)limit) { if (err) atomicExch(err, 10u); break; }
+        }
+        w >>= 14;                                           // (value key, ~index): larger value first, then smaller index
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) { const unsigned long long y = __shfl_xor_sync(0xffffffffu, w, o); w = y > w ? y : w; }
+    if (lane == 0) finish_step(ctl, (int)(~(unsigned)(w & 0x3ffffull) & 0x3ffffu), out_ring, ring_cap);
+}
+int launch_merge_pushed_keys(const unsigned long long* slots, int n, StepCtl* ctl, int* out_ring, int ring_cap, unsigned* err, long long wait_cycles, const LaunchCfg& cfg) {
+    return launch_k(merge_pushed_keys_kernel, dim3(1), dim3(32), 0, cfg, slots, n, ctl, out_ring, ring_cap, err, wait_cycles > 0 ? wait_cycles : kWaitCyclesDefault);
 }
 __global__ void merge_keys_kernel(const unsigned long long* __restrict__ keys, int n, StepCtl* ctl, int* out_ring, int ring_cap) {
     pdl_launch_dependents(); pdl_wait();

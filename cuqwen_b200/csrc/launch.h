@@ -55,9 +55,14 @@ int launch_clear_bitmap(const int* hist, const int* d_hist_len, int vocab, int v
 // Greedy sampler.  best/ticket: one u64 and one u32 of zeroed scratch.  Writes ctl->sampled and, when
 // ctl->auto_advance is set, feeds the token back (token, pos+1, out_ring).  When key_out is non-null the packed
 // (order key << 32 | ~global index) is stored there instead (tensor-parallel ranks merge them later).
+// push_slots / n_push (tensor parallel without a collective call): the packed key, tagged with the step's number, is
+// stored into one 64-bit word per rank instead (kernels.cu: KeyPush); launch_merge_pushed_keys reads them.
 int launch_argmax(const __half* logits, int vocab, int vocab_base, StepCtl* ctl, int* out_ring, int ring_cap,
                   const int* hist, unsigned* bitmap, unsigned long long* best, unsigned* ticket,
-                  unsigned long long* key_out, int* token_out, const LaunchCfg& cfg);
+                  unsigned long long* key_out, int* token_out, const LaunchCfg& cfg,
+                  unsigned long long* const* push_slots = nullptr, int n_push = 0);
+int launch_merge_pushed_keys(const unsigned long long* slots, int n, StepCtl* ctl, int* out_ring, int ring_cap, unsigned* err, long long wait_cycles,
+                             const LaunchCfg& cfg);
 // Merge n packed keys (one per rank) and finish the step like launch_argmax does.
 int launch_merge_keys(const unsigned long long* keys, int n, StepCtl* ctl, int* out_ring, int ring_cap, const LaunchCfg& cfg);
 // x = half(float(x) + sum_r partial[r][:])   (row-parallel layers under tensor parallelism)

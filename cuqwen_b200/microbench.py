@@ -94,7 +94,7 @@ def run(model: str, quant: str, pos: int, which, iters: int, device: int = 0, ro
             for h in range(nkv):
                 kbuf.upload(blk, h * max_seq * hd * 2); vbuf.upload(blk, h * max_seq * hd * 2)
             kv.append((kbuf, vbuf))
-        sm = 148
+        sm = E.sm_count(device)
         nsplit = max(1, min(128, -(-sm // nkv)))
         bo, bml, bc = K.attn_scratch_bytes(nkv, hd, nsplit)
         so, sml, cnt = E.DevBuf(bo, device), E.DevBuf(bml, device), E.DevBuf(bc, device)

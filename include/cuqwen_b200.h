@@ -103,6 +103,10 @@ enum {
                                      * embedding copy, then 6 per layer, then the lm_head): ~first CTA start, last CTA start, ~first dependency
                                      * wait returned, last input staged, last main loop done, last exit, 2 spare ("~" = stored complemented).
                                      * Stamps accumulate: zero the block between steps. */
+    CUQWEN_PTR_TOKEN, CUQWEN_PTR_POS, CUQWEN_PTR_HISTORY_LEN, CUQWEN_PTR_SAMPLED,   /* the four device ints a step reads / writes (QwenState::d_token, d_pos, d_history_len, d_sampled_token) */
+    CUQWEN_PTR_PARTIAL_O, CUQWEN_PTR_PARTIAL_ML,   /* split-KV scratch: fp32 partial outputs, (max, sum) pairs */
+    CUQWEN_PTR_UP, CUQWEN_PTR_MLP_OUT,              /* QwenState::up / mlp_out: allocated for harnesses that write them, unused by the step (as in the reference, src/model.cu:18-20) */
+    CUQWEN_PTR_STREAM,                              /* not a buffer: the cudaStream_t the engine queues its steps on (bytes = 0) */
     CUQWEN_PTR_EMBED = 32, CUQWEN_PTR_NORM, CUQWEN_PTR_LM_HEAD, CUQWEN_PTR_LM_HEAD_SCALE,
     CUQWEN_PTR_IN_NORM = 64, CUQWEN_PTR_WQ, CUQWEN_PTR_SQ, CUQWEN_PTR_BQ, CUQWEN_PTR_WK, CUQWEN_PTR_SK, CUQWEN_PTR_BK,
     CUQWEN_PTR_WV, CUQWEN_PTR_SV, CUQWEN_PTR_BV, CUQWEN_PTR_WO, CUQWEN_PTR_SO, CUQWEN_PTR_POST_NORM,
@@ -125,6 +129,9 @@ int cuqwen_step_profile(cuqwen_engine* e, int token, int pos, float* us, int cap
 
 /* ---- raw device memory helpers (so a host language needs no CUDA binding of its own) ---- */
 int cuqwen_dev_alloc(int device, size_t bytes, void** dev_ptr);
+/* Number of SMs of the device (what benchmark/kernel_profile.cu's callers would read from cudaGetDeviceProperties):
+ * split counts and grid sizes are chosen from it. */
+int cuqwen_dev_sm_count(int device, int* sm_count);
 int cuqwen_dev_free(int device, void* dev_ptr);
 int cuqwen_dev_upload(int device, void* dev_dst, const void* host_src, size_t bytes);
 int cuqwen_dev_download(int device, void* host_dst, const void* dev_src, size_t bytes);

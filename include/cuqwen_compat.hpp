@@ -78,8 +78,12 @@ struct QwenConfig {
     static constexpr float norm_eps = 1e-6f, rope_theta = 1000000.0f, repetition_penalty = 1.1f;
 };
 
-// tuning constants of the reference kernels, kept as names only
-constexpr int ATTN_PARTITIONS = 64, KSPLIT_WARPS = 8, PARTIAL_HEAD_SLOTS = 16, ARGMAX_BLOCKS = 128;
+// tuning constants of the reference kernels (include/config.h:140-186), kept as names with the reference's values so
+// that programs which size buffers or print them compile; this library's kernels choose their own launch shapes
+constexpr int ATTN_PARTITIONS = 64, KSPLIT_WARPS = 8, PARTIAL_HEAD_SLOTS = 16, ARGMAX_BLOCKS = 128, ARGMAX_THREADS = 256;
+constexpr int ATTN_KEYS_CAP = (((QwenConfig::max_seq_len + ATTN_PARTITIONS - 1) / ATTN_PARTITIONS) + 15) / 16 * 16;
+constexpr int GEMV_WARPS_PER_BLOCK = 8;
+constexpr int GEMV_WIDE_WARPS_PER_BLOCK = (QwenConfig::dim >= 4096) ? 32 : (QwenConfig::dim >= 3072) ? 16 : 8;
 
 struct LayerWeights {
     half* input_layernorm_weight;
@@ -175,15 +179,27 @@ inline void malloc_qwen_state(const QwenConfig&, QwenState& s) {
     s.gate = (half*)ptr_of(e, CUQWEN_PTR_GATE); s.logits = (half*)ptr_of(e, CUQWEN_PTR_LOGITS);
     s.key_cache = (half*)ptr_of(e, CUQWEN_PTR_KEY_CACHE); s.value_cache = (half*)ptr_of(e, CUQWEN_PTR_VALUE_CACHE);
     s.d_history = (int*)ptr_of(e, CUQWEN_PTR_HISTORY);
+    // the device ints of the step, the split-KV scratch and the two buffers the reference allocates without using them
+    // (src/model.cu:18-20): all point at engine-owned memory, so a harness that pokes them finds valid addresses
+    s.d_token = (int*)ptr_of(e, CUQWEN_PTR_TOKEN); s.d_pos = (int*)ptr_of(e, CUQWEN_PTR_POS);
+    s.d_history_len = (int*)ptr_of(e, CUQWEN_PTR_HISTORY_LEN); s.d_sampled_token = (int*)ptr_of(e, CUQWEN_PTR_SAMPLED);
+    s.d_partial_out = (float*)ptr_of(e, CUQWEN_PTR_PARTIAL_O);
+    s.d_partial_max = (float*)ptr_of(e, CUQWEN_PTR_PARTIAL_ML); s.d_partial_sum = s.d_partial_max;   // (max, sum) pairs live in one buffer here
+    s.up = (half*)ptr_of(e, CUQWEN_PTR_UP); s.mlp_out = (half*)ptr_of(e, CUQWEN_PTR_MLP_OUT);
+    s.stream = (cudaStream_t)ptr_of(e, CUQWEN_PTR_STREAM);
 }
 inline void free_qwen_state(QwenState& s) {
     if (s.backend && cuqwen_compat::current() == s.backend) { cuqwen_destroy(s.backend); cuqwen_compat::current() = nullptr; }
     s = QwenState{};
 }
 
+// The reference runs the step on `stream` (or on state.stream when it is 0) and waits for it (src/model.cu:193-222).
+// Here the step runs on the engine's own stream; work the caller queued on `stream` before the call is waited for
+// first, and the call returns with the step complete, so the ordering a caller can observe is the same.
 inline int qwen_forward(int token, int pos, const QwenConfig&, QwenState& s, const QwenWeights&, const int* h_history = nullptr,
-                        int history_len = 0, cudaStream_t = 0) {
+                        int history_len = 0, cudaStream_t stream = 0) {
     int next = -1;
+    if (stream != 0 && stream != s.stream && cudaStreamSynchronize(stream) != cudaSuccess) { fprintf(stderr, "qwen_forward: the caller's stream failed\n"); exit(EXIT_FAILURE); }
     if (cuqwen_step(s.backend, token, pos, h_history, history_len, &next)) cuqwen_compat::die("qwen_forward");
     return next;
 }
@@ -246,7 +262,9 @@ inline void launch_gqa_attention_decode(const half* q, const half* key_cache, co
     cuqwen_compat::StreamScope scope_(stream);
     static void *so = nullptr, *sml = nullptr, *cnt = nullptr;
     static size_t have[3] = {0, 0, 0};
-    const int splits = 148 / n_kv_heads > 128 ? 128 : 148 / n_kv_heads;
+    static int sms = 0;
+    if (!sms && cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0) != cudaSuccess) sms = 128;
+    const int splits = sms / n_kv_heads > 128 ? 128 : sms / n_kv_heads < 1 ? 1 : sms / n_kv_heads;
     size_t need[3];
     CUQWEN_K(cuqwen_attn_scratch_bytes(n_kv_heads, head_dim, splits, &need[0], &need[1], &need[2]));
     if (need[0] > have[0] || need[1] > have[1] || need[2] > have[2]) {

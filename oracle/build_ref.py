@@ -16,11 +16,15 @@ It also builds the reference's own PROGRAMS into oracle/_ref/apps/, each from it
       benchmark/cuqwen_benchmark.cu with the reference's own kernels.cu, model.cu, load_weights.cpp: the stock
       program, for a like-for-like run under the reference's own measuring protocol.
 
+For a few (model, quant) pairs a second library ``..._tuned.so`` is built from the same sources with the two launch
+constants the reference's config.h asks users to retune per GPU set to its large-GPU values (see TUNED_KNOBS).
+
 Usage: python oracle/build_ref.py [--ref <CuQwen checkout>] [--only 7b:int4,0.5b:fp16] [--no-apps]
 """
 from __future__ import annotations
 
 import argparse
+import os
 import subprocess
 import sys
 from concurrent.futures import ThreadPoolExecutor
@@ -34,18 +38,44 @@ QUANT_DEF = {"fp16": None, "int8": "QUANT_INT8", "int4": "QUANT_INT4"}
 DEFAULT = [(m, q) for m in ("0.5b", "7b", "14b") for q in ("fp16", "int8", "int4")]
 
 
-def lib_path(model: str, quant: str) -> Path:
-    return OUT / f"libcuqwen_ref_{model.replace('.', '_')}_{quant}.so"
+# The reference's config.h tells users to retune two launch constants per GPU (include/config.h:140-146 and :178-185;
+# the shipped 64 / 128 are its RTX 3090 values, 128 / 256 its values for the widest part it lists).  The "tuned"
+# libraries are the same unmodified sources with exactly that edit made.
+TUNED_KNOBS = {"ATTN_PARTITIONS": 128, "ARGMAX_BLOCKS": 256}
+TUNED = [("7b", "int4"), ("14b", "int8"), ("0.5b", "int4")]
 
 
-def build_one(ref: Path, model: str, quant: str) -> Path:
-    out = lib_path(model, quant)
+def lib_path(model: str, quant: str, tuned: bool = False) -> Path:
+    return OUT / f"libcuqwen_ref_{model.replace('.', '_')}_{quant}{'_tuned' if tuned else ''}.so"
+
+
+def tuned_config(ref: Path) -> Path:
+    """A generated copy of the reference's config.h with the two constants of TUNED_KNOBS changed and nothing else.
+    It is pre-included, so the include guard makes the sources' own #include "config.h" a no-op."""
+    import re
+    text = (ref / "include" / "config.h").read_text()
+    for name, value in TUNED_KNOBS.items():
+        text, n = re.subn(rf"(constexpr\s+int\s+{name}\s*=\s*)\d+(\s*;)", rf"\g<1>{value}\g<2>", text)
+        if n != 1:
+            raise RuntimeError(f"config.h: expected exactly one definition of {name}, found {n}")
+    d = OUT / "tuned_include"
+    d.mkdir(parents=True, exist_ok=True)
+    out = d / "config.h"
+    if not out.exists() or out.read_text() != text:
+        out.write_text(text)
+    return out
+
+
+def build_one(ref: Path, model: str, quant: str, tuned: bool = False) -> Path:
+    out = lib_path(model, quant, tuned)
     srcs = [ref / "src" / "kernels.cu", ref / "src" / "model.cu", ref / "src" / "load_weights.cpp", HERE / "ref_wrap.cu"]
-    deps = srcs + [ROOT / "cuqwen_b200" / "csrc" / "rng.cuh"]
+    deps = srcs + [ROOT / "cuqwen_b200" / "csrc" / "rng.cuh", ref / "include" / "config.h"]
     if out.exists() and all(out.stat().st_mtime > d.stat().st_mtime for d in deps):
         return out
     cmd = ["nvcc", "-O3", "--use_fast_math", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
            "-shared", "-Xcompiler", "-fPIC", "-x", "cu", f"-D{MODEL_DEF[model]}"]
+    if tuned:
+        cmd += ["-include", str(tuned_config(ref))]
     if QUANT_DEF[quant]:
         cmd.append(f"-D{QUANT_DEF[quant]}")
     cmd += ["-I", str(ref / "include"), "-I", str(ROOT / "cuqwen_b200" / "csrc"), *map(str, srcs), "-o", str(out)]
@@ -99,7 +129,7 @@ def build_apps(ref: Path, model: str, quant: str) -> list[Path]:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", default=os.environ.get("CUQWEN_REFERENCE_DIR") or str(ROOT.parent / "reference"))
     ap.add_argument("--only", default="")
     ap.add_argument("--no-apps", action="store_true")
     a = ap.parse_args()
@@ -111,6 +141,8 @@ def main() -> None:
     todo = [tuple(x.split(":")) for x in a.only.split(",") if x] or DEFAULT
     with ThreadPoolExecutor(max_workers=4) as ex:
         for p in ex.map(lambda mq: build_one(ref, *mq), todo):
+            print("built", p.name)
+        for p in ex.map(lambda mq: build_one(ref, *mq, tuned=True), [mq for mq in TUNED if mq in todo]):
             print("built", p.name)
         if not a.no_apps:
             for ps in ex.map(lambda mq: build_apps(ref, *mq), APPS):

@@ -179,18 +179,19 @@ class OracleModel:
 
 # ---- the reference's own CUDA build (oracle/_ref) ----------------------------------------------------------------------
 
-def ref_lib_path(model: str, quant: str) -> Path:
-    return HERE / "_ref" / f"libcuqwen_ref_{model.replace('.', '_')}_{quant}.so"
+def ref_lib_path(model: str, quant: str, tuned: bool = False) -> Path:
+    return HERE / "_ref" / f"libcuqwen_ref_{model.replace('.', '_')}_{quant}{'_tuned' if tuned else ''}.so"
 
 
 _ref_cache = {}
 
 
-def ref_lib(model: str, quant: str):
-    """The reference compiled for (model, quant), or None when oracle/_ref was not built."""
-    key = (model, quant)
+def ref_lib(model: str, quant: str, tuned: bool = False):
+    """The reference compiled for (model, quant), or None when oracle/_ref was not built.  tuned: the build with the
+    reference's own large-GPU launch constants (oracle/build_ref.py)."""
+    key = (model, quant, tuned)
     if key not in _ref_cache:
-        p = ref_lib_path(model, quant)
+        p = ref_lib_path(model, quant, tuned)
         if not p.exists():
             _ref_cache[key] = None
         else:

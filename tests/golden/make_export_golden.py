@@ -20,7 +20,7 @@ HERE = Path(__file__).resolve().parent
 sys.path.insert(0, str(HERE))
 import export_case  # noqa: E402
 
-ref = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+ref = Path(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("CUQWEN_REFERENCE_DIR") or Path(__file__).resolve().parents[3] / "reference")
 sys.modules.setdefault("huggingface_hub", types.SimpleNamespace(snapshot_download=None))   # network helper, unused here
 sys.path.insert(0, str(ref))
 import export_weights as ew  # noqa: E402

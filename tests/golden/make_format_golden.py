@@ -5,13 +5,14 @@ The fixture pins the quantiser and the serialised byte layout (write_fp16 / writ
 seeded matrices, including an all-zero group, exact half-way cases and values that clip.
 """
 import io
+import os
 import sys
 import types
 from pathlib import Path
 
 import numpy as np
 
-ref = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+ref = Path(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("CUQWEN_REFERENCE_DIR") or Path(__file__).resolve().parents[3] / "reference")
 sys.modules.setdefault("huggingface_hub", types.SimpleNamespace(snapshot_download=None))   # network helper, unused here
 sys.path.insert(0, str(ref))
 import export_weights as ew  # noqa: E402

@@ -14,8 +14,8 @@ PROBE = ROOT / "tests" / "compat_probe.cpp"
 
 def compile_probe(out: Path, model: str, quant: str) -> Path:
     exe = out / f"probe_{model}_{quant}"
-    cmd = ["g++", "-std=c++17", f"-DQWEN_MODEL_{model}", f"-DQUANT_{quant}", f"-I{ROOT / 'include'}", "-I/usr/local/cuda/include", str(PROBE), "-o", str(exe),
-           f"-L{ROOT / 'cuqwen_b200'}", "-lcuqwen_b200", "-L/usr/local/cuda/lib64", "-lcudart", f"-Wl,-rpath,{ROOT / 'cuqwen_b200'}"]
+    cmd = ["g++", "-std=c++17", f"-DQWEN_MODEL_{model}", f"-DQUANT_{quant}", f"-I{ROOT / 'include'}", f"-I{build.cuda_home() / 'include'}", str(PROBE), "-o", str(exe),
+           f"-L{ROOT / 'cuqwen_b200'}", "-lcuqwen_b200", f"-L{build.cuda_home() / 'lib64'}", "-lcudart", f"-Wl,-rpath,{ROOT / 'cuqwen_b200'}"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     assert r.returncode == 0, r.stderr
     return exe
@@ -58,7 +58,7 @@ def test_the_references_own_programs_build_against_the_compat_headers(built, tmp
     spec = importlib.util.spec_from_file_location("build_ref", ROOT / "oracle" / "build_ref.py")
     build_ref = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(build_ref)
-    ref = Path("/root/reference")
+    ref = build.reference_dir()
     if not (ref / "src" / "main.cu").exists() or shutil.which("nvcc") is None:
         pytest.skip("no CuQwen checkout on this machine")
     build.build_tokenizer()

@@ -11,7 +11,7 @@ from pathlib import Path
 import numpy as np
 import pytest
 
-from cuqwen_b200 import binfmt
+from cuqwen_b200 import binfmt, build
 
 GOLD = np.load(Path(__file__).parent / "golden" / "format_golden.npz")
 CASES = ("a", "b", "c")
@@ -123,10 +123,10 @@ def test_step_byte_model_matches_published_table():
     assert binfmt.step_bytes(binfmt.MODELS["7b"], 2, 1) - binfmt.step_bytes(binfmt.MODELS["7b"], 2, 0) == 57344
 
 
-@pytest.mark.skipif(not Path("/root/reference/export_weights.py").exists(), reason="reference checkout not on this machine")
+@pytest.mark.skipif(not (build.reference_dir() / "export_weights.py").exists(), reason="reference checkout not on this machine")
 def test_against_reference_import_random_shapes():
     import sys
-    sys.path.insert(0, "/root/reference")
+    sys.path.insert(0, str(build.reference_dir()))
     import export_weights as ew
     rng = np.random.default_rng(11)
     for rows, cols in ((5, 128), (32, 512), (7, 1152)):
