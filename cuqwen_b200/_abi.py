@@ -48,6 +48,8 @@ SIGNATURES = {
     "cuqwen_dev_memset": (_i, [_i, _vp, _i, _sz]),
     "cuqwen_dev_sync": (_i, [_i]),
     "cuqwen_dev_join": (_i, [_i, _vp, _i]),
+    "cuqwen_capture_begin": (_i, [_i]),
+    "cuqwen_capture_replay": (_i, [_i, _i, C.POINTER(_f)]),
     "cuqwen_bench_begin": (_i, [_i]),
     "cuqwen_bench_end": (_i, [_i, C.POINTER(_f)]),
     "cuqwen_k_embedding": (_i, [_i, _vp, _vp, _vp, _i]),

@@ -219,7 +219,9 @@ extern "C" int cuqwen_create(const cuqwen_params* pin, cuqwen_engine** out) {
     e->inter_l = plan.i1 - plan.i0; e->vocab_l = plan.v1 - plan.v0;
     CK(cudaDeviceGetAttribute(&e->sms, cudaDevAttrMultiProcessorCount, p.device));
     if (const char* v = getenv("CUQWEN_ATTN_SPLITS")) { if (atoi(v) > 0) p.attn_splits = atoi(v); }      // tuning override (development aid)
-    e->nsplit = p.attn_splits > 0 ? p.attn_splits : (e->sms + e->n_kv_l - 1) / e->n_kv_l;
+    // one CTA per SM and not one more: the partial kernel takes a whole SM's shared memory, so a 149th CTA would wait for
+    // a second wave (measured at 40/8 heads, 32K keys: 19 splits 40.7 us, 16 splits 26.9 us)
+    e->nsplit = p.attn_splits > 0 ? p.attn_splits : (e->sms / e->n_kv_l > 0 ? e->sms / e->n_kv_l : 1);
     if (e->nsplit > kMaxSplit) e->nsplit = kMaxSplit;
     CK(cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking));
     CK(cudaEventCreate(&e->ev0)); CK(cudaEventCreate(&e->ev1));
@@ -420,10 +422,10 @@ static void describe_step(cuqwen_engine* e, std::vector<HostPhase>& out, int nsp
     // Peer-exchange bookkeeping (tensor parallel): `cur` is the buffer that holds the residual stream, `pending` the
     // exchange whose partials still have to be added to it by the next kernel that reads it.
     const bool peer = e->tp > 1 && e->tp_peer;
-    // SwiGLU output handed to the down projection in staged form: only when the separate gate/up launch will work on
-    // whole 128-row groups (eight tile sets per block), which the launcher decides from the tile-set count
-    const bool hand_over = p.quant != 0 && !(p.flags & CUQWEN_FLAG_NO_HANDOVER) &&
-                           gemv_tile_sets_per_block((e->inter_l + 15) / 16, e->sms, EPI_SWIGLU) == 8;
+    // SwiGLU output handed to the down projection in staged form: only when the gate/up launch will work on whole
+    // 128-row groups, which the launcher decides from the row count
+    const bool hand_over = p.quant != 0 && !(p.flags & CUQWEN_FLAG_NO_HANDOVER) && e->inter_l % 128 == 0 &&
+                           gemv_block_rows(e->inter_l, p.dim, e->sms, EPI_SWIGLU) == 128;
     __half* cur = e->x;
     int pending = -1, next_xi = 0;
     auto take_x = [&](GemvArgs& a) {                                        // a normed GEMV reads the residual stream
@@ -541,7 +543,7 @@ static int record_step(cuqwen_engine* e, cudaStream_t s, bool pdl) {
             if (h.ph.kind == PH_ATTN) { h.ph.at.trace = tr; LK(launch_attn(p.head_dim, h.ph.at, cfg)); ++n; continue; }      // two launches: partials, fold
             h.ph.g.trace = tr;
             LK(launch_gemv(h.ph.quant, h.ph.epi, h.ph.g, cfg));
-            if (h.sum_after) LK(launch_tp_sum(h.sum_src, h.sum_dst, h.sum_slots, e->tp, p.dim, &e->ctl->pad[1], h.sum_seq, t_err, 0, cfg_plain));
+            if (h.sum_after) LK(launch_tp_sum(h.sum_src, h.sum_dst, h.sum_slots, e->tp, p.dim, &e->ctl->pad[1], h.sum_seq, t_err, 0, cfg));
             if (h.reduce) {
                 if (int r = tp_allreduce(e, e->tp_partial, p.dim, s)) return r; ++n; MARK();
                 LK(launch_resid_sum(e->x, e->tp_partial, 1, 0, p.dim, cfg_plain));
@@ -853,6 +855,37 @@ extern "C" int cuqwen_dev_join(int device, void* caller_stream, int leave) {
     cudaStream_t to = leave ? (cudaStream_t)caller_stream : dc->stream;
     CK(cudaEventRecord(dc->ev_join, from));
     CK(cudaStreamWaitEvent(to, dc->ev_join, 0));
+    return CUQWEN_OK;
+}
+// Timing without the caller in the measurement: between cuqwen_capture_begin and cuqwen_capture_replay every
+// cuqwen_k_* call on this device is recorded into a CUDA graph instead of running (same launch attributes as in the
+// engine's step graph); cuqwen_capture_replay instantiates it, replays it once untimed and then `replays` times
+// between two events, and returns the milliseconds per replay.  Call every kernel once before capturing (the first
+// launch of a kernel loads its module, which a capture does not allow).
+extern "C" int cuqwen_capture_begin(int device) {
+    DEV(device); (void)cfg;
+    CK(cudaStreamBeginCapture(dc->stream, cudaStreamCaptureModeThreadLocal));
+    return CUQWEN_OK;
+}
+extern "C" int cuqwen_capture_replay(int device, int replays, float* ms_per_replay) {
+    DEV(device); (void)cfg;
+    cudaGraph_t g = nullptr;
+    CK(cudaStreamEndCapture(dc->stream, &g));
+    if (!g) return fail(CUQWEN_ERR_STATE, "nothing was captured");
+    if (replays < 1 || !ms_per_replay) { cudaGraphDestroy(g); return fail(CUQWEN_ERR_ARG, "replays must be positive"); }
+    cudaGraphExec_t ge = nullptr;
+    cudaError_t e_ = cudaGraphInstantiate(&ge, g, 0);
+    if (e_ == cudaSuccess) e_ = cudaGraphLaunch(ge, dc->stream);
+    if (e_ == cudaSuccess) e_ = cudaEventRecord(dc->ev0, dc->stream);
+    for (int i = 0; i < replays && e_ == cudaSuccess; ++i) e_ = cudaGraphLaunch(ge, dc->stream);
+    if (e_ == cudaSuccess) e_ = cudaEventRecord(dc->ev1, dc->stream);
+    if (e_ == cudaSuccess) e_ = cudaEventSynchronize(dc->ev1);
+    float ms = 0.f;
+    if (e_ == cudaSuccess) e_ = cudaEventElapsedTime(&ms, dc->ev0, dc->ev1);
+    if (ge) cudaGraphExecDestroy(ge);
+    cudaGraphDestroy(g);
+    if (e_ != cudaSuccess) return fail(CUQWEN_ERR_CUDA, "graph replay: %s", cudaGetErrorString(e_));
+    *ms_per_replay = ms / (float)replays;
     return CUQWEN_OK;
 }
 extern "C" int cuqwen_bench_begin(int device) { DEV(device); (void)cfg; CK(cudaEventRecord(dc->ev0, dc->stream)); return CUQWEN_OK; }

@@ -31,8 +31,9 @@ struct alignas(64) GemvArgs {
     float eps;
     int K;                    // input columns, multiple of 128
     int rows;                 // output rows of one matrix (QKV: unused)
-    int nsets;                // number of 16-row tile sets
-    int rw, kw;               // the consumer warps form rw row-warps x kw K-parts x gw group-parts: a CTA block is rw tile sets, each split kw ways along K
+    int nsets;                // EPI_QKV: number of 16-row tile sets (one per block)
+    int brows, nblk;          // rows of a CTA block (at most 16 * rw; the last block may be shorter) and number of blocks
+    int rw, kw;               // the consumer warps form rw row-warps x kw K-parts x gw group-parts: a CTA block is up to rw 16-row tiles, each split kw ways along K
     int gw;                   // warps that share one (row-warp, K-part) cell: they take the 128-column groups of a staged piece in turn
     int pg;                   // 128-column groups per staged row piece
     int nst;                  // stages in the CTA's ring
@@ -85,16 +86,17 @@ template <int EPI> struct EpiMT { static constexpr int MT = (EPI == EPI_SWIGLU |
 // [kp][m][64-byte chunk][row][64 bytes].
 constexpr int kConsumerWarps = 8;
 struct GemvLayout {
-    int piece_bytes, box_rows, box_bytes, stage_bytes, scale_block_bytes;
+    int piece_bytes, box_rows, box_bytes, box_stride, stage_bytes, scale_block_bytes;
     int off_corr, off_xscale, off_red, off_scales, off_stages, off_bars, total;
 };
-__host__ __device__ inline GemvLayout gemv_layout(int K, int group_bytes, int MT, int rw, int kw, int pg, int nst, bool quantised, int nsb) {
+__host__ __device__ inline GemvLayout gemv_layout(int K, int group_bytes, int MT, int box_rows, int kw, int pg, int nst, bool quantised, int nsb) {
     GemvLayout L;
     const int ng = K / kGroup;
     L.piece_bytes = pg * group_bytes;
-    L.box_rows = 16 * rw;
+    L.box_rows = box_rows;
     L.box_bytes = L.box_rows * L.piece_bytes;
-    L.stage_bytes = kw * MT * L.box_bytes;
+    L.box_stride = (L.box_bytes + 127) / 128 * 128;     // a TMA destination is 128-byte aligned; an odd row count times an odd chunk count is not
+    L.stage_bytes = kw * MT * L.box_stride;
     L.scale_block_bytes = quantised ? MT * L.box_rows * ng * 2 : 0;
     // x (fp16 or digits).  Vectors of up to 6144 values are staged from registers (stage_x_regs); longer ones up to
     // 8192 get room for the RMSNorm weight beside them while x is staged.
@@ -107,34 +109,39 @@ __host__ __device__ inline GemvLayout gemv_layout(int K, int group_bytes, int MT
     o = (o + 127) / 128 * 128;               // TMA destinations are 128-byte aligned
     L.off_stages = o; o += nst * L.stage_bytes;
     L.off_bars = o; o += (2 * nst + 5) * 8;  // full[nst], empty[nst], scale full[2], scale empty[2], x staged[1]
+    o += 1024;                               // a block whose row count is not a multiple of 16 lets the last tile's fragment loads run
+                                             // up to 15 rows (960 bytes) past the last box of the last stage: they must stay inside the allocation
     L.total = o;
     return L;
 }
-inline size_t gemv_smem_bytes(int K, int quant, int MT, int rw, int kw, int pg, int nst, int nsb) {
+inline size_t gemv_smem_bytes(int K, int quant, int MT, int box_rows, int kw, int pg, int nst, int nsb) {
     const int gb = quant == Q_I4 ? 64 : quant == Q_I8 ? 128 : 256;
-    return (size_t)gemv_layout(K, gb, MT, rw, kw, pg, nst, quant != Q_F16, nsb).total;
+    return (size_t)gemv_layout(K, gb, MT, box_rows, kw, pg, nst, quant != Q_F16, nsb).total;
 }
 
-// Where the 16 x MT rows of tile set `ts` live.  mrow[m] / mmat[m]: first row of tile m inside matrix mmat[m];
-// row0: first output row (generic) or the row inside its q / k / v matrix (QKV); valid: rows of the tile that exist.
+// Where the 16 x MT rows of tile `rwi` of block `blk` live.  mrow[m] / mmat[m]: first row of tile m inside matrix
+// mmat[m]; row0: first output row (generic) or the row inside its q / k / v matrix (QKV); row_end: one past the last
+// row this tile may write (the block's and the matrix's end; row0 >= row_end = nothing to do).
+// Generic: block blk covers rows [blk * brows, blk * brows + brows), tile rwi the sixteen rows from row0 on.
 template <int EPI>
 struct TileMap {
     int mrow[EpiMT<EPI>::MT];
     int mmat[EpiMT<EPI>::MT];
     const __half* sbase[EpiMT<EPI>::MT];
-    int row0, mat, valid;
+    int row0, mat, row_end;
 };
 template <int EPI>
-__device__ __forceinline__ TileMap<EPI> map_tileset(const GemvArgs& a, int ts) {
+__device__ __forceinline__ TileMap<EPI> map_tile(const GemvArgs& a, int blk, int rwi) {
     constexpr int MT = EpiMT<EPI>::MT;
     const int ng = a.K / kGroup;
     TileMap<EPI> m;
     if (EPI == EPI_QKV) {
+        const int ts = blk;                     // one tile set per block
         const int spt = a.hd / 32;              // tile sets per head: rows i and i + hd/2 of a head travel together (RoPE pairs)
         const int hh = ts / spt, sub = ts % spt;
         const int mat = hh < a.n_heads ? 0 : hh < a.n_heads + a.n_kv ? 1 : 2;
         const int lh = mat == 0 ? hh : mat == 1 ? hh - a.n_heads : hh - a.n_heads - a.n_kv;
-        m.row0 = lh * a.hd + sub * 16; m.mat = mat; m.valid = 16;
+        m.row0 = lh * a.hd + sub * 16; m.mat = mat; m.row_end = m.row0 + 16;
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
             const int row = m.row0 + mt * (a.hd / 2);
@@ -142,12 +149,13 @@ __device__ __forceinline__ TileMap<EPI> map_tileset(const GemvArgs& a, int ts) {
             m.sbase[mt] = a.s[mat] ? a.s[mat] + (size_t)row * ng : nullptr;
         }
     } else {
-        m.row0 = ts * 16; m.mat = 0;
-        m.valid = a.rows - m.row0 < 16 ? a.rows - m.row0 : 16;
+        const int b0 = blk * a.brows;
+        m.row0 = b0 + rwi * 16; m.mat = 0;
+        m.row_end = b0 + a.brows < a.rows ? b0 + a.brows : a.rows;
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
-            m.mrow[mt] = m.row0; m.mmat[mt] = mt;
-            m.sbase[mt] = a.s[mt] ? a.s[mt] + (size_t)m.row0 * ng : nullptr;
+            m.mrow[mt] = b0; m.mmat[mt] = mt;                   // the TMA box and the scale block start at the block's first row
+            m.sbase[mt] = a.s[mt] ? a.s[mt] + (size_t)b0 * ng : nullptr;
         }
     }
     return m;
@@ -157,11 +165,11 @@ __device__ __forceinline__ TileMap<EPI> map_tileset(const GemvArgs& a, int ts) {
 // block so that their latency hides behind the block's arithmetic.  The residual is read through L2: inside a
 // multi-matrix kernel another SM wrote it and L1 may hold an older copy.
 template <int EPI>
-__device__ __forceinline__ void epilogue_fetch(const GemvArgs& a, int row0, int mat, int r, float (&pre)[2]) {
+__device__ __forceinline__ void epilogue_fetch(const GemvArgs& a, int row0, int row_end, int mat, int r, float (&pre)[2]) {
     pre[0] = pre[1] = 0.f;
     if (EPI == EPI_RESID) {
         const int row = row0 + r;
-        if (row < a.rows) pre[0] = __half2float(__ldcg(a.out_h + row));
+        if (row < row_end) pre[0] = __half2float(__ldcg(a.out_h + row));
     } else if (EPI == EPI_QKV) {
         const int ra = row0 + r;
         pre[0] = __half2float(a.bias[mat][ra]);
@@ -173,27 +181,27 @@ __device__ __forceinline__ void epilogue_fetch(const GemvArgs& a, int row0, int 
 
 // Finish one output row (pair).  r = row slot 0..15 inside the tile set; pre = what epilogue_fetch returned for it.
 template <int EPI>
-__device__ __forceinline__ void epilogue(const GemvArgs& a, int row0, int mat, int r, float v0, float v1, const float (&pre)[2], __half* hbuf = nullptr) {
+__device__ __forceinline__ void epilogue(const GemvArgs& a, int row0, int row_end, int mat, int r, float v0, float v1, const float (&pre)[2], __half* hbuf = nullptr) {
     if (EPI == EPI_F16) {
         const int row = row0 + r;
-        if (row < a.rows) a.out_h[row] = __float2half(v0);
+        if (row < row_end) a.out_h[row] = __float2half(v0);
     } else if (EPI == EPI_F32) {
         const int row = row0 + r;
-        if (row < a.rows) a.out_f[row] = v0;
+        if (row < row_end) a.out_f[row] = v0;
     } else if (EPI == EPI_PUSH) {
         const int row = row0 + r;
-        if (row < a.rows) {
+        if (row < row_end) {
             const unsigned vb = __float_as_uint(v0), seq = __float_as_uint(pre[1]);
             for (int d = 0; d < a.npush; ++d) st_pair(a.push[d] + row, vb, seq);      // peer stores (one of them local), value and number in one 64-bit word
         }
     } else if (EPI == EPI_RESID) {
         // reference src/kernels.cu:670-671 and :620-621
         const int row = row0 + r;
-        if (row < a.rows) a.out_h[row] = __float2half(pre[0] + v0);
+        if (row < row_end) a.out_h[row] = __float2half(pre[0] + v0);
     } else if (EPI == EPI_SWIGLU) {
         // reference src/kernels.cu:565-567 (fast-math exp and divide, as that build uses)
         const int row = row0 + r;
-        if (row < a.rows) {
+        if (row < row_end) {
             const float sig = __fdividef(1.0f, 1.0f + __expf(-v0));
             const __half h = __float2half(v0 * sig * v1);
             a.out_h[row] = h;

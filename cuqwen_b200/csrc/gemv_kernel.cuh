@@ -1,8 +1,9 @@
 // The GEMV data path: one producer warp keeps a CTA-wide ring of TMA stages full, eight consumer warps run the
 // tensor-core inner product on it.  See gemv.cuh for the argument block and gemv_math.cuh for the arithmetic.
 //
-// Work split.  The consumer warps form rw row-warps x kw K-parts x gw group-parts (rw * kw * gw <= 16).  A CTA "block" is rw consecutive
-// 16-row tile sets; every ring step brings, for each K-part and tile, one box of (16*rw rows) x piece_bytes.  K-part kp
+// Work split.  The consumer warps form rw row-warps x kw K-parts x gw group-parts (rw * kw * gw <= 8).  A CTA "block" is `brows`
+// consecutive rows (at most 16 * rw: row-warp i takes rows 16 i .. 16 i + 15 of it; `brows` need not be a multiple of 16, the host picks it
+// so that the blocks fill the SMs evenly); every ring step brings, for each K-part and matrix, one box of brows rows x piece_bytes.  K-part kp
 // handles row pieces kp, kp+kw, ...; partial sums of the K-parts are merged in shared memory.  Blocks go to CTAs
 // round-robin.
 //
@@ -52,14 +53,14 @@ template <int Q, int EPI>
 struct GemvGeom {
     static constexpr int MT = EpiMT<EPI>::MT;
     static constexpr int GB = QT<Q>::GB;
-    int piece_bytes, box_rows, box_bytes, stage_bytes, ngrp, PT, S, nblk;
+    int piece_bytes, box_rows, box_bytes, box_stride, stage_bytes, ngrp, PT, S, nblk;
     __device__ __forceinline__ GemvGeom(const GemvArgs& a) {
-        piece_bytes = a.pg * GB; box_rows = 16 * a.rw; box_bytes = box_rows * piece_bytes; stage_bytes = a.kw * MT * box_bytes;
+        piece_bytes = a.pg * GB; box_rows = EPI == EPI_QKV ? 16 : a.brows; box_bytes = box_rows * piece_bytes; box_stride = (box_bytes + 127) / 128 * 128; stage_bytes = a.kw * MT * box_stride;
         ngrp = a.K / kGroup;
         const int rb = Q == Q_I4 ? a.K / 2 : Q == Q_I8 ? a.K : a.K * 2;     // bytes of one weight row
         PT = (rb + piece_bytes - 1) / piece_bytes;                          // pieces in a full row
         S = (PT + a.kw - 1) / a.kw;                                         // ring steps per block
-        nblk = (a.nsets + a.rw - 1) / a.rw;
+        nblk = EPI == EPI_QKV ? a.nsets : a.nblk;
     }
 };
 
@@ -74,21 +75,24 @@ __device__ __forceinline__ void gemv_produce(const GemvArgs& a, RingCtx& R, int 
     const int n_b = cta < G.nblk ? (G.nblk - cta + ncta - 1) / ncta : 0;
     for (int j = 0; j < n_b; ++j) {
         const int blk = cta + j * ncta;
-        const TileMap<EPI> tm = map_tileset<EPI>(a, blk * a.rw);
+        const TileMap<EPI> tm = map_tile<EPI>(a, blk, 0);
         if (kInt) {
             const int sb = R.sj % R.nsb;
             R.wait(R.bar_sempty + sb * 8, ((R.sj / R.nsb) & 1) ^ 1, 3u);
             const int rows_here = min(G.box_rows, (EPI == EPI_QKV ? 16 : a.rows - tm.row0));
             const int bytes_m = rows_here * G.ngrp * 2;
             const uint32_t dst = R.sm0 + R.off_scales + sb * R.scale_block_bytes;
-            if ((bytes_m & 15) == 0) {
+            bool aligned = (bytes_m & 15) == 0;                   // a bulk copy wants 16-byte sizes and addresses
+#pragma unroll
+            for (int m = 0; m < MT; ++m) aligned = aligned && (reinterpret_cast<uintptr_t>(tm.sbase[m]) & 15) == 0;
+            if (aligned) {
                 if (lane == 0) {
                     mbar_expect_tx(R.bar_sfull + sb * 8, (uint32_t)(bytes_m * MT));
 #pragma unroll
                     for (int m = 0; m < MT; ++m) bulk_g2s(dst + m * G.box_rows * G.ngrp * 2, tm.sbase[m], bytes_m, R.bar_sfull + sb * 8);
                 }
             } else {
-                // ragged last block: its scale rows are not a whole number of 16-byte units; copy with plain loads
+                // a block whose scale rows are not whole, aligned 16-byte units (odd row counts, a ragged last block): plain loads
                 __half* sbp = reinterpret_cast<__half*>(R.base + R.off_scales + sb * R.scale_block_bytes);
                 for (int m = 0; m < MT; ++m)
                     for (int idx = lane; idx < rows_here * G.ngrp; idx += 32) sbp[m * G.box_rows * G.ngrp + idx] = tm.sbase[m][idx];
@@ -106,7 +110,7 @@ __device__ __forceinline__ void gemv_produce(const GemvArgs& a, RingCtx& R, int 
             __syncwarp();
             if (lane < nparts * MT) {
                 const int kp = lane / MT, m = lane - kp * MT;
-                tma_load_3d(R.sm0 + R.off_stages + s * R.slot_bytes + (kp * MT + m) * G.box_bytes, &a.tmap[tm.mmat[m]],
+                tma_load_3d(R.sm0 + R.off_stages + s * R.slot_bytes + (kp * MT + m) * G.box_stride, &a.tmap[tm.mmat[m]],
                             0, tm.mrow[m], (kp + p * kw) * (G.piece_bytes / kChunkBytes), R.bar_full + s * 8);
             }
             R.advance();
@@ -148,16 +152,15 @@ __device__ __forceinline__ void gemv_consume(const GemvArgs& a, RingCtx& R, int 
         R.xpar ^= 1u;
     } else if (stage_x<Q>(a.x, a.norm_w, a.eps, a.K, R.base, R.off_corr, corr, xscale, red, NC, a.ngather > 0 ? &gs : nullptr, R.bar_x, R.xpar, a.trace)) R.xpar ^= 1u;
     // a SwiGLU kernel whose block is a whole 128-row group hands its outputs over in staged form as well
-    const bool emit = EPI == EPI_SWIGLU && kInt && a.xd_out != nullptr && rw == 8 && kw == 1 && gw == 1;
+    const bool emit = EPI == EPI_SWIGLU && kInt && a.xd_out != nullptr && a.brows == 128 && rw == 8 && kw == 1 && gw == 1;
     __half* hbuf = reinterpret_cast<__half*>(red);
     if (R.stamp && threadIdx.x == 0) *R.stamp = global_ns();
     if (threadIdx.x == 0) trace_last(a.trace, 3);
 
     for (int j = 0; j < n_b; ++j) {
         const int blk = cta + j * ncta;
-        const int ts = blk * rw + rwi;
-        const bool live = ts < a.nsets && gwi < gw;       // spare warps (rw * kw * gw < 16) only keep the barriers moving
-        const TileMap<EPI> tm = map_tileset<EPI>(a, live ? ts : 0);
+        const TileMap<EPI> tm = map_tile<EPI>(a, blk, rwi);
+        const bool live = tm.row0 < tm.row_end && gwi < gw;       // warps without rows (a short block, spare warps) only keep the barriers moving
         float tot[MT][2];
         float cf[MT][2][4];
 #pragma unroll
@@ -168,8 +171,8 @@ __device__ __forceinline__ void gemv_consume(const GemvArgs& a, RingCtx& R, int 
         }
         const bool merged = kw * gw > 1;                 // K-parts meet in shared memory; lanes 0-15 of the first part finish the rows
         float preA[2] = {0.f, 0.f}, preB[2] = {0.f, 0.f};
-        if (merged) { if (kwi == 0 && gwi == 0 && lane < 16 && live) epilogue_fetch<EPI>(a, tm.row0, tm.mat, lane, preA); }
-        else if (t == 0 && live) { epilogue_fetch<EPI>(a, tm.row0, tm.mat, g, preA); epilogue_fetch<EPI>(a, tm.row0, tm.mat, g + 8, preB); }
+        if (merged) { if (kwi == 0 && gwi == 0 && lane < 16 && live) epilogue_fetch<EPI>(a, tm.row0, tm.row_end, tm.mat, lane, preA); }
+        else if (t == 0 && live) { epilogue_fetch<EPI>(a, tm.row0, tm.row_end, tm.mat, g, preA); epilogue_fetch<EPI>(a, tm.row0, tm.row_end, tm.mat, g + 8, preB); }
         uint32_t sbuf = 0;
         const int sb = R.sj % R.nsb;
         if (kInt) {
@@ -184,13 +187,13 @@ __device__ __forceinline__ void gemv_consume(const GemvArgs& a, RingCtx& R, int 
                 const int grp0 = c * pg;
                 const int ngp = ngrp - grp0 < pg ? ngrp - grp0 : pg;
                 const int cstride = G.box_rows * kChunkBytes;        // chunk-major box: [chunk][row][64 bytes]
-                const uint32_t wrow = R.sm0 + R.off_stages + s * R.slot_bytes + kwi * MT * G.box_bytes + (rwi * 16 + g) * kChunkBytes + t * 16;
+                const uint32_t wrow = R.sm0 + R.off_stages + s * R.slot_bytes + kwi * MT * G.box_stride + (rwi * 16 + g) * kChunkBytes + t * 16;
                 if constexpr (kInt) {
                     constexpr int NI = QT<Q>::NI;
                     for (int gi = gwi; gi < ngp; gi += gw) {
                         const int grp = grp0 + gi;
                         uint4 w[MT][2][NI], xv[2];
-                        load_group_w<Q, MT>(wrow + gi * (GB / kChunkBytes) * cstride, cstride, G.box_bytes, w);
+                        load_group_w<Q, MT>(wrow + gi * (GB / kChunkBytes) * cstride, cstride, G.box_stride, w);
                         load_group_x(R.sm0 + grp * 256, g, t, xv);
                         const int cr = (int)lds32(R.sm0 + R.off_corr + grp * 4);
                         const float xsc = __uint_as_float(lds32(R.sm0 + R.off_xscale + grp * 4));
@@ -213,7 +216,7 @@ __device__ __forceinline__ void gemv_consume(const GemvArgs& a, RingCtx& R, int 
                     }
                 } else {
                     for (int gi = gwi; gi < ngp; gi += gw)
-                        compute_group_f16<MT>(wrow + gi * (GB / kChunkBytes) * cstride, cstride, G.box_bytes, t, xs + (grp0 + gi) * 16, cf);
+                        compute_group_f16<MT>(wrow + gi * (GB / kChunkBytes) * cstride, cstride, G.box_stride, t, xs + (grp0 + gi) * 16, cf);
                 }
             }
             __syncwarp();
@@ -235,15 +238,15 @@ __device__ __forceinline__ void gemv_consume(const GemvArgs& a, RingCtx& R, int 
             if (kwi == 0 && gwi == 0 && lane < 16 && live) {
                 float v0 = 0.f, v1 = 0.f;
                 for (int kp = 0; kp < kw * gw; ++kp) { v0 += red[(kp * rw + rwi) * 32 + lane]; if (MT == 2) v1 += red[(kp * rw + rwi) * 32 + 16 + lane]; }
-                epilogue<EPI>(a, tm.row0, tm.mat, lane, v0, v1, preA);
+                epilogue<EPI>(a, tm.row0, tm.row_end, tm.mat, lane, v0, v1, preA);
             }
             consumer_sync(NC);         // `red` is free again
         } else if (t == 0 && live) {
-            epilogue<EPI>(a, tm.row0, tm.mat, g, tot[0][0], MT == 2 ? tot[MT - 1][0] : 0.f, preA, emit ? hbuf + rwi * 16 : nullptr);
-            epilogue<EPI>(a, tm.row0, tm.mat, g + 8, tot[0][1], MT == 2 ? tot[MT - 1][1] : 0.f, preB, emit ? hbuf + rwi * 16 : nullptr);
+            epilogue<EPI>(a, tm.row0, tm.row_end, tm.mat, g, tot[0][0], MT == 2 ? tot[MT - 1][0] : 0.f, preA, emit ? hbuf + rwi * 16 : nullptr);
+            epilogue<EPI>(a, tm.row0, tm.row_end, tm.mat, g + 8, tot[0][1], MT == 2 ? tot[MT - 1][1] : 0.f, preB, emit ? hbuf + rwi * 16 : nullptr);
         }
         if constexpr (EPI == EPI_SWIGLU && kInt) {
-            if (emit && blk * 8 + 7 < a.nsets) {           // (uniform over the CTA)
+            if (emit && (blk + 1) * 128 <= a.rows) {       // a whole 128-row group (uniform over the CTA)
                 consumer_sync(NC);
                 if (warp == 0) {
                     const int c = lane & 15;
@@ -259,7 +262,7 @@ __device__ __forceinline__ void gemv_consume(const GemvArgs& a, RingCtx& R, int 
 // Ring context of a stand-alone launch: the layout gemv_layout computed for this matrix, an empty ring.
 template <int Q, int EPI>
 __device__ __forceinline__ RingCtx gemv_ring(const GemvArgs& a, unsigned char* smem) {
-    const GemvLayout L = gemv_layout(a.K, QT<Q>::GB, EpiMT<EPI>::MT, a.rw, a.kw, a.pg, a.nst, Q != Q_F16, a.nsb);
+    const GemvLayout L = gemv_layout(a.K, QT<Q>::GB, EpiMT<EPI>::MT, EPI == EPI_QKV ? 16 : a.brows, a.kw, a.pg, a.nst, Q != Q_F16, a.nsb);
     RingCtx R;
     R.sm0 = smem_u32(smem); R.base = smem;
     R.off_corr = L.off_corr; R.off_xscale = L.off_xscale; R.off_red = L.off_red; R.off_scales = L.off_scales;

@@ -10,6 +10,8 @@
 
 #include <cstdio>
 #include <cstdlib>
+#include <mutex>
+#include <vector>
 
 namespace cq {
 
@@ -379,7 +381,26 @@ static EncodeTiledFn encode_tiled() {
 // [chunk][row][64 bytes]: consecutive rows of one chunk are 64 bytes apart, so the 16-byte fragment loads of an MMA
 // operand (eight rows x four 16-byte columns per quarter-warp) touch every bank once.  In a row-major box the rows
 // would be piece_bytes (a multiple of 128) apart and pairs of rows would collide on the same banks.
+// Encoding a map is a driver call of a microsecond or so; a caller that launches the same matrix again and again (the
+// stand-alone entry points, the microbenchmarks) gets it from a small table instead.  A map depends on nothing but the
+// arguments below, so an entry can never go stale.
+namespace {
+struct MapKey { const void* w; size_t row_bytes, rows; int piece_bytes, box_rows; };
+struct MapEntry { MapKey k; CUtensorMap m; };
+std::mutex g_map_mu;
+std::vector<MapEntry> g_maps;
+}  // namespace
+static int encode_weight_map(CUtensorMap* m, const void* w, size_t row_bytes, size_t rows, int piece_bytes, int box_rows);
 int make_weight_map(CUtensorMap* m, const void* w, size_t row_bytes, size_t rows, int piece_bytes, int box_rows) {
+    std::lock_guard<std::mutex> lk(g_map_mu);
+    for (const MapEntry& e : g_maps)
+        if (e.k.w == w && e.k.row_bytes == row_bytes && e.k.rows == rows && e.k.piece_bytes == piece_bytes && e.k.box_rows == box_rows) { *m = e.m; return 0; }
+    if (int r = encode_weight_map(m, w, row_bytes, rows, piece_bytes, box_rows)) return r;
+    if (g_maps.size() >= 4096) g_maps.clear();
+    g_maps.push_back(MapEntry{MapKey{w, row_bytes, rows, piece_bytes, box_rows}, *m});
+    return 0;
+}
+static int encode_weight_map(CUtensorMap* m, const void* w, size_t row_bytes, size_t rows, int piece_bytes, int box_rows) {
     EncodeTiledFn fn = encode_tiled();
     if (!fn) return (int)cudaErrorNotSupported;
     if (row_bytes % kChunkBytes || piece_bytes % kChunkBytes) return (int)cudaErrorInvalidValue;
@@ -397,11 +418,18 @@ static int env_int(const char* name, int dflt) {
     return v && *v ? atoi(v) : dflt;
 }
 
-// Tile sets (16 rows each) per CTA block of a stand-alone launch: as many as keep at least one block per SM.
-int gemv_tile_sets_per_block(int nsets, int sm_count, int epi) {
+// Rows per CTA block: whole 16-row tiles, as many per block (1, 2, 4 or 8) as keep at least one block per SM.
+// (The kernel takes any row count per block.  Cutting the matrix into SM-count nearly equal blocks instead - 26 rows
+// for the 3584-row projections of the 7B model, 138 blocks in one round where whole tiles give 224 - measured slower:
+// down projection 11.8 against 10.4 us in the step, o_proj 5.9 against 5.1.  The 224 blocks of 16 rows run two to an
+// SM, sixteen consumer warps per SM, and the SMs with one block leave their share of the bandwidth to the others.)
+int gemv_block_rows(int rows, int K, int sm_count, int epi) {
+    (void)K;
+    if (epi == EPI_QKV) return 16;
+    const int nsets = (rows + 15) / 16;
     int rw = 1;
-    if (epi != EPI_QKV) while (rw < 8 && nsets / (rw * 2) >= sm_count) rw *= 2;
-    return rw;
+    while (rw < 8 && nsets / (rw * 2) >= sm_count) rw *= 2;
+    return 16 * rw;
 }
 
 // Picks the work split (rw row-warps x kw K-parts), the staged piece size and the ring depth for one GEMV launch.
@@ -414,26 +442,30 @@ int launch_gemv(int quant, int epi, GemvArgs& a, const LaunchCfg& cfg) {
     if (epi == EPI_QKV) {
         if (a.hd % 32 != 0) return (int)cudaErrorInvalidValue;
         a.nsets = (a.n_heads + 2 * a.n_kv) * (a.hd / 32);
+        a.brows = 16; a.nblk = a.nsets;
     } else {
         if (a.rows <= 0) return (int)cudaErrorInvalidValue;
         a.nsets = (a.rows + 15) / 16;
+        a.brows = gemv_block_rows(a.rows, a.K, cfg.sm_count, epi);
+        a.nblk = (a.rows + a.brows - 1) / a.brows;
     }
     const int MT = (epi == EPI_SWIGLU || epi == EPI_QKV) ? 2 : 1;
     const int ngrp = a.K / kGroup;
     const int gb = quant == Q_I4 ? 64 : quant == Q_I8 ? 128 : 256;
     const int pg_max = 256 / gb;                     // row pieces of at most 256 bytes (TMA box limit for byte elements)
     const int kMaxSmem = 225 * 1024;
-    int rw = gemv_tile_sets_per_block(a.nsets, cfg.sm_count, epi);
+    int rw = 1;
+    while (16 * rw < a.brows) rw *= 2;               // row-warps: enough 16-row tiles to cover a block (1, 2, 4 or 8)
     int kw = 8 / rw;                                 // rw * kw may end up below 8 when a row has few pieces: the spare warps idle
-    const int nblk = (a.nsets + rw - 1) / rw;
-    // Shared-memory budget of a CTA.  int4 weights with more blocks than SMs: 110 KB and up to two CTAs per SM's worth
-    // of grid, so that a CTA with a second block need not wait for one with a single block.  int8 / fp16 weights move
-    // two to four times the bytes per row piece, and a ring cut to 110 KB is too shallow for them (measured on the 14B
-    // int8 matrices: gate/up 37.5 us at 110 KB against 28.2 us at 220 KB, lm_head 139 against 119 us): they take the
-    // whole SM.  (Two consecutive kernels of the step never share an SM: a CTA of nine warps takes registers for
-    // twelve, which leaves no room for a second one at 96 to 110 registers per thread; capped at 80 registers they do
-    // share, and the step was slower - 574 against 703 tok/s on the 7B int4 model - because the early weight copies
-    // of the next kernel compete with the loads the running kernel is waiting for.)
+    const int nblk = a.nblk;
+    // Shared-memory budget of a CTA.  int4 weights with more blocks than SMs: 110 KB, two CTAs to an SM (at the 96
+    // registers of the one-matrix kernels two CTAs fit), so that one streams while the other is in its prologue or
+    // epilogue.  int8 / fp16 weights move two to four times the bytes per row piece, and a ring cut to 110 KB is too
+    // shallow for them (measured on the 14B int8 matrices: gate/up 37.5 us at 110 KB against 28.2 us at 220 KB,
+    // lm_head 139 against 119 us): they take the whole SM.
+    // (CTAs of two consecutive kernels of the step do not share an SM at these register counts.  Capped at 80
+    // registers they do, and the step was slower - 574 against 703 tok/s on the 7B int4 model: the early weight
+    // copies of the next kernel compete with the loads the running kernel is waiting for.)
     const int cap_kb = (nblk > cfg.sm_count && quant == Q_I4) ? 110 : 220;
     const int per_sm = cap_kb == 110 ? 2 : 1;
     const int grid = nblk < per_sm * cfg.sm_count ? nblk : per_sm * cfg.sm_count;
@@ -448,8 +480,8 @@ int launch_gemv(int quant, int epi, GemvArgs& a, const LaunchCfg& cfg) {
             const int steps = (pt + kwq - 1) / kwq;
             int want = env_nst > 0 ? env_nst : (rw == 8 ? 6 : steps < 6 ? steps : 6);
             int n = want;
-            while (n > 1 && gemv_smem_bytes(a.K, quant, MT, rw, kwq, q, n, nsb) > (size_t)cap) --n;
-            if (gemv_smem_bytes(a.K, quant, MT, rw, kwq, q, n, nsb) > (size_t)cap) continue;
+            while (n > 1 && gemv_smem_bytes(a.K, quant, MT, a.brows, kwq, q, n, nsb) > (size_t)cap) --n;
+            if (gemv_smem_bytes(a.K, quant, MT, a.brows, kwq, q, n, nsb) > (size_t)cap) continue;
             if (n >= (want < 3 ? want : 3) || q == 1 || env_pg > 0) { pg = q; nst = n; kw = kwq; break; }
             if (!nst || n > nst) { pg = q; nst = n; kw = kwq; }
             if (q == 1) break;
@@ -462,17 +494,17 @@ int launch_gemv(int quant, int epi, GemvArgs& a, const LaunchCfg& cfg) {
     int gw = kConsumerWarps / (rw * kw);              // warps left over share cells, group by group
     while (gw > 1 && gw > pg) gw /= 2;
     a.rw = rw; a.kw = kw; a.gw = gw; a.pg = pg; a.nst = nst; a.nsb = nsb;
-    const size_t smem = gemv_smem_bytes(a.K, quant, MT, rw, kw, pg, nst, nsb);
+    const size_t smem = gemv_smem_bytes(a.K, quant, MT, a.brows, kw, pg, nst, nsb);
     {
         const size_t rbytes = quant == Q_I4 ? a.K / 2 : quant == Q_I8 ? a.K : (size_t)a.K * 2;
         const int nmat = epi == EPI_QKV ? 3 : epi == EPI_SWIGLU ? 2 : 1;
         for (int m = 0; m < nmat; ++m) {
             const size_t rows_m = epi == EPI_QKV ? (size_t)(m == 0 ? a.n_heads : a.n_kv) * a.hd : (size_t)a.rows;
-            if (int r = make_weight_map(&a.tmap[m], a.w[m], rbytes, rows_m, pg * gb, 16 * rw)) return r;
+            if (int r = make_weight_map(&a.tmap[m], a.w[m], rbytes, rows_m, pg * gb, a.brows)) return r;
         }
     }
     const dim3 gridd(grid), block(kGemvThreadsHost);
-    if (env_int("CUQWEN_GEMV_SHOW", 0)) fprintf(stderr, "gemv q%d epi%d K%d nsets%d: rw%d kw%d gw%d pg%d nst%d nsb%d grid%d smem %zu\n", quant, epi, a.K, a.nsets, rw, kw, gw, pg, nst, nsb, grid, smem);
+    if (env_int("CUQWEN_GEMV_SHOW", 0)) fprintf(stderr, "gemv q%d epi%d K%d rows%d: brows%d nblk%d rw%d kw%d gw%d pg%d nst%d nsb%d grid%d smem %zu\n", quant, epi, a.K, a.rows, a.brows, a.nblk, rw, kw, gw, pg, nst, nsb, grid, smem);
     if (quant == Q_I4) return launch_gemv_i4(epi, a, gridd, block, smem, cfg);
     if (quant == Q_I8) return launch_gemv_i8(epi, a, gridd, block, smem, cfg);
     return launch_gemv_f16(epi, a, gridd, block, smem, cfg);

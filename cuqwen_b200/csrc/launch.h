@@ -32,8 +32,8 @@ struct LaunchCfg {
 // GEMV family.  quant: 0 fp16, 1 int8, 2 int4.  epi: cq::Epi.  Chooses the work split (rw, kw, gw), the staged piece
 // size and the ring depth, builds the tensor maps and launches.  Returns a cudaError_t value.
 int launch_gemv(int quant, int epi, GemvArgs& a, const LaunchCfg& cfg);
-// Tile sets (16 rows each) per CTA block that launch_gemv will choose for `nsets` tile sets.
-int gemv_tile_sets_per_block(int nsets, int sm_count, int epi);
+// Rows per CTA block that launch_gemv will choose for a matrix of `rows` rows and K input columns.
+int gemv_block_rows(int rows, int K, int sm_count, int epi);
 
 // Byte-typed 3-D tensor map of a row-major matrix seen as [rows][64-byte chunks]: a box of box_rows rows x piece_bytes
 // lands in shared memory chunk-major, [chunk][row][64 bytes].

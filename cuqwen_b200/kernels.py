@@ -97,3 +97,15 @@ def bench_end(device=0) -> float:
     ms = C.c_float()
     check(_abi.lib().cuqwen_bench_end(device, C.byref(ms)))
     return ms.value
+
+
+def capture_begin(device=0):
+    """From here until capture_replay the kernel calls above are recorded into a CUDA graph instead of running."""
+    check(_abi.lib().cuqwen_capture_begin(device))
+
+
+def capture_replay(replays: int, device=0) -> float:
+    """Replays the recorded graph `replays` times between two CUDA events; returns milliseconds per replay."""
+    ms = C.c_float()
+    check(_abi.lib().cuqwen_capture_replay(device, replays, C.byref(ms)))
+    return ms.value

@@ -39,6 +39,7 @@ class Copies:
         w, s = _weights(rng, rows, cols, quant)
         self.bytes = w.nbytes + (s.nbytes if s is not None else 0)
         n = max(2, -(-min_total_bytes // self.bytes)) if min_total_bytes > 0 else 1      # 0: a single copy (L2-warm timing)
+        n = min(n, 64)
         self.w = [E.DevBuf.from_numpy(w, device) for _ in range(n)]
         self.s = [E.DevBuf.from_numpy(s, device) if s is not None else None for _ in range(n)]
         self.i = 0
@@ -46,6 +47,20 @@ class Copies:
     def next(self):
         self.i = (self.i + 1) % len(self.w)
         return self.w[self.i], self.s[self.i]
+
+
+def graph_time(fn, iters: int, device: int = 0, per_graph: int = 16) -> float:
+    """Microseconds per call of `fn` (which queues kernels through the C ABI) with the caller out of the measurement:
+    `per_graph` calls are recorded into a CUDA graph (cuqwen_capture_begin) and the graph is replayed between two
+    events.  `fn` should rotate over its weight copies with a period that divides `per_graph`."""
+    for _ in range(per_graph):
+        fn()                                # every kernel has run once before the capture; the rotation is back at its start
+    E.sync(device)
+    K.capture_begin(device)
+    for _ in range(per_graph):
+        fn()
+    replays = max(1, iters // per_graph)
+    return K.capture_replay(replays, device) * 1e3 / per_graph
 
 
 def run(model: str, quant: str, pos: int, which, iters: int, device: int = 0, rotate_bytes: int = 3 * L2_BYTES):
@@ -60,15 +75,8 @@ def run(model: str, quant: str, pos: int, which, iters: int, device: int = 0, ro
     eps = float(np.float16(1e-6))
     results = []
 
-    def timed(name, alg_bytes, fn):
-        for _ in range(5):
-            fn()
-        E.sync(device)
-        K.bench_begin(device)
-        for _ in range(iters):
-            fn()
-        ms = K.bench_end(device)
-        us = ms * 1e3 / iters
+    def timed(name, alg_bytes, fn, period=1):
+        us = graph_time(fn, iters, device, period * -(-16 // period))       # whole rotations, at least 16 calls per graph
         results.append({"kernel": name, "us": round(us, 3), "bytes": int(alg_bytes), "gbs": round(alg_bytes / us / 1e3, 1)})
 
     if "qkv" in which:
@@ -82,7 +90,7 @@ def run(model: str, quant: str, pos: int, which, iters: int, device: int = 0, ro
             (wq, sq), (wk, sk), (wv, sv) = cq.next(), ck.next(), cv.next()
             K.fused_attn_block(q, x, wq, wk, wv, sq, sk, sv, bq, bk, bv, qo, ko, vo, d, nh, nkv, hd, dpos, norm_weight=normw, eps=eps,
                                kcache=kc, vcache=vc, max_seq_len=max_seq, device=device)
-        timed("rmsnorm+qkv+bias+rope+kvstore", cq.bytes + ck.bytes + cv.bytes + 2 * d * 2 + (qd + 2 * kd) * 2, f)
+        timed("rmsnorm+qkv+bias+rope+kvstore", cq.bytes + ck.bytes + cv.bytes + 2 * d * 2 + (qd + 2 * kd) * 2, f, max(len(cq.w), len(ck.w)))
     if "attn" in which:
         max_seq = 32768
         ncopy = max(2, -(-rotate_bytes // (2 * nkv * (pos + 1) * hd * 2)))
@@ -95,7 +103,7 @@ def run(model: str, quant: str, pos: int, which, iters: int, device: int = 0, ro
                 kbuf.upload(blk, h * max_seq * hd * 2); vbuf.upload(blk, h * max_seq * hd * 2)
             kv.append((kbuf, vbuf))
         sm = E.sm_count(device)
-        nsplit = max(1, min(128, -(-sm // nkv)))
+        nsplit = max(1, min(128, sm // nkv))
         bo, bml, bc = K.attn_scratch_bytes(nkv, hd, nsplit)
         so, sml, cnt = E.DevBuf(bo, device), E.DevBuf(bml, device), E.DevBuf(bc, device)
         qv, out = h16(qd), E.DevBuf(qd * 2, device)
@@ -105,7 +113,7 @@ def run(model: str, quant: str, pos: int, which, iters: int, device: int = 0, ro
             state["i"] = (state["i"] + 1) % ncopy
             kbuf, vbuf = kv[state["i"]]
             K.gqa_attention_decode(qv, kbuf, vbuf, out, dpos, nh, nkv, hd, max_seq, nsplit, so, sml, cnt, device=device)
-        timed(f"attention(ctx {pos + 1}, {nsplit} splits)", 2 * nkv * (pos + 1) * hd * 2, f)
+        timed(f"attention(ctx {pos + 1}, {nsplit} splits)", 2 * nkv * (pos + 1) * hd * 2, f, ncopy)
     if "oproj" in which:
         c = Copies(rng, d, qd, q, rotate_bytes, device)
         xr = h16(d)
@@ -113,7 +121,7 @@ def run(model: str, quant: str, pos: int, which, iters: int, device: int = 0, ro
         def f():
             w, s = c.next()
             K.gemv_add(q, w, s, xq, xr, d, qd, device=device)
-        timed("o_proj+residual", c.bytes + qd * 2 + d * 4, f)
+        timed("o_proj+residual", c.bytes + qd * 2 + d * 4, f, len(c.w))
     if "gateup" in which:
         cg, cu = Copies(rng, I, d, q, rotate_bytes // 2, device), Copies(rng, I, d, q, rotate_bytes // 2, device)
         out = E.DevBuf(I * 2, device)
@@ -121,7 +129,7 @@ def run(model: str, quant: str, pos: int, which, iters: int, device: int = 0, ro
         def f():
             (wg, sg), (wu, su) = cg.next(), cu.next()
             K.fused_mlp_stage1(q, x, wg, wu, sg, su, out, d, I, norm_weight=normw, eps=eps, device=device)
-        timed("rmsnorm+gate/up+swiglu", cg.bytes + cu.bytes + 2 * d * 2 + I * 2, f)
+        timed("rmsnorm+gate/up+swiglu", cg.bytes + cu.bytes + 2 * d * 2 + I * 2, f, len(cg.w))
     if "down" in which:
         c = Copies(rng, d, I, q, rotate_bytes, device)
         xr = h16(d)
@@ -129,7 +137,7 @@ def run(model: str, quant: str, pos: int, which, iters: int, device: int = 0, ro
         def f():
             w, s = c.next()
             K.gemv_add(q, w, s, xi, xr, d, I, device=device)
-        timed("down+residual", c.bytes + I * 2 + d * 4, f)
+        timed("down+residual", c.bytes + I * 2 + d * 4, f, len(c.w))
     if "lmhead" in which:
         lq = 0 if (cfg["tied"] or q == 0) else 1
         c = Copies(rng, V, d, lq, rotate_bytes, device)
@@ -138,7 +146,7 @@ def run(model: str, quant: str, pos: int, which, iters: int, device: int = 0, ro
         def f():
             w, s = c.next()
             K.gemv(lq, w, s, x, out, V, d, norm_weight=normw, eps=eps, device=device)
-        timed("rmsnorm+lm_head", c.bytes + 2 * d * 2 + V * 2, f)
+        timed("rmsnorm+lm_head", c.bytes + 2 * d * 2 + V * 2, f, len(c.w))
     return results
 
 
@@ -157,15 +165,47 @@ def single_gemv(rows: int, cols: int, quant: str, iters: int, device: int = 0) -
         def f():
             w, s = c.next()
             K.gemv(q, w, s, x, y, rows, cols, device=device)
-        for _ in range(10):
-            f()
-        E.sync(device)
-        K.bench_begin(device)
-        for _ in range(iters):
-            f()
-        us = K.bench_end(device) * 1e3 / iters
+        us = graph_time(f, iters, device, len(c.w) * -(-16 // len(c.w)))
         alg = c.bytes + cols * 2 + rows * 2
         out.append({"kernel": f"gemv {rows}x{cols} {quant} ({label})", "us": round(us, 3), "bytes": int(alg), "gbs": round(alg / us / 1e3, 1)})
+    return out
+
+
+def attention_sweep(lens=(512, 2048, 8192, 32768), heads=((28, 4), (40, 8)), splits=(8, 16, 32, 64, 128), iters: int = 200, device: int = 0) -> list:
+    """Split-KV attention alone (both launches: partials, fold) over context lengths, head layouts and split counts:
+    q fp16 [n_heads, 128] ~ N(0,1), K and V fp16 N(0,1) in the head-major cache layout, rotating over copies worth
+    three L2 sizes.  Algorithmic bytes = 2 * n_kv * len * 128 * 2.  The split count SMs / n_kv (one CTA per SM, what
+    the engine uses) is always part of the sweep."""
+    hd, max_seq = 128, 32768
+    rng = np.random.default_rng(4)
+    sm = E.sm_count(device)
+    out = []
+    for nh, nkv in heads:
+        q = E.DevBuf.from_numpy(rng.standard_normal(nh * hd).astype(np.float16), device)
+        o = E.DevBuf(nh * hd * 2, device)
+        for n in lens:
+            ncopy = max(2, min(16, -(-3 * L2_BYTES // (2 * nkv * n * hd * 2))))
+            blk = rng.standard_normal(n * hd).astype(np.float16)
+            kv = []
+            for _ in range(ncopy):
+                kb, vb = E.DevBuf(nkv * max_seq * hd * 2, device), E.DevBuf(nkv * max_seq * hd * 2, device)
+                for h in range(nkv):
+                    kb.upload(blk, h * max_seq * hd * 2); vb.upload(blk, h * max_seq * hd * 2)
+                kv.append((kb, vb))
+            dpos = E.DevBuf.from_numpy(np.array([n - 1], np.int32), device)
+            alg = 2 * nkv * n * hd * 2
+            for ns in sorted(set(list(splits) + [max(1, min(128, sm // nkv))])):
+                bo, bml, bc = K.attn_scratch_bytes(nkv, hd, ns)
+                so, sml, cnt = E.DevBuf(bo, device), E.DevBuf(bml, device), E.DevBuf(bc, device)
+                st = {"i": 0}
+
+                def f():
+                    st["i"] = (st["i"] + 1) % ncopy
+                    K.gqa_attention_decode(q, kv[st["i"]][0], kv[st["i"]][1], o, dpos, nh, nkv, hd, max_seq, ns, so, sml, cnt, device=device)
+                us = graph_time(f, iters, device, ncopy * -(-16 // ncopy))
+                out.append({"heads": f"{nh}/{nkv}", "len": n, "splits": ns, "us": round(us, 3), "bytes": alg, "gbs": round(alg / us / 1e3, 1)})
+                E.sync(device)
+            del kv
     return out
 
 
@@ -180,7 +220,16 @@ def main():
     ap.add_argument("--rotate-mb", type=int, default=3 * 126)
     ap.add_argument("--json", action="store_true")
     ap.add_argument("--gemv", default="", help="ROWSxCOLS: time one GEMV of that shape instead (e.g. 4864x896), cold and L2-warm")
+    ap.add_argument("--attn-sweep", action="store_true", help="attention alone over lengths x head layouts x split counts")
     a = ap.parse_args()
+    if a.attn_sweep:
+        res = attention_sweep(iters=max(a.iters, 100), device=a.device)
+        if a.json:
+            print(json.dumps({"attention_sweep": res}))
+        else:
+            for r in res:
+                print(f"  heads {r['heads']:<5} len {r['len']:>6} splits {r['splits']:>4} {r['us']:>9.2f} us  {r['bytes'] / 1e6:>8.2f} MB  {r['gbs']:>8.1f} GB/s")
+        return
     if a.gemv:
         rows, cols = (int(v) for v in a.gemv.lower().split("x"))
         res = single_gemv(rows, cols, a.quant, max(a.iters, 200), a.device)

@@ -143,6 +143,13 @@ int cuqwen_dev_sync(int device);
  * so far.  The reference's launch_* take the stream as an argument (include/kernels.cuh:19-160); a binding that
  * wraps each call in join(0) ... join(1) keeps that meaning. */
 int cuqwen_dev_join(int device, void* caller_stream, int leave);
+/* Kernel timing without the calling language in the measurement (benchmark/kernel_profile.cu times its launches from
+ * C++; a host that calls through a binding would otherwise time its own call overhead): between cuqwen_capture_begin
+ * and cuqwen_capture_replay the cuqwen_k_* calls on `device` are recorded into a CUDA graph instead of running;
+ * cuqwen_capture_replay replays it `replays` times between two events and returns the milliseconds per replay.
+ * Every kernel must have run once before the capture starts. */
+int cuqwen_capture_begin(int device);
+int cuqwen_capture_replay(int device, int replays, float* ms_per_replay);
 /* CUDA events on the library's per-device stream, to time a sequence of cuqwen_k_* calls from a host language. */
 int cuqwen_bench_begin(int device);
 int cuqwen_bench_end(int device, float* ms);

@@ -206,6 +206,8 @@ def ref_lib(model: str, quant: str, tuned: bool = False):
                 "ref_logits_int8": (None, [_vp, _vp, _vp, _vp, _i, _i]), "ref_penalty": (None, [_vp, _vp, _vp, _i, _f]),
                 "ref_argmax": (None, [_vp, _vp, _i]), "ref_model_load": (_vp, [C.c_char_p]), "ref_lm_head_quantized": (_i, [_vp]),
                 "ref_forward": (_i, [_vp, _i, _i, _vp, _i]), "ref_decode_n": (_f, [_vp, _i, _i, _i, _vp]),
+                "ref_bench_attention": (_f, [_vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _i]),
+                "ref_bench_gemv_add": (_f, [_vp, _vp, _i, _vp, _vp, _i, _i, _i]),
                 "ref_kv_fill_normal": (None, [_vp, _i, C.c_ulonglong]), "ref_state_ptr": (_vp, [_vp, _i]), "ref_model_free": (None, [_vp]),
             }
             for n, (res, args) in sig.items():

