@@ -31,7 +31,15 @@ struct AttnArgs {
     unsigned* counters;
     unsigned* err;          // receives a non-zero code when a bounded wait expires (may be null)
     int stages;             // ring depth of the partial kernel (0 = its default)
-    unsigned long long* trace;       // optional: timeline words of the partial launch (8) and of the fold launch (8), else null
+    unsigned long long* trace;       // optional: timeline words of the partial launch and of the fold launch, else null
+    // 8-bit cache (attn_partial_kernel<HD, true>): kc / vc point at int8 rows [n_kv][max_seq][hd], one fp32 scale per
+    // cached row and KV head in kscale / vscale [n_kv][max_seq]; a row is  value = int8 * scale, scale = max|row| / 127.
+    // The step's own key and value are not in the cache yet: they arrive in fp16 (k_cur / v_cur, [n_kv][hd]), are
+    // attended to in fp16, and the kernel stores their 8-bit form into row *d_pos for the steps to come.
+    float* kscale;
+    float* vscale;
+    const __half* k_cur;
+    const __half* v_cur;
 };
 
 }  // namespace cq

@@ -17,7 +17,26 @@ constexpr int kSplitThreads = (kSplitWarps + 1) * 32;
 constexpr int kSplitStages = 6;    // four stages being worked on by the four warp pairs, two on their way
 constexpr int kFoldWarps = 16;
 
-inline size_t attn_split_smem_bytes(int hd, int stages) { return (size_t)stages * 2 * kAttnStageKeys * hd * 2 + 128; }
+// stage: 64 K rows, 64 V rows and - 8-bit cache - the 64 + 64 fp32 scales of those rows
+inline size_t attn_stage_bytes(int hd, bool kv8) { return kv8 ? (size_t)2 * kAttnStageKeys * hd + 2 * kAttnStageKeys * 4 : (size_t)2 * kAttnStageKeys * hd * 2; }
+inline size_t attn_split_smem_bytes(int hd, int stages, bool kv8 = false) { return (size_t)stages * attn_stage_bytes(hd, kv8) + 128; }
+
+// One cache row to its 8-bit form: scale = max|x| / 127, q = rint(x / scale) (an all-zero row: scale 0, q 0).  One warp,
+// HD / 32 values per lane; `row8` and `scale` are the row's place in the cache.
+template <int HD>
+__device__ __forceinline__ void kv8_store_row(const __half* src, signed char* row8, float* scale, int lane) {
+    constexpr int N = HD / 32;
+    float v[N];
+    float m = 0.f;
+#pragma unroll
+    for (int i = 0; i < N; ++i) { v[i] = __half2float(__ldcg(src + lane * N + i)); m = fmaxf(m, fabsf(v[i])); }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    const float sc = m / 127.0f, inv = m > 0.f ? 127.0f / m : 0.f;
+#pragma unroll
+    for (int i = 0; i < N; ++i) row8[lane * N + i] = (signed char)__float2int_rn(v[i] * inv);
+    if (lane == 0) *scale = sc;
+}
 
 // Keys per split: an equal share rounded up to whole 16-key tiles, and never less than one ring stage - at short
 // contexts fewer, fuller splits beat many splits of a tile each (512 keys over 4 KV heads: 8 splits 6.7 us, 37 splits
@@ -28,9 +47,10 @@ __device__ __forceinline__ int attn_chunk(int len, int nsplit) {
     return chunk < kAttnStageKeys ? kAttnStageKeys : chunk;
 }
 
-template <int HD>
+template <int HD, bool KV8 = false>
 __global__ void __launch_bounds__(kSplitThreads) attn_partial_kernel(const AttnArgs a) {
-    constexpr int NCH = HD / 32, ROWB = HD * 2, HALF = kAttnStageKeys * ROWB, NCT = kSplitWarps * 32;
+    constexpr int NCH = HD / 32, ROWB = KV8 ? HD : HD * 2, HALF = kAttnStageKeys * ROWB, NCT = kSplitWarps * 32;
+    constexpr int STAGE = 2 * HALF + (KV8 ? 2 * kAttnStageKeys * 4 : 0);      // K rows, V rows, then (8-bit cache) K scales, V scales
     extern __shared__ __align__(128) unsigned char dyn[];
     __shared__ float sm_o[kSplitWarps][kMaxGroup][HD];
     __shared__ float sm_ml[kSplitWarps][kMaxGroup][2];
@@ -56,7 +76,10 @@ __global__ void __launch_bounds__(kSplitThreads) attn_partial_kernel(const AttnA
     const int t0 = split * chunk;
     const int t1 = min(t0 + chunk, len);
     if (t0 >= len) return;                                       // an empty split publishes nothing; the fold skips it
-    const int nstage = (t1 - t0 + kAttnStageKeys - 1) / kAttnStageKeys;
+    // 8-bit cache: row `pos` is not in the cache yet (this kernel puts it there); the ring carries the rows below it
+    const int t1c = KV8 ? min(t1, len - 1) : t1;
+    const bool owns_cur = KV8 && t1 == len;                      // this split ends with the step's own key
+    const int nstage = (t1c - t0 + kAttnStageKeys - 1) / kAttnStageKeys;
 
     if (warp == kSplitWarps) {
         if (lane == 0) {
@@ -66,13 +89,28 @@ __global__ void __launch_bounds__(kSplitThreads) attn_partial_kernel(const AttnA
             for (int sn = 0; sn < nstage; ++sn) {
                 const int s = sn % nst;
                 if (!failed && !mbar_wait(bar_empty + s * 8, ((sn / nst) & 1) ^ 1)) { failed = true; if (a.err) atomicExch(a.err, 5u); }
-                const int n = min(kAttnStageKeys, t1 - t0 - sn * kAttnStageKeys);
-                if (!waited && t0 + sn * kAttnStageKeys + n == len) { pdl_wait(); waited = true; }      // the stage that holds row `pos`
+                const int n = min(kAttnStageKeys, t1c - t0 - sn * kAttnStageKeys);
+                if (!KV8 && !waited && t0 + sn * kAttnStageKeys + n == len) { pdl_wait(); waited = true; }      // the stage that holds row `pos`
                 const uint32_t bytes = (uint32_t)n * ROWB;
-                mbar_expect_tx(bar_full + s * 8, 2 * bytes);
-                bulk_g2s(stage0 + s * 2 * HALF, kb + (size_t)sn * HALF, bytes, bar_full + s * 8);
-                bulk_g2s(stage0 + s * 2 * HALF + HALF, vb + (size_t)sn * HALF, bytes, bar_full + s * 8);
+                if (KV8) {
+                    const uint32_t sbytes = (uint32_t)((n + 3) & ~3) * 4;       // whole 16-byte units; the scale arrays have room past the last row
+                    const size_t k0 = (size_t)kvh * a.max_seq + t0 + (size_t)sn * kAttnStageKeys;
+                    mbar_expect_tx(bar_full + s * 8, 2 * bytes + 2 * sbytes);
+                    bulk_g2s(stage0 + s * STAGE + 2 * HALF, a.kscale + k0, sbytes, bar_full + s * 8);
+                    bulk_g2s(stage0 + s * STAGE + 2 * HALF + kAttnStageKeys * 4, a.vscale + k0, sbytes, bar_full + s * 8);
+                } else {
+                    mbar_expect_tx(bar_full + s * 8, 2 * bytes);
+                }
+                bulk_g2s(stage0 + s * STAGE, kb + (size_t)sn * HALF, bytes, bar_full + s * 8);
+                bulk_g2s(stage0 + s * STAGE + HALF, vb + (size_t)sn * HALF, bytes, bar_full + s * 8);
             }
+        }
+        if (owns_cur) {
+            // the step's own key and value go into the cache in 8-bit form, for the steps to come (nobody reads row `pos` now)
+            pdl_wait();
+            const size_t row = (size_t)kvh * a.max_seq + (len - 1);
+            kv8_store_row<HD>(a.k_cur + (size_t)kvh * HD, reinterpret_cast<signed char*>(const_cast<__half*>(a.kc)) + row * HD, a.kscale + row, lane);
+            kv8_store_row<HD>(a.v_cur + (size_t)kvh * HD, reinterpret_cast<signed char*>(const_cast<__half*>(a.vc)) + row * HD, a.vscale + row, lane);
         }
         return;
     }
@@ -91,13 +129,17 @@ __global__ void __launch_bounds__(kSplitThreads) attn_partial_kernel(const AttnA
         if (threadIdx.x == 0 && sn == 0) trace_last(a.trace, 6);
         if (threadIdx.x == 0 && sn == nstage - 1) trace_last(a.trace, 7);
         const int kb = t0 + sn * kAttnStageKeys + 32 * wh;       // first key of this warp's 32
-        if ((sn & 3) == pair && kb < t1) {
-            const unsigned char* sK = dyn + s * 2 * HALF + 32 * wh * ROWB;
-            attn_tile32<HD>(st, qa, sK, sK + HALF, t1 - kb, a.scale_log2, g, t);
+        if ((sn & 3) == pair && kb < t1c) {
+            const unsigned char* sK = dyn + s * STAGE + 32 * wh * ROWB;
+            const float* sKs = reinterpret_cast<const float*>(dyn + s * STAGE + 2 * HALF) + 32 * wh;
+            attn_tile32<HD, KV8>(st, qa, sK, sK + HALF, t1c - kb, a.scale_log2, g, t, sKs, sKs + kAttnStageKeys);
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_empty + s * 8);
     }
+    if (owns_cur && warp == kSplitWarps - 1)      // the step's own key, in fp16, straight from the q/k/v kernel's output
+        attn_tile<HD, true>(st, qa, reinterpret_cast<const unsigned char*>(a.k_cur + (size_t)kvh * HD), reinterpret_cast<const unsigned char*>(a.v_cur + (size_t)kvh * HD),
+                            1, a.scale_log2, g, t);
     if (threadIdx.x == 0) trace_last(a.trace, 4);
     attn_state_to_smem<HD>(st, &sm_o[warp][0][0], &sm_ml[warp][0][0], g, t);
     asm volatile("bar.sync 1, %0;" ::"r"(NCT) : "memory");

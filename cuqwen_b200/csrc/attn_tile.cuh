@@ -98,14 +98,39 @@ __device__ __forceinline__ void attn_tile(AttnState<HD>& st, const uint32_t (&qa
         }
 }
 
+// Eight signed bytes (two 32-bit words) -> eight fp16 values in four half2 registers, exactly: the byte with its sign
+// bit flipped becomes the mantissa of 1024 + (v + 128) (prmt with 0x64 as the high byte), from which 1152 is taken.
+__device__ __forceinline__ uint4 s8x8_to_h8(uint2 w) {
+    const uint32_t x0 = w.x ^ 0x80808080u, x1 = w.y ^ 0x80808080u;
+    const __half2 off = __halves2half2(__ushort_as_half((unsigned short)0x6480), __ushort_as_half((unsigned short)0x6480));   // 1152
+    uint32_t r[4] = {prmt(x0, 0x64646464u, 0x5140), prmt(x0, 0x64646464u, 0x7362), prmt(x1, 0x64646464u, 0x5140), prmt(x1, 0x64646464u, 0x7362)};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { __half2 h = __hsub2(*reinterpret_cast<__half2*>(&r[i]), off); r[i] = *reinterpret_cast<uint32_t*>(&h); }
+    return make_uint4(r[0], r[1], r[2], r[3]);
+}
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+// Eight consecutive head-dimension values of one cached row as fp16 fragments: from an fp16 row (16 bytes) or, KV8,
+// from an int8 row (8 bytes; the row's scale is applied by the caller, to the score or to the probability).
+template <bool KV8>
+__device__ __forceinline__ uint4 attn_row8(const unsigned char* row, int chunk8) {
+    if (KV8) return s8x8_to_h8(lds64(smem_u32(row + chunk8 * 8)));
+    return lds128(smem_u32(row + chunk8 * 16));
+}
+
 // Two adjacent 16-key tiles (32 keys) in one step.  Same arithmetic per key as attn_tile, but the four 8-key score
 // blocks form four independent MMA chains, the softmax state is updated once for all 32 keys (one maximum, one
 // rescale of O) and every output tile takes two chained MMAs - more independent work per warp between the points
 // where everything waits on a shuffle or an ex2.  nvalid in [1, 32].
-template <int HD>
+// KV8: the rows are int8 (HD bytes each) and sKs / sVs hold the 32 keys' fp32 scales: a key's K scale multiplies its
+// score, its V scale its probability on the way into P.V (the softmax sum keeps the unscaled probability).
+template <int HD, bool KV8 = false>
 __device__ __forceinline__ void attn_tile32(AttnState<HD>& st, const uint32_t (&qa)[HD / 32][4], const unsigned char* sK, const unsigned char* sV,
-                                            int nvalid, float scale_log2, int g, int t) {
-    constexpr int NCH = HD / 32, NC = HD / 64, NMT = HD / 16, ROWB = HD * 2;
+                                            int nvalid, float scale_log2, int g, int t, const float* sKs = nullptr, const float* sVs = nullptr) {
+    constexpr int NCH = HD / 32, NC = HD / 64, NMT = HD / 16, ROWB = KV8 ? HD : HD * 2;
     float sc[4][4];                          // block b = keys 8b .. 8b+7: lane holds head g, keys 8b+2t, 8b+2t+1 in [0], [1]
 #pragma unroll
     for (int b = 0; b < 4; ++b) sc[b][0] = sc[b][1] = sc[b][2] = sc[b][3] = 0.f;
@@ -114,7 +139,7 @@ __device__ __forceinline__ void attn_tile32(AttnState<HD>& st, const uint32_t (&
         uint4 kf[4];
 #pragma unroll
         for (int b = 0; b < 4; ++b)
-            kf[b] = 8 * b + g < nvalid ? lds128(smem_u32(sK + (8 * b + g) * ROWB + (i * 4 + t) * 16)) : make_uint4(0, 0, 0, 0);
+            kf[b] = 8 * b + g < nvalid ? attn_row8<KV8>(sK + (8 * b + g) * ROWB, i * 4 + t) : make_uint4(0, 0, 0, 0);
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
             mma16816(sc[b], qa[i][0], 0u, qa[i][1], 0u, kf[b].x, kf[b].y);
@@ -127,7 +152,7 @@ __device__ __forceinline__ void attn_tile32(AttnState<HD>& st, const uint32_t (&
     for (int b = 0; b < 4; ++b)
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
-            s[b][j] = 8 * b + 2 * t + j < nvalid ? sc[b][j] * scale_log2 : -INFINITY;
+            s[b][j] = 8 * b + 2 * t + j < nvalid ? sc[b][j] * (KV8 ? scale_log2 * sKs[8 * b + 2 * t + j] : scale_log2) : -INFINITY;
             mx = fmaxf(mx, s[b][j]);
         }
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
@@ -140,7 +165,8 @@ __device__ __forceinline__ void attn_tile32(AttnState<HD>& st, const uint32_t (&
     for (int b = 0; b < 4; ++b) {
         const float p0 = ex2(s[b][0] - m_new), p1 = ex2(s[b][1] - m_new);
         psum += p0 + p1;
-        pb[b] = pack_h2(p0, p1);
+        if (KV8) pb[b] = pack_h2(8 * b + 2 * t < nvalid ? p0 * sVs[8 * b + 2 * t] : 0.f, 8 * b + 2 * t + 1 < nvalid ? p1 * sVs[8 * b + 2 * t + 1] : 0.f);
+        else pb[b] = pack_h2(p0, p1);
     }
     st.l_run = st.l_run * alpha + psum;
     st.m_run = m_new;
@@ -157,7 +183,7 @@ __device__ __forceinline__ void attn_tile32(AttnState<HD>& st, const uint32_t (&
             const int kr = 16 * h + 2 * t + (r & 1) + (r >> 1) * 8;
 #pragma unroll
             for (int c = 0; c < NC; ++c)
-                vv[r][c] = kr < nvalid ? lds128(smem_u32(sV + kr * ROWB + (c * 8 + g) * 16)) : make_uint4(0, 0, 0, 0);
+                vv[r][c] = kr < nvalid ? attn_row8<KV8>(sV + kr * ROWB, c * 8 + g) : make_uint4(0, 0, 0, 0);
         }
 #pragma unroll
         for (int c = 0; c < NC; ++c)

@@ -326,6 +326,25 @@ int launch_dequant(int quant, const void* w, const __half* s, __half* out, long 
     return launch_k(dequant_kernel, dim3(blocks), dim3(256), 0, cfg, quant, (const uint8_t*)w, s, out, rows, cols);
 }
 
+// The same N(0,1) values as fill_normal_kernel, stored as 8-bit cache rows: one warp per row of `hd` values.
+__global__ void fill_normal_q8_kernel(signed char* dst, float* scales, size_t rows, int hd, uint64_t seed, uint64_t base) {
+    const int lane = threadIdx.x & 31, n = hd / 32;
+    for (size_t r = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < rows; r += (size_t)gridDim.x * (blockDim.x >> 5)) {
+        float v[4], m = 0.f;
+        for (int i = 0; i < n; ++i) { v[i] = __half2float(__float2half(normal_at(seed, base + r * hd + lane * n + i))); m = fmaxf(m, fabsf(v[i])); }
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        const float inv = m > 0.f ? 127.0f / m : 0.f;
+        for (int i = 0; i < n; ++i) dst[r * hd + lane * n + i] = (signed char)__float2int_rn(v[i] * inv);
+        if (lane == 0) scales[r] = m / 127.0f;
+    }
+}
+int launch_fill_normal_q8(void* dst, float* scales, size_t rows, int hd, uint64_t seed, uint64_t base, const LaunchCfg& cfg) {
+    if (hd != 64 && hd != 128) return (int)cudaErrorInvalidValue;
+    int blocks = (int)((rows + 7) / 8 < 8192 ? (rows + 7) / 8 : 8192);
+    if (blocks < 1) blocks = 1;
+    return launch_k(fill_normal_q8_kernel, dim3(blocks), dim3(256), 0, cfg, (signed char*)dst, scales, rows, hd, seed, base);
+}
+
 int launch_fill_normal(__half* dst, size_t n, uint64_t seed, uint64_t base, const LaunchCfg& cfg) {
     int blocks = (int)((n + 255) / 256 < 8192 ? (n + 255) / 256 : 8192);
     if (blocks < 1) blocks = 1;
@@ -337,25 +356,30 @@ size_t attn_scratch_floats_o(int n_kv, int nsplit, int head_dim) { return attn_s
 size_t attn_scratch_floats_ml(int n_kv, int nsplit) { return attn_slots(n_kv, nsplit) * kMaxGroup * 2; }
 size_t attn_scratch_counters(int n_kv, int nsplit) { return attn_counters(n_kv, nsplit); }
 
-static int env_int(const char* name, int dflt);
-// Two launches: partials, then the fold (attn_split.cuh).  Returns the first error.
-template <int HD>
+// Two launches: partials, then the fold (attn_split.cuh).  Returns the first error.  a.kscale != null selects the
+// kernel for the 8-bit cache.
+template <int HD, bool KV8>
 static int launch_attn_split(const AttnArgs& a, const LaunchCfg& cfg) {
     AttnArgs b = a;
-    b.stages = env_int("CUQWEN_ATTN_STAGES", kSplitStages);      // tuning override (development aid)
-    if (b.stages < 2 || b.stages > kSplitStages) b.stages = kSplitStages;
-    const size_t smem = attn_split_smem_bytes(HD, b.stages);
-    cudaError_t e = cudaFuncSetAttribute(attn_partial_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_split_smem_bytes(HD, kSplitStages));
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_partial_kernel<HD>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_fold_kernel<HD>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-    if (e != cudaSuccess) return (int)e;
-    if (int r = launch_k(attn_partial_kernel<HD>, dim3(b.n_kv, b.nsplit), dim3(kSplitThreads), smem, cfg, b)) return r;
+    b.stages = kSplitStages;
+    const size_t smem = attn_split_smem_bytes(HD, b.stages, KV8);
+    static bool once = false;
+    if (!once) {
+        cudaError_t e = cudaFuncSetAttribute(attn_partial_kernel<HD, KV8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_partial_kernel<HD, KV8>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_fold_kernel<HD>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        if (e != cudaSuccess) return (int)e;
+        once = true;
+    }
+    if (int r = launch_k(attn_partial_kernel<HD, KV8>, dim3(b.n_kv, b.nsplit), dim3(kSplitThreads), smem, cfg, b)) return r;
     return launch_k(attn_fold_kernel<HD>, dim3(b.n_kv * b.grp), dim3(kFoldWarps * 32), 0, cfg, b);
 }
 int launch_attn(int head_dim, const AttnArgs& a, const LaunchCfg& cfg) {
     if (a.grp < 1 || a.grp > kMaxGroup || a.nsplit < 1 || a.nsplit > kMaxSplit) return (int)cudaErrorInvalidValue;
-    if (head_dim == 128) return launch_attn_split<128>(a, cfg);
-    if (head_dim == 64) return launch_attn_split<64>(a, cfg);
+    const bool kv8 = a.kscale != nullptr;
+    if (kv8 && (!a.vscale || !a.k_cur || !a.v_cur)) return (int)cudaErrorInvalidValue;
+    if (head_dim == 128) return kv8 ? launch_attn_split<128, true>(a, cfg) : launch_attn_split<128, false>(a, cfg);
+    if (head_dim == 64) return kv8 ? launch_attn_split<64, true>(a, cfg) : launch_attn_split<64, false>(a, cfg);
     return (int)cudaErrorInvalidValue;
 }
 

@@ -73,6 +73,8 @@ int launch_tp_sum(const __half* x, __half* x_next, const void* slots, int n, int
                   const LaunchCfg& cfg);
 // out = half(float(q) * float(scale)) for every weight; quant 1 or 2.
 int launch_dequant(int quant, const void* w, const __half* s, __half* out, long rows, long cols, const LaunchCfg& cfg);
+// The same values as 8-bit cache rows (one fp32 scale per row of hd values): rows * hd values starting at element `base`.
+int launch_fill_normal_q8(void* dst, float* scales, size_t rows, int hd, uint64_t seed, uint64_t base, const LaunchCfg& cfg);
 // Deterministic N(0,1) fp16 fill: element i gets a value that depends only on (seed, base + i).
 int launch_fill_normal(__half* dst, size_t n, uint64_t seed, uint64_t base, const LaunchCfg& cfg);
 
