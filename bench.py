@@ -121,10 +121,11 @@ class ClockSampler:
 def workload_config(a, cfg, qid: int, steps: int) -> dict:
     """The `config` object: identical in both arms (what differs between them is reported under `arm`)."""
     from cuqwen_b200 import binfmt
-    gb = binfmt.step_bytes(cfg, qid, int(a.ctx + steps / 2)) / 1e9
+    kv8 = getattr(a, "kv", "fp16") == "int8" and getattr(a, "impl", "ours") == "ours"
+    gb = binfmt.step_bytes(cfg, qid, int(a.ctx + steps / 2), kv8) / 1e9
     cut = f" CUT TO {a.layers} LAYERS (profiler-sized, not a benchmark value)" if getattr(a, "layers", 0) else ""
     return {"workload": f"Qwen2.5-{a.model.upper()}{cut} {a.quant} random-init (N(0,0.02) weights, seed {SEED}), B=1 greedy decode, "
-                        f"KV context {a.ctx} prefilled with N(0,1) fp16, {steps} steps",
+                        f"KV context {a.ctx} prefilled with N(0,1) fp16{' (stored as int8 rows + scales)' if kv8 else ''}, {steps} steps",
             "l2": f"no flush needed: every step streams {gb:.2f} GB of weights and KV, far beyond the 126 MB L2"}
 
 
@@ -256,12 +257,14 @@ def parity_leg(eng, a, cfg, path, rank, world, local, dist, steps: int = 32):
     if rank != 0:
         return None
     ref.ref_model_free(rm)
-    ok = bool(np.isfinite(worst_rms) and worst_rms <= PARITY_RMS and agree / steps >= 0.99)
+    kv8 = a.kv == "int8"     # the 8-bit cache is outside the parity contract: compared with the same reference, looser bar
+    ok = bool(np.isfinite(worst_rms) and worst_rms <= (1e-1 if kv8 else PARITY_RMS) and agree / steps >= (0.85 if kv8 else 0.99))
     return {"vs": f"reference CUDA build oracle/_ref (qwen_forward, teacher-forced), same file, same KV seed, context {ctx}",
             "steps": steps, "top1_agree": round(agree / steps, 4), "top1_identical": round(strict / steps, 4),
             "max_abs_logit": round(worst_abs, 6), "rel_rms_logit": round(worst_rms, 6),
             "logits_inside_2e-3rel_1e-2abs": round(inside / max(total, 1), 6),
-            "criterion": "top1_agree >= 0.99 and rel_rms_logit <= 0.015", "pass": ok}
+            "criterion": "int8 KV cache, outside the parity contract (sanity bound only): top1_agree >= 0.85 and rel_rms_logit <= 0.1" if kv8 else "top1_agree >= 0.99 and rel_rms_logit <= 0.015",
+            "pass": ok}
 
 
 def run_ours(a):
@@ -281,6 +284,9 @@ def run_ours(a):
     else:
         prm = E.model_params(a.model, a.quant)
     prm.device, prm.tp_rank, prm.tp_size = local, rank, world
+    kv8 = a.kv == "int8"
+    if kv8:
+        prm.flags |= E.FLAG_KV_INT8
     eng = E.Engine(prm)
     eng.load(str(path))
     if world > 1:
@@ -320,13 +326,13 @@ def run_ours(a):
 
     peak, peak_src = peaks()
     mean_ctx = ctx + Kst / 2
-    step_bytes_total = binfmt.step_bytes(cfg, qid, int(mean_ctx))
+    step_bytes_total = binfmt.step_bytes(cfg, qid, int(mean_ctx), kv8)
     out = {
         "metric": METRIC, "value": round(value, 2), "unit": "tok/s", "n_gpus": world, "steps": Kst, "warmup": W,
         "ms_per_step": round(ms / Kst, 5), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "int4 weights x fp16 activations, fp32 accumulate", "data": "synthetic",
         "config": workload_config(a, cfg, qid, Kst),
-        "arm": {"parallelism": f"tp{world}", "attn_splits": eng.params.attn_splits},
+        "arm": {"parallelism": f"tp{world}", "attn_splits": eng.params.attn_splits, "kv_cache": a.kv},
         "e2e": {"value": round(e2e, 2), "unit": "tok/s", "h2d_bytes_per_step": 32, "d2h_bytes_per_step": 8},
         "gpu_launches": Kst * eng.step_launches,
         "clocks": cs.result,
@@ -525,6 +531,7 @@ def main():
     ap.add_argument("--quant", default="int4")
     ap.add_argument("--ctx", type=int, default=8192)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--kv", default="fp16", choices=["fp16", "int8"], help="KV cache format (int8: opt-in 8-bit cache, outside the parity contract)")
     ap.add_argument("--no-parity", action="store_true")
     ap.add_argument("--layers", type=int, default=0, help="cut the model to this many layers (profiler captures only; the JSON line says so)")
     ap.add_argument("--sweep", default="", choices=["", "gemv", "attention"], help="kernel-level sweeps of the other benchmark configurations")

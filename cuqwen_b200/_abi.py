@@ -58,6 +58,7 @@ SIGNATURES = {
     "cuqwen_k_rope": (_i, [_i, _vp, _vp, _i, _i, _i, _vp, _f, _i]),
     "cuqwen_k_kv_store": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i]),
     "cuqwen_k_attention": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp]),
+    "cuqwen_k_attention_kv8": (_i, [_i] + [_vp] * 9 + [_i] * 5 + [_vp, _vp]),
     "cuqwen_k_attention_static": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i]),
     "cuqwen_k_attention_static_status": (_i, [_i, _vp, C.POINTER(C.c_uint)]),
     "cuqwen_k_tp_sum": (_i, [_i, _vp, _vp, _vp, _i, _i, _vp, _i, C.c_longlong]),

@@ -122,15 +122,17 @@ def file_nbytes(cfg: dict, quant: int) -> int:
     return n
 
 
-def step_bytes(cfg: dict, quant: int, ctx: int) -> int:
+def step_bytes(cfg: dict, quant: int, ctx: int, kv_int8: bool = False) -> int:
     """Algorithmic bytes of one decode step: every weight/scale/bias/norm byte once, one embedding row, and the
-    K and V rows [0, ctx) of every layer.  Activations, partials, logits and the KV write are not counted."""
+    K and V rows [0, ctx) of every layer (fp16, or int8 plus one fp32 scale per row and KV head).  Activations,
+    partials, logits and the KV write are not counted."""
     d, I, V = cfg["dim"], cfg["inter"], cfg["vocab"]
     qd, kd = cfg["heads"] * cfg["hd"], cfg["kv"] * cfg["hd"]
     layer = (2 * d * 2 + proj_nbytes(qd, d, quant) + qd * 2 + 2 * (proj_nbytes(kd, d, quant) + kd * 2) + proj_nbytes(d, qd, quant)
              + 2 * proj_nbytes(I, d, quant) + proj_nbytes(d, I, quant))
     head = V * d * 2 if (cfg["tied"] or quant == FP16) else proj_nbytes(V, d, INT8)
-    return cfg["layers"] * layer + d * 2 + head + d * 2 + 2 * cfg["layers"] * kd * 2 * ctx
+    kv_row = cfg["kv"] * (cfg["hd"] + 4) if kv_int8 else kd * 2
+    return cfg["layers"] * layer + d * 2 + head + d * 2 + 2 * cfg["layers"] * kv_row * ctx
 
 
 def write_model(path, cfg: dict, quant: int, tensors: dict, max_seq_len: int = 32768) -> None:

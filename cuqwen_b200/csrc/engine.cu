@@ -159,7 +159,8 @@ struct cuqwen_engine {
     uint64_t weight_bytes = 0;                   // algorithmic bytes of all tensors a step reads (this rank)
     // state
     __half *x = nullptr, *xn = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *att = nullptr, *gate = nullptr, *logits = nullptr;
-    __half *kc = nullptr, *vc = nullptr;
+    __half *kc = nullptr, *vc = nullptr;                  // CUQWEN_FLAG_KV_INT8: int8 rows behind these pointers, scales below
+    float *kscale = nullptr, *vscale = nullptr; bool kv8 = false;
     __half *spare_up = nullptr, *spare_out = nullptr;     // QwenState::up / mlp_out of the source-compatible layer (never read by the step)
     float *part_o = nullptr, *part_ml = nullptr; unsigned* counters = nullptr;
     StepCtl* ctl = nullptr; StepCtl* h_ctl = nullptr;
@@ -233,7 +234,14 @@ extern "C" int cuqwen_create(const cuqwen_params* pin, cuqwen_engine** out) {
     CK(dalloc((void**)&e->att, e->q_dim_l * 2)); CK(dalloc((void**)&e->gate, e->inter_l * 2));
     { const size_t cb = ((size_t)(e->inter_l / kGroup) * 4 + 15) / 16 * 16; CK(dalloc((void**)&e->gate_xd, (size_t)e->inter_l * 2)); CK(dalloc((void**)&e->gate_corr, cb)); CK(dalloc((void**)&e->gate_xscale, cb)); } CK(dalloc((void**)&e->logits, e->vocab_l * 2));
     CK(dalloc((void**)&e->spare_up, (size_t)e->inter_l * 2)); CK(dalloc((void**)&e->spare_out, (size_t)p.dim * 2));
-    CK(dalloc((void**)&e->kc, kvn * 2)); CK(dalloc((void**)&e->vc, kvn * 2));     // zeroed like src/model.cu:37-38
+    e->kv8 = (p.flags & CUQWEN_FLAG_KV_INT8) != 0;
+    if (e->kv8) {
+        const size_t ns = (size_t)p.n_layers * e->n_kv_l * p.max_seq_len + 16;       // room for the bulk copies' 16-byte rounding past the last row
+        CK(dalloc((void**)&e->kc, kvn)); CK(dalloc((void**)&e->vc, kvn));
+        CK(dalloc((void**)&e->kscale, ns * 4)); CK(dalloc((void**)&e->vscale, ns * 4));
+    } else {
+        CK(dalloc((void**)&e->kc, kvn * 2)); CK(dalloc((void**)&e->vc, kvn * 2));     // zeroed like src/model.cu:37-38
+    }
     CK(dalloc((void**)&e->part_o, attn_scratch_floats_o(e->n_kv_l, e->nsplit, p.head_dim) * 4));
     CK(dalloc((void**)&e->part_ml, attn_scratch_floats_ml(e->n_kv_l, e->nsplit) * 4));
     CK(dalloc((void**)&e->counters, attn_scratch_counters(e->n_kv_l, e->nsplit) * 4));
@@ -257,7 +265,7 @@ extern "C" void cuqwen_destroy(cuqwen_engine* e) {
     if (e->tp_rx) cudaFree(e->tp_rx);
     if (e->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(e->comm);
     void* bufs[] = {e->x, e->xn, e->q, e->k, e->v, e->att, e->gate, e->logits, e->kc, e->vc, e->part_o, e->part_ml, e->counters, e->ctl, e->d_hist,
-                    e->bitmap, e->best, e->ticket, e->out_ring, e->tp_partial, e->tp_keys, e->warena, e->step_trace, e->spare_up, e->spare_out, e->x2, e->gate_xd, e->gate_corr, e->gate_xscale};
+                    e->bitmap, e->best, e->ticket, e->out_ring, e->tp_partial, e->tp_keys, e->warena, e->step_trace, e->spare_up, e->spare_out, e->kscale, e->vscale, e->x2, e->gate_xd, e->gate_corr, e->gate_xscale};
     for (void* b : bufs) if (b) cudaFree(b);
     if (e->h_ctl) cudaFreeHost(e->h_ctl);
     if (e->h_out) cudaFreeHost(e->h_out);
@@ -461,7 +469,7 @@ static void describe_step(cuqwen_engine* e, std::vector<HostPhase>& out, int nsp
             a.w[0] = L.q.w; a.w[1] = L.k.w; a.w[2] = L.v.w; a.s[0] = L.q.s; a.s[1] = L.k.s; a.s[2] = L.v.s;
             a.bias[0] = L.bq; a.bias[1] = L.bk; a.bias[2] = L.bv;
             a.q_out = e->q; a.k_out = e->k; a.v_out = e->v;
-            a.kcache = e->kc + l * kv_layer; a.vcache = e->vc + l * kv_layer;
+            if (!e->kv8) { a.kcache = e->kc + l * kv_layer; a.vcache = e->vc + l * kv_layer; }     // 8-bit cache: the attention kernel stores the row
             a.d_pos = &e->ctl->pos; a.n_heads = e->n_heads_l; a.n_kv = e->n_kv_l; a.hd = p.head_dim; a.max_seq = p.max_seq_len;
             a.theta = p.rope_theta; a.rope_fast = (p.flags & CUQWEN_FLAG_ACCURATE_ROPE) ? 0 : 1;
             gemv_phase(p.quant, EPI_QKV, a, false);
@@ -469,7 +477,13 @@ static void describe_step(cuqwen_engine* e, std::vector<HostPhase>& out, int nsp
         {   // split-KV attention + combine
             HostPhase h; memset(&h, 0, sizeof h);
             AttnArgs& a = h.ph.at;
-            a.q = e->q; a.kc = e->kc + l * kv_layer; a.vc = e->vc + l * kv_layer; a.out = e->att; a.d_pos = &e->ctl->pos;
+            a.q = e->q; a.out = e->att; a.d_pos = &e->ctl->pos;
+            if (e->kv8) {
+                const size_t srow = (size_t)l * e->n_kv_l * p.max_seq_len;
+                a.kc = reinterpret_cast<const __half*>(reinterpret_cast<const signed char*>(e->kc) + l * kv_layer);
+                a.vc = reinterpret_cast<const __half*>(reinterpret_cast<const signed char*>(e->vc) + l * kv_layer);
+                a.kscale = e->kscale + srow; a.vscale = e->vscale + srow; a.k_cur = e->k; a.v_cur = e->v;
+            } else { a.kc = e->kc + l * kv_layer; a.vc = e->vc + l * kv_layer; }
             a.n_kv = e->n_kv_l; a.grp = e->plan.grp; a.max_seq = p.max_seq_len; a.nsplit = nsplit;
             a.scale_log2 = (1.0f / sqrtf((float)p.head_dim)) * 1.4426950408889634f;
             a.part_o = e->part_o; a.part_ml = e->part_ml; a.counters = e->counters; a.err = t_err;
@@ -674,6 +688,12 @@ extern "C" int cuqwen_kv_fill_normal(cuqwen_engine* e, int ctx_len, uint64_t see
         for (int h = 0; h < e->n_kv_l; ++h) {
             const size_t local = ((size_t)l * e->n_kv_l + h) * head_stride;
             const uint64_t global = ((uint64_t)l * p.n_kv_heads + (e->plan.kvh0 + h)) * head_stride;
+            if (e->kv8) {      // the same values, quantised row by row
+                const size_t srow = ((size_t)l * e->n_kv_l + h) * p.max_seq_len;
+                CK(launch_fill_normal_q8(reinterpret_cast<signed char*>(e->kc) + local, e->kscale + srow, (size_t)ctx_len, p.head_dim, seed * 2 + 0, global, cfg));
+                CK(launch_fill_normal_q8(reinterpret_cast<signed char*>(e->vc) + local, e->vscale + srow, (size_t)ctx_len, p.head_dim, seed * 2 + 1, global, cfg));
+                continue;
+            }
             CK(launch_fill_normal(e->kc + local, (size_t)ctx_len * p.head_dim, seed * 2 + 0, global, cfg));
             CK(launch_fill_normal(e->vc + local, (size_t)ctx_len * p.head_dim, seed * 2 + 1, global, cfg));
         }
@@ -756,7 +776,8 @@ extern "C" int cuqwen_get_params(const cuqwen_engine* e, cuqwen_params* out) { i
 extern "C" int cuqwen_step_launches(const cuqwen_engine* e) { return e ? e->launches : 0; }
 extern "C" uint64_t cuqwen_step_bytes(const cuqwen_engine* e, int ctx) {
     if (!e) return 0;
-    return e->weight_bytes + (uint64_t)2 * e->p.n_layers * e->n_kv_l * e->p.head_dim * 2 * (uint64_t)ctx;
+    const uint64_t row = e->kv8 ? (uint64_t)e->p.head_dim + 4 : (uint64_t)e->p.head_dim * 2;       // one cached K or V row of one head (8-bit: + its scale)
+    return e->weight_bytes + (uint64_t)2 * e->p.n_layers * e->n_kv_l * row * (uint64_t)ctx;
 }
 
 extern "C" int cuqwen_get_ptr(cuqwen_engine* e, int which, int layer, void** ptr, size_t* bytes) {
@@ -800,7 +821,7 @@ extern "C" int cuqwen_get_ptr(cuqwen_engine* e, int which, int layer, void** ptr
             default: return fail(CUQWEN_ERR_ARG, "unknown pointer id %d", which);
         }
     } else {
-        const size_t kvb = (size_t)p.n_layers * e->n_kv_l * p.max_seq_len * p.head_dim * 2;
+        const size_t kvb = (size_t)p.n_layers * e->n_kv_l * p.max_seq_len * p.head_dim * (e->kv8 ? 1 : 2);
         switch (which) {
             case CUQWEN_PTR_X: r = e->x; b = p.dim * 2; break;
             case CUQWEN_PTR_XN: r = e->xn; b = p.dim * 2; break;
@@ -814,6 +835,8 @@ extern "C" int cuqwen_get_ptr(cuqwen_engine* e, int which, int layer, void** ptr
             case CUQWEN_PTR_VALUE_CACHE: r = e->vc; b = kvb; break;
             case CUQWEN_PTR_HISTORY: r = e->d_hist; b = (size_t)p.max_seq_len * 4; break;
             case CUQWEN_PTR_STEP_TRACE: r = e->step_trace; b = e->step_trace_bytes; break;
+            case CUQWEN_PTR_KEY_SCALE: r = e->kscale; b = e->kv8 ? (size_t)p.n_layers * e->n_kv_l * p.max_seq_len * 4 : 0; break;
+            case CUQWEN_PTR_VALUE_SCALE: r = e->vscale; b = e->kv8 ? (size_t)p.n_layers * e->n_kv_l * p.max_seq_len * 4 : 0; break;
             case CUQWEN_PTR_TOKEN: r = &e->ctl->token; b = 4; break;
             case CUQWEN_PTR_POS: r = &e->ctl->pos; b = 4; break;
             case CUQWEN_PTR_HISTORY_LEN: r = &e->ctl->hist_len; b = 4; break;
@@ -952,6 +975,20 @@ extern "C" int cuqwen_k_attention(int device, const void* q, const void* kc, con
     a.n_kv = n_kv; a.grp = n_heads / n_kv; a.max_seq = max_seq; a.nsplit = nsplit;
     a.scale_log2 = (1.0f / sqrtf((float)hd)) * 1.4426950408889634f;
     a.part_o = (float*)so; a.part_ml = (float*)sml; a.counters = (unsigned*)counters; a.err = t_err;
+    KK(launch_attn(hd, a, cfg)); return CUQWEN_OK;
+}
+extern "C" int cuqwen_k_attention_kv8(int device, const void* q, void* kc8, void* vc8, float* kscale, float* vscale, const void* k_cur, const void* v_cur,
+                                      void* out, const int* d_pos, int n_heads, int n_kv, int hd, int max_seq, int nsplit, void* so, void* sml) {
+    DEV(device);
+    if (n_kv < 1 || n_heads % n_kv || n_heads / n_kv > kMaxGroup || (hd != 64 && hd != 128) || nsplit < 1 || nsplit > kMaxSplit || max_seq < 1 || max_seq % 4)
+        return fail(CUQWEN_ERR_ARG, "unsupported attention shape (heads %d/%d, head_dim %d, splits %d, max_seq_len %d)", n_heads, n_kv, hd, nsplit, max_seq);
+    NOT_NULL(q, kc8, vc8, kscale, vscale, k_cur, v_cur, out, d_pos, so, sml);
+    AttnArgs a{};
+    a.q = (const __half*)q; a.kc = (const __half*)kc8; a.vc = (const __half*)vc8; a.out = (__half*)out; a.d_pos = d_pos;
+    a.n_kv = n_kv; a.grp = n_heads / n_kv; a.max_seq = max_seq; a.nsplit = nsplit;
+    a.scale_log2 = (1.0f / sqrtf((float)hd)) * 1.4426950408889634f;
+    a.part_o = (float*)so; a.part_ml = (float*)sml; a.err = t_err;
+    a.kscale = kscale; a.vscale = vscale; a.k_cur = (const __half*)k_cur; a.v_cur = (const __half*)v_cur;
     KK(launch_attn(hd, a, cfg)); return CUQWEN_OK;
 }
 extern "C" int cuqwen_k_gemv_add(int device, int quant, const void* w, const void* s, const void* in, void* x, int rows, int cols) {

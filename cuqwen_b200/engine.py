@@ -18,11 +18,11 @@ from ._abi import Params, check
 FP16, INT8, INT4 = 0, 1, 2
 QUANT_ID = {"fp16": FP16, "int8": INT8, "int4": INT4}
 MODEL_ID = {"0.5b": 0, "1.5b": 1, "3b": 2, "7b": 3, "14b": 4}
-FLAG_ACCURATE_ROPE, FLAG_NO_PDL, FLAG_NO_GRAPH, FLAG_STEP_TRACE, FLAG_TP_NCCL, FLAG_NO_HANDOVER = 1, 2, 4, 16, 32, 64
+FLAG_ACCURATE_ROPE, FLAG_NO_PDL, FLAG_NO_GRAPH, FLAG_STEP_TRACE, FLAG_TP_NCCL, FLAG_NO_HANDOVER, FLAG_KV_INT8 = 1, 2, 4, 16, 32, 64, 128
 
 # cuqwen_get_ptr ids (include/cuqwen_b200.h)
 PTR = dict(X=0, XN=1, Q=2, K=3, V=4, ATT=5, GATE=6, LOGITS=7, KEY_CACHE=8, VALUE_CACHE=9, HISTORY=10, STEP_TRACE=11, TOKEN=12, POS=13,
-           HISTORY_LEN=14, SAMPLED=15, PARTIAL_O=16, PARTIAL_ML=17, UP=18, MLP_OUT=19, STREAM=20,
+           HISTORY_LEN=14, SAMPLED=15, PARTIAL_O=16, PARTIAL_ML=17, UP=18, MLP_OUT=19, STREAM=20, KEY_SCALE=21, VALUE_SCALE=22,
            EMBED=32, NORM=33, LM_HEAD=34, LM_HEAD_SCALE=35,
            IN_NORM=64, WQ=65, SQ=66, BQ=67, WK=68, SK=69, BK=70, WV=71, SV=72, BV=73, WO=74, SO=75, POST_NORM=76,
            WGATE=77, SGATE=78, WUP=79, SUP=80, WDOWN=81, SDOWN=82)

@@ -53,6 +53,13 @@ def gqa_attention_decode(q, kcache, vcache, out, d_pos, n_heads, n_kv_heads, hea
                                         max_seq_len, n_splits, _p(scratch_o), _p(scratch_ml), _p(counters)))
 
 
+def gqa_attention_decode_kv8(q, kcache8, vcache8, kscale, vscale, k_cur, v_cur, out, d_pos, n_heads, n_kv_heads, head_dim, max_seq_len, n_splits,
+                             scratch_o, scratch_ml, device=0):
+    """cuqwen_k_attention_kv8: int8 caches with fp32 row scales; also stores the step's own key / value into row *d_pos."""
+    check(_abi.lib().cuqwen_k_attention_kv8(device, _p(q), _p(kcache8), _p(vcache8), _p(kscale), _p(vscale), _p(k_cur), _p(v_cur), _p(out), _p(d_pos),
+                                            n_heads, n_kv_heads, head_dim, max_seq_len, n_splits, _p(scratch_o), _p(scratch_ml)))
+
+
 def gqa_attention_decode_static(q, kcache, vcache, out, d_pos, n_heads, n_kv_heads, head_dim, max_seq_len, n_splits,
                                 stream=None, device=0):
     """cuqwen_k_attention_static: same result as gqa_attention_decode, scratch inside the library (no allocation).

@@ -45,7 +45,10 @@ enum {
     /* 8 is unused (it selected a persistent one-launch step kernel that was removed: it never beat the launch chain) */
     CUQWEN_FLAG_STEP_TRACE = 16,    /* profiling: every GEMV / attention launch of a step stamps its timeline (CUQWEN_PTR_STEP_TRACE) */
     CUQWEN_FLAG_TP_NCCL = 32,       /* tensor parallel: sum the row-parallel partials with NCCL all-reduce calls instead of peer stores */
-    CUQWEN_FLAG_NO_HANDOVER = 64    /* the down projection converts its input itself instead of taking it staged from the SwiGLU kernel */
+    CUQWEN_FLAG_NO_HANDOVER = 64,   /* the down projection converts its input itself instead of taking it staged from the SwiGLU kernel */
+    CUQWEN_FLAG_KV_INT8 = 128       /* opt-in, outside the parity contract (the reference keeps fp16, its roadmap names this: README.md:147):
+                                     * the KV cache holds int8 rows with one fp32 scale per token and KV head (scale = max|row| / 127), which
+                                     * halves the bytes attention streams; the step's own key and value are still attended to in fp16 */
 };
 
 /* Mirrors QwenConfig (include/config.h:52-127) as run-time data. */
@@ -107,6 +110,7 @@ enum {
     CUQWEN_PTR_PARTIAL_O, CUQWEN_PTR_PARTIAL_ML,   /* split-KV scratch: fp32 partial outputs, (max, sum) pairs */
     CUQWEN_PTR_UP, CUQWEN_PTR_MLP_OUT,              /* QwenState::up / mlp_out: allocated for harnesses that write them, unused by the step (as in the reference, src/model.cu:18-20) */
     CUQWEN_PTR_STREAM,                              /* not a buffer: the cudaStream_t the engine queues its steps on (bytes = 0) */
+    CUQWEN_PTR_KEY_SCALE, CUQWEN_PTR_VALUE_SCALE,   /* CUQWEN_FLAG_KV_INT8: fp32 [n_layers][n_kv_heads][max_seq_len] row scales; the caches are then int8 in the same layout */
     CUQWEN_PTR_EMBED = 32, CUQWEN_PTR_NORM, CUQWEN_PTR_LM_HEAD, CUQWEN_PTR_LM_HEAD_SCALE,
     CUQWEN_PTR_IN_NORM = 64, CUQWEN_PTR_WQ, CUQWEN_PTR_SQ, CUQWEN_PTR_BQ, CUQWEN_PTR_WK, CUQWEN_PTR_SK, CUQWEN_PTR_BK,
     CUQWEN_PTR_WV, CUQWEN_PTR_SV, CUQWEN_PTR_BV, CUQWEN_PTR_WO, CUQWEN_PTR_SO, CUQWEN_PTR_POST_NORM,
@@ -180,6 +184,13 @@ int cuqwen_k_kv_store(int device, const void* k, const void* v, void* kcache, vo
 int cuqwen_k_attention(int device, const void* q, const void* kcache, const void* vcache, void* out, const int* d_pos,
                        int n_heads, int n_kv_heads, int head_dim, int max_seq_len, int n_splits,
                        void* scratch_o, void* scratch_ml, void* counters);
+/* No counterpart in the reference (8-bit KV cache, its roadmap README.md:147).  cuqwen_k_attention over int8 caches
+ * [n_kv_heads][max_seq_len][head_dim] with fp32 row scales [n_kv_heads][max_seq_len]: attends to cache rows [0, *d_pos)
+ * plus the step's own key / value given in fp16 (k_cur, v_cur: [n_kv_heads][head_dim]), and stores their 8-bit form
+ * into row *d_pos of the caches and scale arrays.  The scale arrays need three entries of room past max_seq_len. */
+int cuqwen_k_attention_kv8(int device, const void* q, void* kcache8, void* vcache8, float* kscale, float* vscale, const void* k_cur, const void* v_cur,
+                           void* out, const int* d_pos, int n_heads, int n_kv_heads, int head_dim, int max_seq_len, int n_splits,
+                           void* scratch_o, void* scratch_ml);
 int cuqwen_attn_scratch_bytes(int n_kv_heads, int head_dim, int n_splits, size_t* bytes_o, size_t* bytes_ml, size_t* bytes_counters);
 /* No counterpart in the reference.  Same computation as cuqwen_k_attention for hosts that may not allocate device
  * memory any more (fixed memory budget, or code that must not stall the device's other streams on cudaMalloc):
