@@ -280,7 +280,7 @@ def run_ours(a):
     path = model_path(a.model, a.quant, a.layers)
     if a.layers:       # profiler-sized variant: explicit dims, and a KV cache just long enough for the run
         prm = E.custom_params(cfg["vocab"], cfg["dim"], cfg["inter"], cfg["layers"], cfg["heads"], cfg["kv"], cfg["hd"], a.quant,
-                              max_seq_len=a.ctx + a.steps + max(a.warmup, 3) + 64)
+                              max_seq_len=(a.ctx + a.steps + max(a.warmup, 3) + 64 + 15) // 16 * 16)
     else:
         prm = E.model_params(a.model, a.quant)
     prm.device, prm.tp_rank, prm.tp_size = local, rank, world

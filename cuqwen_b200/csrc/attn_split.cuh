@@ -6,7 +6,9 @@
 // trades one small extra launch - started early through programmatic dependent launch, so it is already resident when
 // the partials land - for two fence + atomic + reload round trips on the critical path of the last CTAs, and it puts
 // eight consumer warps on the key stream instead of four (warp pair p takes the stages sn with sn % 4 == p, each
-// warp 32 of the stage's 64 keys).
+// warp 32 of the stage's 64 keys).  Sixteen consumer warps of 16 keys each were measured and are slower (8K keys,
+// 28/4 heads: 11.7 against 10.1 us for both launches; 32K: 21.0 against 17.5): the per-tile costs - one rescale of
+// the output, one round of shuffles and exponentials - double while the chain a warp waits on gets no shorter.
 #pragma once
 #include "attn.cuh"
 

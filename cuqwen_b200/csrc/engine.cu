@@ -205,6 +205,8 @@ extern "C" int cuqwen_create(const cuqwen_params* pin, cuqwen_engine** out) {
         (p.n_heads * p.head_dim) % 128 || p.n_heads / p.n_kv_heads > kMaxGroup)
         return fail(CUQWEN_ERR_ARG, "unsupported dims: dim %d inter %d vocab %d layers %d heads %d/%d hd %d", p.dim, p.intermediate_size, p.vocab_size,
                     p.n_layers, p.n_heads, p.n_kv_heads, p.head_dim);
+    if ((p.flags & CUQWEN_FLAG_KV_INT8) && p.max_seq_len % 4)
+        return fail(CUQWEN_ERR_ARG, "the 8-bit KV cache needs max_seq_len to be a multiple of 4 (its row scales travel in 16-byte units); got %d", p.max_seq_len);
     // exchanges of a step are numbered 0 .. 2 * n_layers + 1 inside a window of kSeqPerStep numbers (common.cuh)
     if (p.tp_size > 1 && 2 * p.n_layers + 2 > (int)kSeqPerStep)
         return fail(CUQWEN_ERR_ARG, "tensor parallelism supports at most %d layers (this model has %d)", (int)kSeqPerStep / 2 - 1, p.n_layers);

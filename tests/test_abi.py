@@ -108,3 +108,15 @@ def test_tensor_parallel_layer_bound(built):
     with pytest.raises(CuQwenError) as err:
         E.Engine(prm)
     assert err.value.code == 1 and "layers" in str(err.value)
+
+
+def test_int8_kv_cache_needs_an_aligned_max_seq_len(built):
+    """The 8-bit cache's row scales are fetched in 16-byte units: a max_seq_len that is not a multiple of 4 is refused
+    at creation instead of faulting on the device."""
+    from cuqwen_b200 import engine as E
+    from cuqwen_b200._abi import CuQwenError
+    prm = E.custom_params(1024, 256, 512, 2, 4, 2, 64, "int4", max_seq_len=66)
+    prm.flags = E.FLAG_KV_INT8
+    with pytest.raises(CuQwenError) as err:
+        E.Engine(prm)
+    assert err.value.code == 1 and "multiple of 4" in str(err.value)
