@@ -287,6 +287,7 @@ def run_ours(a):
     kv8 = a.kv == "int8"
     if kv8:
         prm.flags |= E.FLAG_KV_INT8
+    prm.flags |= a.flags
     eng = E.Engine(prm)
     eng.load(str(path))
     if world > 1:
@@ -531,6 +532,7 @@ def main():
     ap.add_argument("--quant", default="int4")
     ap.add_argument("--ctx", type=int, default=8192)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--flags", type=int, default=0, help="extra CUQWEN_FLAG_* bits for the engine (comparison variants)")
     ap.add_argument("--kv", default="fp16", choices=["fp16", "int8"], help="KV cache format (int8: opt-in 8-bit cache, outside the parity contract)")
     ap.add_argument("--no-parity", action="store_true")
     ap.add_argument("--layers", type=int, default=0, help="cut the model to this many layers (profiler captures only; the JSON line says so)")

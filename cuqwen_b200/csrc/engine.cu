@@ -193,7 +193,6 @@ extern "C" int cuqwen_create(const cuqwen_params* pin, cuqwen_engine** out) {
         const ModelRow& m = kModels[p.model_id];
         p.vocab_size = m.vocab; p.dim = m.dim; p.intermediate_size = m.inter; p.n_layers = m.layers; p.n_heads = m.heads; p.n_kv_heads = m.kv; p.head_dim = m.hd;
     }
-    if (const char* f = getenv("CUQWEN_FLAGS")) p.flags |= (uint32_t)atoi(f);   // development aid: OR extra CUQWEN_FLAG_* bits in
     if (p.max_seq_len <= 0) p.max_seq_len = 32768;
     if (p.tp_size <= 0) p.tp_size = 1;
     if (p.norm_eps == 0.f) p.norm_eps = 1e-6f;
@@ -221,7 +220,6 @@ extern "C" int cuqwen_create(const cuqwen_params* pin, cuqwen_engine** out) {
     e->q_dim_l = e->n_heads_l * p.head_dim; e->kv_dim_l = e->n_kv_l * p.head_dim;
     e->inter_l = plan.i1 - plan.i0; e->vocab_l = plan.v1 - plan.v0;
     CK(cudaDeviceGetAttribute(&e->sms, cudaDevAttrMultiProcessorCount, p.device));
-    if (const char* v = getenv("CUQWEN_ATTN_SPLITS")) { if (atoi(v) > 0) p.attn_splits = atoi(v); }      // tuning override (development aid)
     // one CTA per SM and not one more: the partial kernel takes a whole SM's shared memory, so a 149th CTA would wait for
     // a second wave (measured at 40/8 heads, 32K keys: 19 splits 40.7 us, 16 splits 26.9 us)
     e->nsplit = p.attn_splits > 0 ? p.attn_splits : (e->sms / e->n_kv_l > 0 ? e->sms / e->n_kv_l : 1);
@@ -759,8 +757,8 @@ extern "C" int cuqwen_tp_init(cuqwen_engine* e, const void* id_bytes, size_t n) 
     if (nr != ncclSuccess) return fail(CUQWEN_ERR_NCCL, "all-reduce of the peer-mapping status: %s", g_nccl.GetErrorString(nr));
     CK(ce);
     e->tp_peer = all_ok == 1;
-    e->tp_sum_separate = true;                      // the slots are summed once by a small kernel; 0 = every CTA of the next GEMV sums them while staging x (measured slower)
-    if (const char* v = getenv("CUQWEN_TP_SUM_KERNEL")) e->tp_sum_separate = atoi(v) != 0;       // development aid
+    // the slots are summed once by a small kernel; CUQWEN_FLAG_TP_SUM_IN_GEMV: every CTA of the next GEMV sums them while staging x (measured slower, kept for comparison)
+    e->tp_sum_separate = !(e->p.flags & CUQWEN_FLAG_TP_SUM_IN_GEMV);
     return CUQWEN_OK;
 }
 

@@ -33,8 +33,6 @@ struct RingCtx {
     uint32_t nsb;                 // scale blocks in shared memory (1 or 2): block j uses buffer j % nsb in phase (j / nsb) & 1
     unsigned* err;                // device word that receives a code when a bounded wait expires (may be null)
     bool failed;                  // a wait of this thread expired: stop waiting, finish with meaningless numbers
-    bool skip_math;               // development aid: consume the ring without doing the arithmetic
-    unsigned long long* stamp;    // development aid: where this CTA's consumers put the time x staging ended (may be null)
 
     __device__ __forceinline__ void advance() { if (++slot == nslots) { slot = 0; par ^= 1u; } }
     __device__ __forceinline__ void wait(uint32_t bar, uint32_t parity, unsigned code) {
@@ -154,7 +152,6 @@ __device__ __forceinline__ void gemv_consume(const GemvArgs& a, RingCtx& R, int 
     // a SwiGLU kernel whose block is a whole 128-row group hands its outputs over in staged form as well
     const bool emit = EPI == EPI_SWIGLU && kInt && a.xd_out != nullptr && a.brows == 128 && rw == 8 && kw == 1 && gw == 1;
     __half* hbuf = reinterpret_cast<__half*>(red);
-    if (R.stamp && threadIdx.x == 0) *R.stamp = global_ns();
     if (threadIdx.x == 0) trace_last(a.trace, 3);
 
     for (int j = 0; j < n_b; ++j) {
@@ -183,7 +180,7 @@ __device__ __forceinline__ void gemv_consume(const GemvArgs& a, RingCtx& R, int 
             const int s = R.slot;
             R.wait(R.bar_full + s * 8, R.par, 1u);
             const int c = kwi + p * kw;
-            if (live && c < G.PT && !R.skip_math) {
+            if (live && c < G.PT) {
                 const int grp0 = c * pg;
                 const int ngp = ngrp - grp0 < pg ? ngrp - grp0 : pg;
                 const int cstride = G.box_rows * kChunkBytes;        // chunk-major box: [chunk][row][64 bytes]
@@ -269,10 +266,7 @@ __device__ __forceinline__ RingCtx gemv_ring(const GemvArgs& a, unsigned char* s
     R.scale_block_bytes = L.scale_block_bytes; R.off_stages = L.off_stages; R.slot_bytes = L.stage_bytes; R.nslots = a.nst;
     R.bar_full = R.sm0 + L.off_bars; R.bar_empty = R.bar_full + a.nst * 8; R.bar_sfull = R.bar_empty + a.nst * 8; R.bar_sempty = R.bar_sfull + 16;
     R.bar_x = R.bar_sempty + 16; R.xpar = 0u;
-    R.slot = 0; R.par = 0; R.sj = 0; R.nsb = (uint32_t)a.nsb; R.err = a.err; R.failed = false; R.skip_math = false; R.stamp = nullptr;
-#ifdef CQ_SKIP_MATH
-    R.skip_math = true;      // development build: consume the ring without arithmetic (measures the copy path)
-#endif
+    R.slot = 0; R.par = 0; R.sj = 0; R.nsb = (uint32_t)a.nsb; R.err = a.err; R.failed = false;
     return R;
 }
 

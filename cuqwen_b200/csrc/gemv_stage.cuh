@@ -90,53 +90,57 @@ struct GatherSrc {
     unsigned* err;
     long long limit;         // SM cycles after which the re-read loop gives up
 };
+// One chunk of eight values: x's chunk plus the ranks' partials for it, summed in rank order.  gave_up: set (and kept)
+// once the bounded re-read loop has expired for this thread.
+__device__ __forceinline__ uint4 gather_chunk(const GatherSrc& gs, int K, int c8, const uint4& xo, bool& gave_up) {
+    constexpr int RB = 2;                                  // source ranks whose loads are in flight together
+    float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int r0 = 0; r0 < gs.n; r0 += RB) {
+        unsigned long long q[RB][8];
+        unsigned long long t0 = 0ull;
+        for (;;) {
+            bool ok = true;
+#pragma unroll
+            for (int j = 0; j < RB; ++j)
+                if (r0 + j < gs.n) {
+                    const uint2* p = gs.slots + (size_t)(r0 + j) * K + (size_t)c8 * 8;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) ld_pair2(p + 2 * i, q[j][2 * i], q[j][2 * i + 1]);
+                }
+#pragma unroll
+            for (int j = 0; j < RB; ++j)
+                if (r0 + j < gs.n) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) ok = ok && pair_seq(q[j][i]) == gs.seq;
+                }
+            if (ok || gave_up) break;
+            const unsigned long long now = (unsigned long long)sm_cycles();      // the SM's cycle counter: cheap to read
+            if (t0 == 0ull) t0 = now | 1ull;
+            else if (now - t0 > (unsigned long long)gs.limit) { gave_up = true; if (gs.err) atomicExch(gs.err, 8u); break; }
+        }
+#pragma unroll
+        for (int j = 0; j < RB; ++j)
+            if (r0 + j < gs.n) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) s[i] += pair_val(q[j][i]);
+            }
+    }
+    uint4 xn;
+    const __half2* h = reinterpret_cast<const __half2*>(&xo);
+    __half2* o = reinterpret_cast<__half2*>(&xn);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) { const float2 f = __half22float2(h[k]); o[k] = __floats2half2_rn(f.x + s[2 * k], f.y + s[2 * k + 1]); }
+    return xn;
+}
 template <bool PARKW>
 __device__ __forceinline__ float park_gather(const __half* x, const __half* norm_w, const GatherSrc& gs, int K, int nchunk, uint4* raw, uint4* wraw, int nthreads) {
-    constexpr int RB = 2;                                  // source ranks whose loads are in flight together
     float ss = 0.f;
     bool gave_up = false;
     for (int c8 = threadIdx.x; c8 < nchunk; c8 += nthreads) {
         const uint4 xo = __ldcg(reinterpret_cast<const uint4*>(x) + c8);
         uint4 wv = make_uint4(0u, 0u, 0u, 0u);
         if (PARKW) wv = __ldg(reinterpret_cast<const uint4*>(norm_w) + c8);
-        float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        for (int r0 = 0; r0 < gs.n; r0 += RB) {
-            unsigned long long q[RB][8];
-            unsigned long long t0 = 0ull;
-            for (;;) {
-                bool ok = true;
-#pragma unroll
-                for (int j = 0; j < RB; ++j)
-                    if (r0 + j < gs.n) {
-                        const uint2* p = gs.slots + (size_t)(r0 + j) * K + (size_t)c8 * 8;
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) ld_pair2(p + 2 * i, q[j][2 * i], q[j][2 * i + 1]);
-                    }
-#pragma unroll
-                for (int j = 0; j < RB; ++j)
-                    if (r0 + j < gs.n) {
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) ok = ok && pair_seq(q[j][i]) == gs.seq;
-                    }
-                if (ok || gave_up) break;
-                const unsigned long long now = (unsigned long long)sm_cycles();      // the SM's cycle counter: cheap to read
-                if (t0 == 0ull) t0 = now | 1ull;
-                else if (now - t0 > (unsigned long long)gs.limit) { gave_up = true; if (gs.err) atomicExch(gs.err, 8u); break; }
-            }
-#pragma unroll
-            for (int j = 0; j < RB; ++j)
-                if (r0 + j < gs.n) {
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) s[i] += pair_val(q[j][i]);
-                }
-        }
-        uint4 xn;
-        {
-            const __half2* h = reinterpret_cast<const __half2*>(&xo);
-            __half2* o = reinterpret_cast<__half2*>(&xn);
-#pragma unroll
-            for (int k = 0; k < 4; ++k) { const float2 f = __half22float2(h[k]); o[k] = __floats2half2_rn(f.x + s[2 * k], f.y + s[2 * k + 1]); }
-        }
+        const uint4 xn = gather_chunk(gs, K, c8, xo, gave_up);
         raw[c8] = xn;
         if (PARKW) wraw[c8] = wv;
         if (gs.store_next) reinterpret_cast<uint4*>(gs.x_next)[c8] = xn;
@@ -212,7 +216,7 @@ __device__ __forceinline__ void digits_of_chunk(uint4 v, int c8, bool live, unsi
 // one 128-column group, as digits_of_chunk wants.
 template <int Q, int NB>
 __device__ __forceinline__ void stage_x_regs(const __half* x, const __half* norm_w, float eps, int K, unsigned char* xd, int* corr, float* xscale,
-                                             float* red, int nthreads, unsigned long long* trace = nullptr) {
+                                             float* red, int nthreads, unsigned long long* trace = nullptr, const GatherSrc* gs = nullptr) {
     const int nchunk = K / 8;
     uint4 v[NB], w[NB];
 #pragma unroll
@@ -222,6 +226,17 @@ __device__ __forceinline__ void stage_x_regs(const __half* x, const __half* norm
         if (c8 < nchunk) {
             v[i] = __ldcg(reinterpret_cast<const uint4*>(x) + c8);
             if (norm_w) w[i] = __ldg(reinterpret_cast<const uint4*>(norm_w) + c8);
+        }
+    }
+    if (gs) {      // tensor parallel: x plus the partials the ranks pushed (same words, same order as tp_sum_kernel)
+        bool gave_up = false;
+#pragma unroll
+        for (int i = 0; i < NB; ++i) {
+            const int c8 = i * nthreads + threadIdx.x;
+            if (c8 < nchunk) {
+                v[i] = gather_chunk(*gs, K, c8, v[i], gave_up);
+                if (gs->store_next) reinterpret_cast<uint4*>(gs->x_next)[c8] = v[i];
+            }
         }
     }
     if (norm_w) {
@@ -259,9 +274,9 @@ __device__ __forceinline__ bool stage_x(const __half* x, const __half* norm_w, f
     uint4* wraw = raw + nchunk;
     const bool w_parked = norm_w && 4 * K <= xarea_bytes;
     const bool gather = gs && gs->n > 0;
-    if (!gather && nchunk <= 3 * nthreads && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (!norm_w || (reinterpret_cast<uintptr_t>(norm_w) & 15) == 0)) {
-        if (nchunk <= 2 * nthreads) stage_x_regs<Q, 2>(x, norm_w, eps, K, xd, corr, xscale, red, nthreads, trace);
-        else stage_x_regs<Q, 3>(x, norm_w, eps, K, xd, corr, xscale, red, nthreads, trace);
+    if (nchunk <= 3 * nthreads && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (!norm_w || (reinterpret_cast<uintptr_t>(norm_w) & 15) == 0)) {
+        if (nchunk <= 2 * nthreads) stage_x_regs<Q, 2>(x, norm_w, eps, K, xd, corr, xscale, red, nthreads, trace, gather ? gs : nullptr);
+        else stage_x_regs<Q, 3>(x, norm_w, eps, K, xd, corr, xscale, red, nthreads, trace, gather ? gs : nullptr);
         return false;
     }
     const bool bulk = bar_x != 0u && !gather && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (!norm_w || (w_parked && (reinterpret_cast<uintptr_t>(norm_w) & 15) == 0));

@@ -437,11 +437,6 @@ static int encode_weight_map(CUtensorMap* m, const void* w, size_t row_bytes, si
 
 constexpr int kGemvThreadsHost = (kConsumerWarps + 1) * 32;
 
-static int env_int(const char* name, int dflt) {
-    const char* v = getenv(name);
-    return v && *v ? atoi(v) : dflt;
-}
-
 // Rows per CTA block: whole 16-row tiles, as many per block (1, 2, 4 or 8) as keep at least one block per SM.
 // (The kernel takes any row count per block.  Cutting the matrix into SM-count nearly equal blocks instead - 26 rows
 // for the 3584-row projections of the 7B model, 138 blocks in one round where whole tiles give 224 - measured slower:
@@ -459,7 +454,6 @@ int gemv_block_rows(int rows, int K, int sm_count, int epi) {
 // Picks the work split (rw row-warps x kw K-parts), the staged piece size and the ring depth for one GEMV launch.
 //   many tile sets: blocks of up to 8 tile sets (128 rows), every consumer warp walks the whole K of its 16 rows;
 //   few tile sets: one tile set per CTA, its K split over the eight consumer warps.
-// Tuning overrides (development aid): CUQWEN_GEMV_PG, CUQWEN_GEMV_NST, CUQWEN_GEMV_CAP_KB.
 int launch_gemv(int quant, int epi, GemvArgs& a, const LaunchCfg& cfg) {
     if (a.K <= 0 || a.K % kGroup != 0 || a.K > 24576) return (int)cudaErrorInvalidValue;
     if (quant < 0 || quant > 2) return (int)cudaErrorInvalidValue;
@@ -494,19 +488,18 @@ int launch_gemv(int quant, int epi, GemvArgs& a, const LaunchCfg& cfg) {
     const int per_sm = cap_kb == 110 ? 2 : 1;
     const int grid = nblk < per_sm * cfg.sm_count ? nblk : per_sm * cfg.sm_count;
     const int nsb = nblk <= grid ? 1 : 2;            // a second scale block only when some CTA has a second block
-    int cap = env_int("CUQWEN_GEMV_CAP_KB", cap_kb) * 1024;
-    const int env_pg = env_int("CUQWEN_GEMV_PG", 0), env_nst = env_int("CUQWEN_GEMV_NST", 0);
+    int cap = cap_kb * 1024;
     int pg = 0, nst = 0;
     for (int pass = 0; pass < 2 && !nst; ++pass) {
-        for (int q = env_pg > 0 ? (env_pg < pg_max ? env_pg : pg_max) : pg_max; q >= 1; --q) {
+        for (int q = pg_max; q >= 1; --q) {
             const int pt = (ngrp + q - 1) / q;
             int kwq = kw; while (kwq > 1 && kwq > pt) kwq /= 2;                   // no more K-parts than pieces
             const int steps = (pt + kwq - 1) / kwq;
-            int want = env_nst > 0 ? env_nst : (rw == 8 ? 6 : steps < 6 ? steps : 6);
+            int want = rw == 8 ? 6 : steps < 6 ? steps : 6;
             int n = want;
             while (n > 1 && gemv_smem_bytes(a.K, quant, MT, a.brows, kwq, q, n, nsb) > (size_t)cap) --n;
             if (gemv_smem_bytes(a.K, quant, MT, a.brows, kwq, q, n, nsb) > (size_t)cap) continue;
-            if (n >= (want < 3 ? want : 3) || q == 1 || env_pg > 0) { pg = q; nst = n; kw = kwq; break; }
+            if (n >= (want < 3 ? want : 3) || q == 1) { pg = q; nst = n; kw = kwq; break; }
             if (!nst || n > nst) { pg = q; nst = n; kw = kwq; }
             if (q == 1) break;
             nst = 0;
@@ -528,7 +521,6 @@ int launch_gemv(int quant, int epi, GemvArgs& a, const LaunchCfg& cfg) {
         }
     }
     const dim3 gridd(grid), block(kGemvThreadsHost);
-    if (env_int("CUQWEN_GEMV_SHOW", 0)) fprintf(stderr, "gemv q%d epi%d K%d rows%d: brows%d nblk%d rw%d kw%d gw%d pg%d nst%d nsb%d grid%d smem %zu\n", quant, epi, a.K, a.rows, a.brows, a.nblk, rw, kw, gw, pg, nst, nsb, grid, smem);
     if (quant == Q_I4) return launch_gemv_i4(epi, a, gridd, block, smem, cfg);
     if (quant == Q_I8) return launch_gemv_i8(epi, a, gridd, block, smem, cfg);
     return launch_gemv_f16(epi, a, gridd, block, smem, cfg);

@@ -61,15 +61,14 @@ def check_ranks(ranks, toks, want):
     assert same >= 10, (ranks[0]["toks"].tolist(), toks)
 
 
-@pytest.mark.parametrize("flags,sum_kernel", [(0, 0), (0, 1), (E.FLAG_TP_NCCL, 0)], ids=["peer_stores", "peer_stores_sum_kernel", "nccl_allreduce"])
+@pytest.mark.parametrize("flags", [E.FLAG_TP_SUM_IN_GEMV, 0, E.FLAG_TP_NCCL], ids=["peer_stores_sum_in_gemv", "peer_stores_sum_kernel", "nccl_allreduce"])
 @pytest.mark.parametrize("quant", [2, 0])
-def test_two_ranks_match_one_gpu(built, tmp_path, monkeypatch, quant, flags, sum_kernel):
+def test_two_ranks_match_one_gpu(built, tmp_path, quant, flags):
     if gpu_count() < 2:
         pytest.skip("needs two GPUs")
-    monkeypatch.setenv("CUQWEN_TP_SUM_KERNEL", str(sum_kernel))      # 1: the many-rank variant (slots summed once by a small kernel)
     ranks, toks, want = run_ranks(tmp_path, CFG, 2, quant, flags)
-    per_layer = 10 if flags else 8 if sum_kernel else 6                       # 6 = qkv, attention x2, o_proj, gate/up, down; NCCL adds an all-reduce and a residual kernel twice, the sum kernel adds 2
-    tail = 3 + (2 if flags else 1)                                            # lm_head, penalty, sampler + (key all-gather and merge | merge of the pushed keys)
+    per_layer = 10 if flags == E.FLAG_TP_NCCL else 8 if flags == 0 else 6                       # 6 = qkv, attention x2, o_proj, gate/up, down; NCCL adds an all-reduce and a residual kernel twice, the sum kernel adds 2
+    tail = 3 + (2 if flags == E.FLAG_TP_NCCL else 1)                                            # lm_head, penalty, sampler + (key all-gather and merge | merge of the pushed keys)
     assert int(ranks[0]["launches"]) == 1 + per_layer * CFG["layers"] + tail
     check_ranks(ranks, toks, want)
 
