@@ -40,6 +40,14 @@ struct AttnArgs {
     float* vscale;
     const __half* k_cur;
     const __half* v_cur;
+    // Hand-over to a quantised o_proj (head_dim 128 only: a head is then exactly one 128-column scale group): besides
+    // the fp16 output the fold also writes it in the staged form a quantised GEMV's inner loop reads (digit blocks,
+    // corrections, scales: gemv_stage.cuh), so that the o_proj CTAs fetch it with three bulk copies instead of each
+    // converting the whole vector again.  quant_out: the consumer's weight format (Q_I4 / Q_I8); null = no hand-over.
+    unsigned char* xd_out;
+    int* corr_out;
+    float* xscale_out;
+    int quant_out;
 };
 
 }  // namespace cq

@@ -11,6 +11,7 @@
 // the output, one round of shuffles and exponentials - double while the chain a warp waits on gets no shorter.
 #pragma once
 #include "attn.cuh"
+#include "gemv_stage.cuh"
 
 namespace cq {
 
@@ -208,11 +209,19 @@ __global__ void __launch_bounds__(kFoldWarps * 32) attn_fold_kernel(const AttnAr
             if (lane < NCOL) { const float4 v = o_w[w][lane]; o.x += v.x * f; o.y += v.y * f; o.z += v.z * f; o.w += v.w * f; }
             Ls += ml_w[w][1] * f;
         }
+        const float inv = 1.0f / Ls;
+        const uint32_t h01 = pack_h2(o.x * inv, o.y * inv), h23 = pack_h2(o.z * inv, o.w * inv);
         if (lane < NCOL) {
-            const float inv = 1.0f / Ls;
-            __half2* dst = reinterpret_cast<__half2*>(a.out + (size_t)head * HD + lane * 4);
-            dst[0] = __floats2half2_rn(o.x * inv, o.y * inv);
-            dst[1] = __floats2half2_rn(o.z * inv, o.w * inv);
+            uint32_t* dst = reinterpret_cast<uint32_t*>(a.out + (size_t)head * HD + lane * 4);
+            dst[0] = h01; dst[1] = h23;
+        }
+        if (HD == 128 && a.xd_out) {
+            // the head's 128 values are one scale group: lane l < 16 collects chunk l (the values of lanes 2l, 2l+1)
+            uint4 v;
+            v.x = __shfl_sync(0xffffffffu, h01, (2 * lane) & 31); v.y = __shfl_sync(0xffffffffu, h23, (2 * lane) & 31);
+            v.z = __shfl_sync(0xffffffffu, h01, (2 * lane + 1) & 31); v.w = __shfl_sync(0xffffffffu, h23, (2 * lane + 1) & 31);
+            if (a.quant_out == Q_I4) digits_of_chunk<Q_I4>(v, head * 16 + (lane & 15), lane < 16, a.xd_out, a.corr_out, a.xscale_out);
+            else digits_of_chunk<Q_I8>(v, head * 16 + (lane & 15), lane < 16, a.xd_out, a.corr_out, a.xscale_out);
         }
         if (lane == 0) trace_last(tr, 5);
     }

@@ -171,6 +171,7 @@ struct cuqwen_engine {
     unsigned char* tp_rx = nullptr; size_t tp_rx_bytes = 0; unsigned char* peer_rx[8] = {}; bool tp_peer = false;
     __half* x2 = nullptr; bool tp_sum_separate = false;
     unsigned char* gate_xd = nullptr; int* gate_corr = nullptr; float* gate_xscale = nullptr;    // SwiGLU output in staged form (see GemvArgs::xd_out)
+    unsigned char* att_xd = nullptr; int* att_corr = nullptr; float* att_xscale = nullptr;       // attention output in staged form (see AttnArgs::xd_out)
     int steps_done = 0;                          // mirrors the device-side step counter (StepCtl::pad[1])
     std::vector<cudaEvent_t>* prof = nullptr;    // cuqwen_step_profile: an event is recorded after every launch of the step
     unsigned long long* step_trace = nullptr; size_t step_trace_bytes = 0;     // CUQWEN_FLAG_STEP_TRACE: eight timeline words per launch (tma.cuh)
@@ -233,6 +234,7 @@ extern "C" int cuqwen_create(const cuqwen_params* pin, cuqwen_engine** out) {
     CK(dalloc((void**)&e->q, e->q_dim_l * 2)); CK(dalloc((void**)&e->k, e->kv_dim_l * 2)); CK(dalloc((void**)&e->v, e->kv_dim_l * 2));
     CK(dalloc((void**)&e->att, e->q_dim_l * 2)); CK(dalloc((void**)&e->gate, e->inter_l * 2));
     { const size_t cb = ((size_t)(e->inter_l / kGroup) * 4 + 15) / 16 * 16; CK(dalloc((void**)&e->gate_xd, (size_t)e->inter_l * 2)); CK(dalloc((void**)&e->gate_corr, cb)); CK(dalloc((void**)&e->gate_xscale, cb)); } CK(dalloc((void**)&e->logits, e->vocab_l * 2));
+    { const size_t cb = ((size_t)(e->q_dim_l / kGroup) * 4 + 15) / 16 * 16; CK(dalloc((void**)&e->att_xd, (size_t)e->q_dim_l * 2)); CK(dalloc((void**)&e->att_corr, cb)); CK(dalloc((void**)&e->att_xscale, cb)); }
     CK(dalloc((void**)&e->spare_up, (size_t)e->inter_l * 2)); CK(dalloc((void**)&e->spare_out, (size_t)p.dim * 2));
     e->kv8 = (p.flags & CUQWEN_FLAG_KV_INT8) != 0;
     if (e->kv8) {
@@ -265,7 +267,7 @@ extern "C" void cuqwen_destroy(cuqwen_engine* e) {
     if (e->tp_rx) cudaFree(e->tp_rx);
     if (e->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(e->comm);
     void* bufs[] = {e->x, e->xn, e->q, e->k, e->v, e->att, e->gate, e->logits, e->kc, e->vc, e->part_o, e->part_ml, e->counters, e->ctl, e->d_hist,
-                    e->bitmap, e->best, e->ticket, e->out_ring, e->tp_partial, e->tp_keys, e->warena, e->step_trace, e->spare_up, e->spare_out, e->kscale, e->vscale, e->x2, e->gate_xd, e->gate_corr, e->gate_xscale};
+                    e->bitmap, e->best, e->ticket, e->out_ring, e->tp_partial, e->tp_keys, e->warena, e->step_trace, e->spare_up, e->spare_out, e->kscale, e->vscale, e->x2, e->gate_xd, e->gate_corr, e->gate_xscale, e->att_xd, e->att_corr, e->att_xscale};
     for (void* b : bufs) if (b) cudaFree(b);
     if (e->h_ctl) cudaFreeHost(e->h_ctl);
     if (e->h_out) cudaFreeHost(e->h_out);
@@ -434,6 +436,8 @@ static void describe_step(cuqwen_engine* e, std::vector<HostPhase>& out, int nsp
     // 128-row groups, which the launcher decides from the row count
     const bool hand_over = p.quant != 0 && !(p.flags & CUQWEN_FLAG_NO_HANDOVER) && e->inter_l % 128 == 0 &&
                            gemv_block_rows(e->inter_l, p.dim, e->sms, EPI_SWIGLU) == 128;
+    // attention output handed to o_proj in staged form: a head of 128 values is one scale group
+    const bool att_hand_over = p.quant != 0 && p.head_dim == 128 && !(p.flags & CUQWEN_FLAG_NO_HANDOVER);
     __half* cur = e->x;
     int pending = -1, next_xi = 0;
     auto take_x = [&](GemvArgs& a) {                                        // a normed GEMV reads the residual stream
@@ -487,12 +491,14 @@ static void describe_step(cuqwen_engine* e, std::vector<HostPhase>& out, int nsp
             a.n_kv = e->n_kv_l; a.grp = e->plan.grp; a.max_seq = p.max_seq_len; a.nsplit = nsplit;
             a.scale_log2 = (1.0f / sqrtf((float)p.head_dim)) * 1.4426950408889634f;
             a.part_o = e->part_o; a.part_ml = e->part_ml; a.counters = e->counters; a.err = t_err;
+            if (att_hand_over) { a.xd_out = e->att_xd; a.corr_out = e->att_corr; a.xscale_out = e->att_xscale; a.quant_out = p.quant; }
             h.ph.kind = PH_ATTN;
             out.push_back(h);
         }
         {   // o_proj + residual
             GemvArgs a = gv(e->att, e->q_dim_l);
             a.w[0] = L.o.w; a.s[0] = L.o.s; a.rows = p.dim;
+            if (att_hand_over) { a.xd_in = e->att_xd; a.corr_in = e->att_corr; a.xscale_in = e->att_xscale; }
             if (e->tp == 1) { a.out_h = e->x; gemv_phase(p.quant, EPI_RESID, a, false); }
             else if (peer) { push_to(a); gemv_phase(p.quant, EPI_PUSH, a, false); sum_after_push(); }
             else { a.out_f = e->tp_partial; gemv_phase(p.quant, EPI_F32, a, true); }

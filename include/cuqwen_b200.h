@@ -45,7 +45,7 @@ enum {
     /* 8 is unused (it selected a persistent one-launch step kernel that was removed: it never beat the launch chain) */
     CUQWEN_FLAG_STEP_TRACE = 16,    /* profiling: every GEMV / attention launch of a step stamps its timeline (CUQWEN_PTR_STEP_TRACE) */
     CUQWEN_FLAG_TP_NCCL = 32,       /* tensor parallel: sum the row-parallel partials with NCCL all-reduce calls instead of peer stores */
-    CUQWEN_FLAG_NO_HANDOVER = 64,   /* the down projection converts its input itself instead of taking it staged from the SwiGLU kernel */
+    CUQWEN_FLAG_NO_HANDOVER = 64,   /* o_proj and the down projection convert their input themselves instead of taking it staged from the attention fold / the SwiGLU kernel */
     CUQWEN_FLAG_TP_SUM_IN_GEMV = 256, /* tensor parallel, peer-store exchange: no separate sum kernel; every CTA of the GEMV that consumes the
                                      * vector adds the ranks' partials while it stages its input (comparison variant, measured slower) */
     CUQWEN_FLAG_KV_INT8 = 128       /* opt-in, outside the parity contract (the reference keeps fp16, its roadmap names this: README.md:147):

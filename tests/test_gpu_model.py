@@ -66,11 +66,13 @@ def test_small_model_step_vs_oracle(built, tmp_path, name, quant):
     eng.close(); orc.close()
 
 
+@pytest.mark.parametrize("name", ["wide_mlp", "hd128"])
 @pytest.mark.parametrize("quant", [1, 2])
-def test_staged_handover_of_the_mlp_activation(built, tmp_path, quant):
+def test_staged_handover_of_the_mlp_activation(built, tmp_path, quant, name):
     """The SwiGLU kernel's staged output (digits, corrections, scales) must be exactly what the down projection would
-    have derived from the fp16 vector itself: both paths give the same bits, and both agree with the oracle."""
-    cfg, path = write_small(tmp_path, "wide_mlp", quant)
+    have derived from the fp16 vector itself, and likewise the attention fold's staged output for o_proj (head_dim 128:
+    the "hd128" model): both paths give the same bits, and both agree with the oracle."""
+    cfg, path = write_small(tmp_path, name, quant)
     a, b = make_engine(cfg, quant, path, flags=E.FLAG_ACCURATE_ROPE), make_engine(cfg, quant, path, flags=E.FLAG_ACCURATE_ROPE | E.FLAG_NO_HANDOVER)
     orc = O.OracleModel(str(path), 128)
     for pos, t in enumerate([5, 900, 17, 333, 64, 2]):
