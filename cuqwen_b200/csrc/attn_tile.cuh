@@ -195,6 +195,80 @@ __device__ __forceinline__ void attn_tile32(AttnState<HD>& st, const uint32_t (&
     }
 }
 
+// attn_tile32 over an 8-bit cache.  Same arithmetic per key as attn_tile, but the four 8-key score
+// blocks form four independent MMA chains, the softmax state is updated once for all 32 keys (one maximum, one
+// rescale of O) and every output tile takes two chained MMAs - more independent work per warp between the points
+// where everything waits on a shuffle or an ex2.  nvalid in [1, 32].
+// KV8: the rows are int8 (HD bytes each) and sKs / sVs hold the 32 keys' fp32 scales: a key's K scale multiplies its
+// score, its V scale its probability on the way into P.V (the softmax sum keeps the unscaled probability).
+template <int HD, bool KV8 = true>
+__device__ __forceinline__ void attn_tile32_q8(AttnState<HD>& st, const uint32_t (&qa)[HD / 32][4], const unsigned char* sK, const unsigned char* sV,
+                                            int nvalid, float scale_log2, int g, int t, const float* sKs = nullptr, const float* sVs = nullptr) {
+    constexpr int NCH = HD / 32, NC = HD / 64, NMT = HD / 16, ROWB = KV8 ? HD : HD * 2;
+    float sc[4][4];                          // block b = keys 8b .. 8b+7: lane holds head g, keys 8b+2t, 8b+2t+1 in [0], [1]
+#pragma unroll
+    for (int b = 0; b < 4; ++b) sc[b][0] = sc[b][1] = sc[b][2] = sc[b][3] = 0.f;
+#pragma unroll
+    for (int i = 0; i < NCH; ++i) {
+        uint4 kf[4];
+#pragma unroll
+        for (int b = 0; b < 4; ++b)
+            kf[b] = 8 * b + g < nvalid ? attn_row8<KV8>(sK + (8 * b + g) * ROWB, i * 4 + t) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            mma16816(sc[b], qa[i][0], 0u, qa[i][1], 0u, kf[b].x, kf[b].y);
+            mma16816(sc[b], qa[i][2], 0u, qa[i][3], 0u, kf[b].z, kf[b].w);
+        }
+    }
+    float s[4][2];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int b = 0; b < 4; ++b)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            s[b][j] = 8 * b + 2 * t + j < nvalid ? sc[b][j] * (KV8 ? scale_log2 * sKs[8 * b + 2 * t + j] : scale_log2) : -INFINITY;
+            mx = fmaxf(mx, s[b][j]);
+        }
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float m_new = fmaxf(st.m_run, mx);       // finite: key 0 is always valid
+    const float alpha = ex2(st.m_run - m_new);
+    float psum = 0.f;
+    uint32_t pb[4];
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+        const float p0 = ex2(s[b][0] - m_new), p1 = ex2(s[b][1] - m_new);
+        psum += p0 + p1;
+        if (KV8) pb[b] = pack_h2(8 * b + 2 * t < nvalid ? p0 * sVs[8 * b + 2 * t] : 0.f, 8 * b + 2 * t + 1 < nvalid ? p1 * sVs[8 * b + 2 * t + 1] : 0.f);
+        else pb[b] = pack_h2(p0, p1);
+    }
+    st.l_run = st.l_run * alpha + psum;
+    st.m_run = m_new;
+    const float al = __shfl_sync(0xffffffffu, alpha, (2 * t) * 4), ah = __shfl_sync(0xffffffffu, alpha, (2 * t + 1) * 4);
+    if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+#pragma unroll
+        for (int m = 0; m < NMT; ++m) { st.o[m][0] *= al; st.o[m][1] *= ah; st.o[m][2] *= al; st.o[m][3] *= ah; }
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {            // keys 16h .. 16h+15: one k-step of P.V
+        uint4 vv[4][NC];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const int kr = 16 * h + 2 * t + (r & 1) + (r >> 1) * 8;
+#pragma unroll
+            for (int c = 0; c < NC; ++c)
+                vv[r][c] = kr < nvalid ? attn_row8<KV8>(sV + kr * ROWB, c * 8 + g) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int c = 0; c < NC; ++c)
+#pragma unroll
+            for (int ep = 0; ep < 4; ++ep) {
+                const uint32_t wA = u4c(vv[0][c], ep), wB = u4c(vv[1][c], ep), wC = u4c(vv[2][c], ep), wD = u4c(vv[3][c], ep);
+                mma16816(st.o[c * 4 + ep], prmt(wA, wB, 0x5410), prmt(wA, wB, 0x7632), prmt(wC, wD, 0x5410), prmt(wC, wD, 0x7632), pb[2 * h], pb[2 * h + 1]);
+            }
+    }
+}
+
 // Spill a warp's state to shared memory for the merge of the CTA's warps: o_w [kMaxGroup][HD], ml_w [kMaxGroup][2].
 template <int HD>
 __device__ __forceinline__ void attn_state_to_smem(AttnState<HD>& st, float* o_w, float* ml_w, int g, int t) {

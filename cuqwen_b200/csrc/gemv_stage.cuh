@@ -216,7 +216,7 @@ __device__ __forceinline__ void digits_of_chunk(uint4 v, int c8, bool live, unsi
 // one 128-column group, as digits_of_chunk wants.
 template <int Q, int NB>
 __device__ __forceinline__ void stage_x_regs(const __half* x, const __half* norm_w, float eps, int K, unsigned char* xd, int* corr, float* xscale,
-                                             float* red, int nthreads, unsigned long long* trace = nullptr, const GatherSrc* gs = nullptr) {
+                                             float* red, int nthreads, unsigned long long* trace = nullptr) {
     const int nchunk = K / 8;
     uint4 v[NB], w[NB];
 #pragma unroll
@@ -226,17 +226,6 @@ __device__ __forceinline__ void stage_x_regs(const __half* x, const __half* norm
         if (c8 < nchunk) {
             v[i] = __ldcg(reinterpret_cast<const uint4*>(x) + c8);
             if (norm_w) w[i] = __ldg(reinterpret_cast<const uint4*>(norm_w) + c8);
-        }
-    }
-    if (gs) {      // tensor parallel: x plus the partials the ranks pushed (same words, same order as tp_sum_kernel)
-        bool gave_up = false;
-#pragma unroll
-        for (int i = 0; i < NB; ++i) {
-            const int c8 = i * nthreads + threadIdx.x;
-            if (c8 < nchunk) {
-                v[i] = gather_chunk(*gs, K, c8, v[i], gave_up);
-                if (gs->store_next) reinterpret_cast<uint4*>(gs->x_next)[c8] = v[i];
-            }
         }
     }
     if (norm_w) {
@@ -274,9 +263,11 @@ __device__ __forceinline__ bool stage_x(const __half* x, const __half* norm_w, f
     uint4* wraw = raw + nchunk;
     const bool w_parked = norm_w && 4 * K <= xarea_bytes;
     const bool gather = gs && gs->n > 0;
-    if (nchunk <= 3 * nthreads && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (!norm_w || (reinterpret_cast<uintptr_t>(norm_w) & 15) == 0)) {
-        if (nchunk <= 2 * nthreads) stage_x_regs<Q, 2>(x, norm_w, eps, K, xd, corr, xscale, red, nthreads, trace, gather ? gs : nullptr);
-        else stage_x_regs<Q, 3>(x, norm_w, eps, K, xd, corr, xscale, red, nthreads, trace, gather ? gs : nullptr);
+    // (The tensor-parallel gather stays out of the register path: inlined there it raised every GEMV kernel from 96-110
+    // to 124-126 registers, which ends two CTAs sharing an SM - 690 -> 570 tok/s on one GPU.)
+    if (!gather && nchunk <= 3 * nthreads && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (!norm_w || (reinterpret_cast<uintptr_t>(norm_w) & 15) == 0)) {
+        if (nchunk <= 2 * nthreads) stage_x_regs<Q, 2>(x, norm_w, eps, K, xd, corr, xscale, red, nthreads, trace);
+        else stage_x_regs<Q, 3>(x, norm_w, eps, K, xd, corr, xscale, red, nthreads, trace);
         return false;
     }
     const bool bulk = bar_x != 0u && !gather && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (!norm_w || (w_parked && (reinterpret_cast<uintptr_t>(norm_w) & 15) == 0));
