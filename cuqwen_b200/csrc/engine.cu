@@ -21,6 +21,7 @@
 #include "errors.h"
 #include "gemv.cuh"
 #include "launch.h"
+#include "prefill_gemm.cuh"
 #include "tp_plan.h"
 
 using namespace cq;
@@ -996,6 +997,19 @@ extern "C" int cuqwen_k_attention_kv8(int device, const void* q, void* kc8, void
     a.part_o = (float*)so; a.part_ml = (float*)sml; a.err = t_err;
     a.kscale = kscale; a.vscale = vscale; a.k_cur = (const __half*)k_cur; a.v_cur = (const __half*)v_cur;
     KK(launch_attn(hd, a, cfg)); return CUQWEN_OK;
+}
+extern "C" int cuqwen_k_prefill_gemm(int device, int quant, int mode, const void* x, const void* w0, const void* s0, const void* w1, const void* s1,
+                                     const void* bias, void* out, int n_tokens, int rows, int cols, int out_stride) {
+    DEV(device); (void)cfg;
+    if (bad_q(quant)) return fail(CUQWEN_ERR_ARG, "quant out of range");
+    if (mode < PF_OUT_F16 || mode > PF_SWIGLU) return fail(CUQWEN_ERR_ARG, "mode out of range");
+    NOT_NULL(x, w0, out); SCALES_OK(quant, s0);
+    if (mode == PF_SWIGLU) { NOT_NULL(w1); SCALES_OK(quant, s1); }
+    else if (w1) return fail(CUQWEN_ERR_ARG, "a second matrix only in the SwiGLU mode");
+    PfGemmArgs a; memset(&a, 0, sizeof a);
+    a.s[0] = (const __half*)s0; a.s[1] = (const __half*)s1; a.bias = (const __half*)bias;
+    a.out_h = (__half*)out; a.out_f = (float*)out; a.T = n_tokens; a.R = rows; a.K = cols; a.ldo = out_stride; a.mode = mode; a.err = t_err;
+    KK(launch_prefill_gemm(quant, a, x, w0, w1, dc->stream)); return CUQWEN_OK;
 }
 extern "C" int cuqwen_k_gemv_add(int device, int quant, const void* w, const void* s, const void* in, void* x, int rows, int cols) {
     DEV(device); if (bad_q(quant)) return fail(CUQWEN_ERR_ARG, "quant out of range");

@@ -1,0 +1,319 @@
+// The batched-token GEMM kernel and its launcher (see prefill_gemm.cuh for the design).
+#include "prefill_gemm.cuh"
+
+#include <mutex>
+#include <vector>
+
+namespace cq {
+
+// ---- tcgen05 / tensor-memory primitives (inline PTX) ----------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+// D[tmem] (+)= A[smem desc] * B[smem desc]; fp16 inputs, fp32 accumulation.
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+                 ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// The mbarrier receives one arrival when every MMA issued so far by this thread has finished.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// 32 consecutive fp32 columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
+                   "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+                   "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void sts128(uint32_t addr, uint4 v) {
+    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile in the 128-byte-swizzled canonical layout: rows of 128 bytes,
+// eight-row groups 1024 bytes apart.  Fields: start address >> 4 [0,14), leading byte offset >> 4 [16,30) (unused by
+// swizzled K-major tiles), stride byte offset >> 4 [32,46), descriptor version 1 [46,48), layout type 2 = 128-byte
+// swizzle [61,64).
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+    return (uint64_t)((smem_addr >> 4) & 0x3fffu) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor: D fp32 [4,6) = 1, A and B fp16 (0), both K-major (0), N >> 3 at [17,23), M >> 4 at [24,29).
+constexpr uint32_t kPfIdesc = (1u << 4) | ((uint32_t)(kPfN >> 3) << 17) | ((uint32_t)(kPfM >> 4) << 24);
+
+// 64 weights of one row -> eight 16-byte chunks of fp16(q * scale), stored at the row's swizzled places.
+template <int Q>
+__device__ __forceinline__ void convert_row(uint32_t raw, uint32_t brow, int sw, __half2 sc2) {
+    if (Q == Q_I4) {
+        // two's-complement nibbles, element 2p in the low nibble of byte p: (n ^ 8) | 0x6400 is fp16(1024 + q + 8)
+        const __half2 off = __floats2half2_rn(1032.f, 1032.f);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const uint4 rw = lds128(raw + h * 16);
+            const uint32_t w4[4] = {rw.x, rw.y, rw.z, rw.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint32_t w = w4[i];
+                uint32_t t[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const uint32_t u = ((w >> (4 * j)) & 0x000f000fu) ^ 0x64086408u;          // (element j, element j + 4)
+                    const __half2 hv = __hmul2(__hsub2(*reinterpret_cast<const __half2*>(&u), off), sc2);
+                    t[j] = *reinterpret_cast<const uint32_t*>(&hv);
+                }
+                uint4 o;
+                o.x = __byte_perm(t[0], t[1], 0x5410); o.y = __byte_perm(t[2], t[3], 0x5410);
+                o.z = __byte_perm(t[0], t[1], 0x7632); o.w = __byte_perm(t[2], t[3], 0x7632);
+                sts128(brow + (((h * 4 + i) ^ sw) << 4), o);
+            }
+        }
+    } else {
+        // signed bytes: (b ^ 0x80) under a 0x64 exponent byte is fp16(1024 + b + 128)
+        const __half2 off = __floats2half2_rn(1152.f, 1152.f);
+#pragma unroll
+        for (int h = 0; h < 4; ++h) {
+            const uint4 rw = lds128(raw + h * 16);
+            const uint32_t w4[4] = {rw.x, rw.y, rw.z, rw.w};
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                uint32_t t[4];
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const uint32_t x = w4[2 * i + j] ^ 0x80808080u;
+                    const uint32_t lo = __byte_perm(x, 0x64646464u, 0x4140), hi = __byte_perm(x, 0x64646464u, 0x4342);
+                    const __half2 a = __hmul2(__hsub2(*reinterpret_cast<const __half2*>(&lo), off), sc2);
+                    const __half2 b = __hmul2(__hsub2(*reinterpret_cast<const __half2*>(&hi), off), sc2);
+                    t[2 * j] = *reinterpret_cast<const uint32_t*>(&a); t[2 * j + 1] = *reinterpret_cast<const uint32_t*>(&b);
+                }
+                sts128(brow + (((h * 2 + i) ^ sw) << 4), make_uint4(t[0], t[1], t[2], t[3]));
+            }
+        }
+    }
+}
+
+template <int Q>
+__global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const __grid_constant__ PfGemmArgs a) {
+    extern __shared__ unsigned char pf_smem_raw[];
+    const uint32_t base = (smem_u32(pf_smem_raw) + 1023u) & ~1023u;
+    const uint32_t bars = base + kPfStages * kPfStageBytes;
+    const uint32_t bar_full = bars, bar_conv = bars + 8 * kPfStages, bar_empty = bars + 16 * kPfStages, bar_done = bars + 24 * kPfStages;
+    const uint32_t tmem_slot = bar_done + 8;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tm = blockIdx.x, tn = blockIdx.y;
+    const bool swiglu = a.mode == PF_SWIGLU;
+    const int rows_mat = swiglu ? kPfN / 2 : kPfN;            // rows of each matrix in this tile
+    const int nmat = swiglu ? 2 : 1;
+    const int row0 = tn * rows_mat;
+    const int nkb = a.K / kPfKB;
+    constexpr int kRawKb = Q == Q_I4 ? 32 : 64;               // raw bytes of one row in one K block
+    bool failed = false;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kPfStages; ++s) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_conv + 8 * s, kPfConvWarps); mbar_init(bar_empty + 8 * s, 1); }
+        mbar_init(bar_done, 1);
+        mbar_fence_init();
+    }
+    if (warp == 1) { tmem_alloc(tmem_slot, kPfN); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = lds32(tmem_slot);
+
+    if (warp == 0) {
+        if (lane == 0) {
+            const uint32_t wbytes = Q == Q_F16 ? (uint32_t)kPfBBytes : (uint32_t)(kPfN * kRawKb);
+            for (int kb = 0; kb < nkb && !failed; ++kb) {
+                const int s = kb % kPfStages; const uint32_t ph = (uint32_t)(kb / kPfStages) & 1u;
+                if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u)) { failed = true; break; }
+                const uint32_t st = base + s * kPfStageBytes;
+                mbar_expect_tx(bar_full + 8 * s, (uint32_t)kPfABytes + wbytes);
+                tma_load_2d(st, &a.tx, kb * kPfKB, tm * kPfM, bar_full + 8 * s);
+                for (int m = 0; m < nmat; ++m) {
+                    if (Q == Q_F16) tma_load_2d(st + kPfABytes + m * rows_mat * 128, &a.tw[m], kb * kPfKB, row0, bar_full + 8 * s);
+                    else tma_load_2d(st + kPfABytes + kPfBBytes + m * rows_mat * kRawKb, &a.tw[m], kb * kRawKb, row0, bar_full + 8 * s);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            for (int kb = 0; kb < nkb && !failed; ++kb) {
+                const int s = kb % kPfStages; const uint32_t ph = (uint32_t)(kb / kPfStages) & 1u;
+                if (!mbar_wait(bar_full + 8 * s, ph)) { failed = true; break; }
+                if (Q != Q_F16 && !mbar_wait(bar_conv + 8 * s, ph)) { failed = true; break; }
+                tc_fence_after();
+                const uint32_t st = base + s * kPfStageBytes;
+#pragma unroll
+                for (int k4 = 0; k4 < kPfKB / 16; ++k4)
+                    umma_f16(tmem, umma_desc(st + k4 * 32), umma_desc(st + kPfABytes + k4 * 32), kPfIdesc, (uint32_t)((kb | k4) != 0));
+                umma_commit(bar_empty + 8 * s);            // the stage may be refilled once these MMAs have read it
+            }
+            umma_commit(bar_done);
+        }
+    } else {
+        const int c = threadIdx.x - 64;                       // B row of this thread, 0..255
+        const int mat = swiglu ? c >> 7 : 0, rin = swiglu ? c & 127 : c;
+        const int grow = row0 + rin;
+        const bool valid = grow < a.R;
+        if (Q != Q_F16) {
+            const int ngrp = a.K / kGroup;
+            const __half* srow = a.s[mat] + (size_t)(valid ? grow : 0) * ngrp;
+            __half sc = valid ? srow[0] : __float2half(0.f);
+            for (int kb = 0; kb < nkb && !failed; ++kb) {
+                const int s = kb % kPfStages; const uint32_t ph = (uint32_t)(kb / kPfStages) & 1u;
+                const __half sc_use = sc;
+                if ((kb & 1) && kb + 1 < nkb) sc = valid ? srow[(kb + 1) >> 1] : sc;       // the next group's scale, ahead of its use
+                if (!mbar_wait(bar_full + 8 * s, ph)) { failed = true; break; }
+                const uint32_t st = base + s * kPfStageBytes;
+                convert_row<Q == Q_F16 ? Q_I8 : Q>(st + kPfABytes + kPfBBytes + c * kRawKb, st + kPfABytes + c * 128, c & 7, __half2half2(sc_use));
+                fence_async_smem();                            // the tensor core reads through the async proxy
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_conv + 8 * s);
+            }
+        }
+        // epilogue: TMEM lane = token, column = weight row of the tile
+        if (!failed && !mbar_wait(bar_done, 0u)) failed = true;
+        tc_fence_after();
+        if (!failed) {
+            const int q = warp & 3, hh = (warp - 2) >> 2;
+            const int token = tm * kPfM + q * 32 + lane;
+            const bool tv = token < a.T;
+            const uint32_t tlane = tmem + ((uint32_t)(q * 32) << 16);
+            if (!swiglu) {
+#pragma unroll 1
+                for (int ch = 0; ch < 4; ++ch) {
+                    const int col = hh * 128 + ch * 32;
+                    float v[32];
+                    tmem_ld32(tlane + (uint32_t)col, v);
+                    const int r = row0 + col;
+                    if (tv && r < a.R) {
+                    if (a.mode == PF_OUT_F32) {
+                        float* dst = a.out_f + (size_t)token * a.ldo + r;
+#pragma unroll
+                        for (int i = 0; i < 32; i += 4) if (r + i < a.R) *reinterpret_cast<float4*>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                    } else {
+                        __half* dst = a.out_h + (size_t)token * a.ldo + r;
+#pragma unroll
+                        for (int i = 0; i < 32; i += 8) {
+                            if (r + i >= a.R) break;
+                            float add[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                            if (a.mode == PF_RESID) {
+                                const uint4 o = *reinterpret_cast<const uint4*>(dst + i);
+                                const __half2* oh = reinterpret_cast<const __half2*>(&o);
+#pragma unroll
+                                for (int k = 0; k < 4; ++k) { const float2 f = __half22float2(oh[k]); add[2 * k] = f.x; add[2 * k + 1] = f.y; }
+                            } else if (a.bias) {
+                                const uint4 o = *reinterpret_cast<const uint4*>(a.bias + r + i);
+                                const __half2* oh = reinterpret_cast<const __half2*>(&o);
+#pragma unroll
+                                for (int k = 0; k < 4; ++k) { const float2 f = __half22float2(oh[k]); add[2 * k] = f.x; add[2 * k + 1] = f.y; }
+                            }
+                            uint4 o;
+                            __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) oh[k] = __floats2half2_rn(add[2 * k] + v[i + 2 * k], add[2 * k + 1] + v[i + 2 * k + 1]);
+                            *reinterpret_cast<uint4*>(dst + i) = o;
+                        }
+                    }
+                    }
+                    __syncwarp();
+                }
+            } else {
+#pragma unroll 1
+                for (int ch = 0; ch < 2; ++ch) {
+                    const int col = hh * 64 + ch * 32;
+                    float g[32], u[32];
+                    tmem_ld32(tlane + (uint32_t)col, g);
+                    tmem_ld32(tlane + (uint32_t)(128 + col), u);
+                    const int r = row0 + col;
+                    __half* dst = a.out_h + (size_t)token * a.ldo + r;
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        if (!tv || r + i >= a.R) break;
+                        uint4 o;
+                        __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const float g0 = g[i + 2 * k], g1 = g[i + 2 * k + 1];
+                            const float s0 = __fdividef(1.0f, 1.0f + __expf(-g0)), s1 = __fdividef(1.0f, 1.0f + __expf(-g1));
+                            oh[k] = __floats2half2_rn(g0 * s0 * u[i + 2 * k], g1 * s1 * u[i + 2 * k + 1]);
+                        }
+                        *reinterpret_cast<uint4*>(dst + i) = o;
+                    }
+                    __syncwarp();
+                }
+            }
+        }
+    }
+    if (failed && a.err) atomicExch(a.err, 11u);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem, kPfN);
+}
+
+// ---- host side ------------------------------------------------------------------------------------------------------
+typedef CUresult (*PfEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                               const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static PfEncodeFn pf_encode() {
+    static PfEncodeFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) p = nullptr;
+        return (PfEncodeFn)p;
+    }();
+    return fn;
+}
+// Row-major 2-D map: `cols` elements a row (row pitch = cols * elem bytes), box box_cols x box_rows.
+static int pf_map(CUtensorMap* m, const void* p, CUtensorMapDataType dt, int elem, size_t rows, size_t cols, int box_cols, int box_rows, bool swizzle) {
+    PfEncodeFn fn = pf_encode();
+    if (!fn) return (int)cudaErrorNotSupported;
+    const cuuint64_t dims[2] = {cols, rows}, strides[1] = {cols * (size_t)elem};
+    const cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows}, estr[2] = {1, 1};
+    const CUresult r = fn(m, dt, 2, const_cast<void*>(p), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          swizzle ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
+template <int Q>
+static int pf_go(const PfGemmArgs& a, dim3 grid, cudaStream_t stream) {
+    static bool once = false;
+    if (!once) {
+        const cudaError_t e = cudaFuncSetAttribute(prefill_gemm_kernel<Q>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmemBytes);
+        if (e != cudaSuccess) return (int)e;
+        once = true;
+    }
+    prefill_gemm_kernel<Q><<<grid, kPfThreads, kPfSmemBytes, stream>>>(a);
+    return (int)cudaGetLastError();
+}
+
+int launch_prefill_gemm(int quant, PfGemmArgs& a, const void* x, const void* w0, const void* w1, cudaStream_t stream) {
+    if (a.T <= 0 || a.R <= 0 || a.K <= 0 || a.K % kGroup || a.R % 8 || a.ldo % 8 || quant < 0 || quant > 2) return (int)cudaErrorInvalidValue;
+    if ((a.mode == PF_SWIGLU) != (w1 != nullptr)) return (int)cudaErrorInvalidValue;
+    const int rows_mat = a.mode == PF_SWIGLU ? kPfN / 2 : kPfN;
+    if (int r = pf_map(&a.tx, x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (size_t)a.T, (size_t)a.K, kPfKB, kPfM, true)) return r;
+    const void* w[2] = {w0, w1};
+    for (int m = 0; m < (w1 ? 2 : 1); ++m) {
+        int r;
+        if (quant == Q_F16) r = pf_map(&a.tw[m], w[m], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (size_t)a.R, (size_t)a.K, kPfKB, rows_mat, true);
+        else {
+            const size_t rb = quant == Q_I4 ? (size_t)a.K / 2 : (size_t)a.K;
+            r = pf_map(&a.tw[m], w[m], CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (size_t)a.R, rb, quant == Q_I4 ? 32 : 64, rows_mat, false);
+        }
+        if (r) return r;
+    }
+    const dim3 grid((a.T + kPfM - 1) / kPfM, (a.R + rows_mat - 1) / rows_mat);
+    if (quant == Q_I4) return pf_go<Q_I4>(a, grid, stream);
+    if (quant == Q_I8) return pf_go<Q_I8>(a, grid, stream);
+    return pf_go<Q_F16>(a, grid, stream);
+}
+
+}  // namespace cq

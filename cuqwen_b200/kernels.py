@@ -68,6 +68,15 @@ def gqa_attention_decode_static(q, kcache, vcache, out, d_pos, n_heads, n_kv_hea
                                                head_dim, max_seq_len, n_splits))
 
 
+PF_OUT_F16, PF_OUT_F32, PF_RESID, PF_SWIGLU = 0, 1, 2, 3
+
+
+def prefill_gemm(quant, mode, x, w0, s0, out, n_tokens, rows, cols, out_stride=None, w1=None, s1=None, bias=None, device=0):
+    """cuqwen_k_prefill_gemm: out[t][r] = x[t] . W[r] for n_tokens rows at once on the tcgen05 tensor cores."""
+    check(_abi.lib().cuqwen_k_prefill_gemm(device, quant, mode, _p(x), _p(w0), _p(s0), _p(w1), _p(s1), _p(bias), _p(out), n_tokens, rows, cols,
+                                           rows if out_stride is None else out_stride))
+
+
 def gemv_add(quant, w, scale, inp, x_inout, rows, cols, device=0):
     check(_abi.lib().cuqwen_k_gemv_add(device, quant, _p(w), _p(scale), _p(inp), _p(x_inout), rows, cols))
 

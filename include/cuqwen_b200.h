@@ -193,6 +193,14 @@ int cuqwen_k_attention(int device, const void* q, const void* kcache, const void
 int cuqwen_k_attention_kv8(int device, const void* q, void* kcache8, void* vcache8, float* kscale, float* vscale, const void* k_cur, const void* v_cur,
                            void* out, const int* d_pos, int n_heads, int n_kv_heads, int head_dim, int max_seq_len, int n_splits,
                            void* scratch_o, void* scratch_ml);
+/* No counterpart in the reference, which prefills one token at a time through the decode kernels (src/main.cu:86-92;
+ * batched prefill is on its roadmap, README.md:145).  Batched-token GEMM on the tcgen05 tensor cores:
+ * out[t][r] = sum_k x[t][k] * W[r][k] for n_tokens rows of x ([n_tokens][cols] fp16) and a weight matrix in the model
+ * file's format (quant 0 fp16 / 1 int8 / 2 int4, scales [rows][cols / 128] fp16).  mode 0: fp16 output (+ bias[r]);
+ * 1: fp32 output; 2: out (fp16) += result, the residual add; 3: SwiGLU of two matrices, out = silu(W0 x) * (W1 x).
+ * out_stride = elements between consecutive tokens of out.  rows and out_stride are multiples of 8, cols of 128. */
+int cuqwen_k_prefill_gemm(int device, int quant, int mode, const void* x, const void* w0, const void* s0, const void* w1, const void* s1,
+                          const void* bias, void* out, int n_tokens, int rows, int cols, int out_stride);
 int cuqwen_attn_scratch_bytes(int n_kv_heads, int head_dim, int n_splits, size_t* bytes_o, size_t* bytes_ml, size_t* bytes_counters);
 /* No counterpart in the reference.  Same computation as cuqwen_k_attention for hosts that may not allocate device
  * memory any more (fixed memory budget, or code that must not stall the device's other streams on cudaMalloc):
