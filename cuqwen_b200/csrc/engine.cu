@@ -21,6 +21,7 @@
 #include "errors.h"
 #include "gemv.cuh"
 #include "launch.h"
+#include "prefill.cuh"
 #include "prefill_gemm.cuh"
 #include "tp_plan.h"
 
@@ -173,6 +174,8 @@ struct cuqwen_engine {
     __half* x2 = nullptr; bool tp_sum_separate = false;
     unsigned char* gate_xd = nullptr; int* gate_corr = nullptr; float* gate_xscale = nullptr;    // SwiGLU output in staged form (see GemvArgs::xd_out)
     unsigned char* att_xd = nullptr; int* att_corr = nullptr; float* att_xscale = nullptr;       // attention output in staged form (see AttnArgs::xd_out)
+    // batched prefill workspace (cuqwen_prefill), allocated at the first call for kPrefillChunk tokens
+    __half *pf_x = nullptr, *pf_xn = nullptr, *pf_q = nullptr, *pf_att = nullptr, *pf_g = nullptr; float* pf_qkv = nullptr; int* pf_tok = nullptr;
     int steps_done = 0;                          // mirrors the device-side step counter (StepCtl::pad[1])
     std::vector<cudaEvent_t>* prof = nullptr;    // cuqwen_step_profile: an event is recorded after every launch of the step
     unsigned long long* step_trace = nullptr; size_t step_trace_bytes = 0;     // CUQWEN_FLAG_STEP_TRACE: eight timeline words per launch (tma.cuh)
@@ -268,7 +271,8 @@ extern "C" void cuqwen_destroy(cuqwen_engine* e) {
     if (e->tp_rx) cudaFree(e->tp_rx);
     if (e->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(e->comm);
     void* bufs[] = {e->x, e->xn, e->q, e->k, e->v, e->att, e->gate, e->logits, e->kc, e->vc, e->part_o, e->part_ml, e->counters, e->ctl, e->d_hist,
-                    e->bitmap, e->best, e->ticket, e->out_ring, e->tp_partial, e->tp_keys, e->warena, e->step_trace, e->spare_up, e->spare_out, e->kscale, e->vscale, e->x2, e->gate_xd, e->gate_corr, e->gate_xscale, e->att_xd, e->att_corr, e->att_xscale};
+                    e->bitmap, e->best, e->ticket, e->out_ring, e->tp_partial, e->tp_keys, e->warena, e->step_trace, e->spare_up, e->spare_out, e->kscale, e->vscale, e->x2, e->gate_xd, e->gate_corr, e->gate_xscale, e->att_xd, e->att_corr, e->att_xscale,
+                    e->pf_x, e->pf_xn, e->pf_q, e->pf_att, e->pf_g, e->pf_qkv, e->pf_tok};
     for (void* b : bufs) if (b) cudaFree(b);
     if (e->h_ctl) cudaFreeHost(e->h_ctl);
     if (e->h_out) cudaFreeHost(e->h_out);
@@ -631,6 +635,79 @@ extern "C" int cuqwen_step(cuqwen_engine* e, int token, int pos, const int* hist
     CK(cudaStreamSynchronize(e->stream));
     if (e->h_out[1]) return fail(CUQWEN_ERR_TIMEOUT, "a bounded device-side wait expired (code %d)", e->h_out[1]);
     if (out_token) *out_token = e->h_out[0];
+    return CUQWEN_OK;
+}
+
+// ---------------------------------------------------------------------------
+// batched prefill: the prompt's tokens go through every layer as tiles, the KV cache rows [pos0, pos0 + n) come out.
+// The reference runs qwen_forward once per prompt token for the same effect (src/main.cu:86-92).
+// ---------------------------------------------------------------------------
+constexpr int kPrefillChunk = 2048;
+#define PK(call) do { int r_ = (call); if (r_) return fail(r_ == (int)cudaErrorInvalidValue ? CUQWEN_ERR_ARG : CUQWEN_ERR_CUDA, "%s: %s", #call, cudaGetErrorString((cudaError_t)r_)); } while (0)
+
+static int prefill_gemm(cuqwen_engine* e, int mode, const __half* x, const Mat& w0, const Mat* w1, void* out, int T, int ldo) {
+    PfGemmArgs a; memset(&a, 0, sizeof a);
+    a.s[0] = w0.s; a.s[1] = w1 ? w1->s : nullptr; a.out_h = (__half*)out; a.out_f = (float*)out;
+    a.T = T; a.R = w0.rows; a.K = w0.cols; a.ldo = ldo; a.mode = mode; a.err = t_err;
+    PK(launch_prefill_gemm(e->p.quant, a, x, w0.w, w1 ? w1->w : nullptr, e->stream));
+    return CUQWEN_OK;
+}
+
+extern "C" int cuqwen_prefill(cuqwen_engine* e, const int* tokens, int n_tokens, int pos0) {
+    if (!e || !tokens) return fail(CUQWEN_ERR_ARG, "null argument");
+    if (!e->loaded) return fail(CUQWEN_ERR_STATE, "cuqwen_prefill before cuqwen_load");
+    if (e->tp > 1) return fail(CUQWEN_ERR_ARG, "cuqwen_prefill runs on one GPU (tp_size 1); feed the prompt through cuqwen_step on tensor-parallel engines");
+    if (e->kv8) return fail(CUQWEN_ERR_ARG, "cuqwen_prefill writes the fp16 KV cache; not available with CUQWEN_FLAG_KV_INT8");
+    const cuqwen_params& p = e->p;
+    if (n_tokens < 1 || pos0 < 0 || pos0 + n_tokens > p.max_seq_len) return fail(CUQWEN_ERR_ARG, "prefill range [%d, %d) outside the cache", pos0, pos0 + n_tokens);
+    if (p.head_dim != 64 && p.head_dim != 128) return fail(CUQWEN_ERR_ARG, "cuqwen_prefill supports head_dim 64 and 128");
+    for (int i = 0; i < n_tokens; ++i) if (tokens[i] < 0 || tokens[i] >= p.vocab_size) return fail(CUQWEN_ERR_ARG, "token %d out of range", tokens[i]);
+    CK(cudaSetDevice(p.device));
+    t_err = reinterpret_cast<unsigned*>(&e->ctl->pad[0]);
+    const int qd = e->q_dim_l, kd = e->kv_dim_l, C = kPrefillChunk;
+    if (!e->pf_x) {
+        CK(cudaMalloc((void**)&e->pf_x, (size_t)C * p.dim * 2)); CK(cudaMalloc((void**)&e->pf_xn, (size_t)C * p.dim * 2));
+        CK(cudaMalloc((void**)&e->pf_qkv, (size_t)C * (qd + 2 * kd) * 4)); CK(cudaMalloc((void**)&e->pf_q, (size_t)C * qd * 2));
+        CK(cudaMalloc((void**)&e->pf_att, (size_t)C * qd * 2)); CK(cudaMalloc((void**)&e->pf_g, (size_t)C * e->inter_l * 2));
+        CK(cudaMalloc((void**)&e->pf_tok, (size_t)C * 4));
+    }
+    const size_t kv_layer = (size_t)e->n_kv_l * p.max_seq_len * p.head_dim;
+    const float eps = __half2float(__float2half(p.norm_eps));
+    const int ldqkv = qd + 2 * kd;
+    CK(cudaMemsetAsync(&e->ctl->pad[0], 0, 4, e->stream));
+    CK(cudaEventRecord(e->ev0, e->stream));
+    for (int c0 = 0; c0 < n_tokens; c0 += C) {
+        const int T = n_tokens - c0 < C ? n_tokens - c0 : C, pos = pos0 + c0;
+        CK(cudaMemcpyAsync(e->pf_tok, tokens + c0, (size_t)T * 4, cudaMemcpyHostToDevice, e->stream));
+        PK(launch_pf_embed(e->embed, e->pf_tok, e->pf_x, T, p.dim, e->stream));
+        for (int l = 0; l < p.n_layers; ++l) {
+            const Layer& L = e->layers[l];
+            PK(launch_pf_rmsnorm(e->pf_x, L.in_norm, e->pf_xn, T, p.dim, eps, e->stream));
+            if (int r = prefill_gemm(e, PF_OUT_F32, e->pf_xn, L.q, nullptr, e->pf_qkv, T, ldqkv)) return r;
+            if (int r = prefill_gemm(e, PF_OUT_F32, e->pf_xn, L.k, nullptr, e->pf_qkv + qd, T, ldqkv)) return r;
+            if (int r = prefill_gemm(e, PF_OUT_F32, e->pf_xn, L.v, nullptr, e->pf_qkv + qd + kd, T, ldqkv)) return r;
+            PfRopeArgs ra; memset(&ra, 0, sizeof ra);
+            ra.qkv = e->pf_qkv; ra.bq = L.bq; ra.bk = L.bk; ra.bv = L.bv; ra.q_out = e->pf_q;
+            ra.kcache = e->kc + l * kv_layer; ra.vcache = e->vc + l * kv_layer;
+            ra.pos0 = pos; ra.n_heads = e->n_heads_l; ra.n_kv = e->n_kv_l; ra.hd = p.head_dim; ra.q_dim = qd; ra.kv_dim = kd; ra.max_seq = p.max_seq_len;
+            ra.rope_fast = (p.flags & CUQWEN_FLAG_ACCURATE_ROPE) ? 0 : 1; ra.theta = p.rope_theta;
+            PK(launch_pf_rope_kv(ra, T, e->stream));
+            if (l == p.n_layers - 1) break;              // the last layer's keys and values are stored: nothing after them feeds the cache
+            PfAttnArgs aa; memset(&aa, 0, sizeof aa);
+            aa.q = e->pf_q; aa.kc = ra.kcache; aa.vc = ra.vcache; aa.out = e->pf_att; aa.T = T; aa.pos0 = pos; aa.n_heads = e->n_heads_l;
+            aa.grp = e->plan.grp; aa.max_seq = p.max_seq_len; aa.ldq = qd; aa.scale_log2 = (1.0f / sqrtf((float)p.head_dim)) * 1.4426950408889634f;
+            PK(launch_prefill_attn(p.head_dim, aa, e->stream));
+            if (int r = prefill_gemm(e, PF_RESID, e->pf_att, L.o, nullptr, e->pf_x, T, p.dim)) return r;
+            PK(launch_pf_rmsnorm(e->pf_x, L.post_norm, e->pf_xn, T, p.dim, eps, e->stream));
+            if (int r = prefill_gemm(e, PF_SWIGLU, e->pf_xn, L.gate, &L.up, e->pf_g, T, e->inter_l)) return r;
+            if (int r = prefill_gemm(e, PF_RESID, e->pf_g, L.down, nullptr, e->pf_x, T, p.dim)) return r;
+        }
+    }
+    CK(cudaEventRecord(e->ev1, e->stream));
+    CK(cudaMemcpyAsync(e->h_out, &e->ctl->pad[0], 4, cudaMemcpyDeviceToHost, e->stream));
+    CK(cudaStreamSynchronize(e->stream));
+    if (e->h_out[0]) return fail(CUQWEN_ERR_TIMEOUT, "a bounded device-side wait expired (code %d)", e->h_out[0]);
+    CK(cudaEventElapsedTime(&e->last_ms, e->ev0, e->ev1));
     return CUQWEN_OK;
 }
 

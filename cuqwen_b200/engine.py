@@ -150,6 +150,11 @@ class Engine:
         check(_abi.lib().cuqwen_decode_n(self._h, first_token, start_pos, n, out.ctypes.data_as(C.POINTER(C.c_int))))
         return out
 
+    def prefill(self, tokens, pos0: int = 0) -> None:
+        """cuqwen_prefill: the KV cache rows [pos0, pos0 + len(tokens)) of these prompt tokens, computed as batched tiles."""
+        t = np.ascontiguousarray(tokens, dtype=np.int32)
+        check(_abi.lib().cuqwen_prefill(self._h, t.ctypes.data_as(C.POINTER(C.c_int)), int(t.size), pos0))
+
     @property
     def last_decode_ms(self) -> float:
         return float(_abi.lib().cuqwen_last_decode_ms(self._h))

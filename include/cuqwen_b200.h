@@ -83,6 +83,14 @@ int cuqwen_step(cuqwen_engine* e, int token, int pos, const int* history, int hi
 /* n greedy steps with the sampled token fed back on the device (no counterpart in the reference, which pays
  * a host round trip per token, src/main.cu:95-112).  out_tokens receives n ids.  history_len = 0 semantics. */
 int cuqwen_decode_n(cuqwen_engine* e, int first_token, int start_pos, int n, int* out_tokens);
+/* Batched prefill (no counterpart in the reference: src/main.cu:86-92 calls qwen_forward once per prompt token and
+ * throws the logits away; README.md:145 lists the batched form as future work).  Runs n_tokens prompt tokens
+ * (host array) through every layer as 128-token tiles - tcgen05 GEMMs over the quantised weights, causal attention
+ * over the cache - and leaves their keys and values in cache rows [pos0, pos0 + n_tokens), as n_tokens calls of
+ * cuqwen_step at positions pos0.. would.  Produces no logits: feed the prompt's last token to cuqwen_step
+ * afterwards (prefill the tokens before it).  One GPU, fp16 KV cache, head_dim 64 or 128.  The device time is
+ * readable through cuqwen_last_decode_ms. */
+int cuqwen_prefill(cuqwen_engine* e, const int* tokens, int n_tokens, int pos0);
 /* Milliseconds the device spent in the last cuqwen_decode_n (CUDA events around the n graph launches). */
 float cuqwen_last_decode_ms(const cuqwen_engine* e);
 

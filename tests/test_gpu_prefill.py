@@ -69,3 +69,75 @@ def test_prefill_gemm_swiglu(built, quant, T, R, Kc):
     sync()
     got = out.numpy(np.float16).reshape(T, R)
     assert close(got, want), report(got, want)
+
+
+CFGS = {
+    "hd128": dict(vocab=2048, dim=512, inter=1280, layers=3, heads=4, kv=2, hd=128, tied=False),
+    "hd64": dict(vocab=1024, dim=256, inter=768, layers=4, heads=4, kv=2, hd=64, tied=True),
+}
+
+
+@pytest.mark.parametrize("quant", [2, 1, 0])
+@pytest.mark.parametrize("name", ["hd128", "hd64"])
+def test_prefill_fills_the_cache_like_token_by_token_steps(built, tmp_path, quant, name):
+    """Engine level: cuqwen_prefill over a prompt (two calls, the second continuing at pos0 > 0 over the first one's
+    rows) against the same prompt fed through cuqwen_step: cache rows close, and the decode step that follows sees
+    the same distribution."""
+    from cuqwen_b200 import engine as E
+    cfg = CFGS[name]
+    path = tmp_path / "m.bin"
+    binfmt.write_model(path, cfg, quant, binfmt.random_tensors(cfg, 11))
+    max_seq = 512
+
+    def make():
+        prm = E.custom_params(cfg["vocab"], cfg["dim"], cfg["inter"], cfg["layers"], cfg["heads"], cfg["kv"], cfg["hd"], quant, max_seq_len=max_seq)
+        e = E.Engine(prm)
+        e.load(str(path))
+        return e
+
+    rng = np.random.default_rng(5)
+    n1, n2 = 200, 77
+    toks = rng.integers(0, cfg["vocab"], size=n1 + n2 + 1).astype(np.int32)
+    a, b = make(), make()
+    for i in range(n1 + n2):
+        a.step(int(toks[i]), i)
+    b.prefill(toks[:n1], 0)
+    b.prefill(toks[n1:n1 + n2], n1)
+    n = n1 + n2
+    shape = (cfg["layers"], cfg["kv"], max_seq, cfg["hd"])
+    for which in ("KEY_CACHE", "VALUE_CACHE"):
+        ca = a.read(which).reshape(shape).astype(np.float64)
+        cb = b.read(which).reshape(shape).astype(np.float64)
+        assert np.isfinite(cb).all()
+        assert not cb[:, :, n:].any(), "rows past the prompt were written"
+        for l in range(cfg["layers"]):
+            rms = np.sqrt(((ca[l, :, :n] - cb[l, :, :n]) ** 2).mean()) / np.sqrt((ca[l, :, :n] ** 2).mean())
+            print(f"{which} layer {l}: rel rms {rms:.2e}")
+            assert rms < 6e-3, f"{which} layer {l}: rel rms {rms:.3e}"
+        assert close(cb[:, :, :n], ca[:, :, :n], rtol=2e-2, atol=3e-2), report(cb[:, :, :n], ca[:, :, :n])
+    ta, tb = a.step(int(toks[n]), n), b.step(int(toks[n]), n)
+    la, lb = a.read("LOGITS").astype(np.float64), b.read("LOGITS").astype(np.float64)
+    rms = np.sqrt(((la - lb) ** 2).mean()) / np.sqrt((la ** 2).mean())
+    print(f"logits after the prompt: rel rms {rms:.2e}, tokens {ta} / {tb}")
+    assert rms < 1.5e-2
+    assert ta == tb or abs(la[ta] - la[tb]) <= 2e-3 * abs(la[ta]) + 1e-2
+    a.close(); b.close()
+
+
+def test_prefill_rejects_what_it_cannot_do(built, tmp_path):
+    from cuqwen_b200 import engine as E
+    from cuqwen_b200._abi import CuQwenError
+    cfg = CFGS["hd128"]
+    path = tmp_path / "m.bin"
+    binfmt.write_model(path, cfg, 2, binfmt.random_tensors(cfg, 11))
+    prm = E.custom_params(cfg["vocab"], cfg["dim"], cfg["inter"], cfg["layers"], cfg["heads"], cfg["kv"], cfg["hd"], 2, max_seq_len=256)
+    e = E.Engine(prm)
+    e.load(str(path))
+    with pytest.raises(CuQwenError):
+        e.prefill(np.zeros(300, np.int32), 0)            # runs past the cache
+    with pytest.raises(CuQwenError):
+        e.prefill(np.array([cfg["vocab"]], np.int32), 0)  # token out of range
+    with pytest.raises(CuQwenError):
+        e.prefill(np.array([1, 2], np.int32), -1)
+    e.prefill(np.array([1, 2, 3], np.int32), 0)           # and the engine still works
+    e.close()
