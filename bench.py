@@ -458,6 +458,7 @@ def run_sweep(a):
     """Kernel-level measurements of the other benchmark configurations, one JSON line each:
       --sweep gemv       the single W4A16 GEMV at the Qwen2.5-0.5B MLP shape (4864 x 896), HBM-cold and L2-warm
       --sweep attention  split-KV attention alone over lengths {512, 2K, 8K, 32K} x heads {28/4, 40/8} x split counts
+      --sweep prefill    a prompt of --prompt tokens through cuqwen_prefill (batched tiles) against the token-by-token path
     --impl reference times the reference's own kernels (launch_gemv_add_fp16 on a zeroed accumulator, src/kernels.cu:640-687;
     launch_gqa_attention_decode with its fixed 64 partitions, :290-323) in C loops inside oracle/_ref."""
     if int(os.environ.get("RANK", "0")) != 0:
@@ -467,6 +468,9 @@ def run_sweep(a):
     from cuqwen_b200 import microbench as MB
     rng = np.random.default_rng(1234)
     L2 = 126 << 20
+    if a.sweep == "prefill":
+        run_prefill_sweep(a, rng)
+        return
     if a.impl == "ours":
         if a.sweep == "gemv":
             rows = MB.single_gemv(4864, 896, "int4", 2000)
@@ -522,12 +526,74 @@ def run_sweep(a):
     emit({"sweep": a.sweep, "impl": "reference", "timing": "CUDA events around a C loop of launches", "rows": rows})
 
 
+def run_prefill_sweep(a, rng):
+    """Time to fill the KV cache for a prompt of a.prompt tokens (model a.model / a.quant, random token ids).
+    ours: cuqwen_prefill (device time between CUDA events, and wall clock around the call with the ids in host memory),
+    beside the same engine's token-by-token path.  --impl reference: the reference's only prefill, qwen_forward once per
+    prompt token (src/main.cu:86-92).  The token-by-token figures are estimates: 32 steps at each of four evenly spaced
+    positions, mean time per step times the prompt length."""
+    from cuqwen_b200 import binfmt
+    from cuqwen_b200 import engine as E
+    cfg = binfmt.MODELS[a.model]
+    path = ensure_model_file(a.model, a.quant)
+    n = a.prompt
+    spots = [n // 8, 3 * n // 8, 5 * n // 8, 7 * n // 8]
+    qid = E.QUANT_ID[a.quant]
+    d, I, nl, qd, kd = cfg["dim"], cfg["inter"], cfg["layers"], cfg["heads"] * cfg["hd"], cfg["kv"] * cfg["hd"]
+    gemm_flop = 2.0 * n * nl * (d * (qd + 2 * kd) + qd * d + 3 * d * I)
+    attn_flop = 4.0 * cfg["heads"] * cfg["hd"] * (n * (n + 1) / 2) * nl
+    if a.impl == "ours":
+        prm = E.model_params(a.model, a.quant)
+        prm.max_seq_len = max(n + 64, 1024)
+        eng = E.Engine(prm)
+        eng.load(str(path))
+        toks = rng.integers(0, cfg["vocab"], size=n).astype(np.int32)
+        eng.prefill(toks[:512], 0)                      # warm-up: workspace allocation, kernel attributes
+        with ClockSampler(0) as cs:
+            t0 = time.perf_counter()
+            eng.prefill(toks, 0)
+            wall = time.perf_counter() - t0
+        ms = eng.last_decode_ms
+        per_tok = []
+        for pos in spots:
+            eng.decode_n(1234 % cfg["vocab"], pos, 8)
+            eng.decode_n(1234 % cfg["vocab"], pos, 32)
+            per_tok.append(eng.last_decode_ms / 32)
+        est = float(np.mean(per_tok)) * n
+        emit({"sweep": "prefill", "impl": "ours", "model": a.model, "quant": a.quant, "prompt_tokens": n,
+              "prefill_ms": round(ms, 3), "prefill_wall_ms": round(wall * 1e3, 3), "prompt_tok_s": round(n / (ms / 1e3), 1),
+              "tflops": round((gemm_flop + attn_flop) / (ms / 1e3) / 1e12, 1), "gemm_flop": gemm_flop, "attention_flop": attn_flop,
+              "token_by_token_ms_estimate": round(est, 1), "token_by_token_ms_per_step_at": dict(zip(map(str, spots), [round(v, 4) for v in per_tok])),
+              "speedup_over_token_by_token": round(est / ms, 1), "clocks": cs.result})
+        eng.close()
+        return
+    from oracle import oracle_py as O
+    import ctypes as C
+    ref = O.ref_lib(a.model, a.quant)
+    if ref is None:
+        emit({"sweep": "prefill", "impl": "reference", "unavailable": "oracle/_ref not built"}); return
+    m = ref.ref_model_load(str(path).encode())
+    ref.ref_kv_fill_normal(m, n, SEED)
+    toks = (C.c_int * 64)()
+    per_tok = []
+    for pos in spots:
+        ref.ref_decode_n(m, 1234 % cfg["vocab"], pos, 8, toks)
+        per_tok.append(ref.ref_decode_n(m, 1234 % cfg["vocab"], pos, 32, toks) / 32)
+    ref.ref_model_free(m)
+    est = float(np.mean(per_tok)) * n
+    emit({"sweep": "prefill", "impl": "reference", "model": a.model, "quant": a.quant, "prompt_tokens": n,
+          "prefill_ms_estimate": round(est, 1), "prompt_tok_s": round(n / (est / 1e3), 1),
+          "ms_per_step_at": dict(zip(map(str, spots), [round(v, 4) for v in per_tok])),
+          "how": "qwen_forward once per prompt token (src/main.cu:86-92): 32 calls at each of four positions, mean x prompt length"})
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=16)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--prompt", type=int, default=8192, help="--sweep prefill: prompt length in tokens")
     ap.add_argument("--model", default="7b")
     ap.add_argument("--quant", default="int4")
     ap.add_argument("--ctx", type=int, default=8192)
@@ -536,7 +602,7 @@ def main():
     ap.add_argument("--kv", default="fp16", choices=["fp16", "int8"], help="KV cache format (int8: opt-in 8-bit cache, outside the parity contract)")
     ap.add_argument("--no-parity", action="store_true")
     ap.add_argument("--layers", type=int, default=0, help="cut the model to this many layers (profiler captures only; the JSON line says so)")
-    ap.add_argument("--sweep", default="", choices=["", "gemv", "attention"], help="kernel-level sweeps of the other benchmark configurations")
+    ap.add_argument("--sweep", default="", choices=["", "gemv", "attention", "prefill"], help="kernel-level sweeps of the other benchmark configurations")
     a = ap.parse_args()
     # Libraries (NCCL's version banner, for one) write to file descriptor 1.  Keep the real stdout aside for the one
     # JSON line and send everything else to stderr.

@@ -141,3 +141,54 @@ def test_prefill_rejects_what_it_cannot_do(built, tmp_path):
         e.prefill(np.array([1, 2], np.int32), -1)
     e.prefill(np.array([1, 2, 3], np.int32), 0)           # and the engine still works
     e.close()
+
+
+@pytest.mark.parametrize("model,quant,n", [("0.5b", "int4", 300), ("0.5b", "fp16", 130), ("7b", "int4", 384)])
+def test_prefill_vs_reference_build_token_by_token(built, tmpdir_big, model, quant, n):
+    """Against the reference's own CUDA build at full model size: the reference prefills by n calls of qwen_forward
+    (src/main.cu:86-92), this engine by one cuqwen_prefill; both then decode eight teacher-forced steps.  Bar: the
+    whole-step criterion (top-1 agreement within the fp16 contract on every step, rms logit difference <= 1.5 %)."""
+    import shutil
+    import subprocess
+    from cuqwen_b200 import build
+    from cuqwen_b200 import engine as E
+    from oracle import oracle_py as O
+    from tests.gpu_util import RTOL
+    ref = O.ref_lib(model, quant)
+    if ref is None:
+        pytest.skip("oracle/_ref not built")
+    cfg = binfmt.MODELS[model]
+    if shutil.disk_usage(tmpdir_big).free < binfmt.file_nbytes(cfg, binfmt.QUANT_ID[quant]) + (2 << 30):
+        pytest.skip("not enough room for the model file")
+    path = tmpdir_big / f"pf_{model}_{quant}.bin"
+    subprocess.run([str(build.GEN_BIN), "--out", str(path), "--model", model, "--quant", quant, "--seed", "42"], check=True)
+    V = cfg["vocab"]
+    rng = np.random.default_rng(9)
+    toks = rng.integers(0, V, size=n).astype(np.int32)
+    try:
+        prm = E.model_params(model, quant)
+        prm.max_seq_len = 1024
+        eng = E.Engine(prm)
+        eng.load(str(path))
+        rm = ref.ref_model_load(str(path).encode())
+        for i in range(n - 1):
+            ref.ref_forward(rm, int(toks[i]), i, None, 0)
+        eng.prefill(toks[:n - 1], 0)
+        tok, agree, worst = int(toks[n - 1]), 0, 0.0
+        steps = 8
+        for i in range(steps):
+            tok_r = ref.ref_forward(rm, tok, n - 1 + i, None, 0)
+            tok_e = eng.step(tok, n - 1 + i)
+            lr = E.download(0, ref.ref_state_ptr(rm, 0), np.float16, V).astype(np.float32)
+            le = eng.read("LOGITS").astype(np.float32)
+            assert np.isfinite(le).all()
+            d = le - lr
+            worst = max(worst, float(np.sqrt((d * d).mean()) / np.sqrt((lr * lr).mean())))
+            agree += tok_e == tok_r or abs(lr[tok_r] - lr[tok_e]) <= RTOL * abs(lr[tok_r]) + 1e-3
+            tok = tok_r
+        ref.ref_model_free(rm)
+        eng.close()
+    finally:
+        path.unlink()
+    print(f"{model} {quant}, prompt {n}: top-1 agreement {agree}/{steps}, rel rms of the logits {worst:.2e}")
+    assert agree == steps and worst <= 1.5e-2
