@@ -204,6 +204,13 @@ inline int qwen_forward(int token, int pos, const QwenConfig&, QwenState& s, con
     return next;
 }
 
+// Not in the reference (its chat loop calls qwen_forward once per prompt token, src/main.cu:86-92): the cache rows
+// [pos0, pos0 + n) of n prompt tokens in one batched pass.  Returns nothing to sample from - call qwen_forward on the
+// prompt's last token afterwards (prefill the tokens before it).
+inline void qwen_prefill(const int* tokens, int n, int pos0, const QwenConfig&, QwenState& s, const QwenWeights&) {
+    if (n > 0 && cuqwen_prefill(s.backend, tokens, n, pos0)) cuqwen_compat::die("qwen_prefill");
+}
+
 // ---- the launch_* operators (device pointers in the reference's layouts; work is queued on the library's stream of
 // device 0, cuqwen_dev_sync(0) waits for it; `stream` arguments are ignored) ----
 #define CUQWEN_K(call) do { if (call) cuqwen_compat::die(#call); } while (0)

@@ -16,6 +16,9 @@ int main(int argc, char** argv) {
     malloc_qwen_state(config, state);
     int tok = 1;
     for (int pos = 0; pos < 4; ++pos) tok = qwen_forward(tok, pos, config, state, weights);
+    const int more[3] = {5, 6, 7};
+    qwen_prefill(more, 3, 4, config, state, weights);              // the shim's batched prefill: cache rows 4..6
+    tok = qwen_forward(tok, 7, config, state, weights);
     launch_rmsnorm(state.x, weights.norm_weight, state.att, config.dim, __float2half(config.norm_eps));
     launch_gemv_add_fp16(weights.layers[0].o_proj_weight, weights.layers[0].o_proj_scale, state.xb, state.x, config.dim, config.n_heads * config.head_dim);
     launch_argmax(state.logits, state.d_sampled_token, config.vocab_size);
