@@ -534,17 +534,21 @@ def run_prefill_sweep(a, rng):
     positions, mean time per step times the prompt length."""
     from cuqwen_b200 import binfmt
     from cuqwen_b200 import engine as E
-    cfg = binfmt.MODELS[a.model]
-    path = ensure_model_file(a.model, a.quant)
+    cfg = model_config(a.model, a.layers)            # --layers cuts the depth for profiler captures (not a benchmark value)
+    path = ensure_model_file(a.model, a.quant, a.layers)
     n = a.prompt
     spots = [n // 8, 3 * n // 8, 5 * n // 8, 7 * n // 8]
     qid = E.QUANT_ID[a.quant]
     d, I, nl, qd, kd = cfg["dim"], cfg["inter"], cfg["layers"], cfg["heads"] * cfg["hd"], cfg["kv"] * cfg["hd"]
-    gemm_flop = 2.0 * n * nl * (d * (qd + 2 * kd) + qd * d + 3 * d * I)
-    attn_flop = 4.0 * cfg["heads"] * cfg["hd"] * (n * (n + 1) / 2) * nl
+    # the last layer stops once its keys and values are stored: it has no attention, o_proj or MLP in a prefill
+    gemm_flop = 2.0 * n * (nl * d * (qd + 2 * kd) + (nl - 1) * (qd * d + 3 * d * I))
+    attn_flop = 4.0 * cfg["heads"] * cfg["hd"] * (n * (n + 1) / 2) * (nl - 1)
     if a.impl == "ours":
-        prm = E.model_params(a.model, a.quant)
-        prm.max_seq_len = max(n + 64, 1024)
+        if a.layers:
+            prm = E.custom_params(cfg["vocab"], cfg["dim"], cfg["inter"], cfg["layers"], cfg["heads"], cfg["kv"], cfg["hd"], a.quant, max_seq_len=max(n + 64, 1024))
+        else:
+            prm = E.model_params(a.model, a.quant)
+            prm.max_seq_len = max(n + 64, 1024)
         eng = E.Engine(prm)
         eng.load(str(path))
         toks = rng.integers(0, cfg["vocab"], size=n).astype(np.int32)
@@ -560,7 +564,7 @@ def run_prefill_sweep(a, rng):
             eng.decode_n(1234 % cfg["vocab"], pos, 32)
             per_tok.append(eng.last_decode_ms / 32)
         est = float(np.mean(per_tok)) * n
-        emit({"sweep": "prefill", "impl": "ours", "model": a.model, "quant": a.quant, "prompt_tokens": n,
+        emit({"sweep": "prefill", "impl": "ours", "model": a.model + (f" cut to {a.layers} layers" if a.layers else ""), "quant": a.quant, "prompt_tokens": n,
               "prefill_ms": round(ms, 3), "prefill_wall_ms": round(wall * 1e3, 3), "prompt_tok_s": round(n / (ms / 1e3), 1),
               "tflops": round((gemm_flop + attn_flop) / (ms / 1e3) / 1e12, 1), "gemm_flop": gemm_flop, "attention_flop": attn_flop,
               "token_by_token_ms_estimate": round(est, 1), "token_by_token_ms_per_step_at": dict(zip(map(str, spots), [round(v, 4) for v in per_tok])),

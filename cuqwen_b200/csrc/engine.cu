@@ -645,11 +645,12 @@ extern "C" int cuqwen_step(cuqwen_engine* e, int token, int pos, const int* hist
 constexpr int kPrefillChunk = 2048;
 #define PK(call) do { int r_ = (call); if (r_) return fail(r_ == (int)cudaErrorInvalidValue ? CUQWEN_ERR_ARG : CUQWEN_ERR_CUDA, "%s: %s", #call, cudaGetErrorString((cudaError_t)r_)); } while (0)
 
-static int prefill_gemm(cuqwen_engine* e, int mode, const __half* x, const Mat& w0, const Mat* w1, void* out, int T, int ldo) {
+static int prefill_gemm(cuqwen_engine* e, int mode, const __half* x, const Mat* const* mats, int nmat, void* out, int T, int ldo) {
     PfGemmArgs a; memset(&a, 0, sizeof a);
-    a.s[0] = w0.s; a.s[1] = w1 ? w1->s : nullptr; a.out_h = (__half*)out; a.out_f = (float*)out;
-    a.T = T; a.R = w0.rows; a.K = w0.cols; a.ldo = ldo; a.mode = mode; a.err = t_err;
-    PK(launch_prefill_gemm(e->p.quant, a, x, w0.w, w1 ? w1->w : nullptr, e->stream));
+    const void* w[3] = {nullptr, nullptr, nullptr}; int rows[3] = {0, 0, 0};
+    for (int m = 0; m < nmat; ++m) { w[m] = mats[m]->w; rows[m] = mats[m]->rows; a.s[m] = mats[m]->s; }
+    a.out_h = (__half*)out; a.out_f = (float*)out; a.T = T; a.K = mats[0]->cols; a.ldo = ldo; a.mode = mode; a.err = t_err;
+    PK(launch_prefill_gemm(e->p.quant, a, x, w, rows, nmat, e->stream));
     return CUQWEN_OK;
 }
 
@@ -683,9 +684,8 @@ extern "C" int cuqwen_prefill(cuqwen_engine* e, const int* tokens, int n_tokens,
         for (int l = 0; l < p.n_layers; ++l) {
             const Layer& L = e->layers[l];
             PK(launch_pf_rmsnorm(e->pf_x, L.in_norm, e->pf_xn, T, p.dim, eps, e->stream));
-            if (int r = prefill_gemm(e, PF_OUT_F32, e->pf_xn, L.q, nullptr, e->pf_qkv, T, ldqkv)) return r;
-            if (int r = prefill_gemm(e, PF_OUT_F32, e->pf_xn, L.k, nullptr, e->pf_qkv + qd, T, ldqkv)) return r;
-            if (int r = prefill_gemm(e, PF_OUT_F32, e->pf_xn, L.v, nullptr, e->pf_qkv + qd + kd, T, ldqkv)) return r;
+            const Mat* qkv[3] = {&L.q, &L.k, &L.v}, *om[1] = {&L.o}, *gu[2] = {&L.gate, &L.up}, *dm[1] = {&L.down};
+            if (int r = prefill_gemm(e, PF_OUT_F32, e->pf_xn, qkv, 3, e->pf_qkv, T, ldqkv)) return r;        // one launch: q, k, v side by side
             PfRopeArgs ra; memset(&ra, 0, sizeof ra);
             ra.qkv = e->pf_qkv; ra.bq = L.bq; ra.bk = L.bk; ra.bv = L.bv; ra.q_out = e->pf_q;
             ra.kcache = e->kc + l * kv_layer; ra.vcache = e->vc + l * kv_layer;
@@ -697,10 +697,10 @@ extern "C" int cuqwen_prefill(cuqwen_engine* e, const int* tokens, int n_tokens,
             aa.q = e->pf_q; aa.kc = ra.kcache; aa.vc = ra.vcache; aa.out = e->pf_att; aa.T = T; aa.pos0 = pos; aa.n_heads = e->n_heads_l;
             aa.grp = e->plan.grp; aa.max_seq = p.max_seq_len; aa.ldq = qd; aa.scale_log2 = (1.0f / sqrtf((float)p.head_dim)) * 1.4426950408889634f;
             PK(launch_prefill_attn(p.head_dim, aa, e->stream));
-            if (int r = prefill_gemm(e, PF_RESID, e->pf_att, L.o, nullptr, e->pf_x, T, p.dim)) return r;
+            if (int r = prefill_gemm(e, PF_RESID, e->pf_att, om, 1, e->pf_x, T, p.dim)) return r;
             PK(launch_pf_rmsnorm(e->pf_x, L.post_norm, e->pf_xn, T, p.dim, eps, e->stream));
-            if (int r = prefill_gemm(e, PF_SWIGLU, e->pf_xn, L.gate, &L.up, e->pf_g, T, e->inter_l)) return r;
-            if (int r = prefill_gemm(e, PF_RESID, e->pf_g, L.down, nullptr, e->pf_x, T, p.dim)) return r;
+            if (int r = prefill_gemm(e, PF_SWIGLU, e->pf_xn, gu, 2, e->pf_g, T, e->inter_l)) return r;
+            if (int r = prefill_gemm(e, PF_RESID, e->pf_g, dm, 1, e->pf_x, T, p.dim)) return r;
         }
     }
     CK(cudaEventRecord(e->ev1, e->stream));
@@ -1085,8 +1085,9 @@ extern "C" int cuqwen_k_prefill_gemm(int device, int quant, int mode, const void
     else if (w1) return fail(CUQWEN_ERR_ARG, "a second matrix only in the SwiGLU mode");
     PfGemmArgs a; memset(&a, 0, sizeof a);
     a.s[0] = (const __half*)s0; a.s[1] = (const __half*)s1; a.bias = (const __half*)bias;
-    a.out_h = (__half*)out; a.out_f = (float*)out; a.T = n_tokens; a.R = rows; a.K = cols; a.ldo = out_stride; a.mode = mode; a.err = t_err;
-    KK(launch_prefill_gemm(quant, a, x, w0, w1, dc->stream)); return CUQWEN_OK;
+    a.out_h = (__half*)out; a.out_f = (float*)out; a.T = n_tokens; a.K = cols; a.ldo = out_stride; a.mode = mode; a.err = t_err;
+    const void* w[2] = {w0, w1}; const int rws[2] = {rows, rows};
+    KK(launch_prefill_gemm(quant, a, x, w, rws, mode == PF_SWIGLU ? 2 : 1, dc->stream)); return CUQWEN_OK;
 }
 extern "C" int cuqwen_k_gemv_add(int device, int quant, const void* w, const void* s, const void* in, void* x, int rows, int cols) {
     DEV(device); if (bad_q(quant)) return fail(CUQWEN_ERR_ARG, "quant out of range");

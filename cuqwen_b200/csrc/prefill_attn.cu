@@ -29,6 +29,8 @@ __device__ __forceinline__ void mma_f16(float (&c)[4], const uint32_t (&a)[4], u
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+__device__ __forceinline__ float pa_ex2(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }   // ex2(-inf) = 0
+
 constexpr int kPaBM = 64, kPaBN = 64, kPaThreads = 128;
 
 // rows [row0, row0 + 64) of a [.][HD] fp16 matrix with row pitch `pitch` elements -> swizzled tile; rows >= row_end zero
@@ -122,13 +124,13 @@ __global__ void __launch_bounds__(kPaThreads) prefill_attn_kernel(const PfAttnAr
         mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
         const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);       // finite from the first tile on: key 0 is visible to every query
-        const float al0 = exp2f(m0 - mn0), al1 = exp2f(m1 - mn1);
+        const float al0 = pa_ex2(m0 - mn0), al1 = pa_ex2(m1 - mn1);
         m0 = mn0; m1 = mn1;
         float rs0 = 0.f, rs1 = 0.f;
         uint32_t pf[4][4];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-            const float e0 = exp2f(s[i][0] - mn0), e1 = exp2f(s[i][1] - mn0), e2 = exp2f(s[i][2] - mn1), e3 = exp2f(s[i][3] - mn1);
+            const float e0 = pa_ex2(s[i][0] - mn0), e1 = pa_ex2(s[i][1] - mn0), e2 = pa_ex2(s[i][2] - mn1), e3 = pa_ex2(s[i][3] - mn1);
             rs0 += e0 + e1; rs1 += e2 + e3;
             pf[i >> 1][(i & 1) * 2] = pack_h2(e0, e1);
             pf[i >> 1][(i & 1) * 2 + 1] = pack_h2(e2, e3);

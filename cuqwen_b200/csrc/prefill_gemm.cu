@@ -51,37 +51,35 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
 // Instruction descriptor: D fp32 [4,6) = 1, A and B fp16 (0), both K-major (0), N >> 3 at [17,23), M >> 4 at [24,29).
 constexpr uint32_t kPfIdesc = (1u << 4) | ((uint32_t)(kPfN >> 3) << 17) | ((uint32_t)(kPfM >> 4) << 24);
 
-// 64 weights of one row -> eight 16-byte chunks of fp16(q * scale), stored at the row's swizzled places.
+// 32 weights (one half of a row's K block) -> four 16-byte chunks of fp16(q * scale), stored at the row's swizzled
+// places.  raw: shared address of the half's bytes; brow: the row in the B tile; chunk0: 0 or 4.
 template <int Q>
-__device__ __forceinline__ void convert_row(uint32_t raw, uint32_t brow, int sw, __half2 sc2) {
+__device__ __forceinline__ void convert_half(uint32_t raw, uint32_t brow, int sw, int chunk0, __half2 sc2) {
     if (Q == Q_I4) {
         // two's-complement nibbles, element 2p in the low nibble of byte p: (n ^ 8) | 0x6400 is fp16(1024 + q + 8)
         const __half2 off = __floats2half2_rn(1032.f, 1032.f);
+        const uint4 rw = lds128(raw);
+        const uint32_t w4[4] = {rw.x, rw.y, rw.z, rw.w};
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            const uint4 rw = lds128(raw + h * 16);
-            const uint32_t w4[4] = {rw.x, rw.y, rw.z, rw.w};
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t w = w4[i];
+            uint32_t t[4];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const uint32_t w = w4[i];
-                uint32_t t[4];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const uint32_t u = ((w >> (4 * j)) & 0x000f000fu) ^ 0x64086408u;          // (element j, element j + 4)
-                    const __half2 hv = __hmul2(__hsub2(*reinterpret_cast<const __half2*>(&u), off), sc2);
-                    t[j] = *reinterpret_cast<const uint32_t*>(&hv);
-                }
-                uint4 o;
-                o.x = __byte_perm(t[0], t[1], 0x5410); o.y = __byte_perm(t[2], t[3], 0x5410);
-                o.z = __byte_perm(t[0], t[1], 0x7632); o.w = __byte_perm(t[2], t[3], 0x7632);
-                sts128(brow + (((h * 4 + i) ^ sw) << 4), o);
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t u = ((w >> (4 * j)) & 0x000f000fu) ^ 0x64086408u;          // (element j, element j + 4)
+                const __half2 hv = __hmul2(__hsub2(*reinterpret_cast<const __half2*>(&u), off), sc2);
+                t[j] = *reinterpret_cast<const uint32_t*>(&hv);
             }
+            uint4 o;
+            o.x = __byte_perm(t[0], t[1], 0x5410); o.y = __byte_perm(t[2], t[3], 0x5410);
+            o.z = __byte_perm(t[0], t[1], 0x7632); o.w = __byte_perm(t[2], t[3], 0x7632);
+            sts128(brow + (((chunk0 + i) ^ sw) << 4), o);
         }
     } else {
         // signed bytes: (b ^ 0x80) under a 0x64 exponent byte is fp16(1024 + b + 128)
         const __half2 off = __floats2half2_rn(1152.f, 1152.f);
 #pragma unroll
-        for (int h = 0; h < 4; ++h) {
+        for (int h = 0; h < 2; ++h) {
             const uint4 rw = lds128(raw + h * 16);
             const uint32_t w4[4] = {rw.x, rw.y, rw.z, rw.w};
 #pragma unroll
@@ -95,7 +93,7 @@ __device__ __forceinline__ void convert_row(uint32_t raw, uint32_t brow, int sw,
                     const __half2 b = __hmul2(__hsub2(*reinterpret_cast<const __half2*>(&hi), off), sc2);
                     t[2 * j] = *reinterpret_cast<const uint32_t*>(&a); t[2 * j + 1] = *reinterpret_cast<const uint32_t*>(&b);
                 }
-                sts128(brow + (((h * 2 + i) ^ sw) << 4), make_uint4(t[0], t[1], t[2], t[3]));
+                sts128(brow + (((chunk0 + h * 2 + i) ^ sw) << 4), make_uint4(t[0], t[1], t[2], t[3]));
             }
         }
     }
@@ -105,25 +103,33 @@ template <int Q>
 __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const __grid_constant__ PfGemmArgs a) {
     extern __shared__ unsigned char pf_smem_raw[];
     const uint32_t base = (smem_u32(pf_smem_raw) + 1023u) & ~1023u;
-    const uint32_t bars = base + kPfStages * kPfStageBytes;
-    const uint32_t bar_full = bars, bar_conv = bars + 8 * kPfStages, bar_empty = bars + 16 * kPfStages, bar_done = bars + 24 * kPfStages;
+    constexpr int NA = pf_na(Q), NB = pf_nb(Q), kRawBytes = pf_raw_bytes(Q);
+    constexpr int kASlot = kPfMH * kPfABytes;                  // X tiles of one slot
+    const uint32_t ring_a = base, ring_raw = ring_a + NA * kASlot, ring_b = ring_raw + NA * kRawBytes;
+    const uint32_t bars = ring_b + NB * kPfBBytes;
+    const uint32_t bar_full = bars, bar_afree = bar_full + 8 * NA, bar_conv = bar_afree + 8 * NA, bar_bfree = bar_conv + 8 * NB, bar_done = bar_bfree + 8 * NB;
     const uint32_t tmem_slot = bar_done + 8;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tm = blockIdx.x, tn = blockIdx.y;
+    const int tm = blockIdx.x, tn = blockIdx.y, mh = a.mh;
     const bool swiglu = a.mode == PF_SWIGLU;
     const int rows_mat = swiglu ? kPfN / 2 : kPfN;            // rows of each matrix in this tile
     const int nmat = swiglu ? 2 : 1;
-    const int row0 = tn * rows_mat;
+    int seg = 0, coff = 0, tseg = tn;                         // plain modes: which matrix this row tile belongs to, its first output column
+    if (!swiglu)
+        while (seg + 1 < a.nseg && tseg >= (a.seg_rows[seg] + kPfN - 1) / kPfN) { tseg -= (a.seg_rows[seg] + kPfN - 1) / kPfN; coff += a.seg_rows[seg]; ++seg; }
+    const int row0 = tseg * rows_mat;                         // first row inside the matrix
+    const int R = a.seg_rows[seg];
     const int nkb = a.K / kPfKB;
     constexpr int kRawKb = Q == Q_I4 ? 32 : 64;               // raw bytes of one row in one K block
     bool failed = false;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kPfStages; ++s) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_conv + 8 * s, kPfConvWarps); mbar_init(bar_empty + 8 * s, 1); }
+        for (int s = 0; s < NA; ++s) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_afree + 8 * s, 1); }
+        for (int s = 0; s < NB; ++s) { mbar_init(bar_conv + 8 * s, kPfConvWarps); mbar_init(bar_bfree + 8 * s, 1); }
         mbar_init(bar_done, 1);
         mbar_fence_init();
     }
-    if (warp == 1) { tmem_alloc(tmem_slot, kPfN); tmem_relinquish(); }
+    if (warp == 1) { tmem_alloc(tmem_slot, (uint32_t)(mh * kPfN)); tmem_relinquish(); }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -133,78 +139,86 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const __gri
         if (lane == 0) {
             const uint32_t wbytes = Q == Q_F16 ? (uint32_t)kPfBBytes : (uint32_t)(kPfN * kRawKb);
             for (int kb = 0; kb < nkb && !failed; ++kb) {
-                const int s = kb % kPfStages; const uint32_t ph = (uint32_t)(kb / kPfStages) & 1u;
-                if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u)) { failed = true; break; }
-                const uint32_t st = base + s * kPfStageBytes;
-                mbar_expect_tx(bar_full + 8 * s, (uint32_t)kPfABytes + wbytes);
-                tma_load_2d(st, &a.tx, kb * kPfKB, tm * kPfM, bar_full + 8 * s);
+                const int sa = kb % NA, sb = kb % NB; const uint32_t pa = (uint32_t)(kb / NA) & 1u;
+                if (!mbar_wait(bar_afree + 8 * sa, pa ^ 1u)) { failed = true; break; }
+                mbar_expect_tx(bar_full + 8 * sa, (uint32_t)(mh * kPfABytes) + wbytes);
+                for (int h = 0; h < mh; ++h)        // a half that lies past the last token arrives as zeros
+                    tma_load_2d(ring_a + sa * kASlot + h * kPfABytes, &a.tx, kb * kPfKB, (tm * mh + h) * kPfM, bar_full + 8 * sa);
                 for (int m = 0; m < nmat; ++m) {
-                    if (Q == Q_F16) tma_load_2d(st + kPfABytes + m * rows_mat * 128, &a.tw[m], kb * kPfKB, row0, bar_full + 8 * s);
-                    else tma_load_2d(st + kPfABytes + kPfBBytes + m * rows_mat * kRawKb, &a.tw[m], kb * kRawKb, row0, bar_full + 8 * s);
+                    if (Q == Q_F16) tma_load_2d(ring_b + sb * kPfBBytes + m * rows_mat * 128, &a.tw[seg + m], kb * kPfKB, row0, bar_full + 8 * sa);    // NB == NA: freed together
+                    else tma_load_2d(ring_raw + sa * kRawBytes + m * rows_mat * kRawKb, &a.tw[seg + m], kb * kRawKb, row0, bar_full + 8 * sa);
                 }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             for (int kb = 0; kb < nkb && !failed; ++kb) {
-                const int s = kb % kPfStages; const uint32_t ph = (uint32_t)(kb / kPfStages) & 1u;
-                if (!mbar_wait(bar_full + 8 * s, ph)) { failed = true; break; }
-                if (Q != Q_F16 && !mbar_wait(bar_conv + 8 * s, ph)) { failed = true; break; }
+                const int sa = kb % NA, sb = kb % NB; const uint32_t pa = (uint32_t)(kb / NA) & 1u, pb = (uint32_t)(kb / NB) & 1u;
+                if (!mbar_wait(bar_full + 8 * sa, pa)) { failed = true; break; }
+                if (Q != Q_F16 && !mbar_wait(bar_conv + 8 * sb, pb)) { failed = true; break; }
                 tc_fence_after();
-                const uint32_t st = base + s * kPfStageBytes;
+                const uint32_t at = ring_a + sa * kASlot, bt = ring_b + sb * kPfBBytes;
+                for (int h = 0; h < mh; ++h)
 #pragma unroll
-                for (int k4 = 0; k4 < kPfKB / 16; ++k4)
-                    umma_f16(tmem, umma_desc(st + k4 * 32), umma_desc(st + kPfABytes + k4 * 32), kPfIdesc, (uint32_t)((kb | k4) != 0));
-                umma_commit(bar_empty + 8 * s);            // the stage may be refilled once these MMAs have read it
+                    for (int k4 = 0; k4 < kPfKB / 16; ++k4)
+                        umma_f16(tmem + (uint32_t)(h * kPfN), umma_desc(at + h * kPfABytes + k4 * 32), umma_desc(bt + k4 * 32), kPfIdesc, (uint32_t)((kb | k4) != 0));
+                umma_commit(bar_afree + 8 * sa);           // both slots may be refilled once these MMAs have read them
+                if (Q != Q_F16) umma_commit(bar_bfree + 8 * sb);
             }
             umma_commit(bar_done);
         }
     } else {
-        const int c = threadIdx.x - 64;                       // B row of this thread, 0..255
+        const int c = (threadIdx.x - 64) & (kPfN - 1);        // B row of this thread, 0..255
+        const int khalf = (threadIdx.x - 64) >> 8;            // sixteen converter warps: which 32 weights of the row's K block
         const int mat = swiglu ? c >> 7 : 0, rin = swiglu ? c & 127 : c;
         const int grow = row0 + rin;
-        const bool valid = grow < a.R;
+        const bool valid = grow < R;
         if (Q != Q_F16) {
             const int ngrp = a.K / kGroup;
-            const __half* srow = a.s[mat] + (size_t)(valid ? grow : 0) * ngrp;
-            __half sc = valid ? srow[0] : __float2half(0.f);
+            const __half* srow = a.s[seg + mat] + (size_t)(valid ? grow : 0) * ngrp;
+            // the scales of the next two groups are already on their way while a group is widened (a load from L2 takes
+            // longer than the MMAs of a K block)
+            const __half zero = __float2half(0.f);
+            __half sc = valid ? srow[0] : zero, sc1 = valid && ngrp > 1 ? srow[1] : zero, sc2 = valid && ngrp > 2 ? srow[2] : zero;
             for (int kb = 0; kb < nkb && !failed; ++kb) {
-                const int s = kb % kPfStages; const uint32_t ph = (uint32_t)(kb / kPfStages) & 1u;
+                const int sa = kb % NA, sb = kb % NB; const uint32_t pa = (uint32_t)(kb / NA) & 1u, pb = (uint32_t)(kb / NB) & 1u;
                 const __half sc_use = sc;
-                if ((kb & 1) && kb + 1 < nkb) sc = valid ? srow[(kb + 1) >> 1] : sc;       // the next group's scale, ahead of its use
-                if (!mbar_wait(bar_full + 8 * s, ph)) { failed = true; break; }
-                const uint32_t st = base + s * kPfStageBytes;
-                convert_row<Q == Q_F16 ? Q_I8 : Q>(st + kPfABytes + kPfBBytes + c * kRawKb, st + kPfABytes + c * 128, c & 7, __half2half2(sc_use));
+                if (kb & 1) { sc = sc1; sc1 = sc2; const int g3 = (kb >> 1) + 3; sc2 = valid && g3 < ngrp ? srow[g3] : zero; }
+                if (!mbar_wait(bar_full + 8 * sa, pa)) { failed = true; break; }
+                if (!mbar_wait(bar_bfree + 8 * sb, pb ^ 1u)) { failed = true; break; }     // the MMAs of two K blocks ago have read this B slot
+#pragma unroll
+                for (int kh = khalf; kh < 2; kh += kPfConvWarps / 8)
+                    convert_half<Q == Q_F16 ? Q_I8 : Q>(ring_raw + sa * kRawBytes + c * kRawKb + kh * (kRawKb / 2), ring_b + sb * kPfBBytes + c * 128, c & 7, kh * 4, __half2half2(sc_use));
                 fence_async_smem();                            // the tensor core reads through the async proxy
                 __syncwarp();
-                if (lane == 0) mbar_arrive(bar_conv + 8 * s);
+                if (lane == 0) mbar_arrive(bar_conv + 8 * sb);
             }
         }
         // epilogue: TMEM lane = token, column = weight row of the tile
         if (!failed && !mbar_wait(bar_done, 0u)) failed = true;
         tc_fence_after();
-        if (!failed) {
-            const int q = warp & 3, hh = (warp - 2) >> 2;
-            const int token = tm * kPfM + q * 32 + lane;
+        for (int h = 0; h < mh && !failed; ++h) {
+            const int q = warp & 3, hh = (warp - 2) >> 2;        // TMEM lane quarter (fixed by the warp's number), column quarter
+            const int token = (tm * mh + h) * kPfM + q * 32 + lane;
             const bool tv = token < a.T;
-            const uint32_t tlane = tmem + ((uint32_t)(q * 32) << 16);
+            const uint32_t tlane = tmem + (uint32_t)(h * kPfN) + ((uint32_t)(q * 32) << 16);
             if (!swiglu) {
 #pragma unroll 1
-                for (int ch = 0; ch < 4; ++ch) {
-                    const int col = hh * 128 + ch * 32;
+                for (int ch = 0; ch < 32 / kPfConvWarps; ++ch) {
+                    const int col = hh * (1024 / kPfConvWarps) + ch * 32;
                     float v[32];
                     tmem_ld32(tlane + (uint32_t)col, v);
                     const int r = row0 + col;
-                    if (tv && r < a.R) {
+                    if (tv && r < R) {
                     if (a.mode == PF_OUT_F32) {
-                        float* dst = a.out_f + (size_t)token * a.ldo + r;
+                        float* dst = a.out_f + (size_t)token * a.ldo + coff + r;
 #pragma unroll
-                        for (int i = 0; i < 32; i += 4) if (r + i < a.R) *reinterpret_cast<float4*>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                        for (int i = 0; i < 32; i += 4) if (r + i < R) *reinterpret_cast<float4*>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
                     } else {
-                        __half* dst = a.out_h + (size_t)token * a.ldo + r;
+                        __half* dst = a.out_h + (size_t)token * a.ldo + coff + r;
 #pragma unroll
                         for (int i = 0; i < 32; i += 8) {
-                            if (r + i >= a.R) break;
+                            if (r + i >= R) break;
                             float add[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
                             if (a.mode == PF_RESID) {
                                 const uint4 o = *reinterpret_cast<const uint4*>(dst + i);
@@ -212,7 +226,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const __gri
 #pragma unroll
                                 for (int k = 0; k < 4; ++k) { const float2 f = __half22float2(oh[k]); add[2 * k] = f.x; add[2 * k + 1] = f.y; }
                             } else if (a.bias) {
-                                const uint4 o = *reinterpret_cast<const uint4*>(a.bias + r + i);
+                                const uint4 o = *reinterpret_cast<const uint4*>(a.bias + coff + r + i);
                                 const __half2* oh = reinterpret_cast<const __half2*>(&o);
 #pragma unroll
                                 for (int k = 0; k < 4; ++k) { const float2 f = __half22float2(oh[k]); add[2 * k] = f.x; add[2 * k + 1] = f.y; }
@@ -229,8 +243,8 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const __gri
                 }
             } else {
 #pragma unroll 1
-                for (int ch = 0; ch < 2; ++ch) {
-                    const int col = hh * 64 + ch * 32;
+                for (int ch = 0; ch < 16 / kPfConvWarps; ++ch) {
+                    const int col = hh * (512 / kPfConvWarps) + ch * 32;
                     float g[32], u[32];
                     tmem_ld32(tlane + (uint32_t)col, g);
                     tmem_ld32(tlane + (uint32_t)(128 + col), u);
@@ -238,7 +252,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const __gri
                     __half* dst = a.out_h + (size_t)token * a.ldo + r;
 #pragma unroll
                     for (int i = 0; i < 32; i += 8) {
-                        if (!tv || r + i >= a.R) break;
+                        if (!tv || r + i >= R) break;
                         uint4 o;
                         __half2* oh = reinterpret_cast<__half2*>(&o);
 #pragma unroll
@@ -257,7 +271,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const __gri
     if (failed && a.err) atomicExch(a.err, 11u);
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) tmem_dealloc(tmem, kPfN);
+    if (warp == 1) tmem_dealloc(tmem, (uint32_t)(mh * kPfN));
 }
 
 // ---- host side ------------------------------------------------------------------------------------------------------
@@ -287,30 +301,37 @@ template <int Q>
 static int pf_go(const PfGemmArgs& a, dim3 grid, cudaStream_t stream) {
     static bool once = false;
     if (!once) {
-        const cudaError_t e = cudaFuncSetAttribute(prefill_gemm_kernel<Q>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmemBytes);
+        const cudaError_t e = cudaFuncSetAttribute(prefill_gemm_kernel<Q>, cudaFuncAttributeMaxDynamicSharedMemorySize, pf_smem_bytes(Q));
         if (e != cudaSuccess) return (int)e;
         once = true;
     }
-    prefill_gemm_kernel<Q><<<grid, kPfThreads, kPfSmemBytes, stream>>>(a);
+    prefill_gemm_kernel<Q><<<grid, kPfThreads, pf_smem_bytes(Q), stream>>>(a);
     return (int)cudaGetLastError();
 }
 
-int launch_prefill_gemm(int quant, PfGemmArgs& a, const void* x, const void* w0, const void* w1, cudaStream_t stream) {
-    if (a.T <= 0 || a.R <= 0 || a.K <= 0 || a.K % kGroup || a.R % 8 || a.ldo % 8 || quant < 0 || quant > 2) return (int)cudaErrorInvalidValue;
-    if ((a.mode == PF_SWIGLU) != (w1 != nullptr)) return (int)cudaErrorInvalidValue;
-    const int rows_mat = a.mode == PF_SWIGLU ? kPfN / 2 : kPfN;
+int launch_prefill_gemm(int quant, PfGemmArgs& a, const void* x, const void* const* w, const int* rows, int nmat, cudaStream_t stream) {
+    if (a.T <= 0 || a.K <= 0 || a.K % kGroup || a.ldo % 8 || quant < 0 || quant > 2 || nmat < 1 || nmat > 3) return (int)cudaErrorInvalidValue;
+    const bool swiglu = a.mode == PF_SWIGLU;
+    if (swiglu && (nmat != 2 || rows[0] != rows[1])) return (int)cudaErrorInvalidValue;
+    const int rows_mat = swiglu ? kPfN / 2 : kPfN;
     if (int r = pf_map(&a.tx, x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (size_t)a.T, (size_t)a.K, kPfKB, kPfM, true)) return r;
-    const void* w[2] = {w0, w1};
-    for (int m = 0; m < (w1 ? 2 : 1); ++m) {
+    int tiles = 0;
+    a.R = 0;
+    for (int m = 0; m < nmat; ++m) {
+        if (!w[m] || rows[m] <= 0 || rows[m] % 8) return (int)cudaErrorInvalidValue;
         int r;
-        if (quant == Q_F16) r = pf_map(&a.tw[m], w[m], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (size_t)a.R, (size_t)a.K, kPfKB, rows_mat, true);
+        if (quant == Q_F16) r = pf_map(&a.tw[m], w[m], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (size_t)rows[m], (size_t)a.K, kPfKB, rows_mat, true);
         else {
             const size_t rb = quant == Q_I4 ? (size_t)a.K / 2 : (size_t)a.K;
-            r = pf_map(&a.tw[m], w[m], CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (size_t)a.R, rb, quant == Q_I4 ? 32 : 64, rows_mat, false);
+            r = pf_map(&a.tw[m], w[m], CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (size_t)rows[m], rb, quant == Q_I4 ? 32 : 64, rows_mat, false);
         }
         if (r) return r;
+        a.seg_rows[m] = rows[m];
+        if (!swiglu || m == 0) { tiles += (rows[m] + rows_mat - 1) / rows_mat; a.R += rows[m]; }
     }
-    const dim3 grid((a.T + kPfM - 1) / kPfM, (a.R + rows_mat - 1) / rows_mat);
+    a.nseg = swiglu ? 1 : nmat;
+    a.mh = a.T > kPfM ? kPfMH : 1;
+    const dim3 grid((a.T + kPfM * a.mh - 1) / (kPfM * a.mh), tiles);
     if (quant == Q_I4) return pf_go<Q_I4>(a, grid, stream);
     if (quant == Q_I8) return pf_go<Q_I8>(a, grid, stream);
     return pf_go<Q_F16>(a, grid, stream);
