@@ -192,3 +192,41 @@ def test_prefill_vs_reference_build_token_by_token(built, tmpdir_big, model, qua
         path.unlink()
     print(f"{model} {quant}, prompt {n}: top-1 agreement {agree}/{steps}, rel rms of the logits {worst:.2e}")
     assert agree == steps and worst <= 1.5e-2
+
+
+def test_prefill_longer_than_one_chunk_and_single_token(built, tmp_path):
+    """A prompt longer than the 2048-token chunk the engine works in (the second chunk attends to the first one's
+    rows), and the smallest call (one token at an odd position), against the token-by-token path."""
+    from cuqwen_b200 import engine as E
+    cfg = dict(vocab=512, dim=256, inter=512, layers=2, heads=2, kv=1, hd=128, tied=True)
+    path = tmp_path / "m.bin"
+    binfmt.write_model(path, cfg, 2, binfmt.random_tensors(cfg, 3))
+    max_seq = 2432
+
+    def make():
+        e = E.Engine(E.custom_params(cfg["vocab"], cfg["dim"], cfg["inter"], cfg["layers"], cfg["heads"], cfg["kv"], cfg["hd"], 2, max_seq_len=max_seq))
+        e.load(str(path))
+        return e
+
+    rng = np.random.default_rng(2)
+    n = 2048 + 331
+    toks = rng.integers(0, cfg["vocab"], size=n + 2).astype(np.int32)
+    a, b = make(), make()
+    for i in range(n + 1):
+        a.step(int(toks[i]), i)
+    b.prefill(toks[:n], 0)
+    b.prefill(toks[n:n + 1], n)
+    shape = (cfg["layers"], cfg["kv"], max_seq, cfg["hd"])
+    for which in ("KEY_CACHE", "VALUE_CACHE"):
+        ca = a.read(which).reshape(shape).astype(np.float64)[:, :, :n + 1]
+        cb = b.read(which).reshape(shape).astype(np.float64)[:, :, :n + 1]
+        rms = np.sqrt(((ca - cb) ** 2).mean()) / np.sqrt((ca ** 2).mean())
+        tail = np.sqrt(((ca[:, :, 2048:] - cb[:, :, 2048:]) ** 2).mean()) / np.sqrt((ca[:, :, 2048:] ** 2).mean())
+        print(f"{which}: rel rms {rms:.2e} (rows of the second chunk {tail:.2e})")
+        assert rms < 5e-3 and tail < 5e-3
+    ta, tb = a.step(int(toks[n + 1]), n + 1), b.step(int(toks[n + 1]), n + 1)
+    la, lb = a.read("LOGITS").astype(np.float64), b.read("LOGITS").astype(np.float64)
+    rms = np.sqrt(((la - lb) ** 2).mean()) / np.sqrt((la ** 2).mean())
+    print(f"logits: rel rms {rms:.2e}, tokens {ta} / {tb}")
+    assert rms < 1.5e-2
+    a.close(); b.close()
