@@ -33,7 +33,7 @@ int main(int argc, char** argv) {
     CUDA_CHECK(cudaMemset(state.d_partial_max, 0, 16));
     CUDA_CHECK(cudaMemset(state.d_token, 0, sizeof(int)));
     CUDA_CHECK(cudaMemset(state.d_history_len, 0, sizeof(int)));
-    if (!state.stream || dev_pos != 3 || dev_tok < 0 || dev_tok >= config.vocab_size) { printf("state fields: pos %d token %d\n", dev_pos, dev_tok); return 1; }
+    if (!state.stream || dev_pos != 7 || dev_tok < 0 || dev_tok >= config.vocab_size) { printf("state fields: pos %d token %d\n", dev_pos, dev_tok); return 1; }
     static_assert(ATTN_KEYS_CAP > 0 && GEMV_WARPS_PER_BLOCK == 8 && GEMV_WIDE_WARPS_PER_BLOCK >= 8 && ARGMAX_THREADS == 256, "knob names");
     printf("%d\n", tok);
     free_qwen_state(state);

@@ -44,6 +44,8 @@ def test_reference_style_program_runs(built, tmpdir_big):
     tok = 1
     for pos in range(4):
         tok = eng.step(tok, pos)
+    eng.prefill([5, 6, 7], 4)               # the probe calls the shim's qwen_prefill the same way
+    tok = eng.step(tok, 7)
     eng.close()
     path.unlink()
     assert int(r.stdout.strip().splitlines()[-1]) == tok
