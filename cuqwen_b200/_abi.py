@@ -65,6 +65,7 @@ SIGNATURES = {
     "cuqwen_k_tp_sum": (_i, [_i, _vp, _vp, _vp, _i, _i, _vp, _i, C.c_longlong]),
     "cuqwen_attn_scratch_bytes": (_i, [_i, _i, _i, C.POINTER(_sz), C.POINTER(_sz), C.POINTER(_sz)]),
     "cuqwen_k_gemv_add": (_i, [_i, _i, _vp, _vp, _vp, _vp, _i, _i]),
+    "cuqwen_k_prefill_attention": (_i, [_i, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i]),
     "cuqwen_k_prefill_gemm": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i]),
     "cuqwen_k_gemv": (_i, [_i, _i, _vp, _vp, _vp, _vp, _f, _vp, _i, _i]),
     "cuqwen_k_gemv_f32": (_i, [_i, _i, _vp, _vp, _vp, _vp, _i, _i]),

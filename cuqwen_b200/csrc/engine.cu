@@ -696,7 +696,8 @@ extern "C" int cuqwen_prefill(cuqwen_engine* e, const int* tokens, int n_tokens,
             PfAttnArgs aa; memset(&aa, 0, sizeof aa);
             aa.q = e->pf_q; aa.kc = ra.kcache; aa.vc = ra.vcache; aa.out = e->pf_att; aa.T = T; aa.pos0 = pos; aa.n_heads = e->n_heads_l;
             aa.grp = e->plan.grp; aa.max_seq = p.max_seq_len; aa.ldq = qd; aa.scale_log2 = (1.0f / sqrtf((float)p.head_dim)) * 1.4426950408889634f;
-            PK(launch_prefill_attn(p.head_dim, aa, e->stream));
+            if (p.head_dim == 128 && !(p.flags & CUQWEN_FLAG_PREFILL_ATTN_MMA)) PK(launch_prefill_attn_tc(aa, e->n_kv_l, t_err, e->stream));
+            else PK(launch_prefill_attn(p.head_dim, aa, e->stream));
             if (int r = prefill_gemm(e, PF_RESID, e->pf_att, om, 1, e->pf_x, T, p.dim)) return r;
             PK(launch_pf_rmsnorm(e->pf_x, L.post_norm, e->pf_xn, T, p.dim, eps, e->stream));
             if (int r = prefill_gemm(e, PF_SWIGLU, e->pf_xn, gu, 2, e->pf_g, T, e->inter_l)) return r;
@@ -1088,6 +1089,20 @@ extern "C" int cuqwen_k_prefill_gemm(int device, int quant, int mode, const void
     a.out_h = (__half*)out; a.out_f = (float*)out; a.T = n_tokens; a.K = cols; a.ldo = out_stride; a.mode = mode; a.err = t_err;
     const void* w[2] = {w0, w1}; const int rws[2] = {rows, rows};
     KK(launch_prefill_gemm(quant, a, x, w, rws, mode == PF_SWIGLU ? 2 : 1, dc->stream)); return CUQWEN_OK;
+}
+extern "C" int cuqwen_k_prefill_attention(int device, int impl, const void* q, const void* kcache, const void* vcache, void* out, int n_tokens, int pos0,
+                                          int n_heads, int n_kv_heads, int head_dim, int max_seq_len, int q_stride) {
+    DEV(device); (void)cfg;
+    NOT_NULL(q, kcache, vcache, out);
+    if (n_kv_heads <= 0 || n_heads % n_kv_heads) return fail(CUQWEN_ERR_ARG, "n_heads must be a multiple of n_kv_heads");
+    if ((impl == 0 && head_dim != 128) || (impl == 1 && head_dim != 64 && head_dim != 128) || impl < 0 || impl > 1) return fail(CUQWEN_ERR_ARG, "impl / head_dim combination not available");
+    PfAttnArgs a; memset(&a, 0, sizeof a);
+    a.q = (const __half*)q; a.kc = (const __half*)kcache; a.vc = (const __half*)vcache; a.out = (__half*)out; a.T = n_tokens; a.pos0 = pos0;
+    a.n_heads = n_heads; a.grp = n_heads / n_kv_heads; a.max_seq = max_seq_len; a.ldq = q_stride;
+    a.scale_log2 = (1.0f / sqrtf((float)head_dim)) * 1.4426950408889634f;
+    if (impl == 0) KK(launch_prefill_attn_tc(a, n_kv_heads, t_err, dc->stream));
+    else KK(launch_prefill_attn(head_dim, a, dc->stream));
+    return CUQWEN_OK;
 }
 extern "C" int cuqwen_k_gemv_add(int device, int quant, const void* w, const void* s, const void* in, void* x, int rows, int cols) {
     DEV(device); if (bad_q(quant)) return fail(CUQWEN_ERR_ARG, "quant out of range");

@@ -18,7 +18,7 @@ from ._abi import Params, check
 FP16, INT8, INT4 = 0, 1, 2
 QUANT_ID = {"fp16": FP16, "int8": INT8, "int4": INT4}
 MODEL_ID = {"0.5b": 0, "1.5b": 1, "3b": 2, "7b": 3, "14b": 4}
-FLAG_ACCURATE_ROPE, FLAG_NO_PDL, FLAG_NO_GRAPH, FLAG_STEP_TRACE, FLAG_TP_NCCL, FLAG_NO_HANDOVER, FLAG_KV_INT8, FLAG_TP_SUM_IN_GEMV = 1, 2, 4, 16, 32, 64, 128, 256
+FLAG_ACCURATE_ROPE, FLAG_NO_PDL, FLAG_NO_GRAPH, FLAG_STEP_TRACE, FLAG_TP_NCCL, FLAG_NO_HANDOVER, FLAG_KV_INT8, FLAG_TP_SUM_IN_GEMV, FLAG_PREFILL_ATTN_MMA = 1, 2, 4, 16, 32, 64, 128, 256, 512
 
 # cuqwen_get_ptr ids (include/cuqwen_b200.h)
 PTR = dict(X=0, XN=1, Q=2, K=3, V=4, ATT=5, GATE=6, LOGITS=7, KEY_CACHE=8, VALUE_CACHE=9, HISTORY=10, STEP_TRACE=11, TOKEN=12, POS=13,

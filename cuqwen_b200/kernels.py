@@ -77,6 +77,12 @@ def prefill_gemm(quant, mode, x, w0, s0, out, n_tokens, rows, cols, out_stride=N
                                            rows if out_stride is None else out_stride))
 
 
+def prefill_attention(impl, q, kcache, vcache, out, n_tokens, pos0, n_heads, n_kv_heads, head_dim, max_seq_len, q_stride=None, device=0):
+    """cuqwen_k_prefill_attention: causal attention of a tile of prompt tokens (impl 0 tcgen05, 1 mma.sync)."""
+    check(_abi.lib().cuqwen_k_prefill_attention(device, impl, _p(q), _p(kcache), _p(vcache), _p(out), n_tokens, pos0, n_heads, n_kv_heads, head_dim,
+                                                max_seq_len, n_heads * head_dim if q_stride is None else q_stride))
+
+
 def gemv_add(quant, w, scale, inp, x_inout, rows, cols, device=0):
     check(_abi.lib().cuqwen_k_gemv_add(device, quant, _p(w), _p(scale), _p(inp), _p(x_inout), rows, cols))
 

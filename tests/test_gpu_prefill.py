@@ -230,3 +230,39 @@ def test_prefill_longer_than_one_chunk_and_single_token(built, tmp_path):
     print(f"logits: rel rms {rms:.2e}, tokens {ta} / {tb}")
     assert rms < 1.5e-2
     a.close(); b.close()
+
+
+def attn_oracle(q, Kc, Vc, pos0, nh, nkv, hd):
+    """float64 causal attention: q [T][nh*hd], caches [nkv][max_seq][hd]; query t sees keys [0, pos0 + t]."""
+    T = q.shape[0]
+    grp = nh // nkv
+    out = np.empty((T, nh * hd))
+    for h in range(nh):
+        kv = h // grp
+        qh = q[:, h * hd:(h + 1) * hd].astype(np.float64)
+        s = qh @ Kc[kv, :pos0 + T].astype(np.float64).T / np.sqrt(hd)
+        mask = np.arange(pos0 + T)[None, :] > (pos0 + np.arange(T))[:, None]
+        s[mask] = -np.inf
+        p = np.exp(s - s.max(axis=1, keepdims=True))
+        out[:, h * hd:(h + 1) * hd] = (p / p.sum(axis=1, keepdims=True)) @ Vc[kv, :pos0 + T].astype(np.float64)
+    return out
+
+
+@pytest.mark.parametrize("impl,hd", [(0, 128), (1, 128), (1, 64)])
+@pytest.mark.parametrize("T,pos0,nh,nkv", [(1, 0, 4, 2), (37, 0, 4, 2), (128, 5, 2, 1), (300, 0, 7, 1), (200, 333, 4, 4), (513, 129, 2, 2)])
+def test_prefill_attention_kernels(built, impl, hd, T, pos0, nh, nkv):
+    rng = np.random.default_rng(T * 7 + pos0 + nh + hd)
+    max_seq = (pos0 + T + 70) // 8 * 8
+    q = rng.standard_normal((T, nh * hd)).astype(np.float16)
+    Kc = rng.standard_normal((nkv, max_seq, hd)).astype(np.float16)
+    Vc = rng.standard_normal((nkv, max_seq, hd)).astype(np.float16)
+    want = attn_oracle(q, Kc, Vc, pos0, nh, nkv, hd)
+    # rows past the last query are never attended to: huge values there must not leak into any output
+    Kp, Vp = Kc.copy(), Vc.copy()
+    Kp[:, pos0 + T:] = 60000.0; Vp[:, pos0 + T:] = -60000.0
+    out = DevBuf(T * nh * hd * 2)
+    K.prefill_attention(impl, dev(q), dev(Kp), dev(Vp), out, T, pos0, nh, nkv, hd, max_seq)
+    sync()
+    got = out.numpy(np.float16).reshape(T, nh * hd)
+    assert np.isfinite(got.astype(np.float32)).all()
+    assert close(got, want), report(got, want)
