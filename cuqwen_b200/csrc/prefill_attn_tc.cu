@@ -2,13 +2,14 @@
 // the reference's decode attention (src/kernels.cu:105-288), which the reference applies once per prompt token
 // (src/main.cu:86-92).  prefill_attn.cu holds the mma.sync kernel this one replaces where head_dim is 128.
 //
-// One CTA = 128 queries of one head.  Per tile of 128 keys:
+// One CTA = 128 queries of one head, two CTAs to an SM.  Per tile of 64 keys:
 //   warp 0      TMA: K and V tiles of the head's KV group (two 64-column boxes each, hardware-swizzled), two slots
-//   warp 1      one lane issues S = Q K^T (eight MMAs 128 x 128 x 16, both operands K-major) into one of two TMEM
-//               buffers, and - once the softmax warps have written P - O += P V (eight MMAs, V as the MN-major B
+//   warp 1      one lane issues S = Q K^T (eight MMAs 128 x 64 x 16, both operands K-major) into one of two TMEM
+//               buffers, and - once the softmax warps have written P - O += P V (four MMAs 128 x 128 x 16, V as the MN-major B
 //               operand straight from its cache layout) into a third
-//   warps 2-5   one query row per thread (TMEM lane = row): read S, scale, mask, running maximum, rescale O in TMEM
-//               by 2^(m_old - m_new), write P = 2^(s - m_new) as fp16 into the swizzled A tile, row sums in fp32
+//   warps 2-5   one query row per thread (TMEM lane = row): read S, scale, mask, write P = 2^(s - m) as fp16 into the
+//               swizzled A tile, row sums in fp32; when a row's maximum outgrows m by 2^8, m moves and O is rescaled
+//               in TMEM by 2^(m_old - m_new) (rare after the first tiles)
 // S of the next tile is issued before the current tile's P is waited for, so Q K^T overlaps the softmax.
 // Every mbarrier wait is bounded; a wait that runs out sets *err and the CTA drains.
 #include "prefill.cuh"
@@ -16,11 +17,17 @@
 
 namespace cq {
 
-constexpr int kTaBM = 128, kTaBN = 128, kTaHD = 128;
+constexpr int kTaBM = 128, kTaBN = 64, kTaHD = 128;
 constexpr int kTaThreads = 192;
-constexpr int kTaTile = 128 * 128 * 2;            // 32 KB: two 64-column blocks of [128 rows][128 bytes]
-constexpr int kTaHalf = kTaTile / 2;
-constexpr int kTaSmem = 6 * kTaTile + 1024 + 256; // Q, K x 2, V x 2, P; alignment slack; barriers
+constexpr int kTaQTile = kTaBM * kTaHD * 2;       // 32 KB: two 64-column blocks of [128 rows][128 bytes]
+constexpr int kTaQHalf = kTaQTile / 2;
+constexpr int kTaKTile = kTaBN * kTaHD * 2;       // 16 KB: two 64-column blocks of [64 keys][128 bytes]
+constexpr int kTaKHalf = kTaKTile / 2;
+constexpr int kTaPTile = kTaBM * kTaBN * 2;       // 16 KB: [128 rows][64 keys]
+// Q, K x 2, V x 2, P; barriers (the dynamic shared memory is declared 1024-byte aligned).  112 KB and at most 170 registers: two CTAs share an SM, one's softmax
+// (a single warp per scheduler, bound by its own dependent chain) runs under the other's MMAs.
+constexpr int kTaSmem = kTaQTile + 4 * kTaKTile + kTaPTile + 256;      // 114,944 B: twice that and the 1 KB the system keeps per CTA fit an SM's 228 KB
+constexpr uint32_t kTaCols = 256;                 // TMEM columns: S x 2 (64 each), O (128)
 
 struct PfAttnTcArgs {
     CUtensorMap tq;          // q as [T][ldq] fp16, box 64 x 128, swizzled
@@ -36,11 +43,11 @@ __device__ __forceinline__ void ta_sts128(uint32_t addr, uint4 v) {
     asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
-__global__ void __launch_bounds__(kTaThreads, 1) prefill_attn_tc_kernel(const __grid_constant__ PfAttnTcArgs a) {
-    extern __shared__ unsigned char ta_smem[];
-    const uint32_t base = (smem_u32(ta_smem) + 1023u) & ~1023u;
-    const uint32_t sQ = base, sK = base + kTaTile, sV = base + 3 * kTaTile, sP = base + 5 * kTaTile;
-    const uint32_t bars = base + 6 * kTaTile;
+__global__ void __launch_bounds__(kTaThreads, 2) prefill_attn_tc_kernel(const __grid_constant__ PfAttnTcArgs a) {
+    extern __shared__ __align__(1024) unsigned char ta_smem[];
+    const uint32_t base = smem_u32(ta_smem);
+    const uint32_t sQ = base, sK = base + kTaQTile, sV = sK + 2 * kTaKTile, sP = sV + 2 * kTaKTile;
+    const uint32_t bars = sP + kTaPTile;
     const uint32_t b_q = bars, b_kvfull = bars + 8, b_kvfree = bars + 24, b_sfull = bars + 40, b_p = bars + 56, b_pv = bars + 64, tmem_slot = bars + 72;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int head = blockIdx.y, kvh = head / a.grp;
@@ -55,26 +62,26 @@ __global__ void __launch_bounds__(kTaThreads, 1) prefill_attn_tc_kernel(const __
         mbar_init(b_p, 4); mbar_init(b_pv, 1);
         mbar_fence_init();
     }
-    if (warp == 1) { tmem_alloc(tmem_slot, 512u); tmem_relinquish(); }
+    if (warp == 1) { tmem_alloc(tmem_slot, kTaCols); tmem_relinquish(); }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = lds32(tmem_slot);
-    const uint32_t tS = tmem, tO = tmem + 256u;
+    const uint32_t tS = tmem, tO = tmem + 2u * kTaBN;
 
     if (warp == 0) {
         if (lane == 0) {
-            mbar_expect_tx(b_q, (uint32_t)kTaTile);
+            mbar_expect_tx(b_q, (uint32_t)kTaQTile);
             tma_load_2d(sQ, &a.tq, head * kTaHD, q0, b_q);
-            tma_load_2d(sQ + kTaHalf, &a.tq, head * kTaHD + 64, q0, b_q);
+            tma_load_2d(sQ + kTaQHalf, &a.tq, head * kTaHD + 64, q0, b_q);
             for (int j = 0; j < nj; ++j) {
                 const int s = j & 1;
                 if (!mbar_wait(b_kvfree + 8 * s, (((uint32_t)j >> 1) & 1u) ^ 1u)) { failed = true; break; }
-                mbar_expect_tx(b_kvfull + 8 * s, 2u * kTaTile);
-                tma_load_3d(sK + s * kTaTile, &a.tk, 0, j * kTaBN, kvh, b_kvfull + 8 * s);
-                tma_load_3d(sK + s * kTaTile + kTaHalf, &a.tk, 64, j * kTaBN, kvh, b_kvfull + 8 * s);
-                tma_load_3d(sV + s * kTaTile, &a.tv, 0, j * kTaBN, kvh, b_kvfull + 8 * s);
-                tma_load_3d(sV + s * kTaTile + kTaHalf, &a.tv, 64, j * kTaBN, kvh, b_kvfull + 8 * s);
+                mbar_expect_tx(b_kvfull + 8 * s, 2u * kTaKTile);
+                tma_load_3d(sK + s * kTaKTile, &a.tk, 0, j * kTaBN, kvh, b_kvfull + 8 * s);
+                tma_load_3d(sK + s * kTaKTile + kTaKHalf, &a.tk, 64, j * kTaBN, kvh, b_kvfull + 8 * s);
+                tma_load_3d(sV + s * kTaKTile, &a.tv, 0, j * kTaBN, kvh, b_kvfull + 8 * s);
+                tma_load_3d(sV + s * kTaKTile + kTaKHalf, &a.tv, 64, j * kTaBN, kvh, b_kvfull + 8 * s);
             }
         }
     } else if (warp == 1) {
@@ -86,8 +93,8 @@ __global__ void __launch_bounds__(kTaThreads, 1) prefill_attn_tc_kernel(const __
                 tc_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < kTaHD / 16; ++ks) {
-                    const uint32_t off = (uint32_t)((ks >> 2) * kTaHalf + (ks & 3) * 32);
-                    umma_f16(tS + (uint32_t)(s * kTaBN), umma_desc_sw128(sQ + off, 16, 1024), umma_desc_sw128(sK + s * kTaTile + off, 16, 1024), idS, (uint32_t)(ks != 0));
+                    umma_f16(tS + (uint32_t)(s * kTaBN), umma_desc_sw128(sQ + (uint32_t)((ks >> 2) * kTaQHalf + (ks & 3) * 32), 16, 1024),
+                             umma_desc_sw128(sK + s * kTaKTile + (uint32_t)((ks >> 2) * kTaKHalf + (ks & 3) * 32), 16, 1024), idS, (uint32_t)(ks != 0));
                 }
                 umma_commit(b_sfull + 8 * s);
                 return true;
@@ -101,8 +108,8 @@ __global__ void __launch_bounds__(kTaThreads, 1) prefill_attn_tc_kernel(const __
                 tc_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < kTaBN / 16; ++ks)       // sixteen keys a step: V rows 16 ks .., P columns 16 ks ..
-                    umma_f16(tO, umma_desc_sw128(sP + (uint32_t)((ks >> 2) * kTaHalf + (ks & 3) * 32), 16, 1024),
-                             umma_desc_sw128(sV + s * kTaTile + ks * 2048, kTaHalf, 1024), idPV, (uint32_t)((j | ks) != 0));
+                    umma_f16(tO, umma_desc_sw128(sP + (uint32_t)(ks * 32), 16, 1024),
+                             umma_desc_sw128(sV + s * kTaKTile + ks * 2048, kTaKHalf, 1024), idPV, (uint32_t)((j | ks) != 0));
                 umma_commit(b_pv);
                 umma_commit(b_kvfree + 8 * s);
             }
@@ -111,6 +118,9 @@ __global__ void __launch_bounds__(kTaThreads, 1) prefill_attn_tc_kernel(const __
         const int r = (warp & 3) * 32 + lane;                             // query row of the tile = TMEM lane
         const int qpos = a.pos0 + q0 + r;
         const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
+        // m is the exponent the row's probabilities are scaled by, not always its running maximum: it moves only when
+        // a tile's maximum exceeds it by more than 2^8 (probabilities then stay below 256, well inside fp16, and the
+        // row sum is fp32), so that most tiles need neither a second pass over S nor a rescale of O in TMEM.
         float m = -INFINITY, l = 0.f;
         for (int j = 0; j < nj && !failed; ++j) {
             const int s = j & 1;
@@ -118,53 +128,53 @@ __global__ void __launch_bounds__(kTaThreads, 1) prefill_attn_tc_kernel(const __
             tc_fence_after();
             const uint32_t ts = tS + (uint32_t)(s * kTaBN) + lane_off;
             const bool diag = j * kTaBN + kTaBN - 1 > a.pos0 + q0;        // some key of this tile may lie past some query (uniform over the CTA)
-            float mx = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                float v[32];
-                tmem_ld32(ts + (uint32_t)(c * 32), v);
+            uint32_t pk[kTaBN / 2];
+            float rs = 0.f, mx = -INFINITY, alpha = 1.f;
+            bool moved = false;
+            for (int pass = 0; pass < 2; ++pass) {
+                rs = 0.f;
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    float x = v[i] * a.scale_log2;
-                    if (diag && j * kTaBN + c * 32 + i > qpos) x = -INFINITY;
-                    mx = fmaxf(mx, x);
+                for (int c = 0; c < kTaBN / 32; ++c) {
+                    float v[32];
+                    tmem_ld32(ts + (uint32_t)(c * 32), v);
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        float x0 = v[i] * a.scale_log2, x1 = v[i + 1] * a.scale_log2;
+                        if (diag && j * kTaBN + c * 32 + i > qpos) x0 = -INFINITY;
+                        if (diag && j * kTaBN + c * 32 + i + 1 > qpos) x1 = -INFINITY;
+                        mx = fmaxf(mx, fmaxf(x0, x1));
+                        const float e0 = ta_ex2(x0 - m), e1 = ta_ex2(x1 - m);      // first pass of the first tile: m = -inf, the values are thrown away
+                        rs += e0 + e1;
+                        pk[c * 16 + (i >> 1)] = pack_h2(e0, e1);
+                    }
                 }
+                if (pass == 1) break;
+                const bool mine = mx > m + 8.0f;                          // also true on the first tile (m = -inf; key 0 is visible to every query)
+                if (!__any_sync(0xffffffffu, mine)) break;                // warp-uniform: the TMEM accesses below are warp-wide
+                if (mine) { alpha = m == -INFINITY ? 0.f : ta_ex2(m - mx); m = mx; }
+                moved = true;
             }
-            const float mn = fmaxf(m, mx);                                // finite from the first tile on: key 0 is visible to every query
-            const float alpha = ta_ex2(m - mn);
-            m = mn;
             if (j > 0) {
                 if (!mbar_wait(b_pv, (uint32_t)(j - 1) & 1u)) { failed = true; break; }   // P V of the previous tile is complete: O and the P tile are ours
                 tc_fence_after();
+                if (moved) {
 #pragma unroll 1
-                for (int c = 0; c < 4; ++c) {
-                    float v[32];
-                    tmem_ld32(tO + lane_off + (uint32_t)(c * 32), v);
+                    for (int c = 0; c < 4; ++c) {
+                        float v[32];
+                        tmem_ld32(tO + lane_off + (uint32_t)(c * 32), v);
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] *= alpha;
-                    tmem_st32(tO + lane_off + (uint32_t)(c * 32), v);
+                        for (int i = 0; i < 32; ++i) v[i] *= alpha;
+                        tmem_st32(tO + lane_off + (uint32_t)(c * 32), v);
+                    }
+                    tmem_wait_st();
                 }
-                tmem_wait_st();
             }
-            float rs = 0.f;
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                float v[32];
-                tmem_ld32(ts + (uint32_t)(c * 32), v);
-                uint32_t pk[16];
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    float x0 = v[i] * a.scale_log2 - mn, x1 = v[i + 1] * a.scale_log2 - mn;
-                    if (diag && j * kTaBN + c * 32 + i > qpos) x0 = -INFINITY;
-                    if (diag && j * kTaBN + c * 32 + i + 1 > qpos) x1 = -INFINITY;
-                    const float e0 = ta_ex2(x0), e1 = ta_ex2(x1);
-                    rs += e0 + e1;
-                    pk[i >> 1] = pack_h2(e0, e1);
-                }
-                const uint32_t prow = sP + (uint32_t)((c >> 1) * kTaHalf + r * 128);
+            for (int c = 0; c < kTaBN / 32; ++c) {
+                const uint32_t prow = sP + (uint32_t)(r * 128);
 #pragma unroll
                 for (int i = 0; i < 4; ++i)
-                    ta_sts128(prow + ((uint32_t)(((c & 1) * 4 + i) ^ (r & 7)) << 4), make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]));
+                    ta_sts128(prow + ((uint32_t)((c * 4 + i) ^ (r & 7)) << 4), make_uint4(pk[c * 16 + 4 * i], pk[c * 16 + 4 * i + 1], pk[c * 16 + 4 * i + 2], pk[c * 16 + 4 * i + 3]));
             }
             l = l * alpha + rs;
             fence_async_smem();                                           // the tensor core reads P through the async proxy
@@ -195,7 +205,7 @@ __global__ void __launch_bounds__(kTaThreads, 1) prefill_attn_tc_kernel(const __
     if (failed && a.err) atomicExch(a.err, 12u);
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) tmem_dealloc(tmem, 512u);
+    if (warp == 1) tmem_dealloc(tmem, kTaCols);
 }
 
 typedef CUresult (*TaEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
