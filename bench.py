@@ -350,6 +350,19 @@ def run_ours(a):
     par = None if (a.no_parity or a.layers) else parity_leg(eng, a, cfg, path, rank, world, local, dist)
     if rank == 0 and par is not None:
         out["parity"] = par
+    if rank == 0 and world == 1 and not kv8 and cfg["hd"] in (64, 128):
+        # the step before the hot path (the "next" row the prefill kernels cover): one prompt through cuqwen_prefill,
+        # after everything timed above (it overwrites the first rows of the synthetic KV fill)
+        n = min(2048, ctx)
+        toks = np.random.default_rng(SEED).integers(0, cfg["vocab"], size=n).astype(np.int32)
+        eng.prefill(toks[:min(512, n)], 0)
+        eng.prefill(toks, 0)
+        pms = eng.last_decode_ms
+        d, I, nl, qd, kd = cfg["dim"], cfg["inter"], cfg["layers"], cfg["heads"] * cfg["hd"], cfg["kv"] * cfg["hd"]
+        flop = 2.0 * n * (nl * d * (qd + 2 * kd) + (nl - 1) * (qd * d + 3 * d * I)) + 4.0 * cfg["heads"] * cfg["hd"] * (n * (n + 1) / 2) * (nl - 1)
+        out["prefill"] = {"prompt_tokens": n, "ms": round(pms, 3), "prompt_tok_s": round(n / (pms / 1e3), 1), "tflops": round(flop / (pms / 1e3) / 1e12, 1),
+                          "what": "cuqwen_prefill: batched tcgen05 GEMMs and attention filling the KV cache for a prompt; the reference does this with one "
+                                  "qwen_forward per token (bench.py --sweep prefill [--impl reference] compares them)"}
     eng.close()
     if rank == 0 and world == 1 and not a.no_cpu_baseline:
         out["cpu_baseline"] = cpu_baseline(path, cfg, ctx)

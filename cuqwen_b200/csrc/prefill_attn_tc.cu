@@ -133,13 +133,15 @@ __global__ void __launch_bounds__(kTaThreads, 2) prefill_attn_tc_kernel(const __
             bool moved = false;
             for (int pass = 0; pass < 2; ++pass) {
                 rs = 0.f;
+                uint32_t raw[kTaBN / 32][32];
+#pragma unroll
+                for (int c = 0; c < kTaBN / 32; ++c) tmem_ld32_issue(ts + (uint32_t)(c * 32), raw[c]);      // both loads in flight, one wait
+                tmem_wait_ld();
 #pragma unroll
                 for (int c = 0; c < kTaBN / 32; ++c) {
-                    float v[32];
-                    tmem_ld32(ts + (uint32_t)(c * 32), v);
 #pragma unroll
                     for (int i = 0; i < 32; i += 2) {
-                        float x0 = v[i] * a.scale_log2, x1 = v[i + 1] * a.scale_log2;
+                        float x0 = __uint_as_float(raw[c][i]) * a.scale_log2, x1 = __uint_as_float(raw[c][i + 1]) * a.scale_log2;
                         if (diag && j * kTaBN + c * 32 + i > qpos) x0 = -INFINITY;
                         if (diag && j * kTaBN + c * 32 + i + 1 > qpos) x1 = -INFINITY;
                         mx = fmaxf(mx, fmaxf(x0, x1));
