@@ -334,7 +334,8 @@ def run_ours(a):
         "dtype": "int4 weights x fp16 activations, fp32 accumulate", "data": "synthetic",
         "config": workload_config(a, cfg, qid, Kst),
         "arm": {"parallelism": f"tp{world}", "attn_splits": eng.params.attn_splits, "kv_cache": a.kv},
-        "e2e": {"value": round(e2e, 2), "unit": "tok/s", "h2d_bytes_per_step": 32, "d2h_bytes_per_step": 8},
+        "e2e": {"value": round(e2e, 2), "unit": "tok/s", "h2d_bytes_per_step": 16, "d2h_bytes_per_step": 12,
+                "how": "cuqwen_step per token: the host writes token / position into a pinned mailbox that the step's first kernel reads over PCIe (16 B), the last kernel writes token + status + sequence number back (12 B) and the host polls for it"},
         "gpu_launches": Kst * eng.step_launches,
         "clocks": cs.result,
     }

@@ -166,6 +166,7 @@ struct cuqwen_engine {
     __half *spare_up = nullptr, *spare_out = nullptr;     // QwenState::up / mlp_out of the source-compatible layer (never read by the step)
     float *part_o = nullptr, *part_ml = nullptr; unsigned* counters = nullptr;
     StepCtl* ctl = nullptr; StepCtl* h_ctl = nullptr;
+    HostIo* hio = nullptr; HostIo* hio_dev = nullptr; int io_seq = 0; bool ctl_dirty = true;   // mailbox of cuqwen_step (launch.h); ctl_dirty: the device block must be rewritten first
     int* d_hist = nullptr; unsigned* bitmap = nullptr; unsigned long long* best = nullptr; unsigned* ticket = nullptr;
     int* out_ring = nullptr; int ring_cap = 65536; int* h_out = nullptr;   // h_out holds ring_cap + 1 ints
     float* tp_partial = nullptr; unsigned long long* tp_keys = nullptr;
@@ -252,6 +253,9 @@ extern "C" int cuqwen_create(const cuqwen_params* pin, cuqwen_engine** out) {
     CK(dalloc((void**)&e->part_ml, attn_scratch_floats_ml(e->n_kv_l, e->nsplit) * 4));
     CK(dalloc((void**)&e->counters, attn_scratch_counters(e->n_kv_l, e->nsplit) * 4));
     CK(dalloc((void**)&e->ctl, sizeof(StepCtl))); CK(cudaMallocHost((void**)&e->h_ctl, sizeof(StepCtl)));
+    CK(cudaHostAlloc((void**)&e->hio, sizeof(HostIo), cudaHostAllocMapped));
+    memset(e->hio, 0, sizeof(HostIo));
+    CK(cudaHostGetDevicePointer((void**)&e->hio_dev, e->hio, 0));
     CK(dalloc((void**)&e->d_hist, (size_t)p.max_seq_len * 4));
     CK(dalloc((void**)&e->bitmap, ((size_t)e->vocab_l + 31) / 32 * 4));
     CK(dalloc((void**)&e->best, 8)); CK(dalloc((void**)&e->ticket, 4));
@@ -275,6 +279,7 @@ extern "C" void cuqwen_destroy(cuqwen_engine* e) {
                     e->pf_x, e->pf_xn, e->pf_q, e->pf_att, e->pf_g, e->pf_qkv, e->pf_tok};
     for (void* b : bufs) if (b) cudaFree(b);
     if (e->h_ctl) cudaFreeHost(e->h_ctl);
+    if (e->hio) cudaFreeHost(e->hio);
     if (e->h_out) cudaFreeHost(e->h_out);
     cudaEventDestroy(e->ev0); cudaEventDestroy(e->ev1);
     cudaStreamDestroy(e->stream);
@@ -559,7 +564,7 @@ static int record_step(cuqwen_engine* e, cudaStream_t s, bool pdl) {
 #define MARK() do { if (e->prof) { cudaEvent_t ev_; CK(cudaEventCreate(&ev_)); CK(cudaEventRecord(ev_, s)); e->prof->push_back(ev_); } } while (0)
 #define LK(call) do { int r_ = (call); if (r_) return fail(CUQWEN_ERR_CUDA, "%s: %s", #call, cudaGetErrorString((cudaError_t)r_)); ++n; MARK(); } while (0)
     MARK();
-    LK(launch_embed(e->embed, &e->ctl->token, e->x, p.dim, cfg_plain));
+    LK(launch_embed_step(e->embed, e->ctl, e->x, p.dim, cfg_plain));
     {
         std::vector<HostPhase> hp;
         describe_step(e, hp, e->nsplit);
@@ -625,16 +630,41 @@ extern "C" int cuqwen_step(cuqwen_engine* e, int token, int pos, const int* hist
         return fail(CUQWEN_ERR_ARG, "token %d / pos %d / history_len %d out of range", token, pos, history_len);
     CK(cudaSetDevice(e->p.device));
     if (int r = ensure_graph(e)) return r;
-    StepCtl c{}; c.token = token; c.pos = pos; c.hist_len = (history && history_len > 0) ? history_len : 0; c.pad[1] = e->steps_done;
-    *e->h_ctl = c;
-    CK(cudaMemcpyAsync(e->ctl, e->h_ctl, sizeof(StepCtl), cudaMemcpyHostToDevice, e->stream));
-    if (c.hist_len) CK(cudaMemcpyAsync(e->d_hist, history, (size_t)c.hist_len * 4, cudaMemcpyHostToDevice, e->stream));
-    if (int r = run_step(e)) return r;
+    const int hist_len = (history && history_len > 0) ? history_len : 0;
+    if (e->ctl_dirty) {         // after cuqwen_decode_n / a profile run / an error: the device block is put back into the host-fed state once
+        StepCtl c{}; c.pad[1] = e->steps_done; c.io_seq = e->io_seq; c.hio = e->hio_dev;
+        *e->h_ctl = c;
+        CK(cudaMemcpyAsync(e->ctl, e->h_ctl, sizeof(StepCtl), cudaMemcpyHostToDevice, e->stream));
+        e->ctl_dirty = false;
+    }
+    if (hist_len) CK(cudaMemcpyAsync(e->d_hist, history, (size_t)hist_len * 4, cudaMemcpyHostToDevice, e->stream));
+    // token, position and history length travel through the mailbox: no copy call on the way in, none on the way out
+    HostIo* h = e->hio;
+    e->io_seq += 1;
+    h->token = token; h->pos = pos; h->hist_len = hist_len;
+    __atomic_thread_fence(__ATOMIC_RELEASE);
+    *(volatile int*)&h->seq_in = e->io_seq;
+    if (int r = run_step(e)) { e->ctl_dirty = true; return r; }
     e->steps_done += 1;
-    CK(cudaMemcpyAsync(e->h_out, &e->ctl->sampled, 8, cudaMemcpyDeviceToHost, e->stream));   // sampled token + wait-expired word
-    CK(cudaStreamSynchronize(e->stream));
-    if (e->h_out[1]) return fail(CUQWEN_ERR_TIMEOUT, "a bounded device-side wait expired (code %d)", e->h_out[1]);
-    if (out_token) *out_token = e->h_out[0];
+    bool got = false;
+    for (long spins = 0; ; ++spins) {
+        if (h->seq_out == e->io_seq) { got = true; break; }
+        if ((spins & 0x3fff) == 0x3fff) {            // now and then ask the driver: an idle stream without a result, or a fault, ends the wait
+            const cudaError_t q = cudaStreamQuery(e->stream);
+            if (q == cudaSuccess) { got = h->seq_out == e->io_seq; break; }
+            if (q != cudaErrorNotReady) { e->ctl_dirty = true; return fail(CUQWEN_ERR_CUDA, "cuqwen_step: %s", cudaGetErrorString(q)); }
+        }
+    }
+    __atomic_thread_fence(__ATOMIC_ACQUIRE);
+    int tok, err;
+    if (got) { tok = h->sampled; err = h->err; }
+    else {                      // the step finished without posting (cannot happen with the kernels of this library): read the block itself
+        CK(cudaMemcpyAsync(e->h_out, &e->ctl->sampled, 8, cudaMemcpyDeviceToHost, e->stream));
+        CK(cudaStreamSynchronize(e->stream));
+        tok = e->h_out[0]; err = e->h_out[1];
+    }
+    if (err) { e->ctl_dirty = true; return fail(CUQWEN_ERR_TIMEOUT, "a bounded device-side wait expired (code %d)", err); }
+    if (out_token) *out_token = tok;
     return CUQWEN_OK;
 }
 
@@ -720,7 +750,8 @@ extern "C" int cuqwen_decode_n(cuqwen_engine* e, int first_token, int start_pos,
         return fail(CUQWEN_ERR_ARG, "decode_n arguments out of range");
     CK(cudaSetDevice(e->p.device));
     if (int r = ensure_graph(e)) return r;
-    StepCtl c{}; c.token = first_token; c.pos = start_pos; c.auto_advance = 1; c.pad[1] = e->steps_done;
+    StepCtl c{}; c.token = first_token; c.pos = start_pos; c.auto_advance = 1; c.pad[1] = e->steps_done; c.io_seq = e->io_seq; c.hio = e->hio_dev;
+    e->ctl_dirty = true;
     *e->h_ctl = c;
     CK(cudaMemcpyAsync(e->ctl, e->h_ctl, sizeof(StepCtl), cudaMemcpyHostToDevice, e->stream));
     CK(cudaEventRecord(e->ev0, e->stream));
@@ -744,7 +775,8 @@ extern "C" int cuqwen_step_profile(cuqwen_engine* e, int token, int pos, float* 
     if (e->tp > 1 && !e->comm) return fail(CUQWEN_ERR_STATE, "cuqwen_step_profile before cuqwen_tp_init");
     if (token < 0 || token >= e->p.vocab_size || pos < 0 || pos >= e->p.max_seq_len) return fail(CUQWEN_ERR_ARG, "token / pos out of range");
     CK(cudaSetDevice(e->p.device));
-    StepCtl c{}; c.token = token; c.pos = pos; c.pad[1] = e->steps_done;
+    StepCtl c{}; c.token = token; c.pos = pos; c.pad[1] = e->steps_done; c.io_seq = e->io_seq; c.hio = e->hio_dev;
+    e->ctl_dirty = true;
     *e->h_ctl = c;
     CK(cudaMemcpyAsync(e->ctl, e->h_ctl, sizeof(StepCtl), cudaMemcpyHostToDevice, e->stream));
     std::vector<cudaEvent_t> evs;

@@ -37,6 +37,26 @@ int launch_embed(const __half* table, const int* d_token, __half* out, int dim, 
     return launch_k(embed_kernel, dim3((dim / 8 + 255) / 256), dim3(256), 0, cfg, table, d_token, out, dim);
 }
 
+// The same as the first launch of a decode step.  One CTA: thread 0 first takes over what the host left in the mailbox
+// (one 16-byte read of mapped host memory), the others wait for it, and only then are the dependent launches released -
+// a later kernel may read ctl->pos before its own dependency wait.
+__global__ void embed_step_kernel(const __half* __restrict__ table, StepCtl* ctl, __half* __restrict__ out, int dim) {
+    if (threadIdx.x == 0 && ctl->hio && !ctl->auto_advance) {
+        int sq, tk, ps, hl;
+        asm volatile("ld.volatile.global.v4.s32 {%0,%1,%2,%3}, [%4];" : "=r"(sq), "=r"(tk), "=r"(ps), "=r"(hl) : "l"(ctl->hio) : "memory");
+        if (sq != ctl->io_seq) { ctl->token = tk; ctl->pos = ps; ctl->hist_len = hl; ctl->io_seq = sq; }
+        __threadfence();
+    }
+    __syncthreads();
+    pdl_launch_dependents();
+    const uint4* src = reinterpret_cast<const uint4*>(table + (size_t)(*(volatile int*)&ctl->token) * dim);
+    uint4* dst = reinterpret_cast<uint4*>(out);
+    for (int i = threadIdx.x; i < dim / 8; i += blockDim.x) dst[i] = src[i];
+}
+int launch_embed_step(const __half* table, StepCtl* ctl, __half* out, int dim, const LaunchCfg& cfg) {
+    return launch_k(embed_step_kernel, dim3(1), dim3(256), 0, cfg, table, ctl, out, dim);
+}
+
 // ---- stand-alone RMSNorm (reference src/kernels.cu:689-751) ----------------
 __global__ void rmsnorm_kernel(const __half* __restrict__ x, const __half* __restrict__ w, __half* __restrict__ out, int dim, float eps) {
     __shared__ float red[40];
@@ -129,6 +149,11 @@ __device__ __forceinline__ void finish_step(StepCtl* ctl, int token, int* out_ri
         const int o = ctl->out_idx;
         if (out_ring && o < ring_cap) out_ring[o] = token;
         ctl->out_idx = o + 1;
+    } else if (ctl->hio) {             // host-fed step: the result goes to the mailbox, its sequence number last
+        HostIo* h = ctl->hio;
+        h->sampled = token; h->err = ctl->pad[0];
+        __threadfence_system();
+        h->seq_out = ctl->io_seq;
     }
 }
 // Tensor parallel: where a rank's best (value, index) goes.  Every rank stores ONE 64-bit word into every rank's key

@@ -13,6 +13,16 @@ struct AttnArgs;
 // Device-resident control block of one decode step.  The graph reads token /
 // pos / hist_len from here; with auto_advance set the sampler feeds its result
 // back so consecutive graph launches need no host round trip.
+// Host-visible mailbox of a step (pinned, mapped host memory): the host writes the inputs of cuqwen_step here and the
+// step's first kernel fetches them; the step's last kernel leaves the result here and the host polls for it.  No copy
+// call and no stream synchronisation lie between a token going in and the next one coming out.  Two 64-byte lines.
+struct HostIo {
+    int seq_in, token, pos, hist_len;      // one 16-byte unit: read by the device with a single load; seq_in is written last
+    int rsv_in[12];
+    volatile int seq_out;                  // = the seq_in this result belongs to, written after the two words below
+    volatile int sampled, err;
+    int rsv_out[13];
+};
 struct StepCtl {
     int token;
     int pos;
@@ -20,7 +30,10 @@ struct StepCtl {
     int auto_advance;
     int out_idx;      // next slot of the output ring (auto_advance only)
     int sampled;      // result of the last step
-    int pad[2];
+    int pad[2];       // [0] a bounded wait expired (code), [1] steps completed
+    int io_seq;       // seq_in of the last mailbox message taken over
+    int rsv;
+    HostIo* hio;      // the mailbox, or null
 };
 
 struct LaunchCfg {
@@ -45,6 +58,8 @@ size_t attn_scratch_floats_ml(int n_kv, int nsplit);
 size_t attn_scratch_counters(int n_kv, int nsplit);   // u32 tickets
 
 int launch_embed(const __half* table, const int* d_token, __half* out, int dim, const LaunchCfg& cfg);
+// First launch of a decode step: takes over a new mailbox message (unless the step feeds itself), then copies the token's row.
+int launch_embed_step(const __half* table, StepCtl* ctl, __half* out, int dim, const LaunchCfg& cfg);
 int launch_rmsnorm(const __half* x, const __half* w, __half* out, int dim, float eps, const LaunchCfg& cfg);
 int launch_rope(__half* q, __half* k, int n_heads, int n_kv, int hd, const int* d_pos, float theta, int fast, const LaunchCfg& cfg);
 int launch_kv_store(const __half* k, const __half* v, __half* kc, __half* vc, const int* d_pos, int n_kv, int max_seq, int hd, const LaunchCfg& cfg);

@@ -78,7 +78,9 @@ void cuqwen_destroy(cuqwen_engine* e);
 /* load_weights (src/load_weights.cpp:36-165): same file format, same validation; returns a code instead of exit(). */
 int cuqwen_load(cuqwen_engine* e, const char* bin_path);
 
-/* qwen_forward (src/model.cu:183-223): one decode step; host token in, host token out, synchronous. */
+/* qwen_forward (src/model.cu:183-223): one decode step; host token in, host token out, synchronous.  Token and
+ * position travel through a pinned host mailbox that the step's kernels read and write themselves (no copy call, no
+ * stream synchronisation; the reference pays three copies and a synchronisation per token, src/model.cu:193-222). */
 int cuqwen_step(cuqwen_engine* e, int token, int pos, const int* history, int history_len, int* out_token);
 
 /* n greedy steps with the sampled token fed back on the device (no counterpart in the reference, which pays
