@@ -115,6 +115,34 @@ def test_decode_n_equals_step_loop_and_history_penalty(built, tmp_path):
     a.close(); b.close()
 
 
+def test_step_mailbox_survives_mode_changes(built, tmp_path):
+    """cuqwen_step hands token and position to the device through a host mailbox and polls it for the result; the
+    device-fed loop (cuqwen_decode_n), a prefill and a history step in between must not leave it out of step."""
+    cfg, path = write_small(tmp_path, "hd64", 2)
+    a, b = make_engine(cfg, 2, path), make_engine(cfg, 2, path)
+    ref, tok = [], 7
+    for i in range(40):                         # a: nothing but plain steps
+        tok = a.step(tok, i)
+        ref.append(tok)
+    got, tok = [], 7
+    for i in range(6):
+        tok = b.step(tok, i); got.append(tok)
+    got += b.decode_n(tok, 6, 9).tolist()       # positions 6..14, the device feeds itself
+    tok = got[-1]
+    for i in range(15, 20):
+        tok = b.step(tok, i); got.append(tok)
+    b.prefill(np.array([1, 2, 3], np.int32), 100)      # rows far away from the ones in use
+    tok = b.step(tok, 20, history=np.array([5, 6], dtype=np.int32)); got.append(tok)
+    hist_tok = tok
+    for i in range(21, 30):
+        tok = b.step(tok, i); got.append(tok)
+    got += b.decode_n(tok, 30, 10).tolist()
+    assert got[:20] == ref[:20]
+    if hist_tok == ref[20]:                      # the penalised step picked the same token: the rest must agree as well
+        assert got == ref
+    a.close(); b.close()
+
+
 def test_attention_split_count_does_not_change_tokens(built, tmp_path):
     cfg, path = write_small(tmp_path, "hd128", 0)
     ref = None
