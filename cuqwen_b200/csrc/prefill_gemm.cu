@@ -14,8 +14,6 @@ namespace cq {
 __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
     return (uint64_t)((smem_addr >> 4) & 0x3fffu) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
 }
-// Instruction descriptor: D fp32 [4,6) = 1, A and B fp16 (0), both K-major (0), N >> 3 at [17,23), M >> 4 at [24,29).
-constexpr uint32_t kPfIdesc = (1u << 4) | ((uint32_t)(kPfN >> 3) << 17) | ((uint32_t)(kPfM >> 4) << 24);
 
 // 32 weights (one half of a row's K block) -> four 16-byte chunks of fp16(q * scale), stored at the row's swizzled
 // places.  raw: shared address of the half's bytes; brow: the row in the B tile; chunk0: 0 or 4.
@@ -65,11 +63,12 @@ __device__ __forceinline__ void convert_half(uint32_t raw, uint32_t brow, int sw
     }
 }
 
-template <int Q>
+template <int Q, int NT>
 __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const __grid_constant__ PfGemmArgs a) {
     extern __shared__ unsigned char pf_smem_raw[];
     const uint32_t base = (smem_u32(pf_smem_raw) + 1023u) & ~1023u;
-    constexpr int NA = pf_na(Q), NB = pf_nb(Q), kRawBytes = pf_raw_bytes(Q);
+    constexpr int NA = pf_na(Q), NB = pf_nb(Q), kRawBytes = pf_raw_bytes(Q, NT), kPfBBytes = NT * 128;
+    constexpr uint32_t kPfIdesc = umma_idesc_f16(kPfM, NT, 0);
     constexpr int kASlot = kPfMH * kPfABytes;                  // X tiles of one slot
     const uint32_t ring_a = base, ring_raw = ring_a + NA * kASlot, ring_b = ring_raw + NA * kRawBytes;
     const uint32_t bars = ring_b + NB * kPfBBytes;
@@ -78,11 +77,11 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const __gri
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tm = blockIdx.x, tn = blockIdx.y, mh = a.mh;
     const bool swiglu = a.mode == PF_SWIGLU;
-    const int rows_mat = swiglu ? kPfN / 2 : kPfN;            // rows of each matrix in this tile
+    const int rows_mat = swiglu ? NT / 2 : NT;                // rows of each matrix in this tile
     const int nmat = swiglu ? 2 : 1;
     int seg = 0, coff = 0, tseg = tn;                         // plain modes: which matrix this row tile belongs to, its first output column
     if (!swiglu)
-        while (seg + 1 < a.nseg && tseg >= (a.seg_rows[seg] + kPfN - 1) / kPfN) { tseg -= (a.seg_rows[seg] + kPfN - 1) / kPfN; coff += a.seg_rows[seg]; ++seg; }
+        while (seg + 1 < a.nseg && tseg >= (a.seg_rows[seg] + NT - 1) / NT) { tseg -= (a.seg_rows[seg] + NT - 1) / NT; coff += a.seg_rows[seg]; ++seg; }
     const int row0 = tseg * rows_mat;                         // first row inside the matrix
     const int R = a.seg_rows[seg];
     const int nkb = a.K / kPfKB;
@@ -95,7 +94,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const __gri
         mbar_init(bar_done, 1);
         mbar_fence_init();
     }
-    if (warp == 1) { tmem_alloc(tmem_slot, (uint32_t)(mh * kPfN)); tmem_relinquish(); }
+    if (warp == 1) { tmem_alloc(tmem_slot, (uint32_t)(mh * NT)); tmem_relinquish(); }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -103,7 +102,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const __gri
 
     if (warp == 0) {
         if (lane == 0) {
-            const uint32_t wbytes = Q == Q_F16 ? (uint32_t)kPfBBytes : (uint32_t)(kPfN * kRawKb);
+            const uint32_t wbytes = Q == Q_F16 ? (uint32_t)kPfBBytes : (uint32_t)(NT * kRawKb);
             for (int kb = 0; kb < nkb && !failed; ++kb) {
                 const int sa = kb % NA, sb = kb % NB; const uint32_t pa = (uint32_t)(kb / NA) & 1u;
                 if (!mbar_wait(bar_afree + 8 * sa, pa ^ 1u)) { failed = true; break; }
@@ -127,16 +126,19 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const __gri
                 for (int h = 0; h < mh; ++h)
 #pragma unroll
                     for (int k4 = 0; k4 < kPfKB / 16; ++k4)
-                        umma_f16(tmem + (uint32_t)(h * kPfN), umma_desc(at + h * kPfABytes + k4 * 32), umma_desc(bt + k4 * 32), kPfIdesc, (uint32_t)((kb | k4) != 0));
+                        umma_f16(tmem + (uint32_t)(h * NT), umma_desc(at + h * kPfABytes + k4 * 32), umma_desc(bt + k4 * 32), kPfIdesc, (uint32_t)((kb | k4) != 0));
                 umma_commit(bar_afree + 8 * sa);           // both slots may be refilled once these MMAs have read them
                 if (Q != Q_F16) umma_commit(bar_bfree + 8 * sb);
             }
             umma_commit(bar_done);
         }
     } else {
-        const int c = (threadIdx.x - 64) & (kPfN - 1);        // B row of this thread, 0..255
-        const int khalf = (threadIdx.x - 64) >> 8;            // sixteen converter warps: which 32 weights of the row's K block
-        const int mat = swiglu ? c >> 7 : 0, rin = swiglu ? c & 127 : c;
+        // a thread widens a whole row of the K block (NT rows = converter threads) or, where there are twice as many
+        // threads as rows, one half of it
+        constexpr int kPerRow = kPfConvWarps * 32 / NT;       // threads per B row: 1 or 2
+        const int c = (threadIdx.x - 64) & (NT - 1);          // B row of this thread
+        const int khalf = (threadIdx.x - 64) / NT;
+        const int mat = swiglu ? c / rows_mat : 0, rin = swiglu ? c % rows_mat : c;
         const int grow = row0 + rin;
         const bool valid = grow < R;
         if (Q != Q_F16) {
@@ -153,7 +155,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const __gri
                 if (!mbar_wait(bar_full + 8 * sa, pa)) { failed = true; break; }
                 if (!mbar_wait(bar_bfree + 8 * sb, pb ^ 1u)) { failed = true; break; }     // the MMAs of two K blocks ago have read this B slot
 #pragma unroll
-                for (int kh = khalf; kh < 2; kh += kPfConvWarps / 8)
+                for (int kh = khalf; kh < 2; kh += kPerRow)
                     convert_half<Q == Q_F16 ? Q_I8 : Q>(ring_raw + sa * kRawBytes + c * kRawKb + kh * (kRawKb / 2), ring_b + sb * kPfBBytes + c * 128, c & 7, kh * 4, __half2half2(sc_use));
                 fence_async_smem();                            // the tensor core reads through the async proxy
                 __syncwarp();
@@ -167,11 +169,11 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const __gri
             const int q = warp & 3, hh = (warp - 2) >> 2;        // TMEM lane quarter (fixed by the warp's number), column quarter
             const int token = (tm * mh + h) * kPfM + q * 32 + lane;
             const bool tv = token < a.T;
-            const uint32_t tlane = tmem + (uint32_t)(h * kPfN) + ((uint32_t)(q * 32) << 16);
+            const uint32_t tlane = tmem + (uint32_t)(h * NT) + ((uint32_t)(q * 32) << 16);
             if (!swiglu) {
 #pragma unroll 1
-                for (int ch = 0; ch < 32 / kPfConvWarps; ++ch) {
-                    const int col = hh * (1024 / kPfConvWarps) + ch * 32;
+                for (int ch = 0; ch < NT / 64; ++ch) {             // eight epilogue warps: two per TMEM lane quarter, half the columns each
+                    const int col = hh * (NT / 2) + ch * 32;
                     float v[32];
                     tmem_ld32(tlane + (uint32_t)col, v);
                     const int r = row0 + col;
@@ -209,11 +211,11 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const __gri
                 }
             } else {
 #pragma unroll 1
-                for (int ch = 0; ch < 16 / kPfConvWarps; ++ch) {
-                    const int col = hh * (512 / kPfConvWarps) + ch * 32;
+                for (int ch = 0; ch < NT / 128; ++ch) {
+                    const int col = hh * (NT / 4) + ch * 32;
                     float g[32], u[32];
                     tmem_ld32(tlane + (uint32_t)col, g);
-                    tmem_ld32(tlane + (uint32_t)(128 + col), u);
+                    tmem_ld32(tlane + (uint32_t)(NT / 2 + col), u);
                     const int r = row0 + col;
                     __half* dst = a.out_h + (size_t)token * a.ldo + r;
 #pragma unroll
@@ -237,7 +239,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const __gri
     if (failed && a.err) atomicExch(a.err, 11u);
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) tmem_dealloc(tmem, (uint32_t)(mh * kPfN));
+    if (warp == 1) tmem_dealloc(tmem, (uint32_t)(mh * NT));
 }
 
 // ---- host side ------------------------------------------------------------------------------------------------------
@@ -263,15 +265,15 @@ static int pf_map(CUtensorMap* m, const void* p, CUtensorMapDataType dt, int ele
     return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
 }
 
-template <int Q>
+template <int Q, int NT>
 static int pf_go(const PfGemmArgs& a, dim3 grid, cudaStream_t stream) {
     static bool once = false;
     if (!once) {
-        const cudaError_t e = cudaFuncSetAttribute(prefill_gemm_kernel<Q>, cudaFuncAttributeMaxDynamicSharedMemorySize, pf_smem_bytes(Q));
+        const cudaError_t e = cudaFuncSetAttribute(prefill_gemm_kernel<Q, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, pf_smem_bytes(Q, NT));
         if (e != cudaSuccess) return (int)e;
         once = true;
     }
-    prefill_gemm_kernel<Q><<<grid, kPfThreads, pf_smem_bytes(Q), stream>>>(a);
+    prefill_gemm_kernel<Q, NT><<<grid, kPfThreads, pf_smem_bytes(Q, NT), stream>>>(a);
     return (int)cudaGetLastError();
 }
 
@@ -279,7 +281,17 @@ int launch_prefill_gemm(int quant, PfGemmArgs& a, const void* x, const void* con
     if (a.T <= 0 || a.K <= 0 || a.K % kGroup || a.ldo % 8 || quant < 0 || quant > 2 || nmat < 1 || nmat > 3) return (int)cudaErrorInvalidValue;
     const bool swiglu = a.mode == PF_SWIGLU;
     if (swiglu && (nmat != 2 || rows[0] != rows[1])) return (int)cudaErrorInvalidValue;
-    const int rows_mat = swiglu ? kPfN / 2 : kPfN;
+    // Tile width: 256 weight rows a CTA, or 128 where the wide tiles would leave more than half of the SMs without a
+    // CTA (short prompts; the projections with few rows): twice the CTAs, each with half the widening and MMA work.
+    int sms = 0, dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    a.mh = a.T > kPfM ? kPfMH : 1;
+    const int mtiles = (a.T + kPfM * a.mh - 1) / (kPfM * a.mh);
+    int wide = 0;
+    for (int m = 0; m < (swiglu ? 1 : nmat); ++m) wide += (rows[m] + (swiglu ? kPfN / 2 : kPfN) - 1) / (swiglu ? kPfN / 2 : kPfN);
+    const int nt = (sms > 0 && wide * mtiles * 2 <= sms) ? kPfN / 2 : kPfN;
+    const int rows_mat = swiglu ? nt / 2 : nt;
     if (int r = pf_map(&a.tx, x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (size_t)a.T, (size_t)a.K, kPfKB, kPfM, true)) return r;
     int tiles = 0;
     a.R = 0;
@@ -296,11 +308,15 @@ int launch_prefill_gemm(int quant, PfGemmArgs& a, const void* x, const void* con
         if (!swiglu || m == 0) { tiles += (rows[m] + rows_mat - 1) / rows_mat; a.R += rows[m]; }
     }
     a.nseg = swiglu ? 1 : nmat;
-    a.mh = a.T > kPfM ? kPfMH : 1;
-    const dim3 grid((a.T + kPfM * a.mh - 1) / (kPfM * a.mh), tiles);
-    if (quant == Q_I4) return pf_go<Q_I4>(a, grid, stream);
-    if (quant == Q_I8) return pf_go<Q_I8>(a, grid, stream);
-    return pf_go<Q_F16>(a, grid, stream);
+    const dim3 grid(mtiles, tiles);
+    if (nt == kPfN) {
+        if (quant == Q_I4) return pf_go<Q_I4, kPfN>(a, grid, stream);
+        if (quant == Q_I8) return pf_go<Q_I8, kPfN>(a, grid, stream);
+        return pf_go<Q_F16, kPfN>(a, grid, stream);
+    }
+    if (quant == Q_I4) return pf_go<Q_I4, kPfN / 2>(a, grid, stream);
+    if (quant == Q_I8) return pf_go<Q_I8, kPfN / 2>(a, grid, stream);
+    return pf_go<Q_F16, kPfN / 2>(a, grid, stream);
 }
 
 }  // namespace cq

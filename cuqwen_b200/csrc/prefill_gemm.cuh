@@ -20,22 +20,22 @@
 namespace cq {
 
 constexpr int kPfM = 128;            // tokens per tile
-constexpr int kPfN = 256;            // weight rows per tile (two matrices of 128 rows each in the SwiGLU mode)
+constexpr int kPfN = 256;            // weight rows per tile (two matrices of 128 rows each in the SwiGLU mode); 128 in the
+                                     // narrow variant the launcher takes when the wide tiles would leave most SMs without a CTA
 constexpr int kPfKB = 64;            // K per pipeline stage: 128 bytes of fp16, one swizzle row
 constexpr int kPfMH = 2;             // token tiles per CTA: two accumulators share every widened weight tile
 constexpr int kPfConvWarps = 8;      // 8: a weight row of a K block per thread; 16: half a row (measured: no faster, the kernel is bound elsewhere)
 constexpr int kPfThreads = (2 + kPfConvWarps) * 32;
 constexpr int kPfABytes = kPfM * 128;          // one X tile of a stage
-constexpr int kPfBBytes = kPfN * 128;          // B tile of a stage
 // Shared memory: a ring of NA slots that TMA fills (kPfMH X tiles + the raw weight rows of a K block: int4 32, int8 64
 // bytes a row) and a ring of NB slots for the fp16 B tile.  The raw data and the X tiles have a TMA round trip to
 // cover, so their ring is the deep one; a widened B tile is consumed by the very next MMAs, two slots suffice.
 // fp16 weights have no raw form: their B tile arrives by TMA, NB = NA.
-__host__ __device__ constexpr int pf_raw_bytes(int quant) { return quant == 2 ? kPfN * 32 : quant == 1 ? kPfN * 64 : 0; }
+__host__ __device__ constexpr int pf_raw_bytes(int quant, int nt) { return quant == 2 ? nt * 32 : quant == 1 ? nt * 64 : 0; }
 __host__ __device__ constexpr int pf_na(int quant) { return quant == 2 ? 4 : 3; }
 __host__ __device__ constexpr int pf_nb(int quant) { return quant == 0 ? 3 : 2; }
-__host__ __device__ constexpr int pf_smem_bytes(int quant) {
-    return pf_na(quant) * (kPfMH * kPfABytes + pf_raw_bytes(quant)) + pf_nb(quant) * kPfBBytes + 1024 /* alignment slack */ + 256 /* barriers, TMEM address */;
+__host__ __device__ constexpr int pf_smem_bytes(int quant, int nt) {
+    return pf_na(quant) * (kPfMH * kPfABytes + pf_raw_bytes(quant, nt)) + pf_nb(quant) * nt * 128 + 1024 /* alignment slack */ + 256 /* barriers, TMEM address */;
 }
 
 enum PfMode : int {
