@@ -131,6 +131,7 @@ __global__ void __launch_bounds__(kTaThreads, 2) prefill_attn_tc_kernel(const __
             uint32_t pk[kTaBN / 2];
             float rs = 0.f, mx = -INFINITY, alpha = 1.f;
             bool moved = false;
+#pragma unroll 1
             for (int pass = 0; pass < 2; ++pass) {
                 rs = 0.f;
                 uint32_t raw[kTaBN / 32][32];
