@@ -361,7 +361,30 @@ def run_ours(a):
         pms = eng.last_decode_ms
         d, I, nl, qd, kd = cfg["dim"], cfg["inter"], cfg["layers"], cfg["heads"] * cfg["hd"], cfg["kv"] * cfg["hd"]
         flop = 2.0 * n * (nl * d * (qd + 2 * kd) + (nl - 1) * (qd * d + 3 * d * I)) + 4.0 * cfg["heads"] * cfg["hd"] * (n * (n + 1) / 2) * (nl - 1)
+        # its dominant kernel alone, the way the dominant decode kernel is reported above: the gate/up + SwiGLU GEMM of
+        # every layer in turn over the prompt's activations (weights 1.9 GB in all: nothing stays in L2), CUDA events
+        gate_ptrs = [(eng.ptr("WGATE", l)[0], eng.ptr("WUP", l)[0], eng.ptr("SGATE", l)[0] or None, eng.ptr("SUP", l)[0] or None) for l in range(nl)]
+        xa = E.DevBuf.from_numpy(np.random.default_rng(1).standard_normal((n, d)).astype(np.float16), eng.device)
+        ga = E.DevBuf(n * I * 2, eng.device)
+
+        def gemm_sweep():
+            for wg, wu, sg, su in gate_ptrs:
+                K.prefill_gemm(qid, K.PF_SWIGLU, xa, wg, sg, ga, n, I, d, w1=wu, s1=su, device=eng.device)
+        gemm_sweep()
+        E.sync(eng.device)
+        K.bench_begin(eng.device)
+        for _ in range(3):
+            gemm_sweep()
+        gsec = K.bench_end(eng.device) / 1e3 / (3 * nl)
+        gflop = 2.0 * n * d * 2 * I
+        tpeak = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
+        burst, sustained = float(tpeak.get("bf16_tflops", 1590.0)), float(tpeak.get("bf16_tflops_sustained", 1400.0))
         out["prefill"] = {"prompt_tokens": n, "ms": round(pms, 3), "prompt_tok_s": round(n / (pms / 1e3), 1), "tflops": round(flop / (pms / 1e3) / 1e12, 1),
+                          "roofline": {"bound": "tensor", "kernel": f"prefill_gemm_kernel<{a.quant}> (gate/up GEMM + SwiGLU, {n} x {d} x {2 * I}, tcgen05)",
+                                       "achieved": round(gflop / gsec / 1e12, 1), "peak": burst, "unit": "TFLOP/s", "frac": round(gflop / gsec / 1e12 / burst, 4),
+                                       "frac_of_sustained": round(gflop / gsec / 1e12 / sustained, 4), "us_per_launch": round(gsec * 1e6, 1),
+                                       "peak_source": ("measured (MEASURED_PEAKS.json bf16_tflops: cuBLAS burst; bf16_tflops_sustained for the second fraction), of measured"
+                                                       if tpeak else "fallback (1590 / 1400 TFLOP/s), of fallback")},
                           "what": "cuqwen_prefill: batched tcgen05 GEMMs and attention filling the KV cache for a prompt; the reference does this with one "
                                   "qwen_forward per token (bench.py --sweep prefill [--impl reference] compares them)"}
     eng.close()
