@@ -15,17 +15,19 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
     return (uint64_t)((smem_addr >> 4) & 0x3fffu) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
 }
 
-// 32 weights (one half of a row's K block) -> four 16-byte chunks of fp16(q * scale), stored at the row's swizzled
-// places.  raw: shared address of the half's bytes; brow: the row in the B tile; chunk0: 0 or 4.
-template <int Q>
-__device__ __forceinline__ void convert_half(uint32_t raw, uint32_t brow, int sw, int chunk0, __half2 sc2) {
+// W weights (32 or 16: one half or one quarter of a row's K block) -> W / 8 sixteen-byte chunks of fp16(q * scale),
+// stored at the row's swizzled places.  raw: shared address of the part's bytes; brow: the row in the B tile; chunk0:
+// the part's first chunk.
+template <int Q, int W>
+__device__ __forceinline__ void convert_part(uint32_t raw, uint32_t brow, int sw, int chunk0, __half2 sc2) {
     if (Q == Q_I4) {
         // two's-complement nibbles, element 2p in the low nibble of byte p: (n ^ 8) | 0x6400 is fp16(1024 + q + 8)
         const __half2 off = __floats2half2_rn(1032.f, 1032.f);
-        const uint4 rw = lds128(raw);
-        const uint32_t w4[4] = {rw.x, rw.y, rw.z, rw.w};
+        uint32_t w4[4];
+        if (W == 32) { const uint4 rw = lds128(raw); w4[0] = rw.x; w4[1] = rw.y; w4[2] = rw.z; w4[3] = rw.w; }
+        else { asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(w4[0]), "=r"(w4[1]) : "r"(raw)); w4[2] = w4[3] = 0u; }
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
+        for (int i = 0; i < W / 8; ++i) {
             const uint32_t w = w4[i];
             uint32_t t[4];
 #pragma unroll
@@ -43,7 +45,7 @@ __device__ __forceinline__ void convert_half(uint32_t raw, uint32_t brow, int sw
         // signed bytes: (b ^ 0x80) under a 0x64 exponent byte is fp16(1024 + b + 128)
         const __half2 off = __floats2half2_rn(1152.f, 1152.f);
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
+        for (int h = 0; h < W / 16; ++h) {
             const uint4 rw = lds128(raw + h * 16);
             const uint32_t w4[4] = {rw.x, rw.y, rw.z, rw.w};
 #pragma unroll
@@ -133,11 +135,11 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const __gri
             umma_commit(bar_done);
         }
     } else {
-        // a thread widens a whole row of the K block (NT rows = converter threads) or, where there are twice as many
-        // threads as rows, one half of it
-        constexpr int kPerRow = kPfConvWarps * 32 / NT;       // threads per B row: 1 or 2
+        // a thread widens a whole row of the K block (as many rows as converter threads), or, with two or four times
+        // as many threads as rows, a half or a quarter of one
+        constexpr int kPerRow = kPfConvWarps * 32 / NT;       // threads per B row: 1, 2 or 4
         const int c = (threadIdx.x - 64) & (NT - 1);          // B row of this thread
-        const int khalf = (threadIdx.x - 64) / NT;
+        const int kpart = (threadIdx.x - 64) / NT;
         const int mat = swiglu ? c / rows_mat : 0, rin = swiglu ? c % rows_mat : c;
         const int grow = row0 + rin;
         const bool valid = grow < R;
@@ -154,9 +156,16 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const __gri
                 if (kb & 1) { sc = sc1; sc1 = sc2; const int g3 = (kb >> 1) + 3; sc2 = valid && g3 < ngrp ? srow[g3] : zero; }
                 if (!mbar_wait(bar_full + 8 * sa, pa)) { failed = true; break; }
                 if (!mbar_wait(bar_bfree + 8 * sb, pb ^ 1u)) { failed = true; break; }     // the MMAs of two K blocks ago have read this B slot
+                {
+                    constexpr int QQ = Q == Q_F16 ? Q_I8 : Q;
+                    const uint32_t rawrow = ring_raw + sa * kRawBytes + c * kRawKb, brow = ring_b + sb * kPfBBytes + c * 128;
+                    if (kPerRow == 4) convert_part<QQ, 16>(rawrow + kpart * (kRawKb / 4), brow, c & 7, kpart * 2, __half2half2(sc_use));
+                    else {
 #pragma unroll
-                for (int kh = khalf; kh < 2; kh += kPerRow)
-                    convert_half<Q == Q_F16 ? Q_I8 : Q>(ring_raw + sa * kRawBytes + c * kRawKb + kh * (kRawKb / 2), ring_b + sb * kPfBBytes + c * 128, c & 7, kh * 4, __half2half2(sc_use));
+                        for (int kh = kpart; kh < 2; kh += kPerRow)
+                            convert_part<QQ, 32>(rawrow + kh * (kRawKb / 2), brow, c & 7, kh * 4, __half2half2(sc_use));
+                    }
+                }
                 fence_async_smem();                            // the tensor core reads through the async proxy
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_conv + 8 * sb);
@@ -172,7 +181,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const __gri
             const uint32_t tlane = tmem + (uint32_t)(h * NT) + ((uint32_t)(q * 32) << 16);
             if (!swiglu) {
 #pragma unroll 1
-                for (int ch = 0; ch < NT / 64; ++ch) {             // eight epilogue warps: two per TMEM lane quarter, half the columns each
+                for (int ch = 0; ch < NT / 64; ++ch) {             // eight epilogue warps: two per TMEM lane quarter, half the columns each (32 columns a warp at the least)
                     const int col = hh * (NT / 2) + ch * 32;
                     float v[32];
                     tmem_ld32(tlane + (uint32_t)col, v);
@@ -211,8 +220,8 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const __gri
                 }
             } else {
 #pragma unroll 1
-                for (int ch = 0; ch < NT / 128; ++ch) {
-                    const int col = hh * (NT / 4) + ch * 32;
+                for (int ch = 0; ch < (NT >= 128 ? NT / 128 : (hh == 0 ? 1 : 0)); ++ch) {       // 64-row tiles: 32 gate + 32 up columns, one warp per lane quarter takes them
+                    const int col = NT >= 128 ? hh * (NT / 4) + ch * 32 : 0;
                     float g[32], u[32];
                     tmem_ld32(tlane + (uint32_t)col, g);
                     tmem_ld32(tlane + (uint32_t)(NT / 2 + col), u);
@@ -281,8 +290,8 @@ int launch_prefill_gemm(int quant, PfGemmArgs& a, const void* x, const void* con
     if (a.T <= 0 || a.K <= 0 || a.K % kGroup || a.ldo % 8 || quant < 0 || quant > 2 || nmat < 1 || nmat > 3) return (int)cudaErrorInvalidValue;
     const bool swiglu = a.mode == PF_SWIGLU;
     if (swiglu && (nmat != 2 || rows[0] != rows[1])) return (int)cudaErrorInvalidValue;
-    // Tile width: 256 weight rows a CTA, or 128 where the wide tiles would leave more than half of the SMs without a
-    // CTA (short prompts; the projections with few rows): twice the CTAs, each with half the widening and MMA work.
+    // Tile width: 256 weight rows a CTA; 128 or 64 where the wide tiles would leave more than half / three quarters of
+    // the SMs without a CTA (short prompts; the projections with few rows): more CTAs, each with less widening and MMA work.
     int sms = 0, dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -290,7 +299,7 @@ int launch_prefill_gemm(int quant, PfGemmArgs& a, const void* x, const void* con
     const int mtiles = (a.T + kPfM * a.mh - 1) / (kPfM * a.mh);
     int wide = 0;
     for (int m = 0; m < (swiglu ? 1 : nmat); ++m) wide += (rows[m] + (swiglu ? kPfN / 2 : kPfN) - 1) / (swiglu ? kPfN / 2 : kPfN);
-    const int nt = (sms > 0 && wide * mtiles * 2 <= sms) ? kPfN / 2 : kPfN;
+    const int nt = (sms > 0 && wide * mtiles * 4 <= sms) ? kPfN / 4 : (sms > 0 && wide * mtiles * 2 <= sms) ? kPfN / 2 : kPfN;
     const int rows_mat = swiglu ? nt / 2 : nt;
     if (int r = pf_map(&a.tx, x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (size_t)a.T, (size_t)a.K, kPfKB, kPfM, true)) return r;
     int tiles = 0;
@@ -314,9 +323,14 @@ int launch_prefill_gemm(int quant, PfGemmArgs& a, const void* x, const void* con
         if (quant == Q_I8) return pf_go<Q_I8, kPfN>(a, grid, stream);
         return pf_go<Q_F16, kPfN>(a, grid, stream);
     }
-    if (quant == Q_I4) return pf_go<Q_I4, kPfN / 2>(a, grid, stream);
-    if (quant == Q_I8) return pf_go<Q_I8, kPfN / 2>(a, grid, stream);
-    return pf_go<Q_F16, kPfN / 2>(a, grid, stream);
+    if (nt == kPfN / 2) {
+        if (quant == Q_I4) return pf_go<Q_I4, kPfN / 2>(a, grid, stream);
+        if (quant == Q_I8) return pf_go<Q_I8, kPfN / 2>(a, grid, stream);
+        return pf_go<Q_F16, kPfN / 2>(a, grid, stream);
+    }
+    if (quant == Q_I4) return pf_go<Q_I4, kPfN / 4>(a, grid, stream);
+    if (quant == Q_I8) return pf_go<Q_I8, kPfN / 4>(a, grid, stream);
+    return pf_go<Q_F16, kPfN / 4>(a, grid, stream);
 }
 
 }  // namespace cq

@@ -21,8 +21,9 @@ def dequant(w, s, quant, cols):
 
 
 @pytest.mark.parametrize("quant", [2, 1, 0])
-# the launcher takes 128-row tiles while 256-row tiles would fill less than half of the SMs: the last case is wide enough for 256
-@pytest.mark.parametrize("T,R,Kc", [(1, 256, 128), (37, 512, 896), (128, 576, 3584), (300, 1024, 1536), (257, 264, 256), (600, 6408, 256)])
+# the launcher takes 64- or 128-row tiles while 256-row tiles would fill less than a quarter / half of the SMs: the last
+# two cases are wide enough for 128 and for 256
+@pytest.mark.parametrize("T,R,Kc", [(1, 256, 128), (37, 512, 896), (128, 576, 3584), (300, 1024, 1536), (257, 264, 256), (300, 6408, 256), (600, 6408, 256)])
 def test_prefill_gemm_plain_modes(built, quant, T, R, Kc):
     rng = np.random.default_rng(T * 131 + R + quant)
     x = rng.standard_normal((T, Kc)).astype(np.float16)
@@ -55,7 +56,7 @@ def test_prefill_gemm_plain_modes(built, quant, T, R, Kc):
 
 
 @pytest.mark.parametrize("quant", [2, 1, 0])
-@pytest.mark.parametrize("T,R,Kc", [(5, 128, 256), (130, 320, 896), (256, 1024, 1536), (300, 4872, 256)])
+@pytest.mark.parametrize("T,R,Kc", [(5, 128, 256), (130, 320, 896), (256, 1024, 1536), (130, 4872, 256), (300, 4872, 256)])
 def test_prefill_gemm_swiglu(built, quant, T, R, Kc):
     rng = np.random.default_rng(T + R * 3 + quant)
     x = rng.standard_normal((T, Kc)).astype(np.float16)
