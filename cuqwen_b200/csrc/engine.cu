@@ -726,7 +726,7 @@ extern "C" int cuqwen_prefill(cuqwen_engine* e, const int* tokens, int n_tokens,
             PfAttnArgs aa; memset(&aa, 0, sizeof aa);
             aa.q = e->pf_q; aa.kc = ra.kcache; aa.vc = ra.vcache; aa.out = e->pf_att; aa.T = T; aa.pos0 = pos; aa.n_heads = e->n_heads_l;
             aa.grp = e->plan.grp; aa.max_seq = p.max_seq_len; aa.ldq = qd; aa.scale_log2 = (1.0f / sqrtf((float)p.head_dim)) * 1.4426950408889634f;
-            if (p.head_dim == 128 && !(p.flags & CUQWEN_FLAG_PREFILL_ATTN_MMA)) PK(launch_prefill_attn_tc(aa, e->n_kv_l, t_err, e->stream));
+            if (!(p.flags & CUQWEN_FLAG_PREFILL_ATTN_MMA)) PK(launch_prefill_attn_tc(p.head_dim, aa, e->n_kv_l, t_err, e->stream));
             else PK(launch_prefill_attn(p.head_dim, aa, e->stream));
             if (int r = prefill_gemm(e, PF_RESID, e->pf_att, om, 1, e->pf_x, T, p.dim)) return r;
             PK(launch_pf_rmsnorm(e->pf_x, L.post_norm, e->pf_xn, T, p.dim, eps, e->stream));
@@ -1127,12 +1127,12 @@ extern "C" int cuqwen_k_prefill_attention(int device, int impl, const void* q, c
     DEV(device); (void)cfg;
     NOT_NULL(q, kcache, vcache, out);
     if (n_kv_heads <= 0 || n_heads % n_kv_heads) return fail(CUQWEN_ERR_ARG, "n_heads must be a multiple of n_kv_heads");
-    if ((impl == 0 && head_dim != 128) || (impl == 1 && head_dim != 64 && head_dim != 128) || impl < 0 || impl > 1) return fail(CUQWEN_ERR_ARG, "impl / head_dim combination not available");
+    if ((head_dim != 64 && head_dim != 128) || impl < 0 || impl > 1) return fail(CUQWEN_ERR_ARG, "impl 0 / 1, head_dim 64 / 128");
     PfAttnArgs a; memset(&a, 0, sizeof a);
     a.q = (const __half*)q; a.kc = (const __half*)kcache; a.vc = (const __half*)vcache; a.out = (__half*)out; a.T = n_tokens; a.pos0 = pos0;
     a.n_heads = n_heads; a.grp = n_heads / n_kv_heads; a.max_seq = max_seq_len; a.ldq = q_stride;
     a.scale_log2 = (1.0f / sqrtf((float)head_dim)) * 1.4426950408889634f;
-    if (impl == 0) KK(launch_prefill_attn_tc(a, n_kv_heads, t_err, dc->stream));
+    if (impl == 0) KK(launch_prefill_attn_tc(head_dim, a, n_kv_heads, t_err, dc->stream));
     else KK(launch_prefill_attn(head_dim, a, dc->stream));
     return CUQWEN_OK;
 }

@@ -14,8 +14,8 @@ struct PfAttnArgs {
     float scale_log2;         // log2(e) / sqrt(hd)
 };
 int launch_prefill_attn(int head_dim, const PfAttnArgs& a, cudaStream_t stream);          // mma.sync, head_dim 64 / 128
-// tcgen05 kernel, head_dim 128 only; kc / vc must be the caches' [n_kv][max_seq][128] base.  *err receives a code when a bounded wait expires.
-int launch_prefill_attn_tc(const PfAttnArgs& a, int n_kv, unsigned* err, cudaStream_t stream);
+// tcgen05 kernel, head_dim 64 / 128; kc / vc must be the caches' [n_kv][max_seq][head_dim] base.  *err receives a code when a bounded wait expires.
+int launch_prefill_attn_tc(int head_dim, const PfAttnArgs& a, int n_kv, unsigned* err, cudaStream_t stream);
 
 struct PfRopeArgs {
     const float* qkv;         // [T][q_dim + 2 kv_dim] fp32 sums

@@ -1,6 +1,6 @@
-// Causal attention for a tile of prompt tokens on the tcgen05 tensor cores (head_dim 128): the batched counterpart of
+// Causal attention for a tile of prompt tokens on the tcgen05 tensor cores (head_dim 64 or 128): the batched counterpart of
 // the reference's decode attention (src/kernels.cu:105-288), which the reference applies once per prompt token
-// (src/main.cu:86-92).  prefill_attn.cu holds the mma.sync kernel this one replaces where head_dim is 128.
+// (src/main.cu:86-92).  prefill_attn.cu holds the mma.sync kernel this one replaces (kept as the comparison variant).
 //
 // One CTA = 128 queries of one head, two CTAs to an SM.  Per tile of 64 keys:
 //   warp 0      TMA: K and V tiles of the head's KV group (two 64-column boxes each, hardware-swizzled), two slots
@@ -17,21 +17,22 @@
 
 namespace cq {
 
-constexpr int kTaBM = 128, kTaBN = 64, kTaHD = 128;
+constexpr int kTaBM = 128, kTaBN = 64;
 constexpr int kTaThreads = 192;
-constexpr int kTaQTile = kTaBM * kTaHD * 2;       // 32 KB: two 64-column blocks of [128 rows][128 bytes]
-constexpr int kTaQHalf = kTaQTile / 2;
-constexpr int kTaKTile = kTaBN * kTaHD * 2;       // 16 KB: two 64-column blocks of [64 keys][128 bytes]
-constexpr int kTaKHalf = kTaKTile / 2;
 constexpr int kTaPTile = kTaBM * kTaBN * 2;       // 16 KB: [128 rows][64 keys]
-// Q, K x 2, V x 2, P; barriers (the dynamic shared memory is declared 1024-byte aligned).  112 KB and at most 170 registers: two CTAs share an SM, one's softmax
-// (a single warp per scheduler, bound by its own dependent chain) runs under the other's MMAs.
-constexpr int kTaSmem = kTaQTile + 4 * kTaKTile + kTaPTile + 256;      // 114,944 B: twice that and the 1 KB the system keeps per CTA fit an SM's 228 KB
-constexpr uint32_t kTaCols = 256;                 // TMEM columns: S x 2 (64 each), O (128)
+// Per head_dim HD (128 or 64): Q tile = HD / 64 blocks of [128 rows][128 bytes], K and V tiles = HD / 64 blocks of
+// [64 keys][128 bytes].  Q, K x 2, V x 2, P, barriers (the dynamic shared memory is declared 1024-byte aligned):
+// 112 KB for HD 128 and at most 170 registers, so two CTAs share an SM and one's softmax (a single warp per scheduler,
+// bound by its own dependent chain) runs under the other's MMAs.  Twice 114,944 B and the 1 KB the system keeps per
+// CTA fit an SM's 228 KB.
+__host__ __device__ constexpr int ta_q_tile(int hd) { return kTaBM * hd * 2; }
+__host__ __device__ constexpr int ta_k_tile(int hd) { return kTaBN * hd * 2; }
+__host__ __device__ constexpr int ta_smem(int hd) { return ta_q_tile(hd) + 4 * ta_k_tile(hd) + kTaPTile + 256; }
+constexpr uint32_t kTaCols = 256;                 // TMEM columns: S x 2 (64 each), O (HD)
 
 struct PfAttnTcArgs {
     CUtensorMap tq;          // q as [T][ldq] fp16, box 64 x 128, swizzled
-    CUtensorMap tk, tv;      // caches as [n_kv][max_seq][128] fp16, box 64 x 128 x 1, swizzled
+    CUtensorMap tk, tv;      // caches as [n_kv][max_seq][hd] fp16, box 64 x 64 x 1, swizzled
     __half* out;
     int T, pos0, n_heads, grp, ldq;
     float scale_log2;
@@ -43,7 +44,9 @@ __device__ __forceinline__ void ta_sts128(uint32_t addr, uint4 v) {
     asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
+template <int HD>
 __global__ void __launch_bounds__(kTaThreads, 2) prefill_attn_tc_kernel(const __grid_constant__ PfAttnTcArgs a) {
+    constexpr int kTaHD = HD, kTaQTile = ta_q_tile(HD), kTaQHalf = kTaBM * 128, kTaKTile = ta_k_tile(HD), kTaKHalf = kTaBN * 128, NBLK = HD / 64;
     extern __shared__ __align__(1024) unsigned char ta_smem[];
     const uint32_t base = smem_u32(ta_smem);
     const uint32_t sQ = base, sK = base + kTaQTile, sV = sK + 2 * kTaKTile, sP = sV + 2 * kTaKTile;
@@ -72,16 +75,15 @@ __global__ void __launch_bounds__(kTaThreads, 2) prefill_attn_tc_kernel(const __
     if (warp == 0) {
         if (lane == 0) {
             mbar_expect_tx(b_q, (uint32_t)kTaQTile);
-            tma_load_2d(sQ, &a.tq, head * kTaHD, q0, b_q);
-            tma_load_2d(sQ + kTaQHalf, &a.tq, head * kTaHD + 64, q0, b_q);
+            for (int b = 0; b < NBLK; ++b) tma_load_2d(sQ + b * kTaQHalf, &a.tq, head * kTaHD + 64 * b, q0, b_q);
             for (int j = 0; j < nj; ++j) {
                 const int s = j & 1;
                 if (!mbar_wait(b_kvfree + 8 * s, (((uint32_t)j >> 1) & 1u) ^ 1u)) { failed = true; break; }
                 mbar_expect_tx(b_kvfull + 8 * s, 2u * kTaKTile);
-                tma_load_3d(sK + s * kTaKTile, &a.tk, 0, j * kTaBN, kvh, b_kvfull + 8 * s);
-                tma_load_3d(sK + s * kTaKTile + kTaKHalf, &a.tk, 64, j * kTaBN, kvh, b_kvfull + 8 * s);
-                tma_load_3d(sV + s * kTaKTile, &a.tv, 0, j * kTaBN, kvh, b_kvfull + 8 * s);
-                tma_load_3d(sV + s * kTaKTile + kTaKHalf, &a.tv, 64, j * kTaBN, kvh, b_kvfull + 8 * s);
+                for (int b = 0; b < NBLK; ++b) {
+                    tma_load_3d(sK + s * kTaKTile + b * kTaKHalf, &a.tk, 64 * b, j * kTaBN, kvh, b_kvfull + 8 * s);
+                    tma_load_3d(sV + s * kTaKTile + b * kTaKHalf, &a.tv, 64 * b, j * kTaBN, kvh, b_kvfull + 8 * s);
+                }
             }
         }
     } else if (warp == 1) {
@@ -162,7 +164,7 @@ __global__ void __launch_bounds__(kTaThreads, 2) prefill_attn_tc_kernel(const __
                 tc_fence_after();
                 if (moved) {
 #pragma unroll 1
-                    for (int c = 0; c < 4; ++c) {
+                    for (int c = 0; c < HD / 32; ++c) {
                         float v[32];
                         tmem_ld32(tO + lane_off + (uint32_t)(c * 32), v);
 #pragma unroll
@@ -191,7 +193,7 @@ __global__ void __launch_bounds__(kTaThreads, 2) prefill_attn_tc_kernel(const __
             const float inv = 1.0f / l;
             const int t = q0 + r;
 #pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < HD / 32; ++c) {
                 float v[32];
                 tmem_ld32(tO + lane_off + (uint32_t)(c * 32), v);
                 if (t < a.T) {
@@ -223,7 +225,21 @@ static TaEncodeFn ta_encode() {
     return fn;
 }
 
-int launch_prefill_attn_tc(const PfAttnArgs& a, int n_kv, unsigned* err, cudaStream_t stream) {
+template <int HD>
+static int ta_go(const PfAttnTcArgs& k, dim3 grid, cudaStream_t stream) {
+    static bool once = false;
+    if (!once) {
+        const cudaError_t e = cudaFuncSetAttribute(prefill_attn_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, ta_smem(HD));
+        if (e != cudaSuccess) return (int)e;
+        once = true;
+    }
+    prefill_attn_tc_kernel<HD><<<grid, kTaThreads, ta_smem(HD), stream>>>(k);
+    return (int)cudaGetLastError();
+}
+
+int launch_prefill_attn_tc(int head_dim, const PfAttnArgs& a, int n_kv, unsigned* err, cudaStream_t stream) {
+    const int kTaHD = head_dim;
+    if (head_dim != 64 && head_dim != 128) return (int)cudaErrorInvalidValue;
     if (a.T <= 0 || a.pos0 < 0 || a.pos0 + a.T > a.max_seq || a.n_heads <= 0 || a.grp <= 0 || a.ldq % 8 || n_kv <= 0) return (int)cudaErrorInvalidValue;
     TaEncodeFn fn = ta_encode();
     if (!fn) return (int)cudaErrorNotSupported;
@@ -245,15 +261,8 @@ int launch_prefill_attn_tc(const PfAttnArgs& a, int n_kv, unsigned* err, cudaStr
                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) return (int)cudaErrorInvalidValue;
     }
     k.out = a.out; k.T = a.T; k.pos0 = a.pos0; k.n_heads = a.n_heads; k.grp = a.grp; k.ldq = a.ldq; k.scale_log2 = a.scale_log2; k.err = err;
-    static bool once = false;
-    if (!once) {
-        const cudaError_t e = cudaFuncSetAttribute(prefill_attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTaSmem);
-        if (e != cudaSuccess) return (int)e;
-        once = true;
-    }
     const dim3 grid((a.T + kTaBM - 1) / kTaBM, a.n_heads);
-    prefill_attn_tc_kernel<<<grid, kTaThreads, kTaSmem, stream>>>(k);
-    return (int)cudaGetLastError();
+    return head_dim == 128 ? ta_go<128>(k, grid, stream) : ta_go<64>(k, grid, stream);
 }
 
 }  // namespace cq

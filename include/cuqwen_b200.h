@@ -46,7 +46,7 @@ enum {
     CUQWEN_FLAG_STEP_TRACE = 16,    /* profiling: every GEMV / attention launch of a step stamps its timeline (CUQWEN_PTR_STEP_TRACE) */
     CUQWEN_FLAG_TP_NCCL = 32,       /* tensor parallel: sum the row-parallel partials with NCCL all-reduce calls instead of peer stores */
     CUQWEN_FLAG_NO_HANDOVER = 64,   /* o_proj and the down projection convert their input themselves instead of taking it staged from the attention fold / the SwiGLU kernel */
-    CUQWEN_FLAG_PREFILL_ATTN_MMA = 512, /* cuqwen_prefill: attention on the mma.sync kernel also where head_dim is 128 (comparison variant; head_dim 64 always uses it) */
+    CUQWEN_FLAG_PREFILL_ATTN_MMA = 512, /* cuqwen_prefill: attention on the mma.sync kernel also where head_dim is 128 (comparison variant) */
     CUQWEN_FLAG_TP_SUM_IN_GEMV = 256, /* tensor parallel, peer-store exchange: no separate sum kernel; every CTA of the GEMV that consumes the
                                      * vector adds the ranks' partials while it stages its input (comparison variant, measured slower) */
     CUQWEN_FLAG_KV_INT8 = 128       /* opt-in, outside the parity contract (the reference keeps fp16, its roadmap names this: README.md:147):
@@ -215,7 +215,7 @@ int cuqwen_k_prefill_gemm(int device, int quant, int mode, const void* x, const 
 /* No counterpart in the reference (see cuqwen_prefill).  Causal attention of n_tokens prompt queries at cache positions
  * pos0 .. pos0 + n_tokens - 1 over the head-major fp16 caches [n_kv_heads][max_seq_len][head_dim], whose rows for those
  * positions must already hold the queries' own keys and values.  q / out: [n_tokens][q_stride] fp16, head h at columns
- * h * head_dim.  impl 0: tcgen05 kernel (head_dim 128), impl 1: mma.sync kernel (head_dim 64 or 128). */
+ * h * head_dim.  impl 0: tcgen05 kernel, impl 1: mma.sync kernel; head_dim 64 or 128. */
 int cuqwen_k_prefill_attention(int device, int impl, const void* q, const void* kcache, const void* vcache, void* out, int n_tokens, int pos0,
                                int n_heads, int n_kv_heads, int head_dim, int max_seq_len, int q_stride);
 int cuqwen_attn_scratch_bytes(int n_kv_heads, int head_dim, int n_splits, size_t* bytes_o, size_t* bytes_ml, size_t* bytes_counters);

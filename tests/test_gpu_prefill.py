@@ -250,7 +250,7 @@ def attn_oracle(q, Kc, Vc, pos0, nh, nkv, hd):
     return out
 
 
-@pytest.mark.parametrize("impl,hd", [(0, 128), (1, 128), (1, 64)])
+@pytest.mark.parametrize("impl,hd", [(0, 128), (0, 64), (1, 128), (1, 64)])
 @pytest.mark.parametrize("T,pos0,nh,nkv", [(1, 0, 4, 2), (37, 0, 4, 2), (128, 5, 2, 1), (300, 0, 7, 1), (200, 333, 4, 4), (513, 129, 2, 2)])
 def test_prefill_attention_kernels(built, impl, hd, T, pos0, nh, nkv):
     rng = np.random.default_rng(T * 7 + pos0 + nh + hd)
