@@ -7,9 +7,9 @@
 //   warp 1      one lane issues S = Q K^T (eight MMAs 128 x 64 x 16, both operands K-major) into one of two TMEM
 //               buffers, and - once the softmax warps have written P - O += P V (four MMAs 128 x 128 x 16, V as the MN-major B
 //               operand straight from its cache layout) into a third
-//   warps 2-5   one query row per thread (TMEM lane = row): read S, scale, mask, write P = 2^(s - m) as fp16 into the
-//               swizzled A tile, row sums in fp32; when a row's maximum outgrows m by 2^8, m moves and O is rescaled
-//               in TMEM by 2^(m_old - m_new) (rare after the first tiles)
+//   warps 2-9   two threads per query row (TMEM lane = row), 32 of the tile's keys each: read S, scale, mask, write
+//               P = 2^(s - m) as fp16 into the swizzled A tile, row sums in fp32; when a row's maximum outgrows m by
+//               2^8, m moves and O is rescaled in TMEM by 2^(m_old - m_new) (rare after the first tiles)
 // S of the next tile is issued before the current tile's P is waited for, so Q K^T overlaps the softmax.
 // Every mbarrier wait is bounded; a wait that runs out sets *err and the CTA drains.
 #include "prefill.cuh"
@@ -18,16 +18,15 @@
 namespace cq {
 
 constexpr int kTaBM = 128, kTaBN = 64;
-constexpr int kTaThreads = 192;
+constexpr int kTaThreads = 320;                   // warp 0 TMA, warp 1 MMA, warps 2-9 softmax
 constexpr int kTaPTile = kTaBM * kTaBN * 2;       // 16 KB: [128 rows][64 keys]
 // Per head_dim HD (128 or 64): Q tile = HD / 64 blocks of [128 rows][128 bytes], K and V tiles = HD / 64 blocks of
 // [64 keys][128 bytes].  Q, K x 2, V x 2, P, barriers (the dynamic shared memory is declared 1024-byte aligned):
-// 112 KB for HD 128 and at most 170 registers, so two CTAs share an SM and one's softmax (a single warp per scheduler,
-// bound by its own dependent chain) runs under the other's MMAs.  Twice 114,944 B and the 1 KB the system keeps per
-// CTA fit an SM's 228 KB.
+// 113 KB for HD 128 and at most 102 registers, so two CTAs share an SM and one's softmax runs under the other's MMAs.
+// Twice 115,456 B and the 1 KB the system keeps per CTA fit an SM's 228 KB.
 __host__ __device__ constexpr int ta_q_tile(int hd) { return kTaBM * hd * 2; }
 __host__ __device__ constexpr int ta_k_tile(int hd) { return kTaBN * hd * 2; }
-__host__ __device__ constexpr int ta_smem(int hd) { return ta_q_tile(hd) + 4 * ta_k_tile(hd) + kTaPTile + 256; }
+__host__ __device__ constexpr int ta_smem(int hd) { return ta_q_tile(hd) + 4 * ta_k_tile(hd) + kTaPTile + 256 + 512; }   // + barriers, + the softmax warps' exchange words
 constexpr uint32_t kTaCols = 256;                 // TMEM columns: S x 2 (64 each), O (HD)
 
 struct PfAttnTcArgs {
@@ -62,7 +61,7 @@ __global__ void __launch_bounds__(kTaThreads, 2) prefill_attn_tc_kernel(const __
     if (threadIdx.x == 0) {
         mbar_init(b_q, 1);
         for (int s = 0; s < 2; ++s) { mbar_init(b_kvfull + 8 * s, 1); mbar_init(b_kvfree + 8 * s, 1); mbar_init(b_sfull + 8 * s, 1); }
-        mbar_init(b_p, 4); mbar_init(b_pv, 1);
+        mbar_init(b_p, 8); mbar_init(b_pv, 1);
         mbar_fence_init();
     }
     if (warp == 1) { tmem_alloc(tmem_slot, kTaCols); tmem_relinquish(); }
@@ -117,87 +116,94 @@ __global__ void __launch_bounds__(kTaThreads, 2) prefill_attn_tc_kernel(const __
             }
         }
     } else {
-        const int r = (warp & 3) * 32 + lane;                             // query row of the tile = TMEM lane
+        // Eight softmax warps: two per TMEM lane quarter (a warp reaches the 32 lanes its number mod 4 names), each with
+        // 32 of a tile's 64 keys and half of the output columns of the same 32 query rows.  The two threads of a row
+        // agree on the row's scaling exponent through 512 bytes of shared memory and two named barriers per tile - so
+        // nothing below leaves the tile loop early: after a wait has run out the warp keeps going without waiting.
+        const int q = warp & 3, hsel = (warp - 2) >> 2;
+        const int r = q * 32 + lane;                                      // query row of the tile = TMEM lane
         const int qpos = a.pos0 + q0 + r;
-        const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
+        const uint32_t lane_off = (uint32_t)(q * 32) << 16;
+        __half* mxbuf = reinterpret_cast<__half*>(ta_smem + (bars - base) + 256);      // [2 halves][128 rows]
+        constexpr int OC = HD / 2;                                        // output columns of this thread
         // m is the exponent the row's probabilities are scaled by, not always its running maximum: it moves only when
         // a tile's maximum exceeds it by more than 2^8 (probabilities then stay below 256, well inside fp16, and the
-        // row sum is fp32), so that most tiles need neither a second pass over S nor a rescale of O in TMEM.
+        // row sum is fp32), so that most tiles need no rescale of O in TMEM.
         float m = -INFINITY, l = 0.f;
-        for (int j = 0; j < nj && !failed; ++j) {
+        for (int j = 0; j < nj; ++j) {
             const int s = j & 1;
-            if (!mbar_wait(b_sfull + 8 * s, ((uint32_t)j >> 1) & 1u)) { failed = true; break; }
+            if (!failed && !mbar_wait(b_sfull + 8 * s, ((uint32_t)j >> 1) & 1u)) failed = true;
             tc_fence_after();
-            const uint32_t ts = tS + (uint32_t)(s * kTaBN) + lane_off;
             const bool diag = j * kTaBN + kTaBN - 1 > a.pos0 + q0;        // some key of this tile may lie past some query (uniform over the CTA)
-            uint32_t pk[kTaBN / 2];
-            float rs = 0.f, mx = -INFINITY, alpha = 1.f;
-            bool moved = false;
-#pragma unroll 1
-            for (int pass = 0; pass < 2; ++pass) {
-                rs = 0.f;
-                uint32_t raw[kTaBN / 32][32];
+            float x[32];
+            tmem_ld32(tS + (uint32_t)(s * kTaBN + hsel * 32) + lane_off, x);
+            float mxl = -INFINITY;
 #pragma unroll
-                for (int c = 0; c < kTaBN / 32; ++c) tmem_ld32_issue(ts + (uint32_t)(c * 32), raw[c]);      // both loads in flight, one wait
-                tmem_wait_ld();
+            for (int i = 0; i < 32; ++i) {
+                x[i] *= a.scale_log2;
+                if (diag && j * kTaBN + hsel * 32 + i > qpos) x[i] = -INFINITY;
+                mxl = fmaxf(mxl, x[i]);
+            }
+            const __half hmx = __float2half_ru(mxl);                      // rounded up: both threads of the row then hold the same two numbers
+            mxbuf[hsel * 128 + r] = hmx;
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            const float mx = fmaxf(__half2float(hmx), __half2float(mxbuf[(hsel ^ 1) * 128 + r]));
+            asm volatile("bar.sync 1, 256;" ::: "memory");                // everybody has read before the next tile's maxima are written
+            float alpha = 1.f;
+            const bool mine = mx > m + 8.0f;                              // also true on the first tile (m = -inf; key 0 is visible to every query)
+            const bool moved = __any_sync(0xffffffffu, mine);             // warp-uniform (the TMEM accesses below are warp-wide); the row's other warp decides alike
+            if (mine) { alpha = m == -INFINITY ? 0.f : ta_ex2(m - mx); m = mx; }
+            float rs = 0.f;
+            uint32_t pk[16];
 #pragma unroll
-                for (int c = 0; c < kTaBN / 32; ++c) {
-#pragma unroll
-                    for (int i = 0; i < 32; i += 2) {
-                        float x0 = __uint_as_float(raw[c][i]) * a.scale_log2, x1 = __uint_as_float(raw[c][i + 1]) * a.scale_log2;
-                        if (diag && j * kTaBN + c * 32 + i > qpos) x0 = -INFINITY;
-                        if (diag && j * kTaBN + c * 32 + i + 1 > qpos) x1 = -INFINITY;
-                        mx = fmaxf(mx, fmaxf(x0, x1));
-                        const float e0 = ta_ex2(x0 - m), e1 = ta_ex2(x1 - m);      // first pass of the first tile: m = -inf, the values are thrown away
-                        rs += e0 + e1;
-                        pk[c * 16 + (i >> 1)] = pack_h2(e0, e1);
-                    }
-                }
-                if (pass == 1) break;
-                const bool mine = mx > m + 8.0f;                          // also true on the first tile (m = -inf; key 0 is visible to every query)
-                if (!__any_sync(0xffffffffu, mine)) break;                // warp-uniform: the TMEM accesses below are warp-wide
-                if (mine) { alpha = m == -INFINITY ? 0.f : ta_ex2(m - mx); m = mx; }
-                moved = true;
+            for (int i = 0; i < 32; i += 2) {
+                const float e0 = ta_ex2(x[i] - m), e1 = ta_ex2(x[i + 1] - m);
+                rs += e0 + e1;
+                pk[i >> 1] = pack_h2(e0, e1);
             }
             if (j > 0) {
-                if (!mbar_wait(b_pv, (uint32_t)(j - 1) & 1u)) { failed = true; break; }   // P V of the previous tile is complete: O and the P tile are ours
+                if (!failed && !mbar_wait(b_pv, (uint32_t)(j - 1) & 1u)) failed = true;   // P V of the previous tile is complete: O and the P tile are ours
                 tc_fence_after();
                 if (moved) {
 #pragma unroll 1
-                    for (int c = 0; c < HD / 32; ++c) {
+                    for (int c = 0; c < OC / 32; ++c) {
                         float v[32];
-                        tmem_ld32(tO + lane_off + (uint32_t)(c * 32), v);
+                        tmem_ld32(tO + lane_off + (uint32_t)(hsel * OC + c * 32), v);
 #pragma unroll
                         for (int i = 0; i < 32; ++i) v[i] *= alpha;
-                        tmem_st32(tO + lane_off + (uint32_t)(c * 32), v);
+                        tmem_st32(tO + lane_off + (uint32_t)(hsel * OC + c * 32), v);
                     }
                     tmem_wait_st();
                 }
             }
+            const uint32_t prow = sP + (uint32_t)(r * 128);
 #pragma unroll
-            for (int c = 0; c < kTaBN / 32; ++c) {
-                const uint32_t prow = sP + (uint32_t)(r * 128);
-#pragma unroll
-                for (int i = 0; i < 4; ++i)
-                    ta_sts128(prow + ((uint32_t)((c * 4 + i) ^ (r & 7)) << 4), make_uint4(pk[c * 16 + 4 * i], pk[c * 16 + 4 * i + 1], pk[c * 16 + 4 * i + 2], pk[c * 16 + 4 * i + 3]));
-            }
+            for (int i = 0; i < 4; ++i)
+                ta_sts128(prow + ((uint32_t)((hsel * 4 + i) ^ (r & 7)) << 4), make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]));
             l = l * alpha + rs;
             fence_async_smem();                                           // the tensor core reads P through the async proxy
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(b_p);
         }
+        // the row's sum: the second half hands its part to the first, which hands back the total
+        float* lbuf = reinterpret_cast<float*>(mxbuf);                    // 128 floats
+        if (hsel == 1) lbuf[r] = l;
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        if (hsel == 0) { l += lbuf[r]; lbuf[r] = l; }
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        if (hsel == 1) l = lbuf[r];
         if (!failed && !mbar_wait(b_pv, (uint32_t)(nj - 1) & 1u)) failed = true;
         tc_fence_after();
-        if (!failed) {
+        {
             const float inv = 1.0f / l;
             const int t = q0 + r;
 #pragma unroll 1
-            for (int c = 0; c < HD / 32; ++c) {
+            for (int c = 0; c < OC / 32; ++c) {
                 float v[32];
-                tmem_ld32(tO + lane_off + (uint32_t)(c * 32), v);
-                if (t < a.T) {
-                    __half* dst = a.out + (size_t)t * a.ldq + head * kTaHD + c * 32;
+                tmem_ld32(tO + lane_off + (uint32_t)(hsel * OC + c * 32), v);
+                if (t < a.T && !failed) {
+                    __half* dst = a.out + (size_t)t * a.ldq + head * kTaHD + hsel * OC + c * 32;
 #pragma unroll
                     for (int i = 0; i < 32; i += 8)
                         *reinterpret_cast<uint4*>(dst + i) = make_uint4(pack_h2(v[i] * inv, v[i + 1] * inv), pack_h2(v[i + 2] * inv, v[i + 3] * inv),
