@@ -312,14 +312,11 @@ def run_ours(a):
     value = Kst / (ms / 1e3)
 
     # ---- e2e: one cuqwen_step per token, host token in, sampled token out ----
-    tok = first
-    for i in range(W):
-        tok = eng.step(tok, ctx + i)
+    # (cuqwen_step_loop: the per-token calls in a C loop, as the reference arm's loop is; no Python between the tokens)
+    eng.step_loop(first, ctx, W)
     barrier(dist, local)
     t0 = time.perf_counter()
-    tok = first
-    for i in range(Kst):
-        tok = eng.step(tok, ctx + i)
+    eng.step_loop(first, ctx, Kst)
     e2e_s = time.perf_counter() - t0
     barrier(dist, local)
     e2e_s = max_over_ranks(dist, local, e2e_s)
@@ -335,7 +332,7 @@ def run_ours(a):
         "config": workload_config(a, cfg, qid, Kst),
         "arm": {"parallelism": f"tp{world}", "attn_splits": eng.params.attn_splits, "kv_cache": a.kv},
         "e2e": {"value": round(e2e, 2), "unit": "tok/s", "h2d_bytes_per_step": 16, "d2h_bytes_per_step": 12,
-                "how": "cuqwen_step per token: the host writes token / position into a pinned mailbox that the step's first kernel reads over PCIe (16 B), the last kernel writes token + status + sequence number back (12 B) and the host polls for it"},
+                "how": "cuqwen_step per token (C loop, cuqwen_step_loop): the host writes token / position into a pinned mailbox that the step's first kernel reads over PCIe (16 B), the last kernel writes token + status + sequence number back (12 B) and the host polls for it"},
         "gpu_launches": Kst * eng.step_launches,
         "clocks": cs.result,
     }

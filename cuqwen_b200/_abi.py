@@ -29,6 +29,7 @@ SIGNATURES = {
     "cuqwen_load": (_i, [_vp, C.c_char_p]),
     "cuqwen_step": (_i, [_vp, _i, _i, _pi, _i, _pi]),
     "cuqwen_decode_n": (_i, [_vp, _i, _i, _i, _pi]),
+    "cuqwen_step_loop": (_i, [_vp, _i, _i, _i, _pi]),
     "cuqwen_prefill": (_i, [_vp, _pi, _i, _i]),
     "cuqwen_last_decode_ms": (_f, [_vp]),
     "cuqwen_kv_fill_normal": (_i, [_vp, _i, C.c_uint64]),

@@ -742,6 +742,18 @@ extern "C" int cuqwen_prefill(cuqwen_engine* e, const int* tokens, int n_tokens,
     return CUQWEN_OK;
 }
 
+// The host loop of the reference's chat program (src/main.cu:95-112) as one call: n times cuqwen_step, each token
+// going out to the host and the next one coming back in from it.
+extern "C" int cuqwen_step_loop(cuqwen_engine* e, int first_token, int start_pos, int n, int* out_tokens) {
+    if (!e || !out_tokens) return fail(CUQWEN_ERR_ARG, "null argument");
+    int tok = first_token;
+    for (int i = 0; i < n; ++i) {
+        if (int r = cuqwen_step(e, tok, start_pos + i, nullptr, 0, &tok)) return r;
+        out_tokens[i] = tok;
+    }
+    return CUQWEN_OK;
+}
+
 extern "C" int cuqwen_decode_n(cuqwen_engine* e, int first_token, int start_pos, int n, int* out_tokens) {
     if (!e) return fail(CUQWEN_ERR_ARG, "null engine");
     if (!e->loaded) return fail(CUQWEN_ERR_STATE, "cuqwen_decode_n before cuqwen_load");

@@ -150,6 +150,12 @@ class Engine:
         check(_abi.lib().cuqwen_decode_n(self._h, first_token, start_pos, n, out.ctypes.data_as(C.POINTER(C.c_int))))
         return out
 
+    def step_loop(self, first_token: int, start_pos: int, n: int) -> np.ndarray:
+        """cuqwen_step_loop: n calls of cuqwen_step in a C loop, each token making the host round trip."""
+        out = np.empty(n, dtype=np.int32)
+        check(_abi.lib().cuqwen_step_loop(self._h, first_token, start_pos, n, out.ctypes.data_as(C.POINTER(C.c_int))))
+        return out
+
     def prefill(self, tokens, pos0: int = 0) -> None:
         """cuqwen_prefill: the KV cache rows [pos0, pos0 + len(tokens)) of these prompt tokens, computed as batched tiles."""
         t = np.ascontiguousarray(tokens, dtype=np.int32)

@@ -83,6 +83,10 @@ int cuqwen_load(cuqwen_engine* e, const char* bin_path);
  * stream synchronisation; the reference pays three copies and a synchronisation per token, src/model.cu:193-222). */
 int cuqwen_step(cuqwen_engine* e, int token, int pos, const int* history, int history_len, int* out_token);
 
+/* The reference's host loop (src/main.cu:95-112) as one call: n times cuqwen_step with history_len 0, every sampled
+ * token returning to the host before it is fed to the next step (unlike cuqwen_decode_n below). */
+int cuqwen_step_loop(cuqwen_engine* e, int first_token, int start_pos, int n, int* out_tokens);
+
 /* n greedy steps with the sampled token fed back on the device (no counterpart in the reference, which pays
  * a host round trip per token, src/main.cu:95-112).  out_tokens receives n ids.  history_len = 0 semantics. */
 int cuqwen_decode_n(cuqwen_engine* e, int first_token, int start_pos, int n, int* out_tokens);

@@ -106,6 +106,7 @@ def test_decode_n_equals_step_loop_and_history_penalty(built, tmp_path):
         loop.append(tok)
     got = b.decode_n(9, 5, 20)
     assert got.tolist() == loop and b.last_decode_ms > 0
+    assert b.step_loop(9, 5, 20).tolist() == loop            # the same tokens with a host round trip each
     # penalty: distinct ids are rescaled exactly once, on top of the un-penalised logits
     base = a.step(11, 25)
     plain = a.read("LOGITS").copy()
