@@ -3,25 +3,25 @@
 // or fp16).  The reference has no such path: it prefills one token at a time through the decode kernels
 // (src/main.cu:86-92; its roadmap names the batched form, README.md:145).
 //
-// One CTA computes a 256-token x 256-row tile as two 128-token halves (one half when the launch has at most 128
-// tokens).  UMMA shape M = 128 (tokens) x N = 256 (weight rows) x K = 16, fp16 operands from shared memory in the
-// K-major 128-byte-swizzled canonical layout, one fp32 accumulator of 256 tensor-memory columns per half: the widened
-// weight tile, which costs the CUDA cores more than one half's MMAs cost the tensor core, is used twice.
-// Per 64-column K block:
-//   warp 0     one lane issues the TMA copies: the X tile (128 x 64 fp16, hardware-swizzled) and the raw weight rows
-//   warps 2-9  quantised weights: one row per thread, 64 weights -> fp16 * scale -> the swizzled B tile
-//              (fp16 weights arrive swizzled by TMA and skip this)
+// One CTA computes a 256-token x NT-row tile as two 128-token halves (one half when the launch has at most 128
+// tokens); NT = 256 weight rows, or 128 / 64 where 256-row tiles would leave most SMs without a CTA.  UMMA shape
+// M = 128 (tokens) x N = NT x K = 16, fp16 operands from shared memory in the K-major 128-byte-swizzled canonical
+// layout, one fp32 accumulator of NT tensor-memory columns per half: the widened weight tile, which costs the CUDA
+// cores more than one half's MMAs cost the tensor core, is used twice.  Per 64-column K block:
+//   warp 0     one lane issues the TMA copies into a ring of three or four slots: the X tiles (128 x 64 fp16,
+//              hardware-swizzled) and the raw weight rows
+//   warps 2-9  quantised weights: a row (or a half / quarter of one) per thread, fp16(q) * scale into the swizzled B
+//              tile, a ring of two slots (fp16 weights arrive swizzled by TMA and skip this)
 //   warp 1     one lane issues four tcgen05.mma (K = 16 each) per half and commits the slots back to their fillers
-// After the last K block warps 2-9 read the accumulator (tcgen05.ld, warp w owns TMEM lanes 32 * (w % 4) ..) and apply
-// the epilogue.  Every mbarrier wait is bounded (tma.cuh); a wait that runs out sets *err and the CTA drains.
+// After the last K block warps 2-9 read the accumulators (tcgen05.ld, warp w owns TMEM lanes 32 * (w % 4) ..) and
+// apply the epilogue.  Every mbarrier wait is bounded (tma.cuh); a wait that runs out sets *err and the CTA drains.
 #pragma once
 #include "tma.cuh"
 
 namespace cq {
 
 constexpr int kPfM = 128;            // tokens per tile
-constexpr int kPfN = 256;            // weight rows per tile (two matrices of 128 rows each in the SwiGLU mode); 128 in the
-                                     // narrow variant the launcher takes when the wide tiles would leave most SMs without a CTA
+constexpr int kPfN = 256;            // weight rows per tile at the most (two matrices of half as many rows each in the SwiGLU mode)
 constexpr int kPfKB = 64;            // K per pipeline stage: 128 bytes of fp16, one swizzle row
 constexpr int kPfMH = 2;             // token tiles per CTA: two accumulators share every widened weight tile
 constexpr int kPfConvWarps = 8;      // 8: a weight row of a K block per thread; 16: half a row (measured: no faster, the kernel is bound elsewhere)
@@ -50,7 +50,7 @@ struct PfGemmArgs {
     CUtensorMap tw[3];         // weights: bytes [rows][row bytes], box (raw bytes of a K block) x rows; fp16: box 64 x rows, swizzled
     const __half* s[3];        // scales [rows][K / 128] (quantised formats)
     // Plain modes: up to three matrices over the same X side by side in one launch (q, k and v: 16-CTA launches of
-    // their own would leave most of the GPU idle); matrix i owns ceil(seg_rows[i] / 256) row tiles and the output
+    // their own would leave most of the GPU idle); matrix i owns ceil(seg_rows[i] / NT) row tiles and the output
     // columns after those of the matrices before it.  PF_SWIGLU: tw[0] / tw[1] are gate and up, nseg = 1.
     int seg_rows[3];
     int nseg;
